@@ -1,0 +1,198 @@
+"""The step function.
+
+``ModelRunner.step(entries)`` runs exactly the tokens it is given, as one batch, against the
+cache that earlier steps left, writes their keys and values into the requests' pages, and
+returns 32-bit logits at the wanted places (none, some or all).  The reference's counterpart
+is the device half of ``LLMEngine.step`` (engine/runtime/engine.py:186-227 with
+engine/runtime/paged_cache.py:79-229); it returns the last row of every sequence, this
+returns the rows that are asked for.
+
+Pages must have been taken from the cache manager before the step (``grow``); the runner
+only reads the block tables.
+"""
+
+from __future__ import annotations
+
+from typing import Any
+
+from ..cache.manager import CacheManager
+from ..cache.storage import CacheStorage
+from .batch import PagedGroupView, StateGroupView, StepContext, StepEntry
+from .model import Model
+from .workspace import Workspace
+
+
+def _align4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class ModelRunner:
+    def __init__(self, model: Model, cache: CacheManager, storage: CacheStorage, ops,
+                 device, max_tokens_per_step: int, max_seqs_per_step: int) -> None:
+        import torch
+
+        self.model, self.cache, self.storage, self.ops, self.device = model, cache, storage, ops, device
+        self.max_tokens, self.max_seqs = int(max_tokens_per_step), int(max_seqs_per_step)
+        self.ws = Workspace(device, min_rows=self.max_tokens)
+        self.page_size = cache.page_size
+        self._torch = torch
+        self._staging_host = None
+        self._staging_dev = None
+        self._ensure_staging(self._staging_ints(self.max_tokens, self.max_seqs, self.max_seqs, 8))
+
+    # --- staging ----------------------------------------------------------------------------
+
+    def _staging_ints(self, n: int, b: int, r: int, width: int) -> int:
+        groups = len(self.cache.paged_groups)
+        per_group = _align4(n) + _align4(b * width)
+        return (3 * _align4(n) + _align4(b + 1) + 2 * _align4(b) + _align4(r)
+                + groups * per_group + 16)
+
+    def _ensure_staging(self, ints: int) -> None:
+        torch = self._torch
+        if self._staging_host is not None and self._staging_host.numel() >= ints:
+            return
+        pin = self.device is not None and str(self.device).startswith("cuda")
+        self._staging_host = torch.empty(ints, dtype=torch.int32, pin_memory=pin)
+        self._staging_np = self._staging_host.numpy()
+        self._staging_dev = torch.empty(ints, dtype=torch.int32, device=self.device)
+        self.ws.version += 1
+
+    # --- one step ---------------------------------------------------------------------------
+
+    def build_context(self, entries: list[StepEntry], pad_to_seqs: int | None = None,
+                      table_width: int | None = None):
+        """Pack the step's index data, copy it to the device and return the context and the
+        device vector of wanted rows.  ``pad_to_seqs``/``table_width`` give a launch of fixed
+        size: missing sequences become single tokens that read and write the scratch page."""
+        import numpy as np
+
+        torch = self._torch
+        ps = self.page_size
+        q_lens = [len(e.tokens) for e in entries]
+        if any(n < 1 for n in q_lens):
+            raise ValueError("every entry of a step needs at least one token")
+        real_b = len(entries)
+        b = max(pad_to_seqs or 0, real_b)
+        pad = b - real_b
+        n = sum(q_lens) + pad
+        rows = sum(len(e.want) for e in entries) + pad
+        tables = [[self.cache.table(g, e.req_id) for e in entries]
+                  for g in range(len(self.cache.paged_groups))]
+        width = max([table_width or 1] + [len(t) for g in tables for t in g])
+        self._ensure_staging(self._staging_ints(n, b, rows, width))
+        buf = self._staging_np
+        off = 0
+
+        def take(count: int):
+            nonlocal off
+            view = (off, count)
+            off += _align4(count)
+            return view
+
+        v_tok, v_pos, v_seq = take(n), take(n), take(n)
+        v_cu, v_ctx, v_state, v_rows = take(b + 1), take(b), take(b), take(rows)
+        v_slots = [take(n) for _ in tables]
+        v_tables = [take(b * width) for _ in tables]
+
+        q_starts, start_positions, logit_rows, cursor = [], [], [], 0
+        for i, e in enumerate(entries):
+            ql = q_lens[i]
+            q_starts.append(cursor)
+            start_positions.append(e.start)
+            buf[v_tok[0] + cursor: v_tok[0] + cursor + ql] = e.tokens
+            buf[v_pos[0] + cursor: v_pos[0] + cursor + ql] = np.arange(e.start, e.start + ql)
+            buf[v_seq[0] + cursor: v_seq[0] + cursor + ql] = i
+            for w in e.want:
+                if not 0 <= w < ql:
+                    raise ValueError(f"wanted place {w} is outside the {ql} tokens of {e.req_id!r}")
+                logit_rows.append(cursor + w)
+            for g, group_tables in enumerate(tables):
+                table = group_tables[i]
+                if len(table) * ps < e.start + ql:
+                    raise ValueError(f"request {e.req_id!r} has no pages for positions up to "
+                                     f"{e.start + ql}; call grow() first")
+                pos = np.arange(e.start, e.start + ql)
+                pages = np.asarray(table, dtype=np.int64)[pos // ps]
+                if (pages < 0).any():
+                    raise ValueError(f"request {e.req_id!r} writes to a page it gave back")
+                buf[v_slots[g][0] + cursor: v_slots[g][0] + cursor + ql] = pages * ps + pos % ps
+                row = v_tables[g][0] + i * width
+                buf[row: row + len(table)] = table
+                buf[row + len(table): row + width] = -1
+            cursor += ql
+        ctx_lens = [s + q for s, q in zip(start_positions, q_lens)]
+        state_slots = [self.cache.state_slot(e.req_id) for e in entries]
+        for j in range(pad):  # padded rows: one token at position 0 on the scratch page
+            i = real_b + j
+            q_starts.append(cursor)
+            start_positions.append(0)
+            q_lens.append(1)
+            ctx_lens.append(1)
+            state_slots.append(self.cache.max_requests)
+            buf[v_tok[0] + cursor] = 0
+            buf[v_pos[0] + cursor] = 0
+            buf[v_seq[0] + cursor] = i
+            logit_rows.append(cursor)
+            for g, st in enumerate(self.storage.paged):
+                buf[v_slots[g][0] + cursor] = st.scratch_page * ps
+                row = v_tables[g][0] + i * width
+                buf[row] = st.scratch_page
+                buf[row + 1: row + width] = -1
+            cursor += 1
+        buf[v_cu[0]: v_cu[0] + b] = q_starts
+        buf[v_cu[0] + b] = n
+        buf[v_ctx[0]: v_ctx[0] + b] = ctx_lens
+        buf[v_state[0]: v_state[0] + b] = state_slots
+        buf[v_rows[0]: v_rows[0] + rows] = logit_rows
+
+        self._staging_dev[:off].copy_(self._staging_host[:off], non_blocking=True)
+        dev = self._staging_dev
+
+        def dview(view, shape=None):
+            t = dev[view[0]: view[0] + view[1]]
+            return t if shape is None else t.view(*shape)
+
+        groups: list[Any] = []
+        for g, st in enumerate(self.storage.paged):
+            groups.append(PagedGroupView(st.k, st.v, ps, st.window, dview(v_tables[g], (b, width)),
+                                         width, dview(v_slots[g])))
+        state_dev = dview(v_state)
+        for st in self.storage.state:
+            groups.append(StateGroupView(st, state_dev, state_slots))
+        ctx = StepContext(
+            ops=self.ops, ws=self.ws, num_tokens=n, num_seqs=b,
+            token_ids=dview(v_tok), positions=dview(v_pos), seq_of_token=dview(v_seq),
+            cu_q=dview(v_cu), ctx_lens=dview(v_ctx), groups=groups,
+            q_starts=q_starts, q_lens=q_lens, start_positions=start_positions,
+            max_q_len=max(q_lens), max_ctx_len=max(ctx_lens), padded=pad_to_seqs is not None,
+        )
+        return ctx, dview(v_rows)
+
+    def reset_fresh_state(self, ctx: StepContext) -> None:
+        """A request whose tokens start at position 0 starts from a zero state."""
+        if not self.storage.state:
+            return
+        torch = self._torch
+        slots = [s for s, p in zip(ctx.groups[len(self.storage.paged)].slots_host,
+                                   ctx.start_positions) if p == 0]
+        if not slots:
+            return
+        index = torch.tensor(slots, dtype=torch.long, device=self.device)
+        for st in self.storage.state:
+            st.index_fill_(1, index, 0.0)
+
+    def step(self, entries: list[StepEntry]):
+        """Run the entries as one batch; return ``[wanted, vocab]`` 32-bit logits in the order
+        of the entries and of their ``want`` lists, or None when nothing is wanted."""
+        ctx, logit_rows = self.build_context(entries)
+        self.reset_fresh_state(ctx)
+        return self.model.forward(ctx, logit_rows)
+
+
+def make_runner(model: Model, ops, device, page_size: int, num_pages: int, max_requests: int,
+                max_tokens_per_step: int) -> ModelRunner:
+    """Cache manager, device storage and step function for ``model``."""
+    cache = CacheManager(model.paged_groups, model.state_groups, num_pages, page_size, max_requests)
+    storage = CacheStorage(cache, model.env.torch_dtype, device)
+    return ModelRunner(model, cache, storage, ops, device, max_tokens_per_step, max_requests)

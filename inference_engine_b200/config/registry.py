@@ -41,11 +41,18 @@ def register_architecture(
     _ARCHITECTURES[name] = Architecture(name, config_class, build_spec, describe)
 
 
+def _load_builtin() -> None:
+    """The package's own architectures register themselves when their module is imported."""
+    from .. import architectures  # noqa: F401
+
+
 def supported_architectures() -> list[str]:
+    _load_builtin()
     return sorted(_ARCHITECTURES)
 
 
 def get_architecture(name: str) -> Architecture:
+    _load_builtin()
     try:
         return _ARCHITECTURES[name]
     except KeyError:

@@ -1,0 +1,50 @@
+// Shared helpers for the engine's kernels (sm_100a).
+//
+// Every exported function is plain C (`extern "C"`), takes raw device pointers and the
+// stream to launch on, allocates nothing, and returns a cudaError_t as int.  Kernels never
+// trap: an index that is out of range (a token id, a page, a slot) is recorded in a device
+// error word and the access is skipped, so the context stays usable and the host can report
+// what went wrong (the caller owns the error word and reads it when it likes).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define IE_API extern "C" __attribute__((visibility("default")))
+
+enum IeDtype { IE_F32 = 0, IE_BF16 = 1 };
+
+enum IeError {
+    IE_OK = 0,
+    IE_ERR_TOKEN_ID = 1,   // a token id outside the vocabulary
+    IE_ERR_PAGE = 2,       // a page or slot outside the cache
+    IE_ERR_POSITION = 3,   // a position outside the rotary table
+    IE_ERR_TABLE = 4,      // a block-table entry that was given back (-1) was read
+};
+
+// Every launch gets `err`, four ints in device memory owned by the caller:
+// [0] = first error code seen, [1] = the offending value, [2] = where (row / token).
+__device__ __forceinline__ void ie_report(int* err, int code, int value, int where) {
+    if (err != nullptr && atomicCAS(&err[0], 0, code) == 0) {
+        err[1] = value;
+        err[2] = where;
+    }
+}
+
+__device__ __forceinline__ float ie_load(const float* p) { return *p; }
+__device__ __forceinline__ float ie_load(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void ie_store(float* p, float v) { *p = v; }
+__device__ __forceinline__ void ie_store(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+#define IE_LAUNCH_CHECK() ((int)cudaGetLastError())

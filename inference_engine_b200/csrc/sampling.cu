@@ -1,0 +1,217 @@
+// Next-token choice on the device: greedy argmax and temperature sampling, with optional
+// top-k / top-p / min-p cut-offs and a repetition penalty, one block per row of logits.
+//
+// Order of operations as in engine/runtime/sampler.py:10-45: repetition penalty, then (not
+// greedy) divide by the temperature, top-k, top-p, min-p, softmax, draw.  The draw is a
+// Gumbel-max over the kept tokens: argmax_i (z_i + g_i) with g_i = -log(-log(u_i)) picks i
+// with probability softmax(z)_i, so no normalisation pass is needed.  u_i comes from the
+// counter-based Philox4x32-10 generator keyed by the request's seed and indexed by (how many
+// tokens the request has produced, i): a request's tokens do not depend on which other
+// requests share the step or on its row in the batch (the property tests/test_engine.py:132-136
+// of the reference asks for; the reference gets it from one torch.Generator per request).
+#include "common.cuh"
+#include <math.h>
+
+namespace {
+constexpr int THREADS = 512;
+
+__device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        unsigned hi0 = __umulhi(0xD2511F53u, c.x), lo0 = 0xD2511F53u * c.x;
+        unsigned hi1 = __umulhi(0xCD9E8D57u, c.z), lo1 = 0xCD9E8D57u * c.z;
+        c = make_uint4(hi1 ^ c.y ^ k.x, lo1, hi0 ^ c.w ^ k.y, lo0);
+        k.x += 0x9E3779B9u; k.y += 0xBB67AE85u;
+    }
+    return c;
+}
+
+__device__ __forceinline__ float uniform_for(unsigned long long seed, unsigned long long draw, unsigned i) {
+    uint4 r = philox4x32_10(make_uint4(i >> 2, (unsigned)draw, (unsigned)(draw >> 32), 0u),
+                            make_uint2((unsigned)seed, (unsigned)(seed >> 32)));
+    unsigned x = (i & 3) == 0 ? r.x : (i & 3) == 1 ? r.y : (i & 3) == 2 ? r.z : r.w;
+    return ((float)(x >> 8) + 0.5f) * (1.0f / 16777216.0f);  // in (0, 1)
+}
+
+struct Best { float v; int i; };
+__device__ __forceinline__ Best better(Best a, Best b) {
+    if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+    return a;
+}
+__device__ Best block_best(Best b, Best* scratch) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Best other{__shfl_xor_sync(0xffffffffu, b.v, o), __shfl_xor_sync(0xffffffffu, b.i, o)};
+        b = better(b, other);
+    }
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = b;
+    __syncthreads();
+    Best r = scratch[0];
+    for (int w = 1; w < THREADS / 32; ++w) r = better(r, scratch[w]);
+    return r;
+}
+__device__ float block_sum(float v, float* scratch) {
+    v = warp_sum(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = 0.f;
+    for (int w = 0; w < THREADS / 32; ++w) r += scratch[w];
+    return r;
+}
+
+// Monotone map of a float onto unsigned ints (larger float -> larger key).
+__device__ __forceinline__ unsigned float_key(float f) {
+    unsigned u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_float(unsigned k) {
+    return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
+// Penalised, temperature-scaled logit i of the row (engine/runtime/sampler.py:48-56).
+__device__ __forceinline__ float scaled_logit(const float* row, int i, float inv_temp, float penalty,
+                                              const unsigned* seen_bits) {
+    float z = row[i];
+    if (seen_bits && (seen_bits[i >> 5] >> (i & 31) & 1u)) z = z > 0.f ? z / penalty : z * penalty;
+    return z * inv_temp;
+}
+
+// The largest threshold t (as a key) such that stat({z >= t}) >= target, found by a radix
+// descent over the 32 key bits, 8 bits a level.  mode 0: stat = count (top-k);
+// mode 1: stat = sum of exp(z - zmax) (top-p, target = top_p * total mass).
+__device__ unsigned radix_threshold(const float* row, int vocab, float inv_temp, float penalty,
+                                    const unsigned* seen_bits, float keep_min, int mode, float target,
+                                    float zmax, float* hist /*[256]*/, float* scratch) {
+    unsigned prefix = 0;
+    float above = 0.f;  // stat of everything strictly above the current bucket range
+    for (int level = 3; level >= 0; --level) {
+        for (int b = threadIdx.x; b < 256; b += THREADS) hist[b] = 0.f;
+        __syncthreads();
+        unsigned shift = level * 8;
+        unsigned mask_hi = level == 3 ? 0u : (0xffffffffu << (shift + 8));
+        for (int i = threadIdx.x; i < vocab; i += THREADS) {
+            float z = scaled_logit(row, i, inv_temp, penalty, seen_bits);
+            if (z < keep_min) continue;
+            unsigned key = float_key(z);
+            if ((key & mask_hi) != (prefix & mask_hi)) continue;
+            atomicAdd(&hist[(key >> shift) & 255u], mode == 0 ? 1.f : expf(z - zmax));
+        }
+        __syncthreads();
+        // thread 0 walks the buckets from the top
+        if (threadIdx.x == 0) {
+            float run = above;
+            int b = 255;
+            for (; b > 0; --b) {
+                if (run + hist[b] >= target) break;
+                run += hist[b];
+            }
+            scratch[0] = run;
+            scratch[1] = (float)b;
+        }
+        __syncthreads();
+        above = scratch[0];
+        prefix |= ((unsigned)scratch[1]) << shift;
+        __syncthreads();
+    }
+    return prefix;
+}
+
+__global__ void __launch_bounds__(THREADS)
+sample_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
+              const int* __restrict__ top_k, const float* __restrict__ top_p,
+              const float* __restrict__ min_p, const float* __restrict__ penalty,
+              const unsigned* __restrict__ seen_bits, int seen_words,
+              const long long* __restrict__ seeds, const long long* __restrict__ draws,
+              int* __restrict__ out_tokens, float* __restrict__ out_logprob) {
+    __shared__ Best best_scratch[THREADS / 32];
+    __shared__ float sum_scratch[THREADS / 32];
+    __shared__ float hist[256];
+    __shared__ float small[2];
+    int r = blockIdx.x;
+    const float* row = logits + (size_t)r * vocab;
+    float temp = temperature ? temperature[r] : 0.f;
+    float pen = penalty ? penalty[r] : 1.f;
+    const unsigned* seen = (seen_bits && pen != 1.f) ? seen_bits + (size_t)r * seen_words : nullptr;
+    bool greedy = !(temp > 0.f);
+    float inv_temp = greedy ? 1.f : 1.f / temp;
+
+    // Pass 1: the maximum of the scaled logits (it is the greedy answer too).
+    Best b{-INFINITY, 0x7fffffff};
+    for (int i = threadIdx.x; i < vocab; i += THREADS) {
+        float z = scaled_logit(row, i, inv_temp, pen, seen);
+        b = better(b, Best{z, i});
+    }
+    b = block_best(b, best_scratch);
+    float zmax = b.v;
+    int choice = b.i;
+    float keep_min = -INFINITY;  // tokens with a scaled logit below this are cut off
+
+    if (!greedy) {
+        int k = top_k ? top_k[r] : 0;
+        float p = top_p ? top_p[r] : 1.f;
+        float mp = min_p ? min_p[r] : 0.f;
+        if (k > 0 && k < vocab) {
+            unsigned key = radix_threshold(row, vocab, inv_temp, pen, seen, keep_min, 0, (float)k,
+                                           zmax, hist, small);
+            keep_min = fmaxf(keep_min, key_float(key));
+        }
+        if (p < 1.f) {
+            float mass = 0.f;
+            for (int i = threadIdx.x; i < vocab; i += THREADS) {
+                float z = scaled_logit(row, i, inv_temp, pen, seen);
+                if (z >= keep_min) mass += expf(z - zmax);
+            }
+            mass = block_sum(mass, sum_scratch);
+            // Keep the smallest set of top tokens whose mass reaches top_p
+            // (engine/runtime/sampler.py:59-68, with its 1e-6 slack).
+            unsigned key = radix_threshold(row, vocab, inv_temp, pen, seen, keep_min, 1,
+                                           fmaxf(p - 1e-6f, 0.f) * mass, zmax, hist, small);
+            keep_min = fmaxf(keep_min, key_float(key));
+        }
+        if (mp > 0.f) {
+            // Drop tokens whose probability is below min_p times the largest probability:
+            // exp(z - zmax) < min_p  <=>  z < zmax + log(min_p)   (sampler.py:39-42)
+            keep_min = fmaxf(keep_min, zmax + logf(mp));
+        }
+        unsigned long long seed = (unsigned long long)seeds[r];
+        unsigned long long draw = (unsigned long long)draws[r];
+        Best g{-INFINITY, 0x7fffffff};
+        for (int i = threadIdx.x; i < vocab; i += THREADS) {
+            float z = scaled_logit(row, i, inv_temp, pen, seen);
+            if (z < keep_min) continue;
+            float u = uniform_for(seed, draw, (unsigned)i);
+            g = better(g, Best{z - logf(-logf(u)), i});
+        }
+        g = block_best(g, best_scratch);
+        choice = g.i;
+    }
+    if (out_logprob) {
+        // log-probability of the chosen token under the model's own distribution, before
+        // temperature and cut-offs (engine/runtime/engine.py:283-298).
+        Best raw{-INFINITY, 0};
+        for (int i = threadIdx.x; i < vocab; i += THREADS) raw = better(raw, Best{row[i], i});
+        raw = block_best(raw, best_scratch);
+        float s = 0.f;
+        for (int i = threadIdx.x; i < vocab; i += THREADS) s += expf(row[i] - raw.v);
+        s = block_sum(s, sum_scratch);
+        if (threadIdx.x == 0) out_logprob[r] = row[choice] - raw.v - logf(s);
+    }
+    if (threadIdx.x == 0) out_tokens[r] = choice;
+}
+}  // namespace
+
+// All per-row arrays but `logits` and `out_tokens` may be null (greedy, nothing cut off).
+IE_API int ie_sample(const float* logits, int num_rows, int vocab, const float* temperature,
+                     const int* top_k, const float* top_p, const float* min_p,
+                     const float* penalty, const unsigned* seen_bits, int seen_words,
+                     const long long* seeds, const long long* draws, int* out_tokens,
+                     float* out_logprob, void* stream) {
+    if (num_rows <= 0) return 0;
+    if (temperature != nullptr && (seeds == nullptr || draws == nullptr)) return (int)cudaErrorInvalidValue;
+    sample_kernel<<<num_rows, THREADS, 0, (cudaStream_t)stream>>>(
+        logits, vocab, temperature, top_k, top_p, min_p, penalty, seen_bits, seen_words, seeds, draws,
+        out_tokens, out_logprob);
+    return IE_LAUNCH_CHECK();
+}

@@ -1,0 +1,177 @@
+"""The engine's kernels as Python calls on torch tensors.
+
+Each method hands raw device pointers and the current CUDA stream to a plain-C function of
+the in-tree shared library (``ctypes``; nothing is allocated on the way).  There is no
+fallback: if the library cannot be built or loaded, or a tensor is not on a CUDA device,
+the call raises.  Matrix products in bfloat16 go to the vendor library through ``torch.mm``
+(the reference uses cuBLAS for them through ``nn.Linear``, engine/model/layers.py:126-129);
+32-bit matrix products, attention, norms, rotary encoding, the cache write, the activation,
+the embedding gather and sampling are the kernels under ``csrc/``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+
+from .build import build_core
+
+_ERRORS = {
+    1: "a token id outside the vocabulary",
+    2: "a page or slot outside the cache",
+    3: "a position outside the rotary table",
+    4: "a block-table entry that was already given back",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _dtype_code(t) -> int:
+    import torch
+
+    if t.dtype == torch.float32:
+        return 0
+    if t.dtype == torch.bfloat16:
+        return 1
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, not {t.dtype}")
+
+
+class CudaOps:
+    name = "cuda-sm100a"
+
+    def __init__(self, device="cuda") -> None:
+        import torch
+
+        if not torch.cuda.is_available():
+            raise KernelError("no CUDA device: the engine has no CPU path")
+        self.torch = torch
+        self.device = torch.device(device)
+        self.lib_path = build_core()
+        try:
+            self.lib = ctypes.CDLL(str(self.lib_path))
+        except OSError as exc:
+            raise KernelError(f"the kernel library {self.lib_path} could not be loaded: {exc}") from exc
+        self._declare()
+        self.err = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self._err_ptr = self.err.data_ptr()
+        self._mm_out_dtype = None
+
+    def _declare(self) -> None:
+        P, I, F = c_void_p, c_int, c_float
+        sigs = {
+            "ie_embedding": [P, I, P, P, I, I, I, P, P],
+            "ie_rmsnorm": [P, P, P, F, P, I, P, I, I, P],
+            "ie_rope_kv_write": [P, P, P, I, I, P, P, P, I, P, I, I, I, I, I, I, P, P],
+            "ie_silu_mul": [P, P, I, I, I, P],
+            "ie_gemm_f32": [P, P, P, I, I, I, P],
+            "ie_paged_attention_generic": [P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, F, I, P, P],
+            "ie_sample": [P, I, I, P, P, P, P, P, P, I, P, P, P, P, P],
+        }
+        for name, args in sigs.items():
+            fn = getattr(self.lib, name)
+            fn.argtypes, fn.restype = args, c_int
+            setattr(self, "_" + name[3:], fn)
+
+    # --- helpers ----------------------------------------------------------------------------
+
+    def _stream(self) -> int:
+        return self.torch.cuda.current_stream().cuda_stream
+
+    def _check(self, code: int, what: str) -> None:
+        if code != 0:
+            raise KernelError(f"{what}: CUDA error {code} at launch")
+
+    @staticmethod
+    def _ptr(t) -> int | None:
+        return None if t is None else t.data_ptr()
+
+    def check_errors(self) -> None:
+        """Read the device error word (this waits for the stream) and raise if a kernel saw
+        an index out of range."""
+        code, value, where = self.err[:3].tolist()
+        if code:
+            self.err.zero_()
+            raise KernelError(f"kernel index check failed: {_ERRORS.get(code, code)} "
+                              f"(value {value}, at row/token {where})")
+
+    # --- kernels ----------------------------------------------------------------------------
+
+    def embedding(self, table, ids, out) -> None:
+        self._check(self._embedding(table.data_ptr(), _dtype_code(table), ids.data_ptr(),
+                                    out.data_ptr(), ids.shape[0], table.shape[1], table.shape[0],
+                                    self._err_ptr, self._stream()), "embedding")
+
+    def rmsnorm(self, h, delta, weight, eps, out, rows=None) -> None:
+        n = h.shape[0] if rows is None else rows.shape[0]
+        self._check(self._rmsnorm(h.data_ptr(), self._ptr(delta), weight.data_ptr(), eps,
+                                  out.data_ptr(), _dtype_code(out), self._ptr(rows), n,
+                                  h.shape[1], self._stream()), "rmsnorm")
+
+    def linear(self, x, w, out) -> None:
+        """``out[M, N] = x[M, K] @ w[N, K]^T``."""
+        torch = self.torch
+        if x.shape[0] == 0:
+            return
+        if x.dtype == torch.float32:
+            if out.dtype != torch.float32 or w.dtype != torch.float32:
+                raise KernelError("the 32-bit matrix product takes and gives 32-bit tensors")
+            self._check(self._gemm_f32(x.data_ptr(), w.data_ptr(), out.data_ptr(), x.shape[0],
+                                       w.shape[0], x.shape[1], self._stream()), "gemm_f32")
+        elif out.dtype == x.dtype:
+            torch.mm(x, w.t(), out=out)
+        else:
+            torch.mm(x, w.t(), out_dtype=out.dtype, out=out)
+
+    def rope_kv_write(self, qkv, positions, table, rotary_dim, q_out, k_cache, v_cache,
+                      slot_mapping, nh, nkv, hd, page_size) -> None:
+        if table is not None and table.shape[2] * 2 != rotary_dim:
+            raise KernelError("rotary table does not match rotary_dim")
+        if rotary_dim > hd or rotary_dim % 2:
+            raise KernelError(f"rotary_dim {rotary_dim} must be even and at most head_dim {hd}")
+        self._check(self._rope_kv_write(
+            qkv.data_ptr(), positions.data_ptr(), self._ptr(table), rotary_dim,
+            0 if table is None else table.shape[0], q_out.data_ptr(), k_cache.data_ptr(),
+            v_cache.data_ptr(), _dtype_code(q_out), self._ptr(slot_mapping), qkv.shape[0],
+            nh, nkv, hd, page_size, k_cache.shape[0], self._err_ptr, self._stream()), "rope_kv_write")
+
+    def paged_attention(self, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, page_size,
+                        scale, window, out) -> None:
+        if hd % 8 or hd > 256:
+            raise KernelError(f"head_dim {hd} is not supported: it must be a multiple of 8, at most 256")
+        self._check(self._paged_attention_generic(
+            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _dtype_code(q),
+            block_tables.data_ptr(), block_tables.shape[1], ctx.seq_of_token.data_ptr(),
+            ctx.positions.data_ptr(), out.data_ptr(), ctx.num_tokens, nh, nkv, hd, page_size,
+            k_cache.shape[0], scale, window, self._err_ptr, self._stream()), "paged_attention")
+
+    def silu_mul(self, gate_up, out) -> None:
+        self._check(self._silu_mul(gate_up.data_ptr(), out.data_ptr(), _dtype_code(out),
+                                   out.shape[0], out.shape[1], self._stream()), "silu_mul")
+
+    def argmax(self, logits, out) -> None:
+        self.sample(logits, out)
+
+    def sample(self, logits, out, temperature=None, top_k=None, top_p=None, min_p=None,
+               penalty=None, seen_bits=None, seeds=None, draws=None, logprob=None) -> None:
+        """One token per row of 32-bit ``logits``; the per-row tensors are optional (absent:
+        greedy, no cut-off, no penalty).  ``seeds`` and ``draws`` (int64) are needed as soon
+        as ``temperature`` is given."""
+        self._check(self._sample(
+            logits.data_ptr(), logits.shape[0], logits.shape[1], self._ptr(temperature),
+            self._ptr(top_k), self._ptr(top_p), self._ptr(min_p), self._ptr(penalty),
+            self._ptr(seen_bits), 0 if seen_bits is None else seen_bits.shape[1],
+            self._ptr(seeds), self._ptr(draws), out.data_ptr(), self._ptr(logprob),
+            self._stream()), "sample")
+
+
+_OPS: dict[str, CudaOps] = {}
+
+
+def get_ops(device="cuda") -> CudaOps:
+    """The process-wide kernel set for ``device``; built and loaded on first use."""
+    key = str(device)
+    if key not in _OPS:
+        _OPS[key] = CudaOps(device)
+    return _OPS[key]

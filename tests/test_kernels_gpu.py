@@ -1,0 +1,265 @@
+"""Each CUDA kernel alone against its plain PyTorch reference (tests/ref_ops.py), at sizes
+other than the engine's test models: widths and vocabularies that are no power of two, odd
+head counts and groups, head sizes in steps of 16."""
+
+from __future__ import annotations
+
+import types
+
+import pytest
+import torch
+
+from tests.ref_ops import RefOps
+
+pytestmark = pytest.mark.gpu
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from inference_engine_b200.kernels import get_ops
+
+    return get_ops("cuda")
+
+
+def _tol(dtype):
+    return dict(atol=2e-6, rtol=2e-6) if dtype == torch.float32 else dict(atol=1e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("vocab,hidden,n", [(331, 80, 7), (1000, 2048, 33), (50, 24, 1)])
+def test_embedding(ops, dtype, vocab, hidden, n):
+    table = torch.randn(vocab, hidden, device="cuda").to(dtype)
+    ids = torch.randint(0, vocab, (n,), device="cuda", dtype=torch.int32)
+    got = torch.empty(n, hidden, device="cuda")
+    want = torch.empty_like(got)
+    ops.embedding(table, ids, got)
+    RefOps().embedding(table, ids, want)
+    assert torch.equal(got, want)
+    ops.check_errors()
+
+
+def test_embedding_reports_a_bad_token_id(ops):
+    from inference_engine_b200.kernels import KernelError
+
+    table = torch.randn(10, 16, device="cuda")
+    ids = torch.tensor([3, 10], device="cuda", dtype=torch.int32)
+    out = torch.empty(2, 16, device="cuda")
+    ops.embedding(table, ids, out)
+    with pytest.raises(KernelError, match="token id"):
+        ops.check_errors()
+    ops.check_errors()  # the error word was cleared
+
+
+@pytest.mark.parametrize("out_dtype", DTYPES)
+@pytest.mark.parametrize("n,hidden,eps", [(5, 80, 3e-6), (33, 2048, 1e-5), (1, 96, 1e-6), (3, 4100, 1e-5)])
+def test_rmsnorm_with_residual_add(ops, out_dtype, n, hidden, eps):
+    h = torch.randn(n, hidden, device="cuda") * 3
+    delta = torch.randn(n, hidden, device="cuda")
+    w = 1 + 0.1 * torch.randn(hidden, device="cuda")
+    for use_delta in (True, False):
+        h1, h2 = h.clone(), h.clone()
+        got = torch.empty(n, hidden, device="cuda", dtype=out_dtype)
+        want = torch.empty_like(got)
+        ops.rmsnorm(h1, delta if use_delta else None, w, eps, got)
+        RefOps().rmsnorm(h2, delta if use_delta else None, w, eps, want)
+        assert torch.equal(h1, h2)  # the residual stream itself: one add, exact
+        torch.testing.assert_close(got.float(), want.float(), **_tol(out_dtype))
+    rows = torch.tensor([n - 1, 0, n // 2], device="cuda", dtype=torch.int32)
+    h1 = h.clone()
+    got = torch.empty(3, hidden, device="cuda", dtype=out_dtype)
+    want = torch.empty_like(got)
+    ops.rmsnorm(h1, delta, w, eps, got, rows)
+    RefOps().rmsnorm(h.clone(), delta, w, eps, want, rows)
+    assert torch.equal(h1, h)  # selected rows: nothing is written back
+    torch.testing.assert_close(got.float(), want.float(), **_tol(out_dtype))
+
+
+def test_rmsnorm_row_does_not_depend_on_the_batch(ops):
+    h = torch.randn(64, 2048, device="cuda")
+    w = torch.randn(2048, device="cuda")
+    full = torch.empty(64, 2048, device="cuda")
+    ops.rmsnorm(h.clone(), None, w, 1e-5, full)
+    one = torch.empty(1, 2048, device="cuda")
+    ops.rmsnorm(h[17:18].clone(), None, w, 1e-5, one)
+    assert torch.equal(full[17:18], one)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 331, 80), (7, 192, 64), (70, 512, 96), (33, 1000, 1030), (130, 65, 17)])
+def test_gemm_f32(ops, m, n, k):
+    x = torch.randn(m, k, device="cuda")
+    w = torch.randn(n, k, device="cuda")
+    got = torch.empty(m, n, device="cuda")
+    ops.linear(x, w, got)
+    want = (x.double() @ w.double().t()).float()
+    torch.testing.assert_close(got, want, atol=1e-4 * k ** 0.5, rtol=1e-5)
+    one = torch.empty(1, n, device="cuda")
+    ops.linear(x[m // 2: m // 2 + 1].contiguous(), w, one)
+    assert torch.equal(one, got[m // 2: m // 2 + 1])  # a row's result does not depend on M
+
+
+@pytest.mark.parametrize("out_dtype", DTYPES)
+@pytest.mark.parametrize("m,n,k", [(1, 328, 80), (7, 192, 64), (70, 512, 96), (33, 1000, 1032)])
+def test_linear_bf16(ops, out_dtype, m, n, k):
+    x = torch.randn(m, k, device="cuda").bfloat16()
+    w = torch.randn(n, k, device="cuda").bfloat16()
+    got = torch.empty(m, n, device="cuda", dtype=out_dtype)
+    ops.linear(x, w, got)
+    want = x.double() @ w.double().t()
+    tol = dict(atol=1e-3 * k ** 0.5, rtol=1e-5) if out_dtype == torch.float32 else dict(atol=0.02 * k ** 0.5, rtol=1e-2)
+    torch.testing.assert_close(got.double(), want, **tol)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,rd,ps", [(4, 2, 16, 16, 16), (3, 1, 32, 32, 8), (5, 5, 48, 48, 4),
+                                             (32, 8, 64, 64, 16), (6, 2, 80, 32, 16), (2, 1, 128, 0, 32)])
+def test_rope_and_cache_write(ops, dtype, nh, nkv, hd, rd, ps):
+    n, pages, maxpos = 37, 9, 500
+    qkv = torch.randn(n, (nh + 2 * nkv) * hd, device="cuda")
+    positions = torch.randint(0, maxpos, (n,), device="cuda", dtype=torch.int32)
+    table = None
+    if rd:
+        ang = torch.rand(maxpos, rd // 2, device="cuda") * 6.28
+        table = torch.stack((ang.cos(), ang.sin()), dim=1).contiguous()
+    slots = torch.randperm(pages * ps, device="cuda")[:n].to(torch.int32)
+    res = []
+    for impl in (ops, RefOps()):
+        q = torch.zeros(n, nh * hd, device="cuda", dtype=dtype)
+        k = torch.zeros(pages, nkv, ps, hd, device="cuda", dtype=dtype)
+        v = torch.zeros_like(k)
+        impl.rope_kv_write(qkv, positions, table, rd, q, k, v, slots, nh, nkv, hd, ps)
+        res.append((q, k, v))
+    for a, b in zip(*res):
+        torch.testing.assert_close(a.float(), b.float(), **_tol(dtype))
+    # a run that borrows another layer's cache rotates queries and writes nothing
+    q = torch.zeros(n, nh * hd, device="cuda", dtype=dtype)
+    k = torch.zeros(pages, nkv, ps, hd, device="cuda", dtype=dtype)
+    v = torch.zeros_like(k)
+    ops.rope_kv_write(qkv, positions, table, rd, q, k, v, None, nh, nkv, hd, ps)
+    torch.testing.assert_close(q.float(), res[1][0].float(), **_tol(dtype))
+    assert not k.any() and not v.any()
+    ops.check_errors()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n,inter", [(5, 192), (33, 8192), (1, 321), (64, 1000)])
+def test_silu_mul(ops, dtype, n, inter):
+    gu = (torch.randn(n, 2 * inter, device="cuda") * 3).to(dtype)
+    got = torch.empty(n, inter, device="cuda", dtype=dtype)
+    want = torch.empty_like(got)
+    ops.silu_mul(gu, got)
+    RefOps().silu_mul(gu, want)
+    torch.testing.assert_close(got.float(), want.float(), **_tol(dtype))
+
+
+def _attention_case(nh, nkv, hd, ps, q_lens, ctx_lens, dtype, seed=0, spike=None):
+    """A random paged cache with shuffled pages and a step of len(q_lens) sequences."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    b = len(q_lens)
+    pages_per_seq = [-(-c // ps) for c in ctx_lens]
+    total = sum(pages_per_seq) + 3
+    perm = torch.randperm(total, device="cuda", generator=g).tolist()
+    width = max(pages_per_seq)
+    tables = torch.full((b, width), -1, dtype=torch.int32)
+    cursor = 0
+    for i, n in enumerate(pages_per_seq):
+        tables[i, :n] = torch.tensor(perm[cursor:cursor + n], dtype=torch.int32)
+        cursor += n
+    k = torch.randn(total, nkv, ps, hd, device="cuda", generator=g)
+    v = torch.randn(total, nkv, ps, hd, device="cuda", generator=g)
+    n_tok = sum(q_lens)
+    q = torch.randn(n_tok, nh * hd, device="cuda", generator=g)
+    positions, seqs = [], []
+    for i, (ql, cl) in enumerate(zip(q_lens, ctx_lens)):
+        positions += list(range(cl - ql, cl))
+        seqs += [i] * ql
+    if spike is not None:
+        # One far key per sequence gets a score that stands out for every query of that
+        # sequence: the output must be (nearly) that key's value, wherever its page lies.
+        for i, key_pos in enumerate(spike):
+            page, off = int(tables[i, key_pos // ps]), key_pos % ps
+            rows = [t for t in range(n_tok) if seqs[t] == i]
+            direction = torch.randn(hd, device="cuda", generator=g)
+            direction = direction / direction.norm()
+            k[page, :, off] = direction * 40.0
+            q.view(n_tok, nh, hd)[rows] = direction * (hd ** 0.5)
+    ctx = types.SimpleNamespace(
+        num_tokens=n_tok, num_seqs=b,
+        positions=torch.tensor(positions, dtype=torch.int32, device="cuda"),
+        seq_of_token=torch.tensor(seqs, dtype=torch.int32, device="cuda"),
+        cu_q=torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device="cuda"),
+        ctx_lens=torch.tensor(ctx_lens, dtype=torch.int32, device="cuda"),
+        q_lens=list(q_lens), start_positions=[c - q for c, q in zip(ctx_lens, q_lens)],
+        q_starts=[0] + list(torch.tensor(q_lens).cumsum(0))[:-1],
+        max_q_len=max(q_lens), max_ctx_len=max(ctx_lens), padded=False)
+    return q.to(dtype), k.to(dtype), v.to(dtype), tables.cuda(), ctx
+
+
+ATTN_SHAPES = [(4, 2, 16, 16), (3, 1, 32, 8), (5, 5, 48, 4), (32, 8, 64, 16), (8, 2, 128, 16),
+               (6, 3, 80, 16), (14, 2, 64, 32), (2, 1, 256, 16)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,ps", ATTN_SHAPES)
+@pytest.mark.parametrize("window", [0, 37])
+def test_paged_attention_mixed_step(ops, dtype, nh, nkv, hd, ps, window):
+    q_lens, ctx_lens = [1, 17, 2, 1, 40], [200, 17, 65, 1, 333]
+    q, k, v, tables, ctx = _attention_case(nh, nkv, hd, ps, q_lens, ctx_lens, dtype)
+    got = torch.empty_like(q)
+    want = torch.empty_like(q)
+    scale = hd ** -0.5
+    ops.paged_attention(q, k, v, tables, ctx, nh, nkv, hd, ps, scale, window, got)
+    RefOps().paged_attention(q, k, v, tables, ctx, nh, nkv, hd, ps, scale, window, want)
+    tol = dict(atol=2e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(got.float(), want.float(), **tol)
+    ops.check_errors()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,ps", [(32, 8, 64, 16), (3, 1, 32, 8), (8, 2, 128, 16)])
+def test_paged_attention_finds_one_far_key(ops, dtype, nh, nkv, hd, ps):
+    """Among hundreds of keys one stands out: at a page's first and last slot, in the first
+    page, deep in the middle, and at the query's own position."""
+    q_lens, ctx_lens = [1, 1, 1, 9, 1], [700, 513, 640, 300, 257]
+    spike = [3, ps - 1, 511, 289, 256]
+    q, k, v, tables, ctx = _attention_case(nh, nkv, hd, ps, q_lens, ctx_lens, dtype, seed=1, spike=spike)
+    got = torch.empty_like(q)
+    ops.paged_attention(q, k, v, tables, ctx, nh, nkv, hd, ps, hd ** -0.5, 0, got)
+    want = torch.empty_like(q)
+    RefOps().paged_attention(q, k, v, tables, ctx, nh, nkv, hd, ps, hd ** -0.5, 0, want)
+    tol = dict(atol=2e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(got.float(), want.float(), **tol)
+    # and the answer really is that key's value (for queries that can see it)
+    seqs, pos = ctx.seq_of_token.tolist(), ctx.positions.tolist()
+    for t in range(ctx.num_tokens):
+        i = seqs[t]
+        if pos[t] < spike[i]:
+            continue
+        page, off = int(tables[i, spike[i] // ps]), spike[i] % ps
+        expect = v[page, :, off].float().repeat_interleave(nh // nkv, dim=0).reshape(-1)
+        torch.testing.assert_close(got[t].float(), expect, atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_window_edge(ops, dtype):
+    """The key just inside the window counts, the one just outside does not."""
+    nh, nkv, hd, ps, window = 4, 2, 32, 8, 24
+    for key_pos, visible in ((100 - window + 1, True), (100 - window, False)):
+        q, k, v, tables, ctx = _attention_case(nh, nkv, hd, ps, [1], [101], dtype, seed=2, spike=[key_pos])
+        got = torch.empty_like(q)
+        ops.paged_attention(q, k, v, tables, ctx, nh, nkv, hd, ps, hd ** -0.5, window, got)
+        page, off = int(tables[0, key_pos // ps]), key_pos % ps
+        expect = v[page, :, off].float().repeat_interleave(nh // nkv, dim=0).reshape(-1)
+        close = torch.allclose(got[0].float(), expect, atol=3e-2, rtol=3e-2)
+        assert close == visible
+        want = torch.empty_like(q)
+        RefOps().paged_attention(q, k, v, tables, ctx, nh, nkv, hd, ps, hd ** -0.5, window, want)
+        torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+
+
+def test_attention_refuses_a_head_size_it_cannot_take(ops):
+    from inference_engine_b200.kernels import KernelError
+
+    q, k, v, tables, ctx = _attention_case(2, 1, 16, 8, [1], [9], torch.float32)
+    with pytest.raises(KernelError, match="head_dim"):
+        ops.paged_attention(q, k, v, tables, ctx, 2, 1, 20, 8, 1.0, 0, torch.empty_like(q))

@@ -114,7 +114,8 @@ def test_linear_bf16(ops, out_dtype, m, n, k):
 @pytest.mark.parametrize("nh,nkv,hd,rd,ps", [(4, 2, 16, 16, 16), (3, 1, 32, 32, 8), (5, 5, 48, 48, 4),
                                              (32, 8, 64, 64, 16), (6, 2, 80, 32, 16), (2, 1, 128, 0, 32)])
 def test_rope_and_cache_write(ops, dtype, nh, nkv, hd, rd, ps):
-    n, pages, maxpos = 37, 9, 500
+    n, maxpos = 37, 500
+    pages = -(-n // ps) + 3
     qkv = torch.randn(n, (nh + 2 * nkv) * hd, device="cuda")
     positions = torch.randint(0, maxpos, (n,), device="cuda", dtype=torch.int32)
     table = None

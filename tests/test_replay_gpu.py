@@ -147,6 +147,8 @@ def test_trace_run_program(cases, tmp_path, dtype):
         timeout=600, env={**os.environ, "PYTHONPATH": ""})
     assert proc.returncode == 0, proc.stderr[-2000:]
     assert proc.stdout.split("\n")[:-1] == [f"done {s['step']}" for s in steps]
+    got = {rid: [] for rid in requests}
+    places = {rid: [] for rid in requests}
     fed = {rid: 0 for rid in requests}
     for s in steps:
         wanted = sum(len(e["want"]) for e in s["entries"])
@@ -154,12 +156,15 @@ def test_trace_run_program(cases, tmp_path, dtype):
         if wanted == 0:
             assert not path.exists()
         else:
+            assert path.stat().st_size == wanted * cfg["vocab_size"] * 4
             arr = torch.from_numpy(np.fromfile(path, dtype="<f4").reshape(wanted, cfg["vocab_size"]).copy())
             r = 0
             for e in s["entries"]:
                 for w in e["want"]:
-                    H.assert_close(arr[r:r + 1], want[e["id"]][fed[e["id"]] + w][None], dtype,
-                                   f"step {s['step']} request {e['id']} place {w}")
+                    got[e["id"]].append(arr[r])
+                    places[e["id"]].append(fed[e["id"]] + w)
                     r += 1
         for e in s["entries"]:
             fed[e["id"]] += len(e["tokens"])
+    for rid in requests:
+        H.assert_close(torch.stack(got[rid]), want[rid][places[rid]], dtype, f"trace_run {dtype} {rid}")

@@ -30,7 +30,8 @@ __device__ __forceinline__ float uniform_for(unsigned long long seed, unsigned l
     uint4 r = philox4x32_10(make_uint4(i >> 2, (unsigned)draw, (unsigned)(draw >> 32), 0u),
                             make_uint2((unsigned)seed, (unsigned)(seed >> 32)));
     unsigned x = (i & 3) == 0 ? r.x : (i & 3) == 1 ? r.y : (i & 3) == 2 ? r.z : r.w;
-    return ((float)(x >> 8) + 0.5f) * (1.0f / 16777216.0f);  // in (0, 1)
+    // 23 random bits plus a half: every value is exact in 32-bit and strictly inside (0, 1)
+    return ((float)(x >> 9) + 0.5f) * (1.0f / 8388608.0f);
 }
 
 struct Best { float v; int i; };

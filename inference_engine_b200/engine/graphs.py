@@ -1,0 +1,79 @@
+"""Decode steps as captured launch sequences (CUDA graphs).
+
+A decode-only step launches a hundred and more small kernels; at small batches their launch
+cost is a large part of the step.  For a few batch sizes (buckets) the whole forward pass is
+captured once and replayed: the step's index data is copied into the same staging addresses,
+padded up to the bucket with rows that read and write the cache's scratch page, and every
+kernel takes lengths and tables from device memory, so one capture serves every context
+length.  Bucket sizes are the reference's (engine/runtime/cuda_graphs.py:20-108).
+"""
+
+from __future__ import annotations
+
+BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+
+
+class DecodeGraphs:
+    def __init__(self, runner, max_num_seqs: int, table_width: int) -> None:
+        import torch
+
+        self.torch, self.runner = torch, runner
+        self.table_width = table_width
+        self.buckets = [b for b in BUCKETS if b <= max_num_seqs]
+        if not self.buckets or self.buckets[-1] < max_num_seqs:
+            self.buckets.append(max_num_seqs)
+        self._graphs: dict[int, tuple] = {}
+        self._version = None
+        self.replays = 0
+
+    def bucket_for(self, num_seqs: int) -> int | None:
+        for b in self.buckets:
+            if b >= num_seqs:
+                return b
+        return None
+
+    def kernels_per_replay(self, num_seqs: int) -> int:
+        """How many of the engine's own kernels one replay for ``num_seqs`` sequences launches."""
+        entry = self._graphs.get(self.bucket_for(num_seqs))
+        return entry[2] if entry else 0
+
+    def can_run(self, entries) -> bool:
+        if not entries or any(len(e.tokens) != 1 for e in entries):
+            return False
+        if self.bucket_for(len(entries)) is None:
+            return False
+        cache = self.runner.cache
+        return all(len(cache.table(g, e.req_id)) <= self.table_width
+                   for e in entries for g in range(len(cache.paged_groups)))
+
+    def run(self, entries):
+        """Returns the ``[len(entries), vocab]`` logits of a decode-only step (every entry
+        must want its one token)."""
+        torch, runner = self.torch, self.runner
+        bucket = self.bucket_for(len(entries))
+        if self._version != runner.ws.version:  # a buffer moved: captured addresses are stale
+            self._graphs.clear()
+        ctx, rows = runner.build_context(entries, pad_to_seqs=bucket, table_width=self.table_width)
+        if bucket not in self._graphs:
+            # Run once outside a capture (buffers get allocated, libraries initialised) ...
+            stream = torch.cuda.Stream()
+            stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(stream):
+                runner.model.forward(ctx, rows)
+            torch.cuda.current_stream().wait_stream(stream)
+            torch.cuda.synchronize()
+            if self._version != runner.ws.version:
+                self._graphs.clear()
+                self._version = runner.ws.version
+                ctx, rows = runner.build_context(entries, pad_to_seqs=bucket,
+                                                 table_width=self.table_width)
+            # ... then record the same launches.
+            graph = torch.cuda.CUDAGraph()
+            before = getattr(runner.ops, "launches", 0)
+            with torch.cuda.graph(graph):
+                logits = runner.model.forward(ctx, rows)
+            self._graphs[bucket] = (graph, logits, getattr(runner.ops, "launches", 0) - before)
+        graph, logits, _ = self._graphs[bucket]
+        graph.replay()
+        self.replays += 1
+        return logits[: len(entries)]

@@ -38,6 +38,7 @@ class ModelRunner:
         self._torch = torch
         self._staging_host = None
         self._staging_dev = None
+        self.last_h2d_bytes = 0
         self._ensure_staging(self._staging_ints(self.max_tokens, self.max_seqs, self.max_seqs, 8))
 
     # --- staging ----------------------------------------------------------------------------
@@ -147,6 +148,7 @@ class ModelRunner:
         buf[v_rows[0]: v_rows[0] + rows] = logit_rows
 
         self._staging_dev[:off].copy_(self._staging_host[:off], non_blocking=True)
+        self.last_h2d_bytes = off * 4
         dev = self._staging_dev
 
         def dview(view, shape=None):

@@ -119,3 +119,8 @@ def build_library(name: str, sources: list[str], defines: list[str] | None = Non
 
 def build_core() -> Path:
     return build_library("ie_b200_core", CORE_SOURCES)
+
+
+def build_all() -> list[Path]:
+    """Every library the package can load (the build check compiles them all)."""
+    return [build_core()]

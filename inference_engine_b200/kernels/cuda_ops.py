@@ -56,7 +56,7 @@ class CudaOps:
         self._declare()
         self.err = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._err_ptr = self.err.data_ptr()
-        self._mm_out_dtype = None
+        self.launches = 0  # launches of this library's kernels (library matrix products not counted)
 
     def _declare(self) -> None:
         P, I, F = c_void_p, c_int, c_float
@@ -80,6 +80,7 @@ class CudaOps:
         return self.torch.cuda.current_stream().cuda_stream
 
     def _check(self, code: int, what: str) -> None:
+        self.launches += 1
         if code != 0:
             raise KernelError(f"{what}: CUDA error {code} at launch")
 

@@ -1,0 +1,4 @@
+from .params import SamplingParams
+from .sampler import Sampler
+
+__all__ = ["Sampler", "SamplingParams"]

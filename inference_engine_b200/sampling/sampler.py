@@ -1,0 +1,81 @@
+"""From a step's logits to one token per finished row, on the device.
+
+One kernel launch serves all rows: greedy rows take the argmax (lowest index on ties, as
+``torch.argmax``), the others are drawn at their temperature after the repetition penalty and
+the top-k / top-p / min-p cut-offs, in the reference's order (engine/runtime/sampler.py:10-45).
+Randomness is counter-based: row ``r`` uses (its request's seed, how many tokens the request
+has produced), so a request's tokens do not depend on its neighbours in the batch.  The
+reference draws with ``torch.multinomial`` from one generator per request
+(engine/runtime/engine.py:156-157); the two agree in distribution, not bit for bit.
+"""
+
+from __future__ import annotations
+
+from typing import Any, Sequence as Seq
+
+
+class Sampler:
+    def __init__(self, ops, device, vocab_size: int) -> None:
+        import torch
+
+        self.ops, self.device, self.vocab_size, self.torch = ops, device, vocab_size, torch
+        self._tokens = torch.empty(0, dtype=torch.int32, device=device)
+
+    def _out(self, rows: int):
+        if self._tokens.numel() < rows:
+            self._tokens = self.torch.empty(max(rows, 64), dtype=self.torch.int32, device=self.device)
+        return self._tokens[:rows]
+
+    def sample(self, logits, params: Seq[Any], seeds: Seq[int], draws: Seq[int],
+               histories: Seq[Seq[int]] | None = None):
+        """``logits``: 32-bit ``[R, vocab]``.  ``params[r]``: the row's SamplingParams,
+        ``seeds[r]``/``draws[r]``: its request's seed and the number of tokens it has already
+        produced; ``histories[r]``: the ids the repetition penalty looks at.
+        Returns ``(tokens, logprobs)``: a list of ints and a list of floats or None."""
+        torch = self.torch
+        rows = logits.shape[0]
+        out = self._out(rows)
+        want_logprobs = any(p.logprobs for p in params)
+        logprob = torch.empty(rows, dtype=torch.float32, device=self.device) if want_logprobs else None
+        if all(p.greedy and p.repetition_penalty == 1.0 for p in params):
+            self.ops.sample(logits, out, logprob=logprob)
+        else:
+            dev = self.device
+            f32 = lambda vals: torch.tensor(vals, dtype=torch.float32, device=dev)  # noqa: E731
+            kwargs = dict(
+                temperature=f32([p.temperature for p in params]),
+                seeds=torch.tensor([s & 0x7FFFFFFFFFFFFFFF for s in seeds], dtype=torch.int64, device=dev),
+                draws=torch.tensor(list(draws), dtype=torch.int64, device=dev),
+            )
+            if any(p.top_k > 0 for p in params):
+                kwargs["top_k"] = torch.tensor([p.top_k for p in params], dtype=torch.int32, device=dev)
+            if any(p.top_p < 1.0 for p in params):
+                kwargs["top_p"] = f32([p.top_p for p in params])
+            if any(p.min_p > 0.0 for p in params):
+                kwargs["min_p"] = f32([p.min_p for p in params])
+            if any(p.repetition_penalty != 1.0 for p in params):
+                kwargs["penalty"] = f32([p.repetition_penalty for p in params])
+                kwargs["seen_bits"] = self._seen_bits(params, histories)
+            self.ops.sample(logits, out, logprob=logprob, **kwargs)
+        tokens = out.tolist()  # the step's one wait for the device
+        return tokens, (logprob.tolist() if logprob is not None else None)
+
+    def _seen_bits(self, params, histories):
+        """One bit per vocabulary entry and row: set where the id occurs in the row's history."""
+        import numpy as np
+
+        words = (self.vocab_size + 31) // 32
+        bits = np.zeros((len(params), words), dtype=np.uint32)
+        for r, (p, hist) in enumerate(zip(params, histories or [])):
+            if p.repetition_penalty == 1.0 or not hist:
+                continue
+            ids = np.unique(np.asarray(hist, dtype=np.int64))
+            np.bitwise_or.at(bits[r], ids >> 5, (np.uint32(1) << (ids & 31).astype(np.uint32)))
+        return self.torch.from_numpy(bits.view(np.int32)).to(self.device)
+
+    def top_logprobs(self, logits_row, k: int) -> list[tuple[int, float]]:
+        """The ``k`` most likely alternatives of one row with their log-probabilities
+        (engine/runtime/engine.py:283-298)."""
+        lp = logits_row.float().log_softmax(-1)
+        top = lp.topk(k)
+        return list(zip(top.indices.tolist(), top.values.tolist()))

@@ -86,3 +86,79 @@ class RefOps:
 
     def check_errors(self):
         return None
+
+
+# --- sampling -----------------------------------------------------------------------------------
+
+
+def philox_uniforms(seed: int, draw: int, n: int):
+    """The uniforms the sampling kernel uses for entries 0..n-1 of a row: Philox4x32-10 with
+    counter (i // 4, draw low, draw high, 0) and key (seed low, seed high); entry i takes word
+    i % 4; u = ((word >> 9) + 0.5) / 2^23."""
+    import numpy as np
+
+    mask = np.uint64(0xFFFFFFFF)
+    i = np.arange(n, dtype=np.uint64)
+    c0 = i >> np.uint64(2)
+    c1 = np.full(n, draw & 0xFFFFFFFF, dtype=np.uint64)
+    c2 = np.full(n, (draw >> 32) & 0xFFFFFFFF, dtype=np.uint64)
+    c3 = np.zeros(n, dtype=np.uint64)
+    k0, k1 = np.uint64(seed & 0xFFFFFFFF), np.uint64((seed >> 32) & 0xFFFFFFFF)
+    m0, m1 = np.uint64(0xD2511F53), np.uint64(0xCD9E8D57)
+    for _ in range(10):
+        p0, p1 = m0 * c0, m1 * c2
+        hi0, lo0, hi1, lo1 = p0 >> np.uint64(32), p0 & mask, p1 >> np.uint64(32), p1 & mask
+        c0, c1, c2, c3 = (hi1 ^ c1 ^ k0) & mask, lo1, (hi0 ^ c3 ^ k1) & mask, lo0
+        k0, k1 = (k0 + np.uint64(0x9E3779B9)) & mask, (k1 + np.uint64(0xBB67AE85)) & mask
+    words = np.stack([c0, c1, c2, c3], axis=1)[np.arange(n), (i & np.uint64(3)).astype(np.int64)]
+    return ((words >> np.uint64(9)).astype(np.float32) + np.float32(0.5)) * np.float32(1.0 / 8388608.0)
+
+
+def _sample_row(row, temperature, top_k, top_p, min_p, penalty, seen, seed, draw):
+    z = row.float().clone()
+    if penalty != 1.0 and seen is not None:
+        idx = seen.nonzero().flatten()
+        z[idx] = torch.where(z[idx] > 0, z[idx] / penalty, z[idx] * penalty)
+    if not temperature > 0:
+        return int(z.argmax()), None
+    z = z * (torch.tensor(1.0) / torch.tensor(temperature, dtype=torch.float32))
+    zmax = z.max()
+    keep_min = torch.tensor(float("-inf"))
+    if 0 < top_k < z.numel():
+        keep_min = torch.maximum(keep_min, z.topk(top_k).values[-1])
+    if top_p < 1.0:
+        kept = z[z >= keep_min].sort(descending=True).values
+        mass = torch.exp(kept - zmax)
+        target = max(top_p - 1e-6, 0.0) * float(mass.sum())
+        first = int((mass.cumsum(0) >= target).nonzero()[0]) if target > 0 else 0
+        keep_min = torch.maximum(keep_min, kept[first])
+    if min_p > 0.0:
+        keep_min = torch.maximum(keep_min, zmax + torch.log(torch.tensor(min_p, dtype=torch.float32)))
+    u = torch.from_numpy(philox_uniforms(seed, draw, z.numel()))
+    score = z - torch.log(-torch.log(u))
+    score[z < keep_min] = float("-inf")
+    return int(score.argmax()), score
+
+
+def _ref_sample(self, logits, out, temperature=None, top_k=None, top_p=None, min_p=None,
+                penalty=None, seen_bits=None, seeds=None, draws=None, logprob=None):
+    logits_c = logits.float().cpu()
+    rows, vocab = logits_c.shape
+
+    def get(t, r, default):
+        return default if t is None else t[r].item()
+
+    for r in range(rows):
+        seen = None
+        if seen_bits is not None:
+            words = seen_bits[r].cpu().to(torch.int64) & 0xFFFFFFFF
+            seen = ((words[:, None] >> torch.arange(32)[None, :]) & 1).reshape(-1)[:vocab].bool()
+        token, _ = _sample_row(logits_c[r], get(temperature, r, 0.0), int(get(top_k, r, 0)),
+                               get(top_p, r, 1.0), get(min_p, r, 0.0), get(penalty, r, 1.0), seen,
+                               int(get(seeds, r, 0)), int(get(draws, r, 0)))
+        out[r] = token
+        if logprob is not None:
+            logprob[r] = logits_c[r].log_softmax(-1)[token]
+
+
+RefOps.sample = _ref_sample

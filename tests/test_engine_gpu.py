@@ -1,0 +1,151 @@
+"""The engine end to end on the GPU: generation through the Python entry points against the
+plain implementation, captured decode steps against eager ones, preemption with few pages,
+seeded sampling that does not depend on the batch."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from tests import helpers as H
+from tests import plain_llama
+from tests.tiny_configs import PAGE_SIZE, TINY_A, TINY_B
+
+pytestmark = pytest.mark.gpu
+
+
+def _engine(cfg, weights, dtype, **kw):
+    from inference_engine_b200.engine.llm_engine import LLMEngine
+    from inference_engine_b200.engine.loading import model_from_tensors
+
+    model, _ = model_from_tensors(cfg, weights, dtype, "cuda", cfg["max_position_embeddings"])
+    kw.setdefault("debug_checks", True)
+    return LLMEngine(model, None, kw.pop("stop_token_ids", ()), **kw)
+
+
+def _check_greedy(cfg, weights, prompt, got, dtype):
+    """Every produced token is the plain implementation's argmax given the same prefix; in
+    bfloat16 a token within a small logit gap of the argmax also counts (near ties flip)."""
+    ids = list(prompt)
+    for i, token in enumerate(got):
+        logits = plain_llama.logits_for(cfg, weights, ids)[-1]
+        best = int(logits.argmax())
+        if token != best:
+            gap = float(logits[best] - logits[token])
+            assert dtype == "bfloat16" and gap < 0.1, (
+                f"token {i}: engine chose {token}, plain chose {best} (gap {gap:.4f})")
+        ids.append(token)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,cfg,lengths,max_tokens", [
+    ("A", TINY_A, [5, 17, 33], 8), ("B", TINY_B, [1, 9, 40, 70], 12)])
+def test_greedy_generation_matches_plain(name, cfg, lengths, max_tokens, dtype):
+    from inference_engine_b200 import SamplingParams
+
+    weights = H.make_weights(cfg, seed=3)
+    engine = _engine(cfg, weights, dtype, num_blocks=64, block_size=PAGE_SIZE[name],
+                     max_num_seqs=4, max_num_batched_tokens=24)
+    prompts = {f"p{i}": H.random_tokens(cfg, n, 40 + i) for i, n in enumerate(lengths)}
+    out = engine.generate(prompts, SamplingParams(temperature=0, max_tokens=max_tokens))
+    for rid, prompt in prompts.items():
+        assert len(out[rid]) == max_tokens
+        _check_greedy(cfg, weights, prompt, out[rid], dtype)
+    assert engine.cache.num_free_pages == [64]
+    assert not engine.has_unfinished()
+
+
+def test_generate_entry_point_and_stop_ids():
+    """`generate(model, tokenizer, prompts, params, stop_token_ids)` yields one output per
+    sequence and step; a stop id is returned as the last token with reason "stop"."""
+    from inference_engine_b200 import SamplingParams, generate
+    from inference_engine_b200.engine.loading import model_from_tensors
+
+    cfg, weights = TINY_A, H.make_weights(TINY_A, seed=4)
+    model, _ = model_from_tensors(cfg, weights, "float32", "cuda", 256)
+    prompts = [H.random_tokens(cfg, n, 50 + n) for n in (6, 21)]
+    free_run = [plain_llama.greedy_generate(cfg, weights, p, 10) for p in prompts]
+    stop = free_run[1][4]
+    outs = list(generate(model, None, prompts, SamplingParams(temperature=0, max_tokens=10), (stop,)))
+    for i, p in enumerate(prompts):
+        mine = [o for o in outs if o.seq_index == i]
+        want = plain_llama.greedy_generate(cfg, weights, p, 10, stop_ids=(stop,))
+        assert [o.token_id for o in mine] == want
+        assert mine[-1].finished and mine[-1].finish_reason == ("stop" if want[-1] == stop else "length")
+        assert all(not o.finished for o in mine[:-1])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_captured_decode_steps_equal_eager_ones(dtype):
+    from inference_engine_b200 import SamplingParams
+
+    cfg, weights = TINY_B, H.make_weights(TINY_B, seed=5)
+    prompts = {f"p{i}": H.random_tokens(cfg, n, 60 + i) for i, n in enumerate([3, 30, 11])}
+    outs = []
+    for graphs in (False, True):
+        engine = _engine(cfg, weights, dtype, num_blocks=40, block_size=8, max_num_seqs=4,
+                         max_num_batched_tokens=64, enable_cuda_graphs=graphs)
+        outs.append(engine.generate(prompts, SamplingParams(temperature=0, max_tokens=20)))
+        if graphs:
+            assert engine.graphs.replays >= 15
+    assert outs[0] == outs[1]
+
+
+def test_preemption_with_few_pages_gives_the_same_tokens():
+    """So few pages that running requests are preempted and prefilled again: the tokens are
+    those of each request alone (engine/runtime tests of the reference: test_engine.py:92-97)."""
+    from inference_engine_b200 import SamplingParams
+
+    cfg, weights = TINY_A, H.make_weights(TINY_A, seed=6)
+    prompts = {f"p{i}": H.random_tokens(cfg, n, 70 + i) for i, n in enumerate([20, 33, 14, 27])}
+    params = SamplingParams(temperature=0, max_tokens=24)
+    roomy = _engine(cfg, weights, "float32", num_blocks=64, block_size=4, max_num_seqs=4,
+                    max_num_batched_tokens=16)
+    want = roomy.generate(prompts, params)
+    tight = _engine(cfg, weights, "float32", num_blocks=24, block_size=4, max_num_seqs=4,
+                    max_num_batched_tokens=16)
+    got = tight.generate(prompts, params)
+    assert tight.scheduler.num_preemptions > 0
+    assert got == want
+    assert tight.cache.num_free_pages == [24]
+
+
+def test_seeded_sampling_does_not_depend_on_the_batch():
+    from inference_engine_b200 import SamplingParams
+
+    cfg, weights = TINY_B, H.make_weights(TINY_B, seed=7)
+    prompts = {f"p{i}": H.random_tokens(cfg, n, 80 + i) for i, n in enumerate([1, 9, 40, 70])}
+    params = SamplingParams(temperature=0.8, max_tokens=12, seed=1234)
+    engine = _engine(cfg, weights, "float32", num_blocks=64, block_size=8, max_num_seqs=4,
+                     max_num_batched_tokens=24)
+    together = engine.generate(prompts, params)
+    for rid, prompt in prompts.items():
+        assert engine.generate({rid: prompt}, params)[rid] == together[rid]
+    assert len({tuple(v) for v in together.values()}) > 1
+    other = engine.generate(prompts, SamplingParams(temperature=0.8, max_tokens=12, seed=99))
+    assert other != together
+
+
+def test_requests_that_cannot_fit_are_refused():
+    from inference_engine_b200 import SamplingParams
+
+    cfg, weights = TINY_A, H.make_weights(TINY_A, seed=8)
+    engine = _engine(cfg, weights, "float32", num_blocks=4, block_size=16, max_num_seqs=2,
+                     max_num_batched_tokens=16)
+    with pytest.raises(ValueError, match="exceeds"):
+        engine.add_request("big", [1] * 60, SamplingParams(max_tokens=10))
+    with pytest.raises(ValueError, match="at least one token"):
+        engine.add_request("empty", [], SamplingParams(max_tokens=1))
+    engine.add_request("ok", [1, 2, 3], SamplingParams(max_tokens=2))
+    with pytest.raises(ValueError, match="duplicate"):
+        engine.add_request("ok", [1], SamplingParams(max_tokens=2))
+    with pytest.raises(ValueError, match="vocabulary"):
+        engine.add_request("bad", [cfg["vocab_size"]], SamplingParams(max_tokens=2))
+    assert engine.abort("ok") and not engine.abort("ok")
+    assert engine.cache.num_free_pages == [4]
+
+
+def test_smoke_entry():
+    import __graft_entry__
+
+    __graft_entry__.smoke()

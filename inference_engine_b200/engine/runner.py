@@ -49,15 +49,29 @@ class ModelRunner:
         return (3 * _align4(n) + _align4(b + 1) + 2 * _align4(b) + _align4(r)
                 + groups * per_group + 16)
 
+    RING = 4  # pinned host buffers in rotation: a step may be packed while earlier copies wait
+
     def _ensure_staging(self, ints: int) -> None:
         torch = self._torch
-        if self._staging_host is not None and self._staging_host.numel() >= ints:
+        if self._staging_host is not None and self._staging_host[0].numel() >= ints:
             return
-        pin = self.device is not None and str(self.device).startswith("cuda")
-        self._staging_host = torch.empty(ints, dtype=torch.int32, pin_memory=pin)
-        self._staging_np = self._staging_host.numpy()
+        cuda = self.device is not None and str(self.device).startswith("cuda")
+        if cuda and self._staging_host is not None:
+            torch.cuda.synchronize()  # copies from the old buffers may still be queued
+        self._staging_host = [torch.empty(ints, dtype=torch.int32, pin_memory=cuda)
+                              for _ in range(self.RING)]
+        self._staging_events = [torch.cuda.Event() if cuda else None for _ in range(self.RING)]
+        self._staging_used = [False] * self.RING
+        self._staging_turn = 0
         self._staging_dev = torch.empty(ints, dtype=torch.int32, device=self.device)
         self.ws.version += 1
+
+    def _next_host_buffer(self):
+        """The next pinned buffer of the ring, once the copy that last read it has run."""
+        i = self._staging_turn = (self._staging_turn + 1) % self.RING
+        if self._staging_used[i] and self._staging_events[i] is not None:
+            self._staging_events[i].synchronize()
+        return i, self._staging_host[i].numpy()
 
     # --- one step ---------------------------------------------------------------------------
 
@@ -82,7 +96,7 @@ class ModelRunner:
                   for g in range(len(self.cache.paged_groups))]
         width = max([table_width or 1] + [len(t) for g in tables for t in g])
         self._ensure_staging(self._staging_ints(n, b, rows, width))
-        buf = self._staging_np
+        turn, buf = self._next_host_buffer()
         off = 0
 
         def take(count: int):
@@ -147,7 +161,10 @@ class ModelRunner:
         buf[v_state[0]: v_state[0] + b] = state_slots
         buf[v_rows[0]: v_rows[0] + rows] = logit_rows
 
-        self._staging_dev[:off].copy_(self._staging_host[:off], non_blocking=True)
+        self._staging_dev[:off].copy_(self._staging_host[turn][:off], non_blocking=True)
+        if self._staging_events[turn] is not None:
+            self._staging_events[turn].record()
+            self._staging_used[turn] = True
         self.last_h2d_bytes = off * 4
         dev = self._staging_dev
 

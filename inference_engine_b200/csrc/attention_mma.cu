@@ -1,0 +1,512 @@
+// Paged attention in bfloat16 on the tensor cores, one build per head size (-DIE_HD=64).
+//
+// Two kernels share the tile code below:
+//   * decode: requests that bring few tokens (tokens x group size <= 16 rows: one decoded
+//     token, or a portion of two or three) -- one block per (request, key/value head, split of
+//     the context).  The group's query heads are rows of one 16-row matrix, so every key and
+//     value is read once for the whole group; the context is split over blocks and over the
+//     four warps of a block (flash-decoding), and a small second kernel merges the splits in
+//     a fixed order.
+//   * prefill: longer portions -- one block per (64 query tokens, query head), four warps of
+//     16 rows each, walking the keys from the start of the window to the last query position
+//     (bottom-right causal mask for portions that start mid-sequence).
+// Keys and values come through the block table row by row (a row is a head's head_dim values
+// of one token, contiguous), are staged in shared memory with cp.async (double buffered,
+// zero-filled outside the valid range) and read with ldmatrix; products are
+// mma.sync.m16n8k16 with 32-bit accumulators.  Scores, the running maximum and sum are
+// 32-bit; the weights are rounded to bfloat16 before they multiply the values, as in the
+// reference's bfloat16 kernel (engine/kernels/paged_attention.py:125-136), whose counterparts
+// these are (together with the FlashAttention varlen call, engine/model/layers.py:246-253).
+// Window: a query at position p sees keys p - window + 1 .. p (window = 0: all).
+#include "common.cuh"
+#include <math.h>
+
+#ifndef IE_HD
+#error "compile with -DIE_HD=<head size, a multiple of 16, at most 128>"
+#endif
+
+namespace {
+constexpr int HD = IE_HD;
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 128, "head size must be a multiple of 16 up to 128");
+constexpr int C = HD / 8;                 // 16-byte chunks per row
+constexpr int KT = HD <= 64 ? 64 : 32;    // keys per tile
+constexpr int NT = KT / 8;                // 8-key score tiles per key tile
+constexpr int KS = HD / 16;               // 16-dim steps of q.k
+constexpr int DT = HD / 8;                // 8-dim tiles of the output
+constexpr int TILE_ELEMS = KT * HD;       // bfloat16 elements of one K or V tile
+constexpr bool SWZ = (C % 8 == 0);
+constexpr int WARPS = 4;
+constexpr int MAX_ROWS = 16;
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ int swz(int row, int c) { return SWZ ? (c ^ (row & 7)) : c; }
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    int bytes = valid ? 16 : 0;  // 0: nothing is read, the 16 bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+// Stage keys key0 .. key0 + KT - 1 of one key/value head into a shared-memory tile.  Keys
+// outside [lo, hi] are zero-filled.  `tid`/`nthreads`: the threads that share the tile.
+__device__ __forceinline__ void load_tile(bf16* tile, const bf16* __restrict__ cache,
+                                          const int* __restrict__ table, int key0, int lo, int hi,
+                                          int kvh, int nkv, int page_shift, int total_pages,
+                                          int tid, int nthreads, int* err) {
+    int page_mask = (1 << page_shift) - 1;
+    for (int idx = tid; idx < KT * C; idx += nthreads) {
+        int row = idx / C, c = idx - row * C;
+        int kpos = key0 + row;
+        bool valid = kpos >= lo && kpos <= hi;
+        const bf16* src = cache;
+        if (valid) {
+            int page = table[kpos >> page_shift];
+            if (page < 0 || page >= total_pages) {
+                ie_report(err, page < 0 ? IE_ERR_TABLE : IE_ERR_PAGE, page, kpos);
+                valid = false;
+            } else {
+                src = cache + ((((size_t)page * nkv + kvh) << page_shift) + (kpos & page_mask)) * HD + c * 8;
+            }
+        }
+        cp_async16(tile + (row * C + swz(row, c)) * 8, src, valid);
+    }
+}
+
+// The state of one warp's 16 rows: running maximum (in log2 units), running sum, output.
+struct RowState {
+    float m[2], l[2];
+    float o[DT][4];
+    __device__ __forceinline__ void init() {
+        m[0] = m[1] = -INFINITY;
+        l[0] = l[1] = 0.f;
+#pragma unroll
+        for (int d = 0; d < DT; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+    }
+};
+
+// One key tile for one warp: scores, mask, online softmax, weighted values.
+//   qf        : the warp's 16 query rows as A fragments
+//   qpos, qlo : for the thread's two rows (lane / 4 and lane / 4 + 8): position of the query
+//               and first key it may see; a row that does not exist has qpos < 0
+//   key_hi    : last key of the range this call may use (split end)
+__device__ __forceinline__ void process_tile(RowState& st, const unsigned (&qf)[KS][4],
+                                             const bf16* ktile, const bf16* vtile, int key0,
+                                             const int (&qpos)[2], const int (&qlo)[2], int key_hi,
+                                             float scale_log2, int lane) {
+    float s[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+        for (int n = 0; n < NT; n += 2) {
+            unsigned b[4];
+            int row = n * 8 + (lane & 7) + ((lane >> 4) << 3);
+            int c = ks * 2 + ((lane >> 3) & 1);
+            ldmatrix_x4(b, ktile + (row * C + swz(row, c)) * 8);
+            mma_bf16(s[n], qf[ks], b[0], b[1]);
+            mma_bf16(s[n + 1], qf[ks], b[2], b[3]);
+        }
+    }
+    float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            int r = j >> 1;
+            int kpos = key0 + n * 8 + (lane & 3) * 2 + (j & 1);
+            bool valid = kpos <= qpos[r] && kpos >= qlo[r] && kpos <= key_hi;
+            float v = valid ? s[n][j] * scale_log2 : -INFINITY;
+            s[n][j] = v;
+            tile_max[r] = fmaxf(tile_max[r], v);
+        }
+    }
+    float alpha[2], m_safe[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        float t = tile_max[r];
+        t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, 1));
+        t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, 2));
+        float m_new = fmaxf(st.m[r], t);
+        m_safe[r] = (m_new == -INFINITY) ? 0.f : m_new;
+        alpha[r] = exp2f(st.m[r] - m_safe[r]);  // 0 when nothing was seen before
+        st.m[r] = m_new;
+        st.l[r] *= alpha[r];
+    }
+#pragma unroll
+    for (int d = 0; d < DT; ++d) {
+        st.o[d][0] *= alpha[0]; st.o[d][1] *= alpha[0];
+        st.o[d][2] *= alpha[1]; st.o[d][3] *= alpha[1];
+    }
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float p = exp2f(s[n][j] - m_safe[j >> 1]);
+            s[n][j] = p;
+            st.l[j >> 1] += p;
+        }
+    }
+#pragma unroll
+    for (int kk = 0; kk < KT / 16; ++kk) {
+        unsigned a[4];
+        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int d = 0; d < DT; d += 2) {
+            unsigned b[4];
+            int row = kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+            int c = d + (lane >> 4);
+            ldmatrix_x4_trans(b, vtile + (row * C + swz(row, c)) * 8);
+            mma_bf16(st.o[d], a, b[0], b[1]);
+            mma_bf16(st.o[d + 1], a, b[2], b[3]);
+        }
+    }
+}
+
+__device__ __forceinline__ void finish_rows(RowState& st) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
+        st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
+    }
+}
+
+// -------------------------------------------------------------------------------------------------
+// Decode: few rows per request.  grid = (requests, kv heads, splits), 4 warps.
+// Partials for splits > 1: part_o[((seq * nkv + kvh) * splits + split) * 16 + row][HD],
+// part_ml[... ][2] = (maximum in log2 units, sum).
+// -------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(WARPS * 32)
+attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache,
+                        const bf16* __restrict__ v_cache, const int* __restrict__ tables,
+                        int table_width, const int* __restrict__ cu_q, const int* __restrict__ ctx_lens,
+                        bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+                        int nh, int nkv, int page_shift, int total_pages, float scale_log2,
+                        int window, int num_splits, int* err) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    bf16* smem = reinterpret_cast<bf16*>(smem_raw);
+    int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int G = nh / nkv;
+    int q0 = cu_q[seq], qlen = cu_q[seq + 1] - q0, ctx = ctx_lens[seq];
+    int rows = qlen * G;
+    if (rows > MAX_ROWS || qlen <= 0) return;  // the prefill kernel takes this request
+    const int* table = tables + (size_t)seq * table_width;
+    int first_qpos = ctx - qlen, hi = ctx - 1;
+    int lo = (window > 0 && first_qpos - window + 1 > 0) ? first_qpos - window + 1 : 0;
+    int total = hi - lo + 1;
+    int per = (((total + num_splits - 1) / num_splits) + KT - 1) / KT * KT;
+    int s_lo = lo + split * per;
+    int s_hi = min(hi, s_lo + per - 1);
+
+    // the thread's two rows
+    int qpos[2], qlo[2];
+    unsigned qf[KS][4];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        int row = (lane >> 2) + r * 8;
+        bool exists = row < rows;
+        int tok = exists ? row / G : 0, g = exists ? row - tok * G : 0;
+        qpos[r] = exists ? first_qpos + tok : -1;
+        qlo[r] = (window > 0 && qpos[r] - window + 1 > 0) ? qpos[r] - window + 1 : 0;
+        const bf16* qrow = q + ((size_t)(q0 + tok) * nh + kvh * G + g) * HD;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            int d = ks * 16 + (lane & 3) * 2;
+            qf[ks][r] = exists ? *reinterpret_cast<const unsigned*>(qrow + d) : 0u;
+            qf[ks][r + 2] = exists ? *reinterpret_cast<const unsigned*>(qrow + d + 8) : 0u;
+        }
+    }
+    RowState st;
+    st.init();
+    // each warp owns two stages of (K tile, V tile)
+    bf16* wbase = smem + (size_t)warp * 4 * TILE_ELEMS;
+    int n_tiles = s_lo <= s_hi ? (s_hi - s_lo) / KT + 1 : 0;
+    int stage = 0;
+    if (warp < n_tiles) {
+        int key0 = s_lo + warp * KT;
+        load_tile(wbase, k_cache, table, key0, s_lo, s_hi, kvh, nkv, page_shift, total_pages, lane, 32, err);
+        load_tile(wbase + TILE_ELEMS, v_cache, table, key0, s_lo, s_hi, kvh, nkv, page_shift, total_pages, lane, 32, err);
+    }
+    cp_async_commit();
+    for (int t = warp; t < n_tiles; t += WARPS) {
+        int key0 = s_lo + t * KT;
+        int next = t + WARPS;
+        bf16* cur = wbase + (size_t)stage * 2 * TILE_ELEMS;
+        bf16* nxt = wbase + (size_t)(stage ^ 1) * 2 * TILE_ELEMS;
+        if (next < n_tiles) {
+            int nkey0 = s_lo + next * KT;
+            load_tile(nxt, k_cache, table, nkey0, s_lo, s_hi, kvh, nkv, page_shift, total_pages, lane, 32, err);
+            load_tile(nxt + TILE_ELEMS, v_cache, table, nkey0, s_lo, s_hi, kvh, nkv, page_shift, total_pages, lane, 32, err);
+        }
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncwarp();
+        process_tile(st, qf, cur, cur + TILE_ELEMS, key0, qpos, qlo, s_hi, scale_log2, lane);
+        __syncwarp();
+        stage ^= 1;
+    }
+    cp_async_wait<0>();
+    finish_rows(st);
+    __syncthreads();  // every warp is done with its tiles: the shared memory is reused below
+
+    // merge the four warps: [warp][row] m, l and [warp][row][HD] o in shared memory
+    float* sm_ml = reinterpret_cast<float*>(smem_raw);            // [WARPS][16][2]
+    float* sm_o = sm_ml + WARPS * MAX_ROWS * 2;                   // [WARPS][16][HD]
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        int row = (lane >> 2) + r * 8;
+        if ((lane & 3) == 0) {
+            sm_ml[(warp * MAX_ROWS + row) * 2] = st.m[r];
+            sm_ml[(warp * MAX_ROWS + row) * 2 + 1] = st.l[r];
+        }
+#pragma unroll
+        for (int d = 0; d < DT; ++d) {
+            float* dst = sm_o + ((size_t)(warp * MAX_ROWS + row)) * HD + d * 8 + (lane & 3) * 2;
+            dst[0] = st.o[d][r * 2];
+            dst[1] = st.o[d][r * 2 + 1];
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < rows * HD; idx += WARPS * 32) {
+        int row = idx / HD, d = idx - row * HD;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) m = fmaxf(m, sm_ml[(w * MAX_ROWS + row) * 2]);
+        float m_safe = (m == -INFINITY) ? 0.f : m;
+        float l = 0.f, o = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+            float f = exp2f(sm_ml[(w * MAX_ROWS + row) * 2] - m_safe);
+            l += sm_ml[(w * MAX_ROWS + row) * 2 + 1] * f;
+            o += sm_o[((size_t)(w * MAX_ROWS + row)) * HD + d] * f;
+        }
+        if (num_splits == 1) {
+            int tok = row / G, g = row - tok * G;
+            out[((size_t)(q0 + tok) * nh + kvh * G + g) * HD + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+        } else {
+            size_t p = (((size_t)seq * nkv + kvh) * num_splits + split) * MAX_ROWS + row;
+            part_o[p * HD + d] = o;
+            if (d == 0) { part_ml[p * 2] = m; part_ml[p * 2 + 1] = l; }
+        }
+    }
+}
+
+// Merge the splits of the decode kernel, always in the order split 0, 1, 2, ...
+__global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                       const int* __restrict__ cu_q, bf16* __restrict__ out,
+                                       int nh, int nkv, int num_splits) {
+    int seq = blockIdx.x, kvh = blockIdx.y;
+    int G = nh / nkv;
+    int q0 = cu_q[seq], qlen = cu_q[seq + 1] - q0;
+    int rows = qlen * G;
+    if (rows > MAX_ROWS || qlen <= 0) return;
+    size_t base = ((size_t)seq * nkv + kvh) * num_splits * MAX_ROWS;
+    for (int idx = threadIdx.x; idx < rows * HD; idx += blockDim.x) {
+        int row = idx / HD, d = idx - row * HD;
+        float m = -INFINITY;
+        for (int s = 0; s < num_splits; ++s) m = fmaxf(m, part_ml[(base + (size_t)s * MAX_ROWS + row) * 2]);
+        float m_safe = (m == -INFINITY) ? 0.f : m;
+        float l = 0.f, o = 0.f;
+        for (int s = 0; s < num_splits; ++s) {
+            size_t p = base + (size_t)s * MAX_ROWS + row;
+            float f = exp2f(part_ml[p * 2] - m_safe);
+            l += part_ml[p * 2 + 1] * f;
+            o += part_o[p * HD + d] * f;
+        }
+        int tok = row / G, g = row - tok * G;
+        out[((size_t)(q0 + tok) * nh + kvh * G + g) * HD + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+    }
+}
+
+// -------------------------------------------------------------------------------------------------
+// Prefill: portions with more than 16 rows.  grid = (64-token tiles over all requests, heads).
+// -------------------------------------------------------------------------------------------------
+constexpr int BM = 64;
+
+__global__ void __launch_bounds__(WARPS * 32)
+attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache,
+                         const bf16* __restrict__ v_cache, const int* __restrict__ tables,
+                         int table_width, const int* __restrict__ cu_q, const int* __restrict__ ctx_lens,
+                         bf16* __restrict__ out, int num_seqs, int nh, int nkv, int page_shift,
+                         int total_pages, float scale_log2, int window, int* err) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    bf16* smem = reinterpret_cast<bf16*>(smem_raw);
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int head = blockIdx.y, G = nh / nkv, kvh = head / G;
+    // which request and which 64-token tile of it is this block's?
+    int tile = blockIdx.x, seq = -1, t0 = 0, q0 = 0, qlen = 0;
+    for (int s = 0; s < num_seqs; ++s) {
+        int a = cu_q[s], n = cu_q[s + 1] - a;
+        int tiles = (n * G > MAX_ROWS) ? (n + BM - 1) / BM : 0;
+        if (tile < tiles) { seq = s; t0 = tile * BM; q0 = a; qlen = n; break; }
+        tile -= tiles;
+    }
+    if (seq < 0) return;
+    int ctx = ctx_lens[seq];
+    const int* table = tables + (size_t)seq * table_width;
+    int first_qpos = ctx - qlen;                 // position of the portion's first token
+    int tile_rows = min(BM, qlen - t0);
+    int cta_qpos_lo = first_qpos + t0, cta_qpos_hi = first_qpos + t0 + tile_rows - 1;
+    int lo = (window > 0 && cta_qpos_lo - window + 1 > 0) ? cta_qpos_lo - window + 1 : 0;
+    int key_begin = (lo / KT) * KT;              // tiles are aligned to absolute position 0
+    int n_tiles = (cta_qpos_hi - key_begin) / KT + 1;
+
+    int qpos[2], qlo[2];
+    unsigned qf[KS][4];
+    int warp_hi = -1;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        int row = warp * 16 + (lane >> 2) + r * 8;
+        bool exists = row < tile_rows;
+        qpos[r] = exists ? cta_qpos_lo + row : -1;
+        qlo[r] = (window > 0 && qpos[r] - window + 1 > 0) ? qpos[r] - window + 1 : 0;
+        const bf16* qrow = q + ((size_t)(q0 + t0 + (exists ? row : 0)) * nh + head) * HD;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            int d = ks * 16 + (lane & 3) * 2;
+            qf[ks][r] = exists ? *reinterpret_cast<const unsigned*>(qrow + d) : 0u;
+            qf[ks][r + 2] = exists ? *reinterpret_cast<const unsigned*>(qrow + d + 8) : 0u;
+        }
+    }
+    warp_hi = min(cta_qpos_lo + warp * 16 + 15, cta_qpos_hi);  // last position this warp's rows see
+    int warp_lo_pos = cta_qpos_lo + warp * 16;
+    int warp_lo = (window > 0 && warp_lo_pos - window + 1 > 0) ? warp_lo_pos - window + 1 : 0;
+    bool warp_has_rows = warp * 16 < tile_rows;
+
+    RowState st;
+    st.init();
+    int stage = 0;
+    load_tile(smem, k_cache, table, key_begin, lo, cta_qpos_hi, kvh, nkv, page_shift, total_pages, threadIdx.x, WARPS * 32, err);
+    load_tile(smem + TILE_ELEMS, v_cache, table, key_begin, lo, cta_qpos_hi, kvh, nkv, page_shift, total_pages, threadIdx.x, WARPS * 32, err);
+    cp_async_commit();
+    for (int t = 0; t < n_tiles; ++t) {
+        int key0 = key_begin + t * KT;
+        bf16* cur = smem + (size_t)stage * 2 * TILE_ELEMS;
+        bf16* nxt = smem + (size_t)(stage ^ 1) * 2 * TILE_ELEMS;
+        if (t + 1 < n_tiles) {
+            load_tile(nxt, k_cache, table, key0 + KT, lo, cta_qpos_hi, kvh, nkv, page_shift, total_pages, threadIdx.x, WARPS * 32, err);
+            load_tile(nxt + TILE_ELEMS, v_cache, table, key0 + KT, lo, cta_qpos_hi, kvh, nkv, page_shift, total_pages, threadIdx.x, WARPS * 32, err);
+        }
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        if (warp_has_rows && key0 <= warp_hi && key0 + KT - 1 >= warp_lo)
+            process_tile(st, qf, cur, cur + TILE_ELEMS, key0, qpos, qlo, cta_qpos_hi, scale_log2, lane);
+        __syncthreads();
+        stage ^= 1;
+    }
+    cp_async_wait<0>();
+    finish_rows(st);
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        int row = warp * 16 + (lane >> 2) + r * 8;
+        if (row >= tile_rows) continue;
+        float inv = st.l[r] > 0.f ? 1.0f / st.l[r] : 0.f;
+        bf16* orow = out + ((size_t)(q0 + t0 + row) * nh + head) * HD;
+#pragma unroll
+        for (int d = 0; d < DT; ++d) {
+            __nv_bfloat162 v = __floats2bfloat162_rn(st.o[d][r * 2] * inv, st.o[d][r * 2 + 1] * inv);
+            *reinterpret_cast<__nv_bfloat162*>(orow + d * 8 + (lane & 3) * 2) = v;
+        }
+    }
+}
+
+constexpr size_t DECODE_SMEM = (size_t)WARPS * 4 * TILE_ELEMS * sizeof(bf16);
+constexpr size_t DECODE_MERGE_SMEM = (size_t)WARPS * MAX_ROWS * (2 + HD) * sizeof(float);
+constexpr size_t PREFILL_SMEM = (size_t)4 * TILE_ELEMS * sizeof(bf16);
+static_assert(DECODE_MERGE_SMEM <= DECODE_SMEM, "the merge area reuses the tile area");
+}  // namespace
+
+IE_API int ie_attention_head_dim() { return HD; }
+
+// Floats of scratch the decode kernel needs for `num_seqs` requests at `num_splits` splits:
+// part_o first, then part_ml.
+IE_API long long ie_attention_decode_scratch_floats(int num_seqs, int nkv, int num_splits) {
+    if (num_splits <= 1) return 0;
+    return (long long)num_seqs * nkv * num_splits * MAX_ROWS * (HD + 2);
+}
+
+// Requests with (tokens x group size) <= 16 rows.  `scratch` may be null when num_splits == 1.
+IE_API int ie_attention_decode(const void* q, const void* k_cache, const void* v_cache,
+                               const int* tables, int table_width, const int* cu_q,
+                               const int* ctx_lens, void* out, float* scratch, int num_seqs,
+                               int nh, int nkv, int page_size, int total_pages, float scale,
+                               int window, int num_splits, int* err, void* stream) {
+    if (num_seqs <= 0) return 0;
+    if (nkv <= 0 || nh % nkv != 0 || (page_size & (page_size - 1)) != 0 || num_splits < 1 ||
+        (num_splits > 1 && scratch == nullptr))
+        return (int)cudaErrorInvalidValue;
+    int page_shift = 0;
+    while ((1 << page_shift) < page_size) ++page_shift;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    float* part_o = scratch;
+    float* part_ml = scratch ? scratch + (size_t)num_seqs * nkv * num_splits * MAX_ROWS * HD : nullptr;
+    dim3 grid(num_seqs, nkv, num_splits);
+    attention_decode_kernel<<<grid, WARPS * 32, DECODE_SMEM, s>>>(
+        (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, tables, table_width, cu_q, ctx_lens,
+        (bf16*)out, part_o, part_ml, nh, nkv, page_shift, total_pages, scale * 1.4426950408889634f,
+        window, num_splits, err);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess || num_splits == 1) return (int)e;
+    attention_merge_kernel<<<dim3(num_seqs, nkv), 128, 0, s>>>(part_o, part_ml, cu_q, (bf16*)out, nh, nkv, num_splits);
+    return IE_LAUNCH_CHECK();
+}
+
+// Requests with more than 16 rows.  `max_tiles` bounds the number of 64-token tiles over all
+// such requests (num_tokens / 64 + num_seqs always suffices).
+IE_API int ie_attention_prefill(const void* q, const void* k_cache, const void* v_cache,
+                                const int* tables, int table_width, const int* cu_q,
+                                const int* ctx_lens, void* out, int num_seqs, int max_tiles,
+                                int nh, int nkv, int page_size, int total_pages, float scale,
+                                int window, int* err, void* stream) {
+    if (num_seqs <= 0 || max_tiles <= 0) return 0;
+    if (nkv <= 0 || nh % nkv != 0 || (page_size & (page_size - 1)) != 0) return (int)cudaErrorInvalidValue;
+    int page_shift = 0;
+    while ((1 << page_shift) < page_size) ++page_shift;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PREFILL_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid(max_tiles, nh);
+    attention_prefill_kernel<<<grid, WARPS * 32, PREFILL_SMEM, (cudaStream_t)stream>>>(
+        (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, tables, table_width, cu_q, ctx_lens,
+        (bf16*)out, num_seqs, nh, nkv, page_shift, total_pages, scale * 1.4426950408889634f, window, err);
+    return IE_LAUNCH_CHECK();
+}

@@ -15,6 +15,7 @@ import shutil
 import subprocess
 import sys
 import tempfile
+import threading
 import time
 from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
@@ -47,7 +48,13 @@ def find_nvcc() -> str:
                      "the engine's kernels cannot be built")
 
 
+_BUILD_DIR: Path | None = None
+
+
 def build_dir() -> Path:
+    global _BUILD_DIR
+    if _BUILD_DIR is not None:
+        return _BUILD_DIR
     env = os.environ.get("IE_B200_BUILD_DIR")
     candidates = [Path(env)] if env else []
     candidates.append(CSRC / "_build")
@@ -55,9 +62,10 @@ def build_dir() -> Path:
     for d in candidates:
         try:
             d.mkdir(parents=True, exist_ok=True)
-            probe = d / f".w{os.getpid()}"
+            probe = d / f".w{os.getpid()}-{threading.get_ident()}"
             probe.write_text("")
-            probe.unlink()
+            probe.unlink(missing_ok=True)
+            _BUILD_DIR = d
             return d
         except OSError:
             continue
@@ -99,7 +107,7 @@ def build_library(name: str, sources: list[str], defines: list[str] | None = Non
         return lib
     nvcc = find_nvcc()
     _say(f"building {lib.name} for sm_100a from {len(srcs)} file(s) with {nvcc} (first use only)")
-    tag = f"{name}-{os.getpid()}"
+    tag = f"{name}-{os.getpid()}-{threading.get_ident()}"
     objs = [out_dir / f"{tag}-{s.stem}.o" for s in srcs]
     try:
         with ThreadPoolExecutor(max_workers=min(len(srcs), os.cpu_count() or 2)) as pool:
@@ -121,6 +129,20 @@ def build_core() -> Path:
     return build_library("ie_b200_core", CORE_SOURCES)
 
 
+ATTENTION_HEAD_DIMS = tuple(range(16, 129, 16))  # head sizes the tensor-core attention takes
+
+
+def build_attention(head_dim: int) -> Path:
+    """The bfloat16 tensor-core attention kernels for one head size (compiled on first use
+    for the head size the loaded model has)."""
+    if head_dim not in ATTENTION_HEAD_DIMS:
+        raise BuildError(f"the tensor-core attention takes head sizes {ATTENTION_HEAD_DIMS}, not {head_dim}")
+    return build_library(f"ie_b200_attn_hd{head_dim}", ["attention_mma.cu"], [f"-DIE_HD={head_dim}"])
+
+
 def build_all() -> list[Path]:
     """Every library the package can load (the build check compiles them all)."""
-    return [build_core()]
+    libs = [build_core()]
+    with ThreadPoolExecutor(max_workers=os.cpu_count() or 2) as pool:
+        libs += list(pool.map(build_attention, ATTENTION_HEAD_DIMS))
+    return libs

@@ -14,7 +14,7 @@ from __future__ import annotations
 import ctypes
 from ctypes import c_float, c_int, c_void_p
 
-from .build import build_core
+from .build import ATTENTION_HEAD_DIMS, build_attention, build_core
 
 _ERRORS = {
     1: "a token id outside the vocabulary",
@@ -56,6 +56,8 @@ class CudaOps:
         self._declare()
         self.err = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._err_ptr = self.err.data_ptr()
+        self._attn_libs: dict[int, object] = {}
+        self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.launches = 0  # launches of this library's kernels (library matrix products not counted)
 
     def _declare(self) -> None:
@@ -137,10 +139,71 @@ class CudaOps:
             v_cache.data_ptr(), _dtype_code(q_out), self._ptr(slot_mapping), qkv.shape[0],
             nh, nkv, hd, page_size, k_cache.shape[0], self._err_ptr, self._stream()), "rope_kv_write")
 
+    def _attention_lib(self, hd: int):
+        """The tensor-core attention library for head size ``hd`` (built on first use)."""
+        lib = self._attn_libs.get(hd)
+        if lib is None:
+            lib = ctypes.CDLL(str(build_attention(hd)))
+            P, I, F = c_void_p, c_int, c_float
+            lib.ie_attention_decode.argtypes = [P, P, P, P, I, P, P, P, P, I, I, I, I, I, F, I, I, P, P]
+            lib.ie_attention_prefill.argtypes = [P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P, P]
+            lib.ie_attention_decode_scratch_floats.argtypes = [I, I, I]
+            lib.ie_attention_decode_scratch_floats.restype = ctypes.c_longlong
+            self._attn_libs[hd] = lib
+        return lib
+
+    def decode_splits(self, num_seqs: int, nkv: int) -> int:
+        """Into how many parts the decode kernel cuts each context: enough blocks to fill the
+        GPU twice, whatever the contexts' lengths (so that a captured launch stays valid)."""
+        blocks = max(num_seqs * nkv, 1)
+        return max(1, min(-(-2 * self.sm_count // blocks), 32))
+
     def paged_attention(self, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, page_size,
                         scale, window, out) -> None:
+        """Attention of every token of the step over its request's cached keys and values.
+        bfloat16 with a head size the tensor-core kernels take and at most 16 query heads per
+        key/value head: requests with few rows go to the split decode kernel, longer portions
+        to the prefill kernel.  Everything else (32-bit, other head sizes) runs the general
+        kernel, whose order of operations does not depend on the batch."""
         if hd % 8 or hd > 256:
             raise KernelError(f"head_dim {hd} is not supported: it must be a multiple of 8, at most 256")
+        if nkv < 1 or nh % nkv:
+            raise KernelError(f"{nh} query heads cannot share {nkv} key/value heads")
+        torch = self.torch
+        groups = nh // nkv
+        total_pages = k_cache.shape[0]
+        if q.dtype == torch.bfloat16 and hd in ATTENTION_HEAD_DIMS and groups <= 16:
+            lib = self._attention_lib(hd)
+            small = [ql * groups <= 16 for ql in ctx.q_lens]
+            stream = self._stream()
+            if any(small):
+                splits = self.decode_splits(ctx.num_seqs, nkv)
+                floats = lib.ie_attention_decode_scratch_floats(ctx.num_seqs, nkv, splits)
+                scratch = None
+                if floats:
+                    ws = getattr(ctx, "ws", None)
+                    scratch = (ws.buffer("attn.partial", 1, floats, torch.float32) if ws is not None
+                               else torch.empty(floats, dtype=torch.float32, device=q.device))
+                self._check(lib.ie_attention_decode(
+                    q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
+                    block_tables.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_lens.data_ptr(), out.data_ptr(),
+                    self._ptr(scratch), ctx.num_seqs, nh, nkv, page_size, total_pages, scale, window,
+                    splits, self._err_ptr, stream), "attention_decode")
+                if splits > 1:
+                    self.launches += 1  # the merge of the splits
+            if not all(small):
+                tiles = sum(-(-ql // 64) for ql, s in zip(ctx.q_lens, small) if not s)
+                self._check(lib.ie_attention_prefill(
+                    q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
+                    block_tables.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_lens.data_ptr(), out.data_ptr(),
+                    ctx.num_seqs, tiles, nh, nkv, page_size, total_pages, scale, window,
+                    self._err_ptr, stream), "attention_prefill")
+            return
+        self.paged_attention_general(q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, page_size,
+                                     scale, window, out)
+
+    def paged_attention_general(self, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd,
+                                page_size, scale, window, out) -> None:
         self._check(self._paged_attention_generic(
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _dtype_code(q),
             block_tables.data_ptr(), block_tables.shape[1], ctx.seq_of_token.data_ptr(),

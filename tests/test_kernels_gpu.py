@@ -204,7 +204,7 @@ ATTN_SHAPES = [(4, 2, 16, 16), (3, 1, 32, 8), (5, 5, 48, 4), (32, 8, 64, 16), (8
 @pytest.mark.parametrize("nh,nkv,hd,ps", ATTN_SHAPES)
 @pytest.mark.parametrize("window", [0, 37])
 def test_paged_attention_mixed_step(ops, dtype, nh, nkv, hd, ps, window):
-    q_lens, ctx_lens = [1, 17, 2, 1, 40], [200, 17, 65, 1, 333]
+    q_lens, ctx_lens = [1, 17, 2, 1, 40, 130, 3, 70], [200, 17, 65, 1, 333, 500, 64, 70]
     q, k, v, tables, ctx = _attention_case(nh, nkv, hd, ps, q_lens, ctx_lens, dtype)
     got = torch.empty_like(q)
     want = torch.empty_like(q)
@@ -214,6 +214,41 @@ def test_paged_attention_mixed_step(ops, dtype, nh, nkv, hd, ps, window):
     tol = dict(atol=2e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
     torch.testing.assert_close(got.float(), want.float(), **tol)
     ops.check_errors()
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps", ATTN_SHAPES)
+@pytest.mark.parametrize("window", [0, 100])
+def test_paged_attention_decode_only_and_prefill_only(ops, nh, nkv, hd, ps, window):
+    """bfloat16: a decode-only step (every context length around tile and page edges, cut
+    into several splits) and a prefill-only step (portions longer than a 64-token tile, from
+    the start of a sequence and from its middle)."""
+    dtype = torch.bfloat16
+    cases = [([1] * 9, [1, 15, 16, 17, 63, 64, 65, 1000, 257]),
+             ([200, 65, 130, 64], [200, 65, 700, 128])]
+    for q_lens, ctx_lens in cases:
+        q, k, v, tables, ctx = _attention_case(nh, nkv, hd, ps, q_lens, ctx_lens, dtype, seed=3)
+        got = torch.empty_like(q)
+        want = torch.empty_like(q)
+        ops.paged_attention(q, k, v, tables, ctx, nh, nkv, hd, ps, hd ** -0.5, window, got)
+        RefOps().paged_attention(q, k, v, tables, ctx, nh, nkv, hd, ps, hd ** -0.5, window, want)
+        torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+        general = torch.empty_like(q)
+        ops.paged_attention_general(q, k, v, tables, ctx, nh, nkv, hd, ps, hd ** -0.5, window, general)
+        torch.testing.assert_close(general.float(), want.float(), atol=2e-2, rtol=2e-2)
+    ops.check_errors()
+
+
+def test_decode_attention_with_many_splits_is_the_same_as_one(ops):
+    """A single request fills the GPU by cutting its context into many splits; the merged
+    result equals the unsplit one up to rounding."""
+    nh, nkv, hd, ps = 8, 2, 64, 16
+    q, k, v, tables, ctx = _attention_case(nh, nkv, hd, ps, [1], [3000], torch.bfloat16, seed=4)
+    assert ops.decode_splits(1, nkv) > 8
+    got = torch.empty_like(q)
+    ops.paged_attention(q, k, v, tables, ctx, nh, nkv, hd, ps, hd ** -0.5, 0, got)
+    want = torch.empty_like(q)
+    RefOps().paged_attention(q, k, v, tables, ctx, nh, nkv, hd, ps, hd ** -0.5, 0, want)
+    torch.testing.assert_close(got.float(), want.float(), atol=1e-2, rtol=1e-2)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

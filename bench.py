@@ -334,26 +334,37 @@ def run_reference(args) -> dict:
             write_random_model(dict(LLAMA_1B), tmp, seed=0)
             model = load_model(tmp, device="cuda", dtype=torch.bfloat16)
         blocks = -(-args.batch * (PROMPT_LEN + args.warmup + args.steps + 64) // BLOCK_SIZE)
-        engine = RefEngine(model, _StubTokenizer(), (), num_blocks=blocks, block_size=BLOCK_SIZE,
-                           max_num_seqs=max(args.batch, 8), max_num_batched_tokens=4 * PROMPT_LEN,
-                           enable_prefix_caching=False, max_model_len=MAX_CONTEXT)
         g = torch.Generator().manual_seed(2)
         prompts = torch.randint(0, LLAMA_1B["vocab_size"], (args.batch, PROMPT_LEN), generator=g).tolist()
         params = RefParams(temperature=0.0, max_tokens=args.warmup + args.steps + 8)
-        for i, p in enumerate(prompts):
-            engine.add_request(f"ref-{i}", p, params)
+
+        def attempt(tag: str, **mode):
+            engine = RefEngine(model, _StubTokenizer(), (), num_blocks=blocks, block_size=BLOCK_SIZE,
+                               max_num_seqs=max(args.batch, 8), max_num_batched_tokens=4 * PROMPT_LEN,
+                               enable_prefix_caching=False, max_model_len=MAX_CONTEXT, **mode)
+            for i, p in enumerate(prompts):
+                engine.add_request(f"ref-{tag}-{i}", p, params)
+            produced = 0
+            while produced < args.batch * args.warmup:
+                produced += len(engine.step())
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            tokens = 0
+            for _ in range(args.steps):
+                tokens += len(engine.step())
+            torch.cuda.synchronize()
+            return tokens, time.perf_counter() - t0
+
         sampler = ClockSampler()
         sampler.start()
-        produced = 0
-        while produced < args.batch * args.warmup:
-            produced += len(engine.step())
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        tokens = 0
-        for _ in range(args.steps):
-            tokens += len(engine.step())
-        torch.cuda.synchronize()
-        elapsed = time.perf_counter() - t0
+        mode = "default (Triton decode kernel, CUDA graphs)"
+        try:
+            tokens, elapsed = attempt("default")
+        except Exception as first:  # its fast path needs a newer torch than this image has
+            mode = (f"eager (use_triton=False, its bench_decode.py 'eager' mode); the default mode "
+                    f"raised {type(first).__name__}: {str(first)[:120]}")
+            torch.cuda.synchronize()
+            tokens, elapsed = attempt("eager", use_triton=False)
         clocks = sampler.stop()
         tps = tokens / elapsed
         return {
@@ -364,6 +375,7 @@ def run_reference(args) -> dict:
             "data": "synthetic: seeded random weights N(0, 0.02), uniform-random token ids",
             "config": {"model": "llama-3.2-1b-shape", "global_batch": args.batch,
                        "seq_len": PROMPT_LEN, "block_size": BLOCK_SIZE, "parallelism": "single-gpu",
+                       "mode": mode,
                        "timing": "wall clock around LLMEngine.step(), synchronised on both sides"},
             "e2e": {"value": round(tps, 1), "unit": "tokens/s"},
             "clocks": clocks,

@@ -19,7 +19,9 @@
 // these are (together with the FlashAttention varlen call, engine/model/layers.py:246-253).
 // Window: a query at position p sees keys p - window + 1 .. p (window = 0: all).
 #include "common.cuh"
+#include "ie_no_alloc.h"
 #include <math.h>
+#include <stdio.h>
 
 #ifndef IE_HD
 #error "compile with -DIE_HD=<head size, a multiple of 16, at most 128>"
@@ -509,4 +511,71 @@ IE_API int ie_attention_prefill(const void* q, const void* k_cache, const void* 
         (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, tables, table_width, cu_q, ctx_lens,
         (bf16*)out, num_seqs, nh, nkv, page_shift, total_pages, scale * 1.4426950408889634f, window, err);
     return IE_LAUNCH_CHECK();
+}
+
+// -------------------------------------------------------------------------------------------------
+// The decode kernel for callers that cannot allocate device memory (declared in ie_no_alloc.h).
+// The split partials live in a fixed array that is part of this library's device image.
+// -------------------------------------------------------------------------------------------------
+namespace {
+// Scratch for the split partials of `ie_attention_decode_static`.  Every GPU that loads this
+// library holds these 4 MiB until the process exits.
+static __device__ __align__(256) float g_static_decode_scratch[IE_STATIC_DECODE_SCRATCH_FLOATS];
+
+constexpr int MAX_DEVICES = 64;
+// In host code the array's name is only a handle; the device address is looked up once per
+// device with cudaGetSymbolAddress and kept here.
+float* g_static_scratch_ptr[MAX_DEVICES] = {nullptr};
+
+int fail(char* msg, int msg_len, int code, const char* text) {
+    if (msg != nullptr && msg_len > 0) snprintf(msg, (size_t)msg_len, "%s", text);
+    return code;
+}
+}  // namespace
+
+IE_API long long ie_attention_decode_static_capacity_floats() { return IE_STATIC_DECODE_SCRATCH_FLOATS; }
+
+IE_API int ie_attention_decode_static(const void* q, const void* k_cache, const void* v_cache,
+                                      const int* tables, int table_width, const int* cu_q,
+                                      const int* ctx_lens, void* out, int num_seqs, int nh, int nkv,
+                                      int page_size, int total_pages, float scale, int window,
+                                      int num_splits, int* err, void* stream, char* msg, int msg_len) {
+    if (msg != nullptr && msg_len > 0) msg[0] = 0;
+    if (num_seqs <= 0) return 0;
+    if (nkv <= 0 || nh % nkv != 0 || num_splits < 1)
+        return fail(msg, msg_len, (int)cudaErrorInvalidValue, "ie_attention_decode_static: bad head counts or split count");
+    long long need = ie_attention_decode_scratch_floats(num_seqs, nkv, num_splits);
+    if (need > IE_STATIC_DECODE_SCRATCH_FLOATS) {
+        char text[512];
+        snprintf(text, sizeof(text),
+                 "ie_attention_decode_static: %d requests x %d key/value heads x %d splits need %lld "
+                 "floats of scratch, the built-in array holds %lld; use fewer splits or smaller batches, "
+                 "or call ie_attention_decode with scratch of your own",
+                 num_seqs, nkv, num_splits, need, (long long)IE_STATIC_DECODE_SCRATCH_FLOATS);
+        return fail(msg, msg_len, IE_STATIC_SCRATCH_TOO_SMALL, text);
+    }
+    float* scratch = nullptr;
+    if (num_splits > 1) {
+        int dev = -1;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return fail(msg, msg_len, (int)e, "ie_attention_decode_static: cudaGetDevice failed");
+        if (dev < 0 || dev >= MAX_DEVICES)
+            return fail(msg, msg_len, (int)cudaErrorInvalidDevice, "ie_attention_decode_static: device index out of range");
+        if (g_static_scratch_ptr[dev] == nullptr) {
+            // First call on this device (it is the current one): ask the runtime where this
+            // device's copy of the array lives.  Not an allocation; do it before any capture.
+            float* ptr = nullptr;
+            e = cudaGetSymbolAddress((void**)&ptr, g_static_decode_scratch);
+            if (e != cudaSuccess || ptr == nullptr)
+                return fail(msg, msg_len, e != cudaSuccess ? (int)e : (int)cudaErrorInvalidSymbol,
+                            "ie_attention_decode_static: cudaGetSymbolAddress failed for the scratch array");
+            g_static_scratch_ptr[dev] = ptr;
+        }
+        scratch = g_static_scratch_ptr[dev];
+    }
+    int rc = ie_attention_decode(q, k_cache, v_cache, tables, table_width, cu_q, ctx_lens, out, scratch,
+                                 num_seqs, nh, nkv, page_size, total_pages, scale, window, num_splits,
+                                 err, stream);
+    if (rc != 0) return fail(msg, msg_len, rc, "ie_attention_decode_static: the kernel launch failed");
+    return 0;
 }

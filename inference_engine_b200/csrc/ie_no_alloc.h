@@ -1,0 +1,58 @@
+// ie_attention_decode_static -- paged decode attention for callers that cannot allocate.
+//
+// This entry point has no counterpart in the reference: it is an addition of this library.
+//
+// Who it is for.  Some hosts of this library are not allowed to call cudaMalloc (or any
+// routine that allocates device memory on their behalf) at the point where they run attention:
+// a plugin inside a runtime that owns all device memory and hands out none, code running
+// while the memory pool is frozen, or a latency-critical loop whose owner forbids allocator
+// calls.  The regular entry point, ie_attention_decode, needs scratch memory for the partial
+// results of its context splits and expects the caller to bring it.  This variant brings its
+// own: a fixed array compiled into the library's device image.
+//
+// What it does.  Exactly what ie_attention_decode does (same kernels, same results) for
+// requests with at most 16 rows (tokens x query heads per key/value head).  Inputs and outputs
+// are still the caller's.  It calls no cudaMalloc, cudaFree or allocating library routine.
+//
+// Limits and rules.
+//   * The scratch array holds IE_STATIC_DECODE_SCRATCH_FLOATS floats (4 MiB).  A call needs
+//     num_seqs * nkv * num_splits * 16 * (head_dim + 2) floats when num_splits > 1 and none
+//     when num_splits == 1.  A call that needs more is refused with
+//     IE_STATIC_SCRATCH_TOO_SMALL and a message that says how much was asked for; nothing is
+//     launched.  Every GPU that loads the library holds the array until the process exits.
+//   * The first call with num_splits > 1 on a device looks up the array's device address
+//     (cudaGetSymbolAddress, with that device current; the address is kept per device).
+//     Make that first call outside any stream capture.
+//   * All calls share the one array, and it keeps what the last call left.  Nothing in it has
+//     to start at zero: a call writes every partial it later reads.  Because it is shared,
+//     two calls whose kernels can overlap on the GPU (different streams, no dependency) race
+//     on it; run such calls on one stream or order them with events.
+//   * `msg`, if not null, receives a zero-terminated explanation when the return value is
+//     not 0 (at most msg_len bytes).
+#pragma once
+
+#define IE_STATIC_DECODE_SCRATCH_FLOATS (1 << 20)
+#define IE_STATIC_SCRATCH_TOO_SMALL (-1001)
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// Floats the built-in scratch array holds.
+long long ie_attention_decode_static_capacity_floats(void);
+
+// q [tokens, nh * head_dim], out likewise (bfloat16); k_cache, v_cache
+// [pages, nkv, page_size, head_dim] (bfloat16); tables [num_seqs, table_width] int32 (page of
+// every 'page_size' positions); cu_q [num_seqs + 1] first token of each request; ctx_lens
+// [num_seqs] tokens cached after this step; err: 4 ints of device memory for index-check
+// reports, or null; stream: a cudaStream_t.  Returns 0, a cudaError_t, or
+// IE_STATIC_SCRATCH_TOO_SMALL.
+int ie_attention_decode_static(const void* q, const void* k_cache, const void* v_cache,
+                               const int* tables, int table_width, const int* cu_q,
+                               const int* ctx_lens, void* out, int num_seqs, int nh, int nkv,
+                               int page_size, int total_pages, float scale, int window,
+                               int num_splits, int* err, void* stream, char* msg, int msg_len);
+
+#ifdef __cplusplus
+}
+#endif

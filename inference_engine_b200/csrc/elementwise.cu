@@ -38,9 +38,9 @@ IE_API int ie_embedding(const void* table, int table_dtype, const int* ids, floa
 // the row's width and the block size, never on the other rows of the step.
 // ---------------------------------------------------------------------------------------------
 template <typename OutT, int THREADS>
-__global__ void rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta,
-                               const float* __restrict__ weight, float eps, OutT* __restrict__ out,
-                               const int* __restrict__ rows, int hidden) {
+__global__ void rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, int num_partials,
+                               size_t partial_stride, const float* __restrict__ weight, float eps,
+                               OutT* __restrict__ out, const int* __restrict__ rows, int hidden) {
     __shared__ float partial[THREADS / 32];
     __shared__ float inv_rms;
     int r = blockIdx.x;
@@ -51,7 +51,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ 
     float ss = 0.f;
     for (int i = threadIdx.x; i < hidden; i += THREADS) {
         float x = hrow[i];
-        if (drow) x += drow[i];
+        if (drow) for (int p = 0; p < num_partials; ++p) x += drow[p * partial_stride + i];
         if (write_back) hrow[i] = x;
         ss += x * x;
     }
@@ -69,20 +69,109 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ 
     OutT* orow = out + (size_t)r * hidden;
     for (int i = threadIdx.x; i < hidden; i += THREADS) {
         float x = hrow[i];
-        if (drow && !write_back) x += drow[i];
+        if (drow && !write_back) for (int p = 0; p < num_partials; ++p) x += drow[p * partial_stride + i];
         ie_store(orow + i, weight[i] * (x * scale));
     }
 }
 
-IE_API int ie_rmsnorm(float* h, const float* delta, const float* weight, float eps, void* out,
-                      int out_dtype, const int* rows, int num_rows, int hidden, void* stream) {
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u = make_uint2(*reinterpret_cast<unsigned*>(&lo), *reinterpret_cast<unsigned*>(&hi));
+    *reinterpret_cast<uint2*>(p) = u;
+}
+
+// The same result for rows whose width is a multiple of 4 and at most THREADS * 4 * VPT: every
+// thread keeps its part of the row in registers, so the row is read once and all loads are in
+// flight together (a decode step's few rows are bound by latency, not bandwidth).  The order
+// in which a row's squares are added depends only on the row's width.
+template <typename OutT, int THREADS, int VPT>
+__global__ void __launch_bounds__(THREADS)
+rmsnorm_vec_kernel(float* __restrict__ h, const float* __restrict__ delta, int num_partials,
+                   size_t partial_stride, const float* __restrict__ weight, float eps,
+                   OutT* __restrict__ out, const int* __restrict__ rows, int hidden) {
+    __shared__ float partial[THREADS / 32];
+    __shared__ float inv_rms;
+    int r = blockIdx.x;
+    size_t src = (size_t)(rows ? rows[r] : r) * hidden;
+    bool write_back = (rows == nullptr) && (delta != nullptr);
+    float4 x[VPT];
+    float ss = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+        int i = (v * THREADS + threadIdx.x) * 4;
+        x[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < hidden) x[v] = *reinterpret_cast<const float4*>(h + src + i);
+    }
+    if (delta) {
+        for (int p = 0; p < num_partials; ++p) {
+#pragma unroll
+            for (int v = 0; v < VPT; ++v) {
+                int i = (v * THREADS + threadIdx.x) * 4;
+                if (i < hidden) {
+                    float4 d = *reinterpret_cast<const float4*>(delta + p * partial_stride + src + i);
+                    x[v].x += d.x; x[v].y += d.y; x[v].z += d.z; x[v].w += d.w;
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+        int i = (v * THREADS + threadIdx.x) * 4;
+        if (i < hidden) {
+            if (write_back) *reinterpret_cast<float4*>(h + src + i) = x[v];
+            ss += x[v].x * x[v].x; ss += x[v].y * x[v].y; ss += x[v].z * x[v].z; ss += x[v].w * x[v].w;
+        }
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float total = 0.f;
+#pragma unroll
+        for (int w = 0; w < THREADS / 32; ++w) total += partial[w];
+        inv_rms = 1.0f / sqrtf(total / (float)hidden + eps);
+    }
+    __syncthreads();
+    float scale = inv_rms;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+        int i = (v * THREADS + threadIdx.x) * 4;
+        if (i < hidden) {
+            float4 w = *reinterpret_cast<const float4*>(weight + i);
+            float4 o = make_float4(w.x * (x[v].x * scale), w.y * (x[v].y * scale),
+                                   w.z * (x[v].z * scale), w.w * (x[v].w * scale));
+            store4(out + (size_t)r * hidden + i, o);
+        }
+    }
+}
+
+template <typename OutT>
+static int launch_rmsnorm(float* h, const float* delta, int num_partials, size_t partial_stride,
+                          const float* weight, float eps, OutT* out, const int* rows, int num_rows,
+                          int hidden, cudaStream_t s) {
+    if (hidden % 4 == 0 && hidden <= 128 * 4 * 2)
+        rmsnorm_vec_kernel<OutT, 128, 2><<<num_rows, 128, 0, s>>>(h, delta, num_partials, partial_stride, weight, eps, out, rows, hidden);
+    else if (hidden % 4 == 0 && hidden <= 256 * 4 * 2)
+        rmsnorm_vec_kernel<OutT, 256, 2><<<num_rows, 256, 0, s>>>(h, delta, num_partials, partial_stride, weight, eps, out, rows, hidden);
+    else if (hidden % 4 == 0 && hidden <= 512 * 4 * 4)
+        rmsnorm_vec_kernel<OutT, 512, 4><<<num_rows, 512, 0, s>>>(h, delta, num_partials, partial_stride, weight, eps, out, rows, hidden);
+    else
+        rmsnorm_kernel<OutT, 256><<<num_rows, 256, 0, s>>>(h, delta, num_partials, partial_stride, weight, eps, out, rows, hidden);
+    return IE_LAUNCH_CHECK();
+}
+
+// `delta` may be the sum of `num_partials` arrays `partial_stride` floats apart (the parts of
+// a matrix product that was split along its inner dimension); they are added in order.
+IE_API int ie_rmsnorm(float* h, const float* delta, int num_partials, long long partial_stride,
+                      const float* weight, float eps, void* out, int out_dtype, const int* rows,
+                      int num_rows, int hidden, void* stream) {
     if (num_rows <= 0) return 0;
+    if (delta != nullptr && num_partials < 1) return (int)cudaErrorInvalidValue;
     cudaStream_t s = (cudaStream_t)stream;
     if (out_dtype == IE_BF16)
-        rmsnorm_kernel<__nv_bfloat16, 256><<<num_rows, 256, 0, s>>>(h, delta, weight, eps, (__nv_bfloat16*)out, rows, hidden);
-    else
-        rmsnorm_kernel<float, 256><<<num_rows, 256, 0, s>>>(h, delta, weight, eps, (float*)out, rows, hidden);
-    return IE_LAUNCH_CHECK();
+        return launch_rmsnorm(h, delta, num_partials, (size_t)partial_stride, weight, eps, (__nv_bfloat16*)out, rows, num_rows, hidden, s);
+    return launch_rmsnorm(h, delta, num_partials, (size_t)partial_stride, weight, eps, (float*)out, rows, num_rows, hidden, s);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -138,53 +227,141 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const int* _
     }
 }
 
-IE_API int ie_rope_kv_write(const float* qkv, const int* positions, const float* table,
-                            int rotary_dim, int table_rows, void* q_out, void* k_cache,
-                            void* v_cache, int dtype, const int* slot_mapping, int num_tokens,
-                            int nh, int nkv, int hd, int page_size, int total_pages, int* err, void* stream) {
-    if (num_tokens <= 0) return 0;
-    cudaStream_t s = (cudaStream_t)stream;
-    int threads = (nh + 2 * nkv) * hd >= 1024 ? 256 : 128;
-    if (dtype == IE_BF16)
+// The same for rotary_dim == head_dim (or no rotation) and head_dim a multiple of 8: a thread
+// takes four neighbouring dims of a head's low half and the four that pair with them in the
+// high half, so all its loads are independent 16-byte loads.  `qkv` may be the sum of
+// `num_partials` arrays (the parts of a matrix product split along its inner dimension).
+template <typename T>
+__global__ void __launch_bounds__(128)
+rope_kv_write_vec_kernel(const float* __restrict__ qkv, int num_partials, size_t partial_stride,
+                         const int* __restrict__ positions, const float* __restrict__ table,
+                         int table_rows, T* __restrict__ q_out, T* __restrict__ k_cache,
+                         T* __restrict__ v_cache, const int* __restrict__ slot_mapping,
+                         int nh, int nkv, int hd, int page_size, int total_pages, int* err) {
+    int n = blockIdx.x;
+    int half = hd / 2, per_head = hd / 8;
+    int heads = slot_mapping ? nh + 2 * nkv : nh;
+    int item = blockIdx.y * blockDim.x + threadIdx.x;
+    if (item >= heads * per_head) return;
+    int head = item / per_head, d = (item - head * per_head) * 4;
+    int pos = positions[n];
+    bool rotate = table != nullptr && head < nh + nkv;
+    if (rotate && (pos < 0 || pos >= table_rows)) {
+        ie_report(err, IE_ERR_POSITION, pos, n);
+        rotate = false;
+    }
+    size_t base = (size_t)n * (nh + 2 * nkv) * hd + (size_t)head * hd + d;
+    float4 lo = *reinterpret_cast<const float4*>(qkv + base);
+    float4 hi = *reinterpret_cast<const float4*>(qkv + base + half);
+    for (int p = 1; p < num_partials; ++p) {
+        float4 a = *reinterpret_cast<const float4*>(qkv + p * partial_stride + base);
+        float4 b = *reinterpret_cast<const float4*>(qkv + p * partial_stride + base + half);
+        lo.x += a.x; lo.y += a.y; lo.z += a.z; lo.w += a.w;
+        hi.x += b.x; hi.y += b.y; hi.z += b.z; hi.w += b.w;
+    }
+    if (rotate) {
+        float4 c = *reinterpret_cast<const float4*>(table + (size_t)pos * hd + d);
+        float4 sn = *reinterpret_cast<const float4*>(table + (size_t)pos * hd + half + d);
+        float4 olo = make_float4(lo.x * c.x - hi.x * sn.x, lo.y * c.y - hi.y * sn.y,
+                                 lo.z * c.z - hi.z * sn.z, lo.w * c.w - hi.w * sn.w);
+        float4 ohi = make_float4(hi.x * c.x + lo.x * sn.x, hi.y * c.y + lo.y * sn.y,
+                                 hi.z * c.z + lo.z * sn.z, hi.w * c.w + lo.w * sn.w);
+        lo = olo; hi = ohi;
+    }
+    T* dst;
+    if (head < nh) {
+        dst = q_out + (size_t)n * nh * hd + (size_t)head * hd + d;
+    } else {
+        int slot = slot_mapping[n];
+        int page = slot >= 0 ? slot / page_size : -1, off = slot >= 0 ? slot % page_size : 0;
+        if (page < 0 || page >= total_pages) {
+            if (d == 0) ie_report(err, IE_ERR_PAGE, slot, n);
+            return;
+        }
+        bool is_k = head < nh + nkv;
+        int kh = is_k ? head - nh : head - nh - nkv;
+        dst = (is_k ? k_cache : v_cache) + (((size_t)page * nkv + kh) * page_size + off) * hd + d;
+    }
+    store4(dst, lo);
+    store4(dst + half, hi);
+}
+
+template <typename T>
+static int launch_rope(const float* qkv, int num_partials, size_t partial_stride, const int* positions,
+                       const float* table, int rotary_dim, int table_rows, T* q_out, T* k_cache,
+                       T* v_cache, const int* slot_mapping, int num_tokens, int nh, int nkv, int hd,
+                       int page_size, int total_pages, int* err, cudaStream_t s) {
+    bool rotates = table != nullptr && rotary_dim > 0;
+    if (hd % 8 == 0 && (!rotates || rotary_dim == hd)) {
+        int heads = slot_mapping ? nh + 2 * nkv : nh;
+        dim3 grid(num_tokens, (heads * (hd / 8) + 127) / 128);
+        rope_kv_write_vec_kernel<<<grid, 128, 0, s>>>(qkv, num_partials, partial_stride, positions,
+            rotates ? table : nullptr, table_rows, q_out, k_cache, v_cache, slot_mapping, nh, nkv, hd,
+            page_size, total_pages, err);
+    } else {
+        if (num_partials != 1) return (int)cudaErrorInvalidValue;
+        int threads = (nh + 2 * nkv) * hd >= 1024 ? 256 : 128;
         rope_kv_write_kernel<<<num_tokens, threads, 0, s>>>(qkv, positions, table, rotary_dim, table_rows,
-            (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, slot_mapping,
-            nh, nkv, hd, page_size, total_pages, err);
-    else
-        rope_kv_write_kernel<<<num_tokens, threads, 0, s>>>(qkv, positions, table, rotary_dim, table_rows,
-            (float*)q_out, (float*)k_cache, (float*)v_cache, slot_mapping,
-            nh, nkv, hd, page_size, total_pages, err);
+            q_out, k_cache, v_cache, slot_mapping, nh, nkv, hd, page_size, total_pages, err);
+    }
     return IE_LAUNCH_CHECK();
+}
+
+IE_API int ie_rope_kv_write(const float* qkv, int num_partials, long long partial_stride,
+                            const int* positions, const float* table, int rotary_dim, int table_rows,
+                            void* q_out, void* k_cache, void* v_cache, int dtype,
+                            const int* slot_mapping, int num_tokens, int nh, int nkv, int hd,
+                            int page_size, int total_pages, int* err, void* stream) {
+    if (num_tokens <= 0) return 0;
+    if (num_partials < 1) return (int)cudaErrorInvalidValue;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == IE_BF16)
+        return launch_rope(qkv, num_partials, (size_t)partial_stride, positions, table, rotary_dim, table_rows,
+                           (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
+                           slot_mapping, num_tokens, nh, nkv, hd, page_size, total_pages, err, s);
+    return launch_rope(qkv, num_partials, (size_t)partial_stride, positions, table, rotary_dim, table_rows,
+                       (float*)q_out, (float*)k_cache, (float*)v_cache,
+                       slot_mapping, num_tokens, nh, nkv, hd, page_size, total_pages, err, s);
 }
 
 // ---------------------------------------------------------------------------------------------
 // SiLU-and-multiply: out[n, i] = silu(gu[n, i]) * gu[n, I + i], silu(g) = g / (1 + exp(-g))
 // (engine/model/layers.py:277-281; engine/kernels/fused.py:82-90 evaluates it in 32-bit too)
 // ---------------------------------------------------------------------------------------------
-template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter,
-                                size_t total) {
+template <typename T, typename InT>
+__global__ void silu_mul_kernel(const InT* __restrict__ gate_up, int num_partials, size_t partial_stride,
+                                T* __restrict__ out, int inter, size_t total) {
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; idx < total; idx += stride) {
         size_t row = idx / inter;
         int i = (int)(idx - row * inter);
-        float g = ie_load(gate_up + row * 2 * inter + i);
-        float u = ie_load(gate_up + row * 2 * inter + inter + i);
+        float g = 0.f, u = 0.f;
+        for (int p = 0; p < num_partials; ++p) {
+            g += ie_load(gate_up + p * partial_stride + row * 2 * inter + i);
+            u += ie_load(gate_up + p * partial_stride + row * 2 * inter + inter + i);
+        }
         ie_store(out + idx, g / (1.0f + expf(-g)) * u);
     }
 }
 
-IE_API int ie_silu_mul(const void* gate_up, void* out, int dtype, int num_rows, int inter,
-                       void* stream) {
+// `gate_up` has the output's dtype, or is 32-bit (in_dtype), possibly the sum of `num_partials`
+// arrays `partial_stride` elements apart.
+IE_API int ie_silu_mul(const void* gate_up, int in_dtype, int num_partials, long long partial_stride,
+                       void* out, int dtype, int num_rows, int inter, void* stream) {
     size_t total = (size_t)num_rows * inter;
     if (total == 0) return 0;
+    if (num_partials < 1 || (in_dtype != dtype && in_dtype != IE_F32)) return (int)cudaErrorInvalidValue;
     cudaStream_t s = (cudaStream_t)stream;
     int threads = 256;
     size_t want = (total + threads - 1) / threads;
     int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
-    if (dtype == IE_BF16)
-        silu_mul_kernel<<<blocks, threads, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
+    size_t ps = (size_t)partial_stride;
+    if (dtype == IE_BF16 && in_dtype == IE_BF16)
+        silu_mul_kernel<<<blocks, threads, 0, s>>>((const __nv_bfloat16*)gate_up, num_partials, ps, (__nv_bfloat16*)out, inter, total);
+    else if (dtype == IE_BF16)
+        silu_mul_kernel<<<blocks, threads, 0, s>>>((const float*)gate_up, num_partials, ps, (__nv_bfloat16*)out, inter, total);
     else
-        silu_mul_kernel<<<blocks, threads, 0, s>>>((const float*)gate_up, (float*)out, inter, total);
+        silu_mul_kernel<<<blocks, threads, 0, s>>>((const float*)gate_up, num_partials, ps, (float*)out, inter, total);
     return IE_LAUNCH_CHECK();
 }

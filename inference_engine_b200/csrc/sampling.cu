@@ -201,7 +201,69 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
     }
     if (threadIdx.x == 0) out_tokens[r] = choice;
 }
+
+// Greedy choice for many rows at once: every row is cut into `chunks` pieces that different
+// blocks scan, then one warp per row picks the best piece (lowest index on ties, as above).
+__global__ void __launch_bounds__(256)
+argmax_chunk_kernel(const float* __restrict__ logits, int vocab, int chunks, float* __restrict__ part_v,
+                    int* __restrict__ part_i) {
+    __shared__ Best scratch[8];
+    int r = blockIdx.x, c = blockIdx.y;
+    int len = (vocab + chunks - 1) / chunks;
+    int lo = c * len, hi = min(vocab, lo + len);
+    const float* row = logits + (size_t)r * vocab;
+    Best b{-INFINITY, 0x7fffffff};
+    int i = lo + threadIdx.x;
+    for (; i + 3 * 256 < hi; i += 4 * 256) {  // four independent loads in flight per thread
+        float v0 = row[i], v1 = row[i + 256], v2 = row[i + 512], v3 = row[i + 768];
+        b = better(b, Best{v0, i}); b = better(b, Best{v1, i + 256});
+        b = better(b, Best{v2, i + 512}); b = better(b, Best{v3, i + 768});
+    }
+    for (; i < hi; i += 256) b = better(b, Best{row[i], i});
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Best other{__shfl_xor_sync(0xffffffffu, b.v, o), __shfl_xor_sync(0xffffffffu, b.i, o)};
+        b = better(b, other);
+    }
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = b;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        Best best = scratch[0];
+        for (int w = 1; w < 8; ++w) best = better(best, scratch[w]);
+        part_v[(size_t)r * chunks + c] = best.v;
+        part_i[(size_t)r * chunks + c] = best.i;
+    }
+}
+
+__global__ void argmax_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i,
+                                    int chunks, int* __restrict__ out_tokens) {
+    int r = blockIdx.x;
+    Best b{-INFINITY, 0x7fffffff};
+    for (int c = threadIdx.x; c < chunks; c += 32)
+        b = better(b, Best{part_v[(size_t)r * chunks + c], part_i[(size_t)r * chunks + c]});
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Best other{__shfl_xor_sync(0xffffffffu, b.v, o), __shfl_xor_sync(0xffffffffu, b.i, o)};
+        b = better(b, other);
+    }
+    if (threadIdx.x == 0) out_tokens[r] = b.i;
+}
 }  // namespace
+
+// Greedy tokens for all rows.  `scratch` holds 2 * num_rows * chunks 32-bit words.
+IE_API int ie_argmax(const float* logits, int num_rows, int vocab, int chunks, void* scratch,
+                     int* out_tokens, void* stream) {
+    if (num_rows <= 0) return 0;
+    if (chunks < 1 || scratch == nullptr) return (int)cudaErrorInvalidValue;
+    cudaStream_t s = (cudaStream_t)stream;
+    float* part_v = (float*)scratch;
+    int* part_i = (int*)scratch + (size_t)num_rows * chunks;
+    argmax_chunk_kernel<<<dim3(num_rows, chunks), 256, 0, s>>>(logits, vocab, chunks, part_v, part_i);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    argmax_final_kernel<<<num_rows, 32, 0, s>>>(part_v, part_i, chunks, out_tokens);
+    return IE_LAUNCH_CHECK();
+}
 
 // All per-row arrays but `logits` and `out_tokens` may be null (greedy, nothing cut off).
 IE_API int ie_sample(const float* logits, int num_rows, int vocab, const float* temperature,

@@ -57,16 +57,18 @@ class CudaOps:
         self.err = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._err_ptr = self.err.data_ptr()
         self._attn_libs: dict[int, object] = {}
+        self._argmax_scratch = None
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.launches = 0  # launches of this library's kernels (library matrix products not counted)
 
     def _declare(self) -> None:
-        P, I, F = c_void_p, c_int, c_float
+        P, I, F, L = c_void_p, c_int, c_float, ctypes.c_longlong
         sigs = {
             "ie_embedding": [P, I, P, P, I, I, I, P, P],
-            "ie_rmsnorm": [P, P, P, F, P, I, P, I, I, P],
-            "ie_rope_kv_write": [P, P, P, I, I, P, P, P, I, P, I, I, I, I, I, I, P, P],
-            "ie_silu_mul": [P, P, I, I, I, P],
+            "ie_rmsnorm": [P, P, I, L, P, F, P, I, P, I, I, P],
+            "ie_rope_kv_write": [P, I, L, P, P, I, I, P, P, P, I, P, I, I, I, I, I, I, P, P],
+            "ie_silu_mul": [P, I, I, L, P, I, I, I, P],
+            "ie_argmax": [P, I, I, I, P, P, P],
             "ie_gemm_f32": [P, P, P, I, I, I, P],
             "ie_paged_attention_generic": [P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, F, I, P, P],
             "ie_sample": [P, I, I, P, P, P, P, P, P, I, P, P, P, P, P],
@@ -106,9 +108,18 @@ class CudaOps:
                                     out.data_ptr(), ids.shape[0], table.shape[1], table.shape[0],
                                     self._err_ptr, self._stream()), "embedding")
 
+    @staticmethod
+    def _partials(t) -> tuple[int, int]:
+        """A 3-D tensor ``[S, rows, cols]`` stands for the sum of its S slices (the parts of a
+        matrix product split along the inner dimension): (S, elements between slices)."""
+        if t is None or t.dim() == 2:
+            return 1, 0
+        return t.shape[0], t.stride(0)
+
     def rmsnorm(self, h, delta, weight, eps, out, rows=None) -> None:
         n = h.shape[0] if rows is None else rows.shape[0]
-        self._check(self._rmsnorm(h.data_ptr(), self._ptr(delta), weight.data_ptr(), eps,
+        parts, stride = self._partials(delta)
+        self._check(self._rmsnorm(h.data_ptr(), self._ptr(delta), parts, stride, weight.data_ptr(), eps,
                                   out.data_ptr(), _dtype_code(out), self._ptr(rows), n,
                                   h.shape[1], self._stream()), "rmsnorm")
 
@@ -133,10 +144,11 @@ class CudaOps:
             raise KernelError("rotary table does not match rotary_dim")
         if rotary_dim > hd or rotary_dim % 2:
             raise KernelError(f"rotary_dim {rotary_dim} must be even and at most head_dim {hd}")
+        parts, stride = self._partials(qkv)
         self._check(self._rope_kv_write(
-            qkv.data_ptr(), positions.data_ptr(), self._ptr(table), rotary_dim,
+            qkv.data_ptr(), parts, stride, positions.data_ptr(), self._ptr(table), rotary_dim,
             0 if table is None else table.shape[0], q_out.data_ptr(), k_cache.data_ptr(),
-            v_cache.data_ptr(), _dtype_code(q_out), self._ptr(slot_mapping), qkv.shape[0],
+            v_cache.data_ptr(), _dtype_code(q_out), self._ptr(slot_mapping), q_out.shape[0],
             nh, nkv, hd, page_size, k_cache.shape[0], self._err_ptr, self._stream()), "rope_kv_write")
 
     def _attention_lib(self, hd: int):
@@ -211,17 +223,29 @@ class CudaOps:
             k_cache.shape[0], scale, window, self._err_ptr, self._stream()), "paged_attention")
 
     def silu_mul(self, gate_up, out) -> None:
-        self._check(self._silu_mul(gate_up.data_ptr(), out.data_ptr(), _dtype_code(out),
-                                   out.shape[0], out.shape[1], self._stream()), "silu_mul")
+        parts, stride = self._partials(gate_up)
+        self._check(self._silu_mul(gate_up.data_ptr(), _dtype_code(gate_up), parts, stride,
+                                   out.data_ptr(), _dtype_code(out), out.shape[0], out.shape[1],
+                                   self._stream()), "silu_mul")
 
     def argmax(self, logits, out) -> None:
-        self.sample(logits, out)
+        """Greedy token of every row (lowest index on ties)."""
+        rows = logits.shape[0]
+        chunks = max(1, min(2 * self.sm_count // max(rows, 1), 64))
+        need = 2 * rows * chunks
+        if self._argmax_scratch is None or self._argmax_scratch.numel() < need:
+            self._argmax_scratch = self.torch.empty(max(need, 4096), dtype=self.torch.int32, device=self.device)
+        self._check(self._argmax(logits.data_ptr(), rows, logits.shape[1], chunks,
+                                 self._argmax_scratch.data_ptr(), out.data_ptr(), self._stream()), "argmax")
+        self.launches += 1
 
     def sample(self, logits, out, temperature=None, top_k=None, top_p=None, min_p=None,
                penalty=None, seen_bits=None, seeds=None, draws=None, logprob=None) -> None:
         """One token per row of 32-bit ``logits``; the per-row tensors are optional (absent:
         greedy, no cut-off, no penalty).  ``seeds`` and ``draws`` (int64) are needed as soon
         as ``temperature`` is given."""
+        if temperature is None and penalty is None and logprob is None:
+            return self.argmax(logits, out)
         self._check(self._sample(
             logits.data_ptr(), logits.shape[0], logits.shape[1], self._ptr(temperature),
             self._ptr(top_k), self._ptr(top_p), self._ptr(min_p), self._ptr(penalty),

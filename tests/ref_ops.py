@@ -18,6 +18,8 @@ class RefOps:
         out.copy_(table[ids.long()].float())
 
     def rmsnorm(self, h, delta, weight, eps, out, rows=None):
+        if delta is not None and delta.dim() == 3:  # the parts of a split matrix product
+            delta = delta.sum(0)
         if rows is None:
             if delta is not None:
                 h.add_(delta)
@@ -34,6 +36,8 @@ class RefOps:
 
     def rope_kv_write(self, qkv, positions, table, rotary_dim, q_out, k_cache, v_cache,
                       slot_mapping, nh, nkv, hd, page_size):
+        if qkv.dim() == 3:
+            qkv = qkv.sum(0)
         n = qkv.shape[0]
         q = qkv[:, : nh * hd].reshape(n, nh, hd).float()
         k = qkv[:, nh * hd: (nh + nkv) * hd].reshape(n, nkv, hd).float()
@@ -77,6 +81,8 @@ class RefOps:
             out[t] = torch.einsum("hk,khd->hd", probs, v).reshape(nh * hd).to(out.dtype)
 
     def silu_mul(self, gate_up, out):
+        if gate_up.dim() == 3:
+            gate_up = gate_up.float().sum(0)
         i = out.shape[1]
         g, u = gate_up[:, :i].float(), gate_up[:, i:].float()
         out.copy_((g / (1 + torch.exp(-g)) * u).to(out.dtype))

@@ -75,6 +75,45 @@ def test_rmsnorm_with_residual_add(ops, out_dtype, n, hidden, eps):
     torch.testing.assert_close(got.float(), want.float(), **_tol(out_dtype))
 
 
+@pytest.mark.parametrize("out_dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [80, 2048, 4100])
+def test_consumers_add_the_parts_of_a_split_matrix_product(ops, out_dtype, hidden):
+    """Norm, rotary/cache write and activation accept their input as S partial sums."""
+    n, parts = 5, 3
+    h = torch.randn(n, hidden, device="cuda")
+    delta = torch.randn(parts, n, hidden, device="cuda")
+    w = torch.randn(hidden, device="cuda")
+    h1, h2 = h.clone(), h.clone()
+    got = torch.empty(n, hidden, device="cuda", dtype=out_dtype)
+    want = torch.empty_like(got)
+    ops.rmsnorm(h1, delta, w, 1e-5, got)
+    RefOps().rmsnorm(h2, delta, w, 1e-5, want)
+    torch.testing.assert_close(h1, h2, atol=1e-6, rtol=1e-6)
+    torch.testing.assert_close(got.float(), want.float(), **_tol(out_dtype))
+    inter = hidden // 2 if hidden % 2 == 0 else hidden
+    gu = torch.randn(parts, n, 2 * inter, device="cuda")
+    got = torch.empty(n, inter, device="cuda", dtype=out_dtype)
+    want = torch.empty_like(got)
+    ops.silu_mul(gu, got)
+    RefOps().silu_mul(gu, want)
+    torch.testing.assert_close(got.float(), want.float(), **_tol(out_dtype))
+    nh, nkv, hd, ps = 4, 2, 16, 8
+    qkv = torch.randn(parts, n, (nh + 2 * nkv) * hd, device="cuda")
+    positions = torch.arange(n, device="cuda", dtype=torch.int32)
+    ang = torch.rand(16, hd // 2, device="cuda")
+    table = torch.stack((ang.cos(), ang.sin()), dim=1).contiguous()
+    slots = torch.arange(n, device="cuda", dtype=torch.int32) + 3
+    res = []
+    for impl in (ops, RefOps()):
+        q = torch.zeros(n, nh * hd, device="cuda", dtype=out_dtype)
+        k = torch.zeros(2, nkv, ps, hd, device="cuda", dtype=out_dtype)
+        v = torch.zeros_like(k)
+        impl.rope_kv_write(qkv, positions, table, hd, q, k, v, slots, nh, nkv, hd, ps)
+        res.append((q, k, v))
+    for a, b in zip(*res):
+        torch.testing.assert_close(a.float(), b.float(), **_tol(out_dtype))
+
+
 def test_rmsnorm_row_does_not_depend_on_the_batch(ops):
     h = torch.randn(64, 2048, device="cuda")
     w = torch.randn(2048, device="cuda")

@@ -31,11 +31,10 @@ namespace {
 constexpr int HD = IE_HD;
 static_assert(HD % 16 == 0 && HD >= 16 && HD <= 128, "head size must be a multiple of 16 up to 128");
 constexpr int C = HD / 8;                 // 16-byte chunks per row
-constexpr int KT = HD <= 64 ? 64 : 32;    // keys per tile
-constexpr int NT = KT / 8;                // 8-key score tiles per key tile
+constexpr int KT_PREFILL = HD <= 64 ? 64 : 32;  // keys per tile, prefill kernel
+constexpr int KT_DECODE = HD <= 64 ? 32 : 16;   // keys per tile and warp, decode kernel
 constexpr int KS = HD / 16;               // 16-dim steps of q.k
 constexpr int DT = HD / 8;                // 8-dim tiles of the output
-constexpr int TILE_ELEMS = KT * HD;       // bfloat16 elements of one K or V tile
 constexpr bool SWZ = (C % 8 == 0);
 constexpr int WARPS = 4;
 constexpr int MAX_ROWS = 16;
@@ -74,6 +73,7 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 
 // Stage keys key0 .. key0 + KT - 1 of one key/value head into a shared-memory tile.  Keys
 // outside [lo, hi] are zero-filled.  `tid`/`nthreads`: the threads that share the tile.
+template <int KT>
 __device__ __forceinline__ void load_tile(bf16* tile, const bf16* __restrict__ cache,
                                           const int* __restrict__ table, int key0, int lo, int hi,
                                           int kvh, int nkv, int page_shift, int total_pages,
@@ -114,10 +114,12 @@ struct RowState {
 //   qpos, qlo : for the thread's two rows (lane / 4 and lane / 4 + 8): position of the query
 //               and first key it may see; a row that does not exist has qpos < 0
 //   key_hi    : last key of the range this call may use (split end)
+template <int KT>
 __device__ __forceinline__ void process_tile(RowState& st, const unsigned (&qf)[KS][4],
                                              const bf16* ktile, const bf16* vtile, int key0,
                                              const int (&qpos)[2], const int (&qlo)[2], int key_hi,
                                              float scale_log2, int lane) {
+    constexpr int NT = KT / 8;  // 8-key score tiles per key tile
     float s[NT][4];
 #pragma unroll
     for (int n = 0; n < NT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
@@ -209,8 +211,10 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
                         const bf16* __restrict__ v_cache, const int* __restrict__ tables,
                         int table_width, const int* __restrict__ cu_q, const int* __restrict__ ctx_lens,
                         bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
-                        int nh, int nkv, int page_shift, int total_pages, float scale_log2,
-                        int window, int num_splits, int* err) {
+                        int* __restrict__ tickets, int nh, int nkv, int page_shift, int total_pages,
+                        float scale_log2, int window, int num_splits, int* err) {
+    constexpr int KT = KT_DECODE, TILE_ELEMS = KT * HD;
+    __shared__ int is_last;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
     int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
@@ -253,8 +257,8 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
     int stage = 0;
     if (warp < n_tiles) {
         int key0 = s_lo + warp * KT;
-        load_tile(wbase, k_cache, table, key0, s_lo, s_hi, kvh, nkv, page_shift, total_pages, lane, 32, err);
-        load_tile(wbase + TILE_ELEMS, v_cache, table, key0, s_lo, s_hi, kvh, nkv, page_shift, total_pages, lane, 32, err);
+        load_tile<KT>(wbase, k_cache, table, key0, s_lo, s_hi, kvh, nkv, page_shift, total_pages, lane, 32, err);
+        load_tile<KT>(wbase + TILE_ELEMS, v_cache, table, key0, s_lo, s_hi, kvh, nkv, page_shift, total_pages, lane, 32, err);
     }
     cp_async_commit();
     for (int t = warp; t < n_tiles; t += WARPS) {
@@ -264,13 +268,13 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
         bf16* nxt = wbase + (size_t)(stage ^ 1) * 2 * TILE_ELEMS;
         if (next < n_tiles) {
             int nkey0 = s_lo + next * KT;
-            load_tile(nxt, k_cache, table, nkey0, s_lo, s_hi, kvh, nkv, page_shift, total_pages, lane, 32, err);
-            load_tile(nxt + TILE_ELEMS, v_cache, table, nkey0, s_lo, s_hi, kvh, nkv, page_shift, total_pages, lane, 32, err);
+            load_tile<KT>(nxt, k_cache, table, nkey0, s_lo, s_hi, kvh, nkv, page_shift, total_pages, lane, 32, err);
+            load_tile<KT>(nxt + TILE_ELEMS, v_cache, table, nkey0, s_lo, s_hi, kvh, nkv, page_shift, total_pages, lane, 32, err);
         }
         cp_async_commit();
         cp_async_wait<1>();
         __syncwarp();
-        process_tile(st, qf, cur, cur + TILE_ELEMS, key0, qpos, qlo, s_hi, scale_log2, lane);
+        process_tile<KT>(st, qf, cur, cur + TILE_ELEMS, key0, qpos, qlo, s_hi, scale_log2, lane);
         __syncwarp();
         stage ^= 1;
     }
@@ -318,29 +322,31 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
             if (d == 0) { part_ml[p * 2] = m; part_ml[p * 2 + 1] = l; }
         }
     }
-}
-
-// Merge the splits of the decode kernel, always in the order split 0, 1, 2, ...
-__global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                       const int* __restrict__ cu_q, bf16* __restrict__ out,
-                                       int nh, int nkv, int num_splits) {
-    int seq = blockIdx.x, kvh = blockIdx.y;
-    int G = nh / nkv;
-    int q0 = cu_q[seq], qlen = cu_q[seq + 1] - q0;
-    int rows = qlen * G;
-    if (rows > MAX_ROWS || qlen <= 0) return;
+    if (num_splits == 1) return;
+    // The block that finishes last for this (request, key/value head) merges all splits, always
+    // in the order 0, 1, 2, ...  The ticket counter goes back to zero for the next launch.
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int ticket = atomicAdd(&tickets[seq * nkv + kvh], 1);
+        is_last = (ticket == num_splits - 1);
+        if (is_last) tickets[seq * nkv + kvh] = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
     size_t base = ((size_t)seq * nkv + kvh) * num_splits * MAX_ROWS;
-    for (int idx = threadIdx.x; idx < rows * HD; idx += blockDim.x) {
+    for (int idx = threadIdx.x; idx < rows * HD; idx += WARPS * 32) {
         int row = idx / HD, d = idx - row * HD;
         float m = -INFINITY;
-        for (int s = 0; s < num_splits; ++s) m = fmaxf(m, part_ml[(base + (size_t)s * MAX_ROWS + row) * 2]);
+        for (int s = 0; s < num_splits; ++s) m = fmaxf(m, __ldcg(part_ml + (base + (size_t)s * MAX_ROWS + row) * 2));
         float m_safe = (m == -INFINITY) ? 0.f : m;
         float l = 0.f, o = 0.f;
         for (int s = 0; s < num_splits; ++s) {
             size_t p = base + (size_t)s * MAX_ROWS + row;
-            float f = exp2f(part_ml[p * 2] - m_safe);
-            l += part_ml[p * 2 + 1] * f;
-            o += part_o[p * HD + d] * f;
+            float f = exp2f(__ldcg(part_ml + p * 2) - m_safe);
+            l += __ldcg(part_ml + p * 2 + 1) * f;
+            o += __ldcg(part_o + p * HD + d) * f;
         }
         int tok = row / G, g = row - tok * G;
         out[((size_t)(q0 + tok) * nh + kvh * G + g) * HD + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
@@ -358,6 +364,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
                          int table_width, const int* __restrict__ cu_q, const int* __restrict__ ctx_lens,
                          bf16* __restrict__ out, int num_seqs, int nh, int nkv, int page_shift,
                          int total_pages, float scale_log2, int window, int* err) {
+    constexpr int KT = KT_PREFILL, TILE_ELEMS = KT * HD;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -405,22 +412,22 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
     RowState st;
     st.init();
     int stage = 0;
-    load_tile(smem, k_cache, table, key_begin, lo, cta_qpos_hi, kvh, nkv, page_shift, total_pages, threadIdx.x, WARPS * 32, err);
-    load_tile(smem + TILE_ELEMS, v_cache, table, key_begin, lo, cta_qpos_hi, kvh, nkv, page_shift, total_pages, threadIdx.x, WARPS * 32, err);
+    load_tile<KT>(smem, k_cache, table, key_begin, lo, cta_qpos_hi, kvh, nkv, page_shift, total_pages, threadIdx.x, WARPS * 32, err);
+    load_tile<KT>(smem + TILE_ELEMS, v_cache, table, key_begin, lo, cta_qpos_hi, kvh, nkv, page_shift, total_pages, threadIdx.x, WARPS * 32, err);
     cp_async_commit();
     for (int t = 0; t < n_tiles; ++t) {
         int key0 = key_begin + t * KT;
         bf16* cur = smem + (size_t)stage * 2 * TILE_ELEMS;
         bf16* nxt = smem + (size_t)(stage ^ 1) * 2 * TILE_ELEMS;
         if (t + 1 < n_tiles) {
-            load_tile(nxt, k_cache, table, key0 + KT, lo, cta_qpos_hi, kvh, nkv, page_shift, total_pages, threadIdx.x, WARPS * 32, err);
-            load_tile(nxt + TILE_ELEMS, v_cache, table, key0 + KT, lo, cta_qpos_hi, kvh, nkv, page_shift, total_pages, threadIdx.x, WARPS * 32, err);
+            load_tile<KT>(nxt, k_cache, table, key0 + KT, lo, cta_qpos_hi, kvh, nkv, page_shift, total_pages, threadIdx.x, WARPS * 32, err);
+            load_tile<KT>(nxt + TILE_ELEMS, v_cache, table, key0 + KT, lo, cta_qpos_hi, kvh, nkv, page_shift, total_pages, threadIdx.x, WARPS * 32, err);
         }
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
         if (warp_has_rows && key0 <= warp_hi && key0 + KT - 1 >= warp_lo)
-            process_tile(st, qf, cur, cur + TILE_ELEMS, key0, qpos, qlo, cta_qpos_hi, scale_log2, lane);
+            process_tile<KT>(st, qf, cur, cur + TILE_ELEMS, key0, qpos, qlo, cta_qpos_hi, scale_log2, lane);
         __syncthreads();
         stage ^= 1;
     }
@@ -440,10 +447,10 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
     }
 }
 
-constexpr size_t DECODE_SMEM = (size_t)WARPS * 4 * TILE_ELEMS * sizeof(bf16);
+constexpr size_t DECODE_SMEM_TILES = (size_t)WARPS * 4 * KT_DECODE * HD * sizeof(bf16);
 constexpr size_t DECODE_MERGE_SMEM = (size_t)WARPS * MAX_ROWS * (2 + HD) * sizeof(float);
-constexpr size_t PREFILL_SMEM = (size_t)4 * TILE_ELEMS * sizeof(bf16);
-static_assert(DECODE_MERGE_SMEM <= DECODE_SMEM, "the merge area reuses the tile area");
+constexpr size_t PREFILL_SMEM = (size_t)4 * KT_PREFILL * HD * sizeof(bf16);
+constexpr size_t DECODE_SMEM = DECODE_SMEM_TILES > DECODE_MERGE_SMEM ? DECODE_SMEM_TILES : DECODE_MERGE_SMEM;
 }  // namespace
 
 IE_API int ie_attention_head_dim() { return HD; }
@@ -455,15 +462,18 @@ IE_API long long ie_attention_decode_scratch_floats(int num_seqs, int nkv, int n
     return (long long)num_seqs * nkv * num_splits * MAX_ROWS * (HD + 2);
 }
 
-// Requests with (tokens x group size) <= 16 rows.  `scratch` may be null when num_splits == 1.
+// Requests with (tokens x group size) <= 16 rows.  With num_splits > 1 the kernel needs
+// `scratch` (ie_attention_decode_scratch_floats floats; contents do not matter) and `tickets`
+// (num_seqs * nkv ints that are zero before the first launch; every launch leaves them zero
+// again).  Both may be null when num_splits == 1.
 IE_API int ie_attention_decode(const void* q, const void* k_cache, const void* v_cache,
                                const int* tables, int table_width, const int* cu_q,
-                               const int* ctx_lens, void* out, float* scratch, int num_seqs,
-                               int nh, int nkv, int page_size, int total_pages, float scale,
-                               int window, int num_splits, int* err, void* stream) {
+                               const int* ctx_lens, void* out, float* scratch, int* tickets,
+                               int num_seqs, int nh, int nkv, int page_size, int total_pages,
+                               float scale, int window, int num_splits, int* err, void* stream) {
     if (num_seqs <= 0) return 0;
     if (nkv <= 0 || nh % nkv != 0 || (page_size & (page_size - 1)) != 0 || num_splits < 1 ||
-        (num_splits > 1 && scratch == nullptr))
+        (num_splits > 1 && (scratch == nullptr || tickets == nullptr)))
         return (int)cudaErrorInvalidValue;
     int page_shift = 0;
     while ((1 << page_shift) < page_size) ++page_shift;
@@ -480,11 +490,8 @@ IE_API int ie_attention_decode(const void* q, const void* k_cache, const void* v
     dim3 grid(num_seqs, nkv, num_splits);
     attention_decode_kernel<<<grid, WARPS * 32, DECODE_SMEM, s>>>(
         (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, tables, table_width, cu_q, ctx_lens,
-        (bf16*)out, part_o, part_ml, nh, nkv, page_shift, total_pages, scale * 1.4426950408889634f,
-        window, num_splits, err);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess || num_splits == 1) return (int)e;
-    attention_merge_kernel<<<dim3(num_seqs, nkv), 128, 0, s>>>(part_o, part_ml, cu_q, (bf16*)out, nh, nkv, num_splits);
+        (bf16*)out, part_o, part_ml, tickets, nh, nkv, page_shift, total_pages,
+        scale * 1.4426950408889634f, window, num_splits, err);
     return IE_LAUNCH_CHECK();
 }
 
@@ -521,11 +528,15 @@ namespace {
 // Scratch for the split partials of `ie_attention_decode_static`.  Every GPU that loads this
 // library holds these 4 MiB until the process exits.
 static __device__ __align__(256) float g_static_decode_scratch[IE_STATIC_DECODE_SCRATCH_FLOATS];
+// Ticket counters of the split merge (one per request and key/value head).  They have to be
+// zero when a launch starts; a launch leaves them zero, and every call clears them anyway.
+static __device__ __align__(256) int g_static_decode_tickets[IE_STATIC_DECODE_MAX_TICKETS];
 
 constexpr int MAX_DEVICES = 64;
 // In host code the array's name is only a handle; the device address is looked up once per
 // device with cudaGetSymbolAddress and kept here.
 float* g_static_scratch_ptr[MAX_DEVICES] = {nullptr};
+int* g_static_tickets_ptr[MAX_DEVICES] = {nullptr};
 
 int fail(char* msg, int msg_len, int code, const char* text) {
     if (msg != nullptr && msg_len > 0) snprintf(msg, (size_t)msg_len, "%s", text);
@@ -545,16 +556,18 @@ IE_API int ie_attention_decode_static(const void* q, const void* k_cache, const 
     if (nkv <= 0 || nh % nkv != 0 || num_splits < 1)
         return fail(msg, msg_len, (int)cudaErrorInvalidValue, "ie_attention_decode_static: bad head counts or split count");
     long long need = ie_attention_decode_scratch_floats(num_seqs, nkv, num_splits);
-    if (need > IE_STATIC_DECODE_SCRATCH_FLOATS) {
+    if (need > IE_STATIC_DECODE_SCRATCH_FLOATS || (num_splits > 1 && (long long)num_seqs * nkv > IE_STATIC_DECODE_MAX_TICKETS)) {
         char text[512];
         snprintf(text, sizeof(text),
                  "ie_attention_decode_static: %d requests x %d key/value heads x %d splits need %lld "
-                 "floats of scratch, the built-in array holds %lld; use fewer splits or smaller batches, "
-                 "or call ie_attention_decode with scratch of your own",
-                 num_seqs, nkv, num_splits, need, (long long)IE_STATIC_DECODE_SCRATCH_FLOATS);
+                 "floats of scratch, the built-in array holds %lld (and %d ticket counters); use fewer "
+                 "splits or smaller batches, or call ie_attention_decode with scratch of your own",
+                 num_seqs, nkv, num_splits, need, (long long)IE_STATIC_DECODE_SCRATCH_FLOATS,
+                 (int)IE_STATIC_DECODE_MAX_TICKETS);
         return fail(msg, msg_len, IE_STATIC_SCRATCH_TOO_SMALL, text);
     }
     float* scratch = nullptr;
+    int* tickets = nullptr;
     if (num_splits > 1) {
         int dev = -1;
         cudaError_t e = cudaGetDevice(&dev);
@@ -569,12 +582,22 @@ IE_API int ie_attention_decode_static(const void* q, const void* k_cache, const 
             if (e != cudaSuccess || ptr == nullptr)
                 return fail(msg, msg_len, e != cudaSuccess ? (int)e : (int)cudaErrorInvalidSymbol,
                             "ie_attention_decode_static: cudaGetSymbolAddress failed for the scratch array");
+            int* tptr = nullptr;
+            e = cudaGetSymbolAddress((void**)&tptr, g_static_decode_tickets);
+            if (e != cudaSuccess || tptr == nullptr)
+                return fail(msg, msg_len, e != cudaSuccess ? (int)e : (int)cudaErrorInvalidSymbol,
+                            "ie_attention_decode_static: cudaGetSymbolAddress failed for the ticket array");
             g_static_scratch_ptr[dev] = ptr;
+            g_static_tickets_ptr[dev] = tptr;
         }
         scratch = g_static_scratch_ptr[dev];
+        tickets = g_static_tickets_ptr[dev];
+        // the tickets must start at zero; the partials need no clearing (written before read)
+        e = cudaMemsetAsync(tickets, 0, (size_t)num_seqs * nkv * sizeof(int), (cudaStream_t)stream);
+        if (e != cudaSuccess) return fail(msg, msg_len, (int)e, "ie_attention_decode_static: clearing the tickets failed");
     }
     int rc = ie_attention_decode(q, k_cache, v_cache, tables, table_width, cu_q, ctx_lens, out, scratch,
-                                 num_seqs, nh, nkv, page_size, total_pages, scale, window, num_splits,
+                                 tickets, num_seqs, nh, nkv, page_size, total_pages, scale, window, num_splits,
                                  err, stream);
     if (rc != 0) return fail(msg, msg_len, rc, "ie_attention_decode_static: the kernel launch failed");
     return 0;

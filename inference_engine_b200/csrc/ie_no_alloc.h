@@ -23,8 +23,13 @@
 //   * The first call with num_splits > 1 on a device looks up the array's device address
 //     (cudaGetSymbolAddress, with that device current; the address is kept per device).
 //     Make that first call outside any stream capture.
-//   * All calls share the one array, and it keeps what the last call left.  Nothing in it has
-//     to start at zero: a call writes every partial it later reads.  Because it is shared,
+//   * A second small array (IE_STATIC_DECODE_MAX_TICKETS ints) holds one ticket counter per
+//     request and key/value head, by which the last block to finish knows it has to merge the
+//     splits.  Counters must be zero when the kernel starts: every call clears the ones it
+//     uses (cudaMemsetAsync on the caller's stream) before the launch.  num_seqs * nkv beyond
+//     that count is refused like too large a scratch need.
+//   * All calls share the arrays, and they keep what the last call left.  The partial results
+//     need no clearing: a call writes every partial it later reads.  Because they are shared,
 //     two calls whose kernels can overlap on the GPU (different streams, no dependency) race
 //     on it; run such calls on one stream or order them with events.
 //   * `msg`, if not null, receives a zero-terminated explanation when the return value is
@@ -32,6 +37,7 @@
 #pragma once
 
 #define IE_STATIC_DECODE_SCRATCH_FLOATS (1 << 20)
+#define IE_STATIC_DECODE_MAX_TICKETS 8192
 #define IE_STATIC_SCRATCH_TOO_SMALL (-1001)
 
 #ifdef __cplusplus

@@ -21,13 +21,14 @@ class Workspace:
         import torch
 
         need = rows * cols
-        buf = self._buffers.get(name)
-        if buf is None or buf.dtype != dtype or buf.numel() < need:
+        key = (name, dtype)  # the same name may be wanted in two precisions by different paths
+        buf = self._buffers.get(key)
+        if buf is None or buf.numel() < need:
             cap_rows = rows if rows_cap is None else max(rows, self.min_rows, rows_cap)
             buf = torch.empty(max(cap_rows * cols, 1), dtype=dtype, device=self.device)
-            if name in self._buffers:
+            if key in self._buffers:
                 self.version += 1
-            self._buffers[name] = buf
+            self._buffers[key] = buf
         return buf[:need].view(rows, cols)
 
     def bytes(self) -> int:

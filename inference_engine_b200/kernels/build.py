@@ -26,7 +26,7 @@ NVCC_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC", "--expt-r
 
 # Sources of the always-needed library.  Kernels specialised on a model's sizes are listed
 # in SPECIALISED and built by `build_specialised` with -D flags.
-CORE_SOURCES = ["elementwise.cu", "gemm_f32.cu", "attention_generic.cu", "sampling.cu"]
+CORE_SOURCES = ["elementwise.cu", "gemm_f32.cu", "gemm_skinny.cu", "attention_generic.cu", "sampling.cu"]
 
 
 class BuildError(RuntimeError):
@@ -96,7 +96,7 @@ def _compile_one(nvcc: str, src: Path, obj: Path, defines: list[str]) -> None:
 def build_library(name: str, sources: list[str], defines: list[str] | None = None,
                   verbose: bool = True) -> Path:
     """Build (or find) ``lib<name>-<hash>.so`` from ``sources`` under ``csrc/``."""
-    defines = list(defines or [])
+    defines = list(defines or []) + os.environ.get("IE_B200_NVCC_FLAGS", "").split()
     srcs = [CSRC / s for s in sources]
     for s in srcs:
         if not s.exists():

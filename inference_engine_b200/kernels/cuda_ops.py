@@ -58,6 +58,8 @@ class CudaOps:
         self._err_ptr = self.err.data_ptr()
         self._attn_libs: dict[int, object] = {}
         self._argmax_scratch = None
+        self.force_skinny = False  # tests run every few-row product through the streaming kernel
+        self._tickets = None
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.launches = 0  # launches of this library's kernels (library matrix products not counted)
 
@@ -70,6 +72,7 @@ class CudaOps:
             "ie_silu_mul": [P, I, I, L, P, I, I, I, P],
             "ie_argmax": [P, I, I, I, P, P, P],
             "ie_gemm_f32": [P, P, P, I, I, I, P],
+            "ie_gemm_skinny_bf16": [P, P, P, I, I, I, I, I, I, P],
             "ie_paged_attention_generic": [P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, F, I, P, P],
             "ie_sample": [P, I, I, P, P, P, P, P, P, I, P, P, P, P, P],
         }
@@ -123,20 +126,57 @@ class CudaOps:
                                   out.data_ptr(), _dtype_code(out), self._ptr(rows), n,
                                   h.shape[1], self._stream()), "rmsnorm")
 
-    def linear(self, x, w, out) -> None:
-        """``out[M, N] = x[M, K] @ w[N, K]^T``."""
+    SKINNY_ROWS = 16  # up to this many rows a bfloat16 product runs the weight-streaming kernel
+
+    def skinny_split(self, n_out: int, k: int) -> tuple[int, int]:
+        """(slice of the inner dimension per split, number of splits) for a few-row product:
+        enough warps to fill the GPU, slices of whole 256-wide stages."""
+        fblocks = -(-n_out // 16)
+        want = max(1, (self.sm_count * 8) // fblocks)
+        per = max(256, (k // want) // 128 * 128)
+        per = min(per, -(-k // 16) * 16)
+        return per, -(-k // per)
+
+    def linear(self, x, w, out=None, *, ws=None, tag="linear", out_dtype=None, allow_split=False):
+        """``x[M, K] @ w[N, K]^T``.  With ``out`` given the product is written there; otherwise a
+        buffer named ``tag`` is taken from ``ws``.  With ``allow_split`` the result may come back
+        as ``[S, M, N]`` partial sums (32-bit) that the consumer adds in order."""
         torch = self.torch
-        if x.shape[0] == 0:
-            return
+        m, k = x.shape
+        n = w.shape[0]
+        if out is not None:
+            out_dtype = out.dtype
         if x.dtype == torch.float32:
-            if out.dtype != torch.float32 or w.dtype != torch.float32:
+            if out_dtype != torch.float32 or w.dtype != torch.float32:
                 raise KernelError("the 32-bit matrix product takes and gives 32-bit tensors")
-            self._check(self._gemm_f32(x.data_ptr(), w.data_ptr(), out.data_ptr(), x.shape[0],
-                                       w.shape[0], x.shape[1], self._stream()), "gemm_f32")
-        elif out.dtype == x.dtype:
+            if out is None:
+                out = ws.buffer(tag, m, n, torch.float32)
+            if m:
+                self._check(self._gemm_f32(x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k,
+                                           self._stream()), "gemm_f32")
+            return out
+        # The weight-streaming kernel pays where the library leaves SMs idle: few output
+        # features (fewer 16-feature blocks than SMs) and a long inner dimension to split.
+        skinny = (0 < m <= self.SKINNY_ROWS and k % 8 == 0 and x.is_contiguous() and w.is_contiguous()
+                  and (self.force_skinny or (allow_split and out is None and -(-n // 16) <= self.sm_count)))
+        if skinny:
+            per, splits = self.skinny_split(n, k) if allow_split and out is None else (-(-k // 16) * 16, 1)
+            if splits > 1:
+                out = ws.buffer(tag, splits * m, n, torch.float32).view(splits, m, n)
+            elif out is None:
+                out = ws.buffer(tag, m, n, out_dtype)
+            self._check(self._gemm_skinny_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), _dtype_code(out),
+                                               m, n, k, per, splits, self._stream()), "gemm_skinny")
+            return out
+        if out is None:
+            out = ws.buffer(tag, m, n, out_dtype)
+        if m == 0:
+            return out
+        if out.dtype == x.dtype:
             torch.mm(x, w.t(), out=out)
         else:
             torch.mm(x, w.t(), out_dtype=out.dtype, out=out)
+        return out
 
     def rope_kv_write(self, qkv, positions, table, rotary_dim, q_out, k_cache, v_cache,
                       slot_mapping, nh, nkv, hd, page_size) -> None:
@@ -157,18 +197,25 @@ class CudaOps:
         if lib is None:
             lib = ctypes.CDLL(str(build_attention(hd)))
             P, I, F = c_void_p, c_int, c_float
-            lib.ie_attention_decode.argtypes = [P, P, P, P, I, P, P, P, P, I, I, I, I, I, F, I, I, P, P]
+            lib.ie_attention_decode.argtypes = [P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, F, I, I, P, P]
             lib.ie_attention_prefill.argtypes = [P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P, P]
             lib.ie_attention_decode_scratch_floats.argtypes = [I, I, I]
             lib.ie_attention_decode_scratch_floats.restype = ctypes.c_longlong
             self._attn_libs[hd] = lib
         return lib
 
+    def _decode_tickets(self, count: int):
+        """Zeroed counters for the decode kernel's split merge; every launch leaves them zero."""
+        if self._tickets is None or self._tickets.numel() < count:
+            self._tickets = self.torch.zeros(max(count, 4096), dtype=self.torch.int32, device=self.device)
+        return self._tickets
+
     def decode_splits(self, num_seqs: int, nkv: int) -> int:
-        """Into how many parts the decode kernel cuts each context: enough blocks to fill the
-        GPU twice, whatever the contexts' lengths (so that a captured launch stays valid)."""
+        """Into how many parts the decode kernel cuts each context: as many blocks as are
+        resident at once (three per SM), whatever the contexts' lengths (so that a captured
+        launch stays valid)."""
         blocks = max(num_seqs * nkv, 1)
-        return max(1, min(-(-2 * self.sm_count // blocks), 32))
+        return max(1, min(self.sm_count * 3 // blocks, 32))
 
     def paged_attention(self, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, page_size,
                         scale, window, out) -> None:
@@ -191,18 +238,17 @@ class CudaOps:
             if any(small):
                 splits = self.decode_splits(ctx.num_seqs, nkv)
                 floats = lib.ie_attention_decode_scratch_floats(ctx.num_seqs, nkv, splits)
-                scratch = None
+                scratch = tickets = None
                 if floats:
                     ws = getattr(ctx, "ws", None)
                     scratch = (ws.buffer("attn.partial", 1, floats, torch.float32) if ws is not None
                                else torch.empty(floats, dtype=torch.float32, device=q.device))
+                    tickets = self._decode_tickets(ctx.num_seqs * nkv)
                 self._check(lib.ie_attention_decode(
                     q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
                     block_tables.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_lens.data_ptr(), out.data_ptr(),
-                    self._ptr(scratch), ctx.num_seqs, nh, nkv, page_size, total_pages, scale, window,
-                    splits, self._err_ptr, stream), "attention_decode")
-                if splits > 1:
-                    self.launches += 1  # the merge of the splits
+                    self._ptr(scratch), self._ptr(tickets), ctx.num_seqs, nh, nkv, page_size,
+                    total_pages, scale, window, splits, self._err_ptr, stream), "attention_decode")
             if not all(small):
                 tiles = sum(-(-ql // 64) for ql, s in zip(ctx.q_lens, small) if not s)
                 self._check(lib.ie_attention_prefill(

@@ -60,8 +60,8 @@ class PagedAttention(Mixer):
 
         n = x.shape[0]
         group = ctx.groups[binding.group]
-        qkv = ctx.ws.buffer("attn.qkv", n, self.q_size + 2 * self.kv_size, torch.float32)
-        ctx.ops.linear(x, self.w_qkv, qkv)
+        qkv = ctx.ops.linear(x, self.w_qkv, ws=ctx.ws, tag="attn.qkv", out_dtype=torch.float32,
+                             allow_split=True)
         q = ctx.ws.buffer("attn.q", n, self.q_size, self.dtype)
         table = self.position.rotary_table() if self.position is not None else None
         rotary_dim = self.position.rotary_dim if self.position is not None else 0
@@ -77,6 +77,5 @@ class PagedAttention(Mixer):
             self.num_heads, self.num_kv_heads, self.head_dim, group.page_size,
             self.scale, self.window or 0, out,
         )
-        delta = ctx.ws.buffer("mixer.delta", n, self.hidden_size, torch.float32)
-        ctx.ops.linear(out, self.w_o, delta)
-        return delta
+        return ctx.ops.linear(out, self.w_o, ws=ctx.ws, tag="mixer.delta", out_dtype=torch.float32,
+                              allow_split=True)

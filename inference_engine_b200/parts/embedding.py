@@ -67,5 +67,4 @@ class LinearHead(Part):
         import torch
 
         logits = ctx.ws.buffer("logits", x.shape[0], self.vocab_size, torch.float32, rows_cap=None)
-        ctx.ops.linear(x, self.weight, logits)
-        return logits
+        return ctx.ops.linear(x, self.weight, logits)

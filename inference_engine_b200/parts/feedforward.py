@@ -43,10 +43,9 @@ class SwiGLU(FeedForward):
         import torch
 
         n, i = x.shape[0], self.intermediate_size
-        gate_up = ctx.ws.buffer("ffn.gate_up", n, 2 * i, self.dtype)
-        ctx.ops.linear(x, self.w_gate_up, gate_up)
+        gate_up = ctx.ops.linear(x, self.w_gate_up, ws=ctx.ws, tag="ffn.gate_up", out_dtype=self.dtype,
+                                 allow_split=True)
         act = ctx.ws.buffer("ffn.act", n, i, self.dtype)
         ctx.ops.silu_mul(gate_up, act)
-        delta = ctx.ws.buffer("ffn.delta", n, self.hidden_size, torch.float32)
-        ctx.ops.linear(act, self.w_down, delta)
-        return delta
+        return ctx.ops.linear(act, self.w_down, ws=ctx.ws, tag="ffn.delta", out_dtype=torch.float32,
+                              allow_split=True)

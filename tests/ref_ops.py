@@ -31,8 +31,11 @@ class RefOps:
         normed = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
         out.copy_((weight * normed).to(out.dtype))
 
-    def linear(self, x, w, out):
+    def linear(self, x, w, out=None, *, ws=None, tag="linear", out_dtype=None, allow_split=False):
+        if out is None:
+            out = ws.buffer(tag, x.shape[0], w.shape[0], out_dtype)
         out.copy_((x.float() @ w.float().t()).to(out.dtype))
+        return out
 
     def rope_kv_write(self, qkv, positions, table, rotary_dim, q_out, k_cache, v_cache,
                       slot_mapping, nh, nkv, hd, page_size):

@@ -30,7 +30,7 @@ def _library():
 
     lib = ctypes.CDLL(str(build_attention(HD)))
     P, I, F = c_void_p, c_int, c_float
-    lib.ie_attention_decode.argtypes = [P, P, P, P, I, P, P, P, P, I, I, I, I, I, F, I, I, P, P]
+    lib.ie_attention_decode.argtypes = [P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, F, I, I, P, P]
     lib.ie_attention_decode_static.argtypes = [P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, P, P, c_char_p, I]
     lib.ie_attention_decode_scratch_floats.argtypes = [I, I, I]
     lib.ie_attention_decode_scratch_floats.restype = ctypes.c_longlong
@@ -69,12 +69,15 @@ def test_static_scratch_entry_point_matches_the_regular_one_twice_in_a_row():
         floats = lib.ie_attention_decode_scratch_floats(b, NKV, splits)
         assert 0 < floats <= lib.ie_attention_decode_static_capacity_floats()
         scratch = torch.empty(floats, dtype=torch.float32, device="cuda")
+        tickets = torch.zeros(b * NKV, dtype=torch.int32, device="cuda")
         want = torch.zeros_like(q)
         rc = lib.ie_attention_decode(q.data_ptr(), k.data_ptr(), v.data_ptr(), tables.data_ptr(),
                                      tables.shape[1], cu_q.data_ptr(), ctx.data_ptr(), want.data_ptr(),
-                                     scratch.data_ptr(), b, NH, NKV, PAGE, k.shape[0], HD ** -0.5, 0,
+                                     scratch.data_ptr(), tickets.data_ptr(), b, NH, NKV, PAGE, k.shape[0], HD ** -0.5, 0,
                                      splits, err.data_ptr(), stream)
         assert rc == 0
+        torch.cuda.synchronize()
+        assert not tickets.any()  # the launch left its counters at zero
         got = torch.zeros_like(q)
         before = torch.cuda.memory_allocated()
         rc = lib.ie_attention_decode_static(q.data_ptr(), k.data_ptr(), v.data_ptr(), tables.data_ptr(),

@@ -71,30 +71,61 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *reinterpret_cast<unsigned*>(&v);
 }
 
-// Stage keys key0 .. key0 + KT - 1 of one key/value head into a shared-memory tile.  Keys
-// outside [lo, hi] are zero-filled.  `tid`/`nthreads`: the threads that share the tile.
-template <int KT>
-__device__ __forceinline__ void load_tile(bf16* tile, const bf16* __restrict__ cache,
-                                          const int* __restrict__ table, int key0, int lo, int hi,
-                                          int kvh, int nkv, int page_shift, int total_pages,
-                                          int tid, int nthreads, int* err) {
+// Staging keys key0 .. key0 + KT - 1 of one key/value head into shared-memory tiles takes two
+// steps that callers keep a whole tile apart, because a dependent trip to memory costs about
+// 1,600 cycles on this part and a block-table lookup in front of every copy would dominate:
+//   fetch_pages  reads the block-table entries a thread's copies will need (into registers);
+//   issue_kv     issues the 16-byte copies of K and V rows from those pages (cp.async).
+// NTHREADS threads share the tile (`tid` among them).  Keys outside [lo, hi] are zero-filled.
+template <int KT, int NTHREADS>
+struct TilePages {
+    static constexpr int ITERS = (KT * C + NTHREADS - 1) / NTHREADS;
+    int page[ITERS];
+};
+
+template <int KT, int NTHREADS>
+__device__ __forceinline__ void fetch_pages(TilePages<KT, NTHREADS>& pg, const int* __restrict__ table,
+                                            int table_width, int key0, int lo, int hi, int page_shift,
+                                            int tid) {
+#pragma unroll
+    for (int i = 0; i < TilePages<KT, NTHREADS>::ITERS; ++i) {
+        int idx = i * NTHREADS + tid;
+        int kpos = key0 + idx / C;
+        int entry = kpos >> page_shift;
+        bool wanted = idx < KT * C && kpos >= lo && kpos <= hi && entry < table_width;
+        pg.page[i] = wanted ? table[entry] : -1;
+    }
+}
+
+// REPORT: a missing page inside [lo, hi] is an error (recorded).  Otherwise (the speculative
+// first load, issued before the context length is known) it is zero-filled silently and the
+// lowest such key position is returned for the caller to judge.
+template <int KT, int NTHREADS, bool REPORT>
+__device__ __forceinline__ int issue_kv(bf16* ktile, bf16* vtile, const TilePages<KT, NTHREADS>& pg,
+                                        const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+                                        int key0, int lo, int hi, int kvh, int nkv, int page_shift,
+                                        int total_pages, int tid, int* err) {
     int page_mask = (1 << page_shift) - 1;
-    for (int idx = tid; idx < KT * C; idx += nthreads) {
+    int bad = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < TilePages<KT, NTHREADS>::ITERS; ++i) {
+        int idx = i * NTHREADS + tid;
+        if (idx >= KT * C) break;
         int row = idx / C, c = idx - row * C;
         int kpos = key0 + row;
-        bool valid = kpos >= lo && kpos <= hi;
-        const bf16* src = cache;
-        if (valid) {
-            int page = table[kpos >> page_shift];
-            if (page < 0 || page >= total_pages) {
-                ie_report(err, page < 0 ? IE_ERR_TABLE : IE_ERR_PAGE, page, kpos);
-                valid = false;
-            } else {
-                src = cache + ((((size_t)page * nkv + kvh) << page_shift) + (kpos & page_mask)) * HD + c * 8;
-            }
+        bool in_range = kpos >= lo && kpos <= hi;
+        int page = pg.page[i];
+        bool valid = in_range && page >= 0 && page < total_pages;
+        if (in_range && !valid) {
+            if (REPORT) ie_report(err, page < 0 ? IE_ERR_TABLE : IE_ERR_PAGE, page, kpos);
+            else bad = min(bad, kpos);
         }
-        cp_async16(tile + (row * C + swz(row, c)) * 8, src, valid);
+        size_t off = valid ? ((((size_t)page * nkv + kvh) << page_shift) + (kpos & page_mask)) * HD + c * 8 : 0;
+        int dst = (row * C + swz(row, c)) * 8;
+        cp_async16(ktile + dst, k_cache + off, valid);
+        cp_async16(vtile + dst, v_cache + off, valid);
     }
+    return bad;
 }
 
 // The state of one warp's 16 rows: running maximum (in log2 units), running sum, output.
@@ -202,36 +233,79 @@ __device__ __forceinline__ void finish_rows(RowState& st) {
 }
 
 // -------------------------------------------------------------------------------------------------
-// Decode: few rows per request.  grid = (requests, kv heads, splits), 4 warps.
+// Decode: few rows per request.  grid = (requests, kv heads, splits), 8 warps, one block per SM.
+//
+// A decode step is bound by latency, not by arithmetic: a dependent trip to memory costs about
+// a microsecond on this part.  So the kernel keeps the chain of dependent loads short and the
+// number of bytes in flight high:
+//   * key tiles are dealt round-robin: tile j (keys lo + j*KT ...) goes to split j % S, and
+//     within a split to warp (j / S) % 8.  Without a window lo is 0, so a warp knows its first
+//     tiles before it knows the context length and fetches their block-table entries at once,
+//     while the lengths are still on their way; later entries are fetched a tile ahead of use;
+//   * every warp owns a ring of three (K, V) tiles in shared memory and keeps two tiles in
+//     flight beyond the one it works on: 192 KB per SM, enough for one block per request and
+//     key/value head to stream at the SM's full rate;
+//   * with splits > 1 the block that finishes last merges the partial results (ticket counter),
+//     always in the order 0, 1, 2, ...
 // Partials for splits > 1: part_o[((seq * nkv + kvh) * splits + split) * 16 + row][HD],
 // part_ml[... ][2] = (maximum in log2 units, sum).
 // -------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(WARPS * 32)
+constexpr int DWARPS = 8;
+constexpr int DSTAGES = 3;
+
+__global__ void __launch_bounds__(DWARPS * 32)
 attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache,
                         const bf16* __restrict__ v_cache, const int* __restrict__ tables,
                         int table_width, const int* __restrict__ cu_q, const int* __restrict__ ctx_lens,
                         bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                         int* __restrict__ tickets, int nh, int nkv, int page_shift, int total_pages,
                         float scale_log2, int window, int num_splits, int* err) {
-    constexpr int KT = KT_DECODE, TILE_ELEMS = KT * HD;
+    constexpr int KT = KT_DECODE, TILE_ELEMS = KT * HD, WARPS = DWARPS;
     __shared__ int is_last;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
     int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int G = nh / nkv;
-    int q0 = cu_q[seq], qlen = cu_q[seq + 1] - q0, ctx = ctx_lens[seq];
+    const int* table = tables + (size_t)seq * table_width;
+    bf16* ring = smem + (size_t)warp * DSTAGES * 2 * TILE_ELEMS;
+    int stride = num_splits * WARPS;          // tiles between two tiles of the same warp
+    int j0 = split + num_splits * warp;       // this warp's first tile
+
+    // 1. lengths (on their way) and, without a window, the block-table entries of the first
+    //    tiles at once: tile j of a request starts at key lo + j*KT and lo is 0
+    typedef TilePages<KT, 32> Pages;
+    int q0 = cu_q[seq], q1 = cu_q[seq + 1], ctx = ctx_lens[seq];
+    bool early = window <= 0;
+    Pages pg[DSTAGES];
+    if (early) {
+#pragma unroll
+        for (int s = 0; s < DSTAGES; ++s)
+            fetch_pages<KT, 32>(pg[s], table, table_width, (j0 + s * stride) * KT, 0, 0x7fffffff, page_shift, lane);
+    }
+    int qlen = q1 - q0;
     int rows = qlen * G;
     if (rows > MAX_ROWS || qlen <= 0) return;  // the prefill kernel takes this request
-    const int* table = tables + (size_t)seq * table_width;
     int first_qpos = ctx - qlen, hi = ctx - 1;
     int lo = (window > 0 && first_qpos - window + 1 > 0) ? first_qpos - window + 1 : 0;
-    int total = hi - lo + 1;
-    int per = (((total + num_splits - 1) / num_splits) + KT - 1) / KT * KT;
-    int s_lo = lo + split * per;
-    int s_hi = min(hi, s_lo + per - 1);
-
-    // the thread's two rows
+    int n_tiles = (hi - lo) / KT + 1;         // tiles of the whole request
+    if (!early) {
+#pragma unroll
+        for (int s = 0; s < DSTAGES; ++s)
+            fetch_pages<KT, 32>(pg[s], table, table_width, lo + (j0 + s * stride) * KT, lo, hi, page_shift, lane);
+    }
+    // 2. the first tiles' keys and values
+#pragma unroll
+    for (int s = 0; s < DSTAGES - 1; ++s) {
+        int j = j0 + s * stride;
+        if (j < n_tiles) {
+            bf16* st_k = ring + (size_t)s * 2 * TILE_ELEMS;
+            issue_kv<KT, 32, true>(st_k, st_k + TILE_ELEMS, pg[s], k_cache, v_cache, lo + j * KT, lo, hi,
+                                   kvh, nkv, page_shift, total_pages, lane, err);
+        }
+        cp_async_commit();
+    }
+    // 3. the queries (they needed cu_q) while those are in flight
     int qpos[2], qlo[2];
     unsigned qf[KS][4];
 #pragma unroll
@@ -251,38 +325,31 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
     }
     RowState st;
     st.init();
-    // each warp owns two stages of (K tile, V tile)
-    bf16* wbase = smem + (size_t)warp * 4 * TILE_ELEMS;
-    int n_tiles = s_lo <= s_hi ? (s_hi - s_lo) / KT + 1 : 0;
-    int stage = 0;
-    if (warp < n_tiles) {
-        int key0 = s_lo + warp * KT;
-        load_tile<KT>(wbase, k_cache, table, key0, s_lo, s_hi, kvh, nkv, page_shift, total_pages, lane, 32, err);
-        load_tile<KT>(wbase + TILE_ELEMS, v_cache, table, key0, s_lo, s_hi, kvh, nkv, page_shift, total_pages, lane, 32, err);
-    }
-    cp_async_commit();
-    for (int t = warp; t < n_tiles; t += WARPS) {
-        int key0 = s_lo + t * KT;
-        int next = t + WARPS;
-        bf16* cur = wbase + (size_t)stage * 2 * TILE_ELEMS;
-        bf16* nxt = wbase + (size_t)(stage ^ 1) * 2 * TILE_ELEMS;
-        if (next < n_tiles) {
-            int nkey0 = s_lo + next * KT;
-            load_tile<KT>(nxt, k_cache, table, nkey0, s_lo, s_hi, kvh, nkv, page_shift, total_pages, lane, 32, err);
-            load_tile<KT>(nxt + TILE_ELEMS, v_cache, table, nkey0, s_lo, s_hi, kvh, nkv, page_shift, total_pages, lane, 32, err);
+    // 4. the ring: the copies of tile i+2 use block-table entries fetched one tile earlier, and
+    //    the entries of tile i+3 are fetched now, so no lookup is waited for
+    Pages next = pg[DSTAGES - 1];
+    int i = 0;
+    for (int j = j0; j < n_tiles; j += stride, ++i) {
+        int pre = j + (DSTAGES - 1) * stride;
+        if (pre < n_tiles) {
+            bf16* st_k = ring + (size_t)((i + DSTAGES - 1) % DSTAGES) * 2 * TILE_ELEMS;
+            issue_kv<KT, 32, true>(st_k, st_k + TILE_ELEMS, next, k_cache, v_cache, lo + pre * KT, lo, hi,
+                                   kvh, nkv, page_shift, total_pages, lane, err);
         }
         cp_async_commit();
-        cp_async_wait<1>();
+        if (pre + stride < n_tiles)
+            fetch_pages<KT, 32>(next, table, table_width, lo + (pre + stride) * KT, lo, hi, page_shift, lane);
+        cp_async_wait<DSTAGES - 1>();
         __syncwarp();
-        process_tile<KT>(st, qf, cur, cur + TILE_ELEMS, key0, qpos, qlo, s_hi, scale_log2, lane);
+        const bf16* cur = ring + (size_t)(i % DSTAGES) * 2 * TILE_ELEMS;
+        process_tile<KT>(st, qf, cur, cur + TILE_ELEMS, lo + j * KT, qpos, qlo, hi, scale_log2, lane);
         __syncwarp();
-        stage ^= 1;
     }
     cp_async_wait<0>();
     finish_rows(st);
     __syncthreads();  // every warp is done with its tiles: the shared memory is reused below
 
-    // merge the four warps: [warp][row] m, l and [warp][row][HD] o in shared memory
+    // merge the warps: [warp][row] m, l and [warp][row][HD] o in shared memory
     float* sm_ml = reinterpret_cast<float*>(smem_raw);            // [WARPS][16][2]
     float* sm_o = sm_ml + WARPS * MAX_ROWS * 2;                   // [WARPS][16][HD]
 #pragma unroll
@@ -411,25 +478,41 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
 
     RowState st;
     st.init();
-    int stage = 0;
-    load_tile<KT>(smem, k_cache, table, key_begin, lo, cta_qpos_hi, kvh, nkv, page_shift, total_pages, threadIdx.x, WARPS * 32, err);
-    load_tile<KT>(smem + TILE_ELEMS, v_cache, table, key_begin, lo, cta_qpos_hi, kvh, nkv, page_shift, total_pages, threadIdx.x, WARPS * 32, err);
-    cp_async_commit();
-    for (int t = 0; t < n_tiles; ++t) {
-        int key0 = key_begin + t * KT;
-        bf16* cur = smem + (size_t)stage * 2 * TILE_ELEMS;
-        bf16* nxt = smem + (size_t)(stage ^ 1) * 2 * TILE_ELEMS;
-        if (t + 1 < n_tiles) {
-            load_tile<KT>(nxt, k_cache, table, key0 + KT, lo, cta_qpos_hi, kvh, nkv, page_shift, total_pages, threadIdx.x, WARPS * 32, err);
-            load_tile<KT>(nxt + TILE_ELEMS, v_cache, table, key0 + KT, lo, cta_qpos_hi, kvh, nkv, page_shift, total_pages, threadIdx.x, WARPS * 32, err);
+    // Three stages of (K, V) tiles; the block-table entries of a tile are fetched one tile
+    // before its copies are issued, so no lookup is waited for inside the loop.
+    typedef TilePages<KT, WARPS * 32> Pages;
+    constexpr int PSTAGES = 3;
+    Pages pg[PSTAGES];
+#pragma unroll
+    for (int s = 0; s < PSTAGES; ++s)
+        fetch_pages<KT, WARPS * 32>(pg[s], table, table_width, key_begin + s * KT, lo, cta_qpos_hi, page_shift, threadIdx.x);
+#pragma unroll
+    for (int s = 0; s < PSTAGES - 1; ++s) {
+        if (s < n_tiles) {
+            bf16* st_k = smem + (size_t)s * 2 * TILE_ELEMS;
+            issue_kv<KT, WARPS * 32, true>(st_k, st_k + TILE_ELEMS, pg[s], k_cache, v_cache, key_begin + s * KT,
+                                           lo, cta_qpos_hi, kvh, nkv, page_shift, total_pages, threadIdx.x, err);
         }
         cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();
+    }
+    Pages next = pg[PSTAGES - 1];
+    for (int t = 0; t < n_tiles; ++t) {
+        int key0 = key_begin + t * KT;
+        int pre = t + PSTAGES - 1;
+        cp_async_wait<PSTAGES - 2>();  // tile t has landed (this thread's part)
+        __syncthreads();               // ... everybody's part; and tile t-1 is no longer read
+        if (pre < n_tiles) {
+            bf16* st_k = smem + (size_t)(pre % PSTAGES) * 2 * TILE_ELEMS;
+            issue_kv<KT, WARPS * 32, true>(st_k, st_k + TILE_ELEMS, next, k_cache, v_cache, key_begin + pre * KT,
+                                           lo, cta_qpos_hi, kvh, nkv, page_shift, total_pages, threadIdx.x, err);
+        }
+        cp_async_commit();
+        if (pre + 1 < n_tiles)
+            fetch_pages<KT, WARPS * 32>(next, table, table_width, key_begin + (pre + 1) * KT, lo, cta_qpos_hi,
+                                        page_shift, threadIdx.x);
+        const bf16* cur = smem + (size_t)(t % PSTAGES) * 2 * TILE_ELEMS;
         if (warp_has_rows && key0 <= warp_hi && key0 + KT - 1 >= warp_lo)
             process_tile<KT>(st, qf, cur, cur + TILE_ELEMS, key0, qpos, qlo, cta_qpos_hi, scale_log2, lane);
-        __syncthreads();
-        stage ^= 1;
     }
     cp_async_wait<0>();
     finish_rows(st);
@@ -447,9 +530,9 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
     }
 }
 
-constexpr size_t DECODE_SMEM_TILES = (size_t)WARPS * 4 * KT_DECODE * HD * sizeof(bf16);
-constexpr size_t DECODE_MERGE_SMEM = (size_t)WARPS * MAX_ROWS * (2 + HD) * sizeof(float);
-constexpr size_t PREFILL_SMEM = (size_t)4 * KT_PREFILL * HD * sizeof(bf16);
+constexpr size_t DECODE_SMEM_TILES = (size_t)DWARPS * DSTAGES * 2 * KT_DECODE * HD * sizeof(bf16);
+constexpr size_t DECODE_MERGE_SMEM = (size_t)DWARPS * MAX_ROWS * (2 + HD) * sizeof(float);
+constexpr size_t PREFILL_SMEM = (size_t)3 * 2 * KT_PREFILL * HD * sizeof(bf16);
 constexpr size_t DECODE_SMEM = DECODE_SMEM_TILES > DECODE_MERGE_SMEM ? DECODE_SMEM_TILES : DECODE_MERGE_SMEM;
 }  // namespace
 
@@ -488,7 +571,7 @@ IE_API int ie_attention_decode(const void* q, const void* k_cache, const void* v
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)num_seqs * nkv * num_splits * MAX_ROWS * HD : nullptr;
     dim3 grid(num_seqs, nkv, num_splits);
-    attention_decode_kernel<<<grid, WARPS * 32, DECODE_SMEM, s>>>(
+    attention_decode_kernel<<<grid, DWARPS * 32, DECODE_SMEM, s>>>(
         (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, tables, table_width, cu_q, ctx_lens,
         (bf16*)out, part_o, part_ml, tickets, nh, nkv, page_shift, total_pages,
         scale * 1.4426950408889634f, window, num_splits, err);

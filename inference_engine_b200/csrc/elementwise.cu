@@ -95,13 +95,16 @@ rmsnorm_vec_kernel(float* __restrict__ h, const float* __restrict__ delta, int n
     int r = blockIdx.x;
     size_t src = (size_t)(rows ? rows[r] : r) * hidden;
     bool write_back = (rows == nullptr) && (delta != nullptr);
-    float4 x[VPT];
+    float4 x[VPT], wt[VPT];
     float ss = 0.f;
 #pragma unroll
     for (int v = 0; v < VPT; ++v) {
         int i = (v * THREADS + threadIdx.x) * 4;
-        x[v] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (i < hidden) x[v] = *reinterpret_cast<const float4*>(h + src + i);
+        x[v] = wt[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < hidden) {
+            x[v] = *reinterpret_cast<const float4*>(h + src + i);
+            wt[v] = *reinterpret_cast<const float4*>(weight + i);  // with the row: one trip to memory
+        }
     }
     if (delta) {
         for (int p = 0; p < num_partials; ++p) {
@@ -138,7 +141,7 @@ rmsnorm_vec_kernel(float* __restrict__ h, const float* __restrict__ delta, int n
     for (int v = 0; v < VPT; ++v) {
         int i = (v * THREADS + threadIdx.x) * 4;
         if (i < hidden) {
-            float4 w = *reinterpret_cast<const float4*>(weight + i);
+            float4 w = wt[v];
             float4 o = make_float4(w.x * (x[v].x * scale), w.y * (x[v].y * scale),
                                    w.z * (x[v].z * scale), w.w * (x[v].w * scale));
             store4(out + (size_t)r * hidden + i, o);

@@ -211,11 +211,12 @@ class CudaOps:
         return self._tickets
 
     def decode_splits(self, num_seqs: int, nkv: int) -> int:
-        """Into how many parts the decode kernel cuts each context: as many blocks as are
-        resident at once (three per SM), whatever the contexts' lengths (so that a captured
-        launch stays valid)."""
+        """Into how many parts the decode kernel cuts each context.  One block per (request,
+        key/value head) streams at an SM's full rate, so contexts are only cut when there are
+        few such blocks (small batches); the number depends on the batch alone, never on the
+        contexts' lengths, so that a captured launch stays valid."""
         blocks = max(num_seqs * nkv, 1)
-        return max(1, min(self.sm_count * 3 // blocks, 32))
+        return max(1, min(64 // blocks, 32))
 
     def paged_attention(self, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, page_size,
                         scale, window, out) -> None:

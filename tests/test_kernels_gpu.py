@@ -307,7 +307,7 @@ def test_decode_attention_with_many_splits_is_the_same_as_one(ops):
     result equals the unsplit one up to rounding."""
     nh, nkv, hd, ps = 8, 2, 64, 16
     q, k, v, tables, ctx = _attention_case(nh, nkv, hd, ps, [1], [3000], torch.bfloat16, seed=4)
-    assert ops.decode_splits(1, nkv) > 8
+    assert ops.decode_splits(1, nkv) >= 8
     got = torch.empty_like(q)
     ops.paged_attention(q, k, v, tables, ctx, nh, nkv, hd, ps, hd ** -0.5, 0, got)
     want = torch.empty_like(q)

@@ -51,7 +51,8 @@ class _Request:
 
 class CacheManager:
     def __init__(self, paged_groups: list[PagedGroupSpec], state_groups: list[StateGroupSpec],
-                 num_pages: int | list[int], page_size: int, max_requests: int) -> None:
+                 num_pages: int | list[int], page_size: int, max_requests: int,
+                 max_pages_per_request: int | None = None) -> None:
         if page_size < 1 or page_size & (page_size - 1):
             raise ValueError("page_size must be a power of two")
         self.paged_groups, self.state_groups = list(paged_groups), list(state_groups)
@@ -60,8 +61,20 @@ class CacheManager:
         if len(counts) != len(self.paged_groups):
             raise ValueError("num_pages needs one entry per paged cache group")
         self.pools = [PagePool(n) for n in counts]
+        self._has_window = any(g.window is not None for g in self.paged_groups)
         self.slots = SlotPool(max_requests)
         self._requests: dict[object, _Request] = {}
+        # A dense copy of the block tables, one row per state slot (the last row is the
+        # padding row of fixed-size launches), kept in step with the lists: the step function
+        # gathers the rows of a whole batch from it in one operation.  numpy is optional here.
+        self.table_rows = None
+        try:
+            import numpy as np
+
+            widths = [min(n, max_pages_per_request or n) for n in counts]
+            self.table_rows = [np.full((max_requests + 1, w), -1, dtype=np.int32) for w in widths]
+        except ImportError:  # pragma: no cover
+            pass
 
     # --- sizes ------------------------------------------------------------------------------
 
@@ -140,10 +153,35 @@ class CacheManager:
             for i in range(first, last_page):
                 if table[i] < 0:
                     table[i] = self.pools[g].allocate()
+                    self._mirror(g, req.state_slot, i, table[i])
+
+    def _mirror(self, group: int, slot: int, index: int, page: int) -> None:
+        if self.table_rows is not None and index < self.table_rows[group].shape[1]:
+            self.table_rows[group][slot, index] = page
+
+    def try_grow(self, req_id, num_computed: int, num_tokens: int) -> bool:
+        """``grow`` if there is room, in one pass; False (and nothing changed) otherwise.  The
+        common case of a decoding request that still has room in its last page costs a few
+        comparisons."""
+        req = self._requests[req_id]
+        last_page = -(-num_tokens // self.page_size)
+        simple = True
+        for g, table in enumerate(req.tables):
+            if self.paged_groups[g].window is not None or len(table) < last_page:
+                simple = False
+                break
+        if simple:
+            return True
+        if not self.can_grow(req_id, num_computed, num_tokens):
+            return False
+        self.grow(req_id, num_computed, num_tokens)
+        return True
 
     def release_behind_window(self, req_id, num_computed: int) -> int:
         """Give back the pages no later query can see: those wholly before
         ``num_computed - window + 1`` in windowed groups.  Returns how many were freed."""
+        if not self._has_window:
+            return 0
         req = self._requests[req_id]
         freed = 0
         for g, table in enumerate(req.tables):
@@ -152,6 +190,7 @@ class CacheManager:
                 if table[i] >= 0:
                     self.pools[g].free(table[i])
                     table[i] = -1
+                    self._mirror(g, req.state_slot, i, -1)
                     freed += 1
             req.released[g] = max(req.released[g], first)
         return freed
@@ -163,6 +202,8 @@ class CacheManager:
             for page in table:
                 if page >= 0:
                     self.pools[g].free(page)
+            if self.table_rows is not None:
+                self.table_rows[g][req.state_slot, : len(table)] = -1
             table.clear()
             req.released[g] = 0
 

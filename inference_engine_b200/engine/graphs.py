@@ -53,8 +53,16 @@ class DecodeGraphs:
         bucket = self.bucket_for(len(entries))
         if self._version != runner.ws.version:  # a buffer moved: captured addresses are stale
             self._graphs.clear()
-        ctx, rows = runner.build_context(entries, pad_to_seqs=bucket, table_width=self.table_width)
-        if bucket not in self._graphs:
+            self._version = runner.ws.version
+        captured = bucket in self._graphs
+        ctx, rows = runner.build_context(entries, pad_to_seqs=bucket, table_width=self.table_width,
+                                         views=not captured)
+        if self._version != runner.ws.version:  # the staging buffer itself had to grow
+            self._graphs.clear()
+            self._version = runner.ws.version
+            captured = False
+            ctx, rows = runner.build_context(entries, pad_to_seqs=bucket, table_width=self.table_width)
+        if not captured:
             # Run once outside a capture (buffers get allocated, libraries initialised) ...
             stream = torch.cuda.Stream()
             stream.wait_stream(torch.cuda.current_stream())

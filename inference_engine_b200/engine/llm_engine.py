@@ -52,11 +52,12 @@ class LLMEngine:
         elt = 2 if self.dtype == "bfloat16" else 4
         if num_blocks is None:
             num_blocks = self._blocks_that_fit(block_size, gpu_memory_utilization, elt)
-        self.cache = CacheManager(model.paged_groups, model.state_groups, num_blocks, block_size,
-                                  max_num_seqs)
-        self.storage = CacheStorage(self.cache, model.env.torch_dtype, self.device)
         self.max_model_len = min(max_model_len or model.spec.max_position_embeddings,
-                                 self.cache.capacity_tokens, model.env.max_positions)
+                                 num_blocks * block_size if model.paged_groups else 2**62,
+                                 model.env.max_positions)
+        self.cache = CacheManager(model.paged_groups, model.state_groups, num_blocks, block_size,
+                                  max_num_seqs, max_pages_per_request=-(-self.max_model_len // block_size))
+        self.storage = CacheStorage(self.cache, model.env.torch_dtype, self.device)
         self.runner = ModelRunner(model, self.cache, self.storage, ops, self.device,
                                   max_num_batched_tokens, max_num_seqs)
         self.scheduler = Scheduler(self.cache, max_num_seqs, max_num_batched_tokens,

@@ -76,7 +76,7 @@ class ModelRunner:
     # --- one step ---------------------------------------------------------------------------
 
     def build_context(self, entries: list[StepEntry], pad_to_seqs: int | None = None,
-                      table_width: int | None = None):
+                      table_width: int | None = None, views: bool = True):
         """Pack the step's index data, copy it to the device and return the context and the
         device vector of wanted rows.  ``pad_to_seqs``/``table_width`` give a launch of fixed
         size: missing sequences become single tokens that read and write the scratch page."""
@@ -87,6 +87,8 @@ class ModelRunner:
         q_lens = [len(e.tokens) for e in entries]
         if any(n < 1 for n in q_lens):
             raise ValueError("every entry of a step needs at least one token")
+        if max(q_lens) == 1 and self.cache.table_rows is not None:
+            return self._build_decode_context(entries, pad_to_seqs, table_width, views)
         real_b = len(entries)
         b = max(pad_to_seqs or 0, real_b)
         pad = b - real_b
@@ -185,6 +187,102 @@ class ModelRunner:
             cu_q=dview(v_cu), ctx_lens=dview(v_ctx), groups=groups,
             q_starts=q_starts, q_lens=q_lens, start_positions=start_positions,
             max_q_len=max(q_lens), max_ctx_len=max(ctx_lens), padded=pad_to_seqs is not None,
+        )
+        return ctx, dview(v_rows)
+
+    def _build_decode_context(self, entries: list[StepEntry], pad_to_seqs: int | None,
+                              table_width: int | None, views: bool = True):
+        """The same packing for a step of single tokens, without a Python loop over what the
+        entries hold: block-table rows are gathered from the cache manager's dense copy."""
+        import numpy as np
+
+        ps, cache = self.page_size, self.cache
+        real_b = len(entries)
+        b = max(pad_to_seqs or 0, real_b)
+        pad = b - real_b
+        positions = np.fromiter((e.start for e in entries), dtype=np.int64, count=real_b)
+        state_slots = [cache.state_slot(e.req_id) for e in entries]
+        slots_arr = np.asarray(state_slots, dtype=np.int64)
+        logit_rows = [i for i, e in enumerate(entries) if e.want]
+        if any(len(e.want) > 1 or (e.want and e.want[0] != 0) for e in entries):
+            raise ValueError("a single-token entry can only want place 0")
+        logit_rows += list(range(real_b, b))
+        rows = len(logit_rows)
+        page_index = positions // ps
+        width = max(table_width or 1, int(page_index.max()) + 1)
+        self._ensure_staging(self._staging_ints(b, b, rows, width))
+        turn, buf = self._next_host_buffer()
+        off = 0
+
+        def take(count: int):
+            nonlocal off
+            view = (off, count)
+            off += _align4(count)
+            return view
+
+        v_tok, v_pos, v_seq = take(b), take(b), take(b)
+        v_cu, v_ctx, v_state, v_rows = take(b + 1), take(b), take(b), take(rows)
+        v_slots = [take(b) for _ in cache.paged_groups]
+        v_tables = [take(b * width) for _ in cache.paged_groups]
+        buf[v_tok[0]: v_tok[0] + real_b] = [e.tokens[0] for e in entries]
+        buf[v_pos[0]: v_pos[0] + real_b] = positions
+        buf[v_seq[0]: v_seq[0] + b] = np.arange(b)
+        buf[v_cu[0]: v_cu[0] + b + 1] = np.arange(b + 1)
+        buf[v_ctx[0]: v_ctx[0] + real_b] = positions + 1
+        buf[v_state[0]: v_state[0] + real_b] = slots_arr
+        buf[v_rows[0]: v_rows[0] + rows] = logit_rows
+        if pad:
+            buf[v_tok[0] + real_b: v_tok[0] + b] = 0
+            buf[v_pos[0] + real_b: v_pos[0] + b] = 0
+            buf[v_ctx[0] + real_b: v_ctx[0] + b] = 1
+            buf[v_state[0] + real_b: v_state[0] + b] = cache.max_requests
+        for g, st in enumerate(self.storage.paged):
+            dense = cache.table_rows[g]
+            cols = min(width, dense.shape[1])
+            block = buf[v_tables[g][0]: v_tables[g][0] + b * width].reshape(b, width)
+            block[:real_b, :cols] = dense[slots_arr, :cols]
+            if cols < width:
+                block[:real_b, cols:] = -1
+            if int(page_index.max()) >= dense.shape[1]:
+                raise ValueError("a request is longer than the cache manager's block tables")
+            pages = dense[slots_arr, page_index]
+            if (pages < 0).any():
+                bad = entries[int(np.argmax(pages < 0))]
+                raise ValueError(f"request {bad.req_id!r} has no page for position {bad.start}; "
+                                 "call grow() first")
+            buf[v_slots[g][0]: v_slots[g][0] + real_b] = pages * ps + positions % ps
+            if pad:
+                block[real_b:, 0] = st.scratch_page
+                block[real_b:, 1:] = -1
+                buf[v_slots[g][0] + real_b: v_slots[g][0] + b] = st.scratch_page * ps
+        self._staging_dev[:off].copy_(self._staging_host[turn][:off], non_blocking=True)
+        if self._staging_events[turn] is not None:
+            self._staging_events[turn].record()
+            self._staging_used[turn] = True
+        self.last_h2d_bytes = off * 4
+        if not views:  # a captured launch sequence already holds these addresses
+            return None, None
+        dev = self._staging_dev
+
+        def dview(view, shape=None):
+            t = dev[view[0]: view[0] + view[1]]
+            return t if shape is None else t.view(*shape)
+
+        groups: list[Any] = []
+        for g, st in enumerate(self.storage.paged):
+            groups.append(PagedGroupView(st.k, st.v, ps, st.window, dview(v_tables[g], (b, width)),
+                                         width, dview(v_slots[g])))
+        state_dev = dview(v_state)
+        all_slots = state_slots + [cache.max_requests] * pad
+        for st in self.storage.state:
+            groups.append(StateGroupView(st, state_dev, all_slots))
+        start_positions = positions.tolist() + [0] * pad
+        ctx = StepContext(
+            ops=self.ops, ws=self.ws, num_tokens=b, num_seqs=b,
+            token_ids=dview(v_tok), positions=dview(v_pos), seq_of_token=dview(v_seq),
+            cu_q=dview(v_cu), ctx_lens=dview(v_ctx), groups=groups,
+            q_starts=list(range(b)), q_lens=[1] * b, start_positions=start_positions,
+            max_q_len=1, max_ctx_len=int(positions.max()) + 1, padded=pad_to_seqs is not None,
         )
         return ctx, dview(v_rows)
 

@@ -135,13 +135,12 @@ class Scheduler:
                 kept.append(seq)
                 continue
             target = seq.num_computed + n
-            while not self.cache.can_grow(seq.seq_id, seq.num_computed, target):
+            while not self.cache.try_grow(seq.seq_id, seq.num_computed, target):
                 victim = queue.pop() if queue else seq
                 self._preempt(victim)
                 if victim is seq:
                     break
             else:
-                self.cache.grow(seq.seq_id, seq.num_computed, target)
                 kept.append(seq)
                 seqs.append(seq)
                 counts.append(n)

@@ -61,6 +61,8 @@ class CudaOps:
         self.force_skinny = False  # tests run every few-row product through the streaming kernel
         self._tickets = None
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self._device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        self._raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
         self.launches = 0  # launches of this library's kernels (library matrix products not counted)
 
     def _declare(self) -> None:
@@ -84,7 +86,11 @@ class CudaOps:
     # --- helpers ----------------------------------------------------------------------------
 
     def _stream(self) -> int:
-        return self.torch.cuda.current_stream().cuda_stream
+        """The raw handle of torch's current stream on this device (asked on every launch, so
+        through the cheap accessor when torch has it)."""
+        if self._raw_stream is not None:
+            return self._raw_stream(self._device_index)
+        return self.torch.cuda.current_stream(self.device).cuda_stream
 
     def _check(self, code: int, what: str) -> None:
         self.launches += 1

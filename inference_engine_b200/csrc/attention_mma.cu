@@ -66,6 +66,13 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], 
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x on the special-function unit (flushes denormals; -inf gives 0): the softmax's exponentials
+// are as many as its multiply-adds are few, so the slower exact exp2f would bound the kernel.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<unsigned*>(&v);
@@ -167,16 +174,31 @@ __device__ __forceinline__ void process_tile(RowState& st, const unsigned (&qf)[
         }
     }
     float tile_max[2] = {-INFINITY, -INFINITY};
+    int last = key0 + KT - 1;
+    bool all_visible = last <= key_hi && last <= qpos[0] && last <= qpos[1] &&
+                       key0 >= qlo[0] && key0 >= qlo[1];
+    if (__all_sync(0xffffffffu, all_visible)) {  // an inner tile: nothing to mask
 #pragma unroll
-    for (int n = 0; n < NT; ++n) {
+        for (int n = 0; n < NT; ++n) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            int r = j >> 1;
-            int kpos = key0 + n * 8 + (lane & 3) * 2 + (j & 1);
-            bool valid = kpos <= qpos[r] && kpos >= qlo[r] && kpos <= key_hi;
-            float v = valid ? s[n][j] * scale_log2 : -INFINITY;
-            s[n][j] = v;
-            tile_max[r] = fmaxf(tile_max[r], v);
+            for (int j = 0; j < 4; ++j) {
+                float v = s[n][j] * scale_log2;
+                s[n][j] = v;
+                tile_max[j >> 1] = fmaxf(tile_max[j >> 1], v);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                int r = j >> 1;
+                int kpos = key0 + n * 8 + (lane & 3) * 2 + (j & 1);
+                bool valid = kpos <= qpos[r] && kpos >= qlo[r] && kpos <= key_hi;
+                float v = valid ? s[n][j] * scale_log2 : -INFINITY;
+                s[n][j] = v;
+                tile_max[r] = fmaxf(tile_max[r], v);
+            }
         }
     }
     float alpha[2], m_safe[2];
@@ -187,7 +209,7 @@ __device__ __forceinline__ void process_tile(RowState& st, const unsigned (&qf)[
         t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, 2));
         float m_new = fmaxf(st.m[r], t);
         m_safe[r] = (m_new == -INFINITY) ? 0.f : m_new;
-        alpha[r] = exp2f(st.m[r] - m_safe[r]);  // 0 when nothing was seen before
+        alpha[r] = fast_exp2(st.m[r] - m_safe[r]);  // 0 when nothing was seen before
         st.m[r] = m_new;
         st.l[r] *= alpha[r];
     }
@@ -200,7 +222,7 @@ __device__ __forceinline__ void process_tile(RowState& st, const unsigned (&qf)[
     for (int n = 0; n < NT; ++n) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            float p = exp2f(s[n][j] - m_safe[j >> 1]);
+            float p = fast_exp2(s[n][j] - m_safe[j >> 1]);
             s[n][j] = p;
             st.l[j >> 1] += p;
         }
@@ -437,7 +459,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int head = blockIdx.y, G = nh / nkv, kvh = head / G;
     // which request and which 64-token tile of it is this block's?
-    int tile = blockIdx.x, seq = -1, t0 = 0, q0 = 0, qlen = 0;
+    // late tiles of a portion see the most keys: they go first so the short ones fill the tail
+    int tile = gridDim.x - 1 - blockIdx.x, seq = -1, t0 = 0, q0 = 0, qlen = 0;
     for (int s = 0; s < num_seqs; ++s) {
         int a = cu_q[s], n = cu_q[s + 1] - a;
         int tiles = (n * G > MAX_ROWS) ? (n + BM - 1) / BM : 0;

@@ -51,6 +51,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
                                int nh, int nkv, int hd, int page_size, int total_pages,
                                float scale, int window, int* err) {
     extern __shared__ float q_smem[];  // [WARPS][hd]
+    ie_pdl_trigger();
+    ie_pdl_wait();
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int head = blockIdx.x * WARPS + warp;
     int token = blockIdx.y;

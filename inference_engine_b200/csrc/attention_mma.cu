@@ -296,7 +296,10 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
 
     // 1. lengths (on their way) and, without a window, the block-table entries of the first
     //    tiles at once: tile j of a request starts at key lo + j*KT and lo is 0
+    //    (lengths and tables were copied in before the step's first kernel; the kernel right
+    //    before this one wrote the newest keys and values, so those wait for it)
     typedef TilePages<KT, 32> Pages;
+    ie_pdl_trigger();
     int q0 = cu_q[seq], q1 = cu_q[seq + 1], ctx = ctx_lens[seq];
     bool early = window <= 0;
     Pages pg[DSTAGES];
@@ -305,6 +308,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
         for (int s = 0; s < DSTAGES; ++s)
             fetch_pages<KT, 32>(pg[s], table, table_width, (j0 + s * stride) * KT, 0, 0x7fffffff, page_shift, lane);
     }
+    ie_pdl_wait();
     int qlen = q1 - q0;
     int rows = qlen * G;
     if (rows > MAX_ROWS || qlen <= 0) return;  // the prefill kernel takes this request
@@ -459,6 +463,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int head = blockIdx.y, G = nh / nkv, kvh = head / G;
     // which request and which 64-token tile of it is this block's?
+    ie_pdl_trigger();
+    ie_pdl_wait();
     // late tiles of a portion see the most keys: they go first so the short ones fill the tail
     int tile = gridDim.x - 1 - blockIdx.x, seq = -1, t0 = 0, q0 = 0, qlen = 0;
     for (int s = 0; s < num_seqs; ++s) {
@@ -560,6 +566,7 @@ constexpr size_t DECODE_SMEM = DECODE_SMEM_TILES > DECODE_MERGE_SMEM ? DECODE_SM
 }  // namespace
 
 IE_API int ie_attention_head_dim() { return HD; }
+IE_API void ie_set_pdl(int enabled) { ie_pdl_enabled() = enabled ? 1 : 0; }
 
 // Floats of scratch the decode kernel needs for `num_seqs` requests at `num_splits` splits:
 // part_o first, then part_ml.
@@ -594,11 +601,10 @@ IE_API int ie_attention_decode(const void* q, const void* k_cache, const void* v
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)num_seqs * nkv * num_splits * MAX_ROWS * HD : nullptr;
     dim3 grid(num_seqs, nkv, num_splits);
-    attention_decode_kernel<<<grid, DWARPS * 32, DECODE_SMEM, s>>>(
-        (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, tables, table_width, cu_q, ctx_lens,
-        (bf16*)out, part_o, part_ml, tickets, nh, nkv, page_shift, total_pages,
-        scale * 1.4426950408889634f, window, num_splits, err);
-    return IE_LAUNCH_CHECK();
+    return ie_launch(attention_decode_kernel, grid, dim3(DWARPS * 32), DECODE_SMEM, s,
+                     (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, tables, table_width, cu_q,
+                     ctx_lens, (bf16*)out, part_o, part_ml, tickets, nh, nkv, page_shift, total_pages,
+                     scale * 1.4426950408889634f, window, num_splits, err);
 }
 
 // Requests with more than 16 rows.  `max_tiles` bounds the number of 64-token tiles over all
@@ -620,10 +626,10 @@ IE_API int ie_attention_prefill(const void* q, const void* k_cache, const void* 
         configured = true;
     }
     dim3 grid(max_tiles, nh);
-    attention_prefill_kernel<<<grid, WARPS * 32, PREFILL_SMEM, (cudaStream_t)stream>>>(
-        (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, tables, table_width, cu_q, ctx_lens,
-        (bf16*)out, num_seqs, nh, nkv, page_shift, total_pages, scale * 1.4426950408889634f, window, err);
-    return IE_LAUNCH_CHECK();
+    return ie_launch(attention_prefill_kernel, grid, dim3(WARPS * 32), PREFILL_SMEM, (cudaStream_t)stream,
+                     (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, tables, table_width, cu_q,
+                     ctx_lens, (bf16*)out, num_seqs, nh, nkv, page_shift, total_pages,
+                     scale * 1.4426950408889634f, window, err);
 }
 
 // -------------------------------------------------------------------------------------------------

@@ -48,3 +48,35 @@ __device__ __forceinline__ float warp_max(float v) {
 }
 
 #define IE_LAUNCH_CHECK() ((int)cudaGetLastError())
+
+// Programmatic dependent launch.  A kernel launched with `ie_launch` may be scheduled while
+// the kernel before it in the stream is still running (once all of that kernel's blocks have
+// called ie_pdl_trigger or exited), so its launch latency and whatever it does before
+// ie_pdl_wait -- index arithmetic, prefetching weights, which no earlier kernel writes --
+// overlap the predecessor.  ie_pdl_wait returns when the predecessor grid has completed and its
+// writes are visible; every kernel calls it before its first read of activations and before any
+// global write, and every thread calls it, so "my predecessor is done" holds transitively.
+__device__ __forceinline__ void ie_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void ie_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::); }
+
+// 1 (default): launch with the programmatic-serialization attribute; 0: plain launches.
+inline int& ie_pdl_enabled() {
+    static int enabled = 1;
+    return enabled;
+}
+
+template <typename... KArgs, typename... Args>
+inline int ie_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                     Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ie_pdl_enabled() ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}

@@ -9,6 +9,8 @@
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                  float* __restrict__ out, int hidden, int vocab, int* err) {
+    ie_pdl_trigger();
+    ie_pdl_wait();
     int row = blockIdx.x;
     int id = ids[row];
     bool ok = id >= 0 && id < vocab;
@@ -24,10 +26,10 @@ IE_API int ie_embedding(const void* table, int table_dtype, const int* ids, floa
     int threads = hidden >= 1024 ? 256 : 128;
     cudaStream_t s = (cudaStream_t)stream;
     if (table_dtype == IE_BF16)
-        embedding_kernel<<<num_tokens, threads, 0, s>>>((const __nv_bfloat16*)table, ids, out, hidden, vocab, err);
-    else
-        embedding_kernel<<<num_tokens, threads, 0, s>>>((const float*)table, ids, out, hidden, vocab, err);
-    return IE_LAUNCH_CHECK();
+        return ie_launch(embedding_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(threads), 0, s,
+                         (const __nv_bfloat16*)table, ids, out, hidden, vocab, err);
+    return ie_launch(embedding_kernel<float>, dim3(num_tokens), dim3(threads), 0, s, (const float*)table, ids,
+                     out, hidden, vocab, err);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -43,6 +45,8 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ 
                                OutT* __restrict__ out, const int* __restrict__ rows, int hidden) {
     __shared__ float partial[THREADS / 32];
     __shared__ float inv_rms;
+    ie_pdl_trigger();
+    ie_pdl_wait();
     int r = blockIdx.x;
     size_t src = (size_t)(rows ? rows[r] : r) * hidden;
     float* hrow = h + src;
@@ -92,19 +96,24 @@ rmsnorm_vec_kernel(float* __restrict__ h, const float* __restrict__ delta, int n
                    OutT* __restrict__ out, const int* __restrict__ rows, int hidden) {
     __shared__ float partial[THREADS / 32];
     __shared__ float inv_rms;
+    ie_pdl_trigger();
     int r = blockIdx.x;
-    size_t src = (size_t)(rows ? rows[r] : r) * hidden;
-    bool write_back = (rows == nullptr) && (delta != nullptr);
     float4 x[VPT], wt[VPT];
     float ss = 0.f;
 #pragma unroll
+    for (int v = 0; v < VPT; ++v) {  // the norm's weights: nobody writes them, no need to wait
+        int i = (v * THREADS + threadIdx.x) * 4;
+        wt[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < hidden) wt[v] = *reinterpret_cast<const float4*>(weight + i);
+    }
+    ie_pdl_wait();
+    size_t src = (size_t)(rows ? rows[r] : r) * hidden;
+    bool write_back = (rows == nullptr) && (delta != nullptr);
+#pragma unroll
     for (int v = 0; v < VPT; ++v) {
         int i = (v * THREADS + threadIdx.x) * 4;
-        x[v] = wt[v] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (i < hidden) {
-            x[v] = *reinterpret_cast<const float4*>(h + src + i);
-            wt[v] = *reinterpret_cast<const float4*>(weight + i);  // with the row: one trip to memory
-        }
+        x[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < hidden) x[v] = *reinterpret_cast<const float4*>(h + src + i);
     }
     if (delta) {
         for (int p = 0; p < num_partials; ++p) {
@@ -154,14 +163,12 @@ static int launch_rmsnorm(float* h, const float* delta, int num_partials, size_t
                           const float* weight, float eps, OutT* out, const int* rows, int num_rows,
                           int hidden, cudaStream_t s) {
     if (hidden % 4 == 0 && hidden <= 128 * 4 * 2)
-        rmsnorm_vec_kernel<OutT, 128, 2><<<num_rows, 128, 0, s>>>(h, delta, num_partials, partial_stride, weight, eps, out, rows, hidden);
-    else if (hidden % 4 == 0 && hidden <= 256 * 4 * 2)
-        rmsnorm_vec_kernel<OutT, 256, 2><<<num_rows, 256, 0, s>>>(h, delta, num_partials, partial_stride, weight, eps, out, rows, hidden);
-    else if (hidden % 4 == 0 && hidden <= 512 * 4 * 4)
-        rmsnorm_vec_kernel<OutT, 512, 4><<<num_rows, 512, 0, s>>>(h, delta, num_partials, partial_stride, weight, eps, out, rows, hidden);
-    else
-        rmsnorm_kernel<OutT, 256><<<num_rows, 256, 0, s>>>(h, delta, num_partials, partial_stride, weight, eps, out, rows, hidden);
-    return IE_LAUNCH_CHECK();
+        return ie_launch(rmsnorm_vec_kernel<OutT, 128, 2>, dim3(num_rows), dim3(128), 0, s, h, delta, num_partials, partial_stride, weight, eps, out, rows, hidden);
+    if (hidden % 4 == 0 && hidden <= 256 * 4 * 2)
+        return ie_launch(rmsnorm_vec_kernel<OutT, 256, 2>, dim3(num_rows), dim3(256), 0, s, h, delta, num_partials, partial_stride, weight, eps, out, rows, hidden);
+    if (hidden % 4 == 0 && hidden <= 512 * 4 * 4)
+        return ie_launch(rmsnorm_vec_kernel<OutT, 512, 4>, dim3(num_rows), dim3(512), 0, s, h, delta, num_partials, partial_stride, weight, eps, out, rows, hidden);
+    return ie_launch(rmsnorm_kernel<OutT, 256>, dim3(num_rows), dim3(256), 0, s, h, delta, num_partials, partial_stride, weight, eps, out, rows, hidden);
 }
 
 // `delta` may be the sum of `num_partials` arrays `partial_stride` floats apart (the parts of
@@ -192,6 +199,8 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const int* _
                                      T* __restrict__ q_out, T* __restrict__ k_cache,
                                      T* __restrict__ v_cache, const int* __restrict__ slot_mapping,
                                      int nh, int nkv, int hd, int page_size, int total_pages, int* err) {
+    ie_pdl_trigger();
+    ie_pdl_wait();
     int n = blockIdx.x;
     int heads = nh + 2 * nkv;
     int half = rotary_dim / 2;
@@ -241,6 +250,8 @@ rope_kv_write_vec_kernel(const float* __restrict__ qkv, int num_partials, size_t
                          int table_rows, T* __restrict__ q_out, T* __restrict__ k_cache,
                          T* __restrict__ v_cache, const int* __restrict__ slot_mapping,
                          int nh, int nkv, int hd, int page_size, int total_pages, int* err) {
+    ie_pdl_trigger();
+    ie_pdl_wait();
     int n = blockIdx.x;
     int half = hd / 2, per_head = hd / 8;
     int heads = slot_mapping ? nh + 2 * nkv : nh;
@@ -298,16 +309,16 @@ static int launch_rope(const float* qkv, int num_partials, size_t partial_stride
     if (hd % 8 == 0 && (!rotates || rotary_dim == hd)) {
         int heads = slot_mapping ? nh + 2 * nkv : nh;
         dim3 grid(num_tokens, (heads * (hd / 8) + 127) / 128);
-        rope_kv_write_vec_kernel<<<grid, 128, 0, s>>>(qkv, num_partials, partial_stride, positions,
-            rotates ? table : nullptr, table_rows, q_out, k_cache, v_cache, slot_mapping, nh, nkv, hd,
-            page_size, total_pages, err);
+        return ie_launch(rope_kv_write_vec_kernel<T>, grid, dim3(128), 0, s, qkv, num_partials, partial_stride,
+                         positions, rotates ? table : (const float*)nullptr, table_rows, q_out, k_cache, v_cache,
+                         slot_mapping, nh, nkv, hd, page_size, total_pages, err);
     } else {
         if (num_partials != 1) return (int)cudaErrorInvalidValue;
         int threads = (nh + 2 * nkv) * hd >= 1024 ? 256 : 128;
-        rope_kv_write_kernel<<<num_tokens, threads, 0, s>>>(qkv, positions, table, rotary_dim, table_rows,
-            q_out, k_cache, v_cache, slot_mapping, nh, nkv, hd, page_size, total_pages, err);
+        return ie_launch(rope_kv_write_kernel<T>, dim3(num_tokens), dim3(threads), 0, s, qkv, positions, table,
+                         rotary_dim, table_rows, q_out, k_cache, v_cache, slot_mapping, nh, nkv, hd, page_size,
+                         total_pages, err);
     }
-    return IE_LAUNCH_CHECK();
 }
 
 IE_API int ie_rope_kv_write(const float* qkv, int num_partials, long long partial_stride,
@@ -334,6 +345,8 @@ IE_API int ie_rope_kv_write(const float* qkv, int num_partials, long long partia
 template <typename T, typename InT>
 __global__ void silu_mul_kernel(const InT* __restrict__ gate_up, int num_partials, size_t partial_stride,
                                 T* __restrict__ out, int inter, size_t total) {
+    ie_pdl_trigger();
+    ie_pdl_wait();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; idx < total; idx += stride) {
@@ -353,6 +366,8 @@ __global__ void silu_mul_kernel(const InT* __restrict__ gate_up, int num_partial
 __global__ void __launch_bounds__(256)
 silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
                        int inter, size_t total_vec) {
+    ie_pdl_trigger();
+    ie_pdl_wait();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total_vec) return;
     int per_row = inter / 8;
@@ -387,15 +402,15 @@ IE_API int ie_silu_mul(const void* gate_up, int in_dtype, int num_partials, long
     size_t ps = (size_t)partial_stride;
     if (dtype == IE_BF16 && in_dtype == IE_BF16 && num_partials == 1 && inter % 8 == 0) {
         size_t total_vec = total / 8;
-        silu_mul_bf16x8_kernel<<<(unsigned)((total_vec + 255) / 256), 256, 0, s>>>(
-            (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total_vec);
-        return IE_LAUNCH_CHECK();
+        return ie_launch(silu_mul_bf16x8_kernel, dim3((unsigned)((total_vec + 255) / 256)), dim3(256), 0, s,
+                         (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total_vec);
     }
     if (dtype == IE_BF16 && in_dtype == IE_BF16)
-        silu_mul_kernel<<<blocks, threads, 0, s>>>((const __nv_bfloat16*)gate_up, num_partials, ps, (__nv_bfloat16*)out, inter, total);
-    else if (dtype == IE_BF16)
-        silu_mul_kernel<<<blocks, threads, 0, s>>>((const float*)gate_up, num_partials, ps, (__nv_bfloat16*)out, inter, total);
-    else
-        silu_mul_kernel<<<blocks, threads, 0, s>>>((const float*)gate_up, num_partials, ps, (float*)out, inter, total);
-    return IE_LAUNCH_CHECK();
+        return ie_launch(silu_mul_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(blocks), dim3(threads), 0, s,
+                         (const __nv_bfloat16*)gate_up, num_partials, ps, (__nv_bfloat16*)out, inter, total);
+    if (dtype == IE_BF16)
+        return ie_launch(silu_mul_kernel<__nv_bfloat16, float>, dim3(blocks), dim3(threads), 0, s,
+                         (const float*)gate_up, num_partials, ps, (__nv_bfloat16*)out, inter, total);
+    return ie_launch(silu_mul_kernel<float, float>, dim3(blocks), dim3(threads), 0, s, (const float*)gate_up,
+                     num_partials, ps, (float*)out, inter, total);
 }

@@ -16,6 +16,8 @@ gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, float*
                 int M, int N, int K) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
+    ie_pdl_trigger();
+    ie_pdl_wait();
     int tid = threadIdx.x;
     int tx = tid % 16, ty = tid / 16;          // 16 x 16 threads, each a 4 x 4 patch
     int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;

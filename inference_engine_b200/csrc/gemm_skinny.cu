@@ -74,7 +74,11 @@ gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, OutT*
     int fblock = blockIdx.x * WARPS + warp;
     int f0 = fblock * FB;
     int split = blockIdx.y;
-    if (f0 >= N) return;  // whole warps leave; there is no block-wide barrier below
+    if (f0 >= N) {  // whole warps leave; there is no block-wide barrier below
+        ie_pdl_trigger();
+        ie_pdl_wait();
+        return;
+    }
     bf16* ring = reinterpret_cast<bf16*>(smem_raw) + (size_t)warp * STAGES * STAGE_ELEMS;
     int k_begin = split * k_per_split;
     int k_end = min(K, k_begin + k_per_split);
@@ -84,11 +88,15 @@ gemm_skinny_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, OutT*
 #pragma unroll
     for (int t = 0; t < NT; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
 
+    // The weights do not depend on the kernel before this one: their first stages are on
+    // their way before we wait for it (its output is our X).
+    ie_pdl_trigger();
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
         if (s < n_tiles) load_stage(ring + s * STAGE_ELEMS, W, f0, k_begin + s * BK, N, K, k_end, lane);
         cp_async_commit();
     }
+    ie_pdl_wait();
     int tok = lane >> 2;  // the token (column) whose X values this lane feeds
     for (int t = 0; t < n_tiles; ++t) {
         int pre = t + STAGES - 1;
@@ -152,10 +160,12 @@ int launch(const bf16* X, const bf16* W, OutT* out, int M, int N, int K, int k_p
     }
     int fblocks = (N + FB - 1) / FB;
     dim3 grid((fblocks + WARPS - 1) / WARPS, splits);
-    gemm_skinny_kernel<NT, OutT><<<grid, WARPS * 32, SMEM_BYTES, s>>>(X, W, out, M, N, K, k_per_split, splits);
-    return IE_LAUNCH_CHECK();
+    return ie_launch(gemm_skinny_kernel<NT, OutT>, grid, dim3(WARPS * 32), SMEM_BYTES, s, X, W, out, M, N, K,
+                     k_per_split, splits);
 }
 }  // namespace
+
+IE_API void ie_set_pdl(int enabled) { ie_pdl_enabled() = enabled ? 1 : 0; }
 
 // `out`: [splits, M, N].  With splits > 1 it must be 32-bit and holds partial sums over slices
 // of `k_per_split` (a multiple of 16) of the inner dimension; with splits == 1 it is the

@@ -208,6 +208,8 @@ __global__ void __launch_bounds__(256)
 argmax_chunk_kernel(const float* __restrict__ logits, int vocab, int chunks, float* __restrict__ part_v,
                     int* __restrict__ part_i) {
     __shared__ Best scratch[8];
+    ie_pdl_trigger();
+    ie_pdl_wait();
     int r = blockIdx.x, c = blockIdx.y;
     int len = (vocab + chunks - 1) / chunks;
     int lo = c * len, hi = min(vocab, lo + len);
@@ -237,6 +239,8 @@ argmax_chunk_kernel(const float* __restrict__ logits, int vocab, int chunks, flo
 
 __global__ void argmax_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i,
                                     int chunks, int* __restrict__ out_tokens) {
+    ie_pdl_trigger();
+    ie_pdl_wait();
     int r = blockIdx.x;
     Best b{-INFINITY, 0x7fffffff};
     for (int c = threadIdx.x; c < chunks; c += 32)
@@ -258,11 +262,11 @@ IE_API int ie_argmax(const float* logits, int num_rows, int vocab, int chunks, v
     cudaStream_t s = (cudaStream_t)stream;
     float* part_v = (float*)scratch;
     int* part_i = (int*)scratch + (size_t)num_rows * chunks;
-    argmax_chunk_kernel<<<dim3(num_rows, chunks), 256, 0, s>>>(logits, vocab, chunks, part_v, part_i);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return (int)e;
-    argmax_final_kernel<<<num_rows, 32, 0, s>>>(part_v, part_i, chunks, out_tokens);
-    return IE_LAUNCH_CHECK();
+    int rc = ie_launch(argmax_chunk_kernel, dim3(num_rows, chunks), dim3(256), 0, s, logits, vocab, chunks,
+                       part_v, part_i);
+    if (rc != 0) return rc;
+    return ie_launch(argmax_final_kernel, dim3(num_rows), dim3(32), 0, s, (const float*)part_v,
+                     (const int*)part_i, chunks, out_tokens);
 }
 
 // All per-row arrays but `logits` and `out_tokens` may be null (greedy, nothing cut off).

@@ -12,6 +12,7 @@ the embedding gather and sampling are the kernels under ``csrc/``.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_void_p
 
 from .build import ATTENTION_HEAD_DIMS, build_attention, build_core
@@ -54,6 +55,9 @@ class CudaOps:
         except OSError as exc:
             raise KernelError(f"the kernel library {self.lib_path} could not be loaded: {exc}") from exc
         self._declare()
+        # programmatic dependent launch between the engine's own kernels (IE_B200_PDL=0: off)
+        self.pdl = os.environ.get("IE_B200_PDL", "1") != "0"
+        self.lib.ie_set_pdl(1 if self.pdl else 0)
         self.err = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._err_ptr = self.err.data_ptr()
         self._attn_libs: dict[int, object] = {}
@@ -202,6 +206,7 @@ class CudaOps:
         lib = self._attn_libs.get(hd)
         if lib is None:
             lib = ctypes.CDLL(str(build_attention(hd)))
+            lib.ie_set_pdl(1 if self.pdl else 0)
             P, I, F = c_void_p, c_int, c_float
             lib.ie_attention_decode.argtypes = [P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, F, I, I, P, P]
             lib.ie_attention_prefill.argtypes = [P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P, P]

@@ -65,6 +65,7 @@ class CudaOps:
         self.force_skinny = False  # tests run every few-row product through the streaming kernel
         self._tickets = None
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.skinny_max_blocks = int(os.environ.get("IE_B200_SKINNY_MAX_BLOCKS", self.sm_count))
         self._device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self._raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
         self.launches = 0  # launches of this library's kernels (library matrix products not counted)
@@ -168,7 +169,7 @@ class CudaOps:
         # The weight-streaming kernel pays where the library leaves SMs idle: few output
         # features (fewer 16-feature blocks than SMs) and a long inner dimension to split.
         skinny = (0 < m <= self.SKINNY_ROWS and k % 8 == 0 and x.is_contiguous() and w.is_contiguous()
-                  and (self.force_skinny or (allow_split and out is None and -(-n // 16) <= self.sm_count)))
+                  and (self.force_skinny or (allow_split and out is None and -(-n // 16) <= self.skinny_max_blocks)))
         if skinny:
             per, splits = self.skinny_split(n, k) if allow_split and out is None else (-(-k // 16) * 16, 1)
             if splits > 1:

@@ -37,6 +37,32 @@ class DecodeGraphs:
         entry = self._graphs.get(self.bucket_for(num_seqs))
         return entry[2] if entry else 0
 
+    def prepare(self, req_ids: list, positions: list[int]):
+        """Pack the next decode step ahead of time (while the device still works on this one)
+        if a captured launch sequence for its batch size exists; None otherwise."""
+        bucket = self.bucket_for(len(req_ids))
+        if bucket is None or bucket not in self._graphs or self._version != self.runner.ws.version:
+            return None
+        cache = self.runner.cache
+        if any(len(cache.table(g, r)) > self.table_width for r in req_ids
+               for g in range(len(cache.paged_groups))):
+            return None
+        handle = self.runner.prepare_decode(req_ids, positions, bucket, self.table_width)
+        if self._version != self.runner.ws.version:
+            return None
+        return (bucket, handle)
+
+    def run_prepared(self, prepared, tokens: list[int]):
+        """Fill the sampled tokens into a step packed by :meth:`prepare` and replay it."""
+        bucket, handle = prepared
+        if bucket not in self._graphs or self._version != self.runner.ws.version:
+            return None
+        self.runner.commit_prepared(handle, tokens)
+        graph, logits, _ = self._graphs[bucket]
+        graph.replay()
+        self.replays += 1
+        return logits[: len(tokens)]
+
     def can_run(self, entries) -> bool:
         if not entries or any(len(e.tokens) != 1 for e in entries):
             return False

@@ -73,6 +73,7 @@ class LLMEngine:
         self._seq_ids = itertools.count()
         self._requests: dict[str, Sequence] = {}
         self._rng = random.Random()
+        self._prepared = None
         self.step_log: deque[dict] = deque(maxlen=240)
         self.steps_total = self.generated_total = self.finished_total = 0
         self.prompt_tokens_total = 0
@@ -151,37 +152,48 @@ class LLMEngine:
     def step(self) -> list[RequestOutput]:
         started = time.perf_counter()
         preempted_before = self.scheduler.num_preemptions
-        batch = self.scheduler.schedule()
-        if batch is None:
-            if self.scheduler.waiting and not self.scheduler.running:
-                raise RuntimeError("scheduler made no progress with an idle engine")
-            return []
-        entries, sampled = [], []
-        decode_tokens = 0
-        for seq, n in zip(batch.seqs, batch.num_tokens):
-            start = seq.num_computed
-            n_prompt = len(seq.prompt_ids)
-            if n == 1 and start >= n_prompt:
-                tokens = [seq.output_ids[start - n_prompt]]
-                decode_tokens += 1
-            elif start + n <= n_prompt:
-                tokens = seq.prompt_ids[start:start + n]
-            else:
-                tokens = (seq.prompt_ids + seq.output_ids)[start:start + n]
-            if not seq.output_ids and start == 0:
-                self.prompt_tokens_total += n_prompt
-            last = start + n == seq.length
-            entries.append(StepEntry(seq.seq_id, tokens, start, [n - 1] if last else []))
-            if last:
-                sampled.append(seq)
-        used_graph = False
-        if self.graphs is not None and len(sampled) == len(entries) and self.graphs.can_run(entries):
-            logits = self.graphs.run(entries)
-            used_graph = True
+        logits = None
+        prepared, self._prepared = self._prepared, None
+        if prepared is not None and self._prepared_still_valid(prepared):
+            # Steady decoding: this step was packed while the device worked on the last one.
+            seqs = prepared[0]
+            logits = self.graphs.run_prepared(prepared[1], [s.output_ids[-1] for s in seqs])
+        if logits is not None:
+            sampled, counts, used_graph = seqs, [1] * len(seqs), True
+            decode_tokens = len(seqs)
         else:
-            logits = self.runner.step(entries)
+            batch = self.scheduler.schedule()
+            if batch is None:
+                if self.scheduler.waiting and not self.scheduler.running:
+                    raise RuntimeError("scheduler made no progress with an idle engine")
+                return []
+            seqs, counts = batch.seqs, batch.num_tokens
+            entries, sampled = [], []
+            decode_tokens = 0
+            for seq, n in zip(seqs, counts):
+                start = seq.num_computed
+                n_prompt = len(seq.prompt_ids)
+                if n == 1 and start >= n_prompt:
+                    tokens = [seq.output_ids[start - n_prompt]]
+                    decode_tokens += 1
+                elif start + n <= n_prompt:
+                    tokens = seq.prompt_ids[start:start + n]
+                else:
+                    tokens = (seq.prompt_ids + seq.output_ids)[start:start + n]
+                if not seq.output_ids and start == 0:
+                    self.prompt_tokens_total += n_prompt
+                last = start + n == seq.length
+                entries.append(StepEntry(seq.seq_id, tokens, start, [n - 1] if last else []))
+                if last:
+                    sampled.append(seq)
+            used_graph = False
+            if self.graphs is not None and len(sampled) == len(entries) and self.graphs.can_run(entries):
+                logits = self.graphs.run(entries)
+                used_graph = True
+            else:
+                logits = self.runner.step(entries)
 
-        for seq, n in zip(batch.seqs, batch.num_tokens):
+        for seq, n in zip(seqs, counts):
             seq.num_computed += n
             self.cache.release_behind_window(seq.seq_id, seq.num_computed)
 
@@ -189,9 +201,12 @@ class LLMEngine:
         if sampled:
             params = [s.params for s in sampled]
             needs_history = any(p.repetition_penalty != 1.0 for p in params)
-            tokens, logprobs = self.sampler.sample(
+            pending = self.sampler.launch(
                 logits, params, [s.seed for s in sampled], [len(s.output_ids) for s in sampled],
                 [s.all_ids for s in sampled] if needs_history else None)
+            if used_graph and len(sampled) == len(seqs):
+                self._prepared = self._prepare_next(seqs)  # while the device is busy
+            tokens, logprobs = self.sampler.collect(pending)
             for row, (seq, token) in enumerate(zip(sampled, tokens)):
                 seq.output_ids.append(token)
                 text, finished, reason = seq.processor.process(token)
@@ -214,13 +229,38 @@ class LLMEngine:
         self.step_log.append({
             "step": self.steps_total,
             "ms": round((time.perf_counter() - started) * 1000, 3),
-            "seqs": len(entries),
-            "prefill_tokens": batch.total_tokens - decode_tokens,
+            "seqs": len(seqs),
+            "prefill_tokens": sum(counts) - decode_tokens,
             "decode_tokens": decode_tokens,
             "graph": used_graph,
             "preempted": self.scheduler.num_preemptions - preempted_before,
         })
         return outputs
+
+    # While the device runs a decode step the host already knows what the next one looks like
+    # if nothing else happens (same requests, one position further, tokens = what is being
+    # sampled now): it packs that step's index data ahead of time.  If a request finishes, is
+    # aborted or preempted, or a new one arrives, the packed step is dropped and the scheduler
+    # decides as usual.
+
+    def _prepare_next(self, seqs: list[Sequence]):
+        if self.graphs is None or self.scheduler.waiting or self.scheduler.running != seqs:
+            return None
+        positions = []
+        for seq in seqs:
+            pos = seq.num_computed  # where the token sampled now will go
+            if len(seq.output_ids) + 1 >= seq.params.max_tokens:
+                return None  # it ends with this token
+            if not self.cache.try_grow(seq.seq_id, pos, pos + 1):
+                return None  # pages ran out: the scheduler has to preempt
+            positions.append(pos)
+        handle = self.graphs.prepare([s.seq_id for s in seqs], positions)
+        return (list(seqs), handle) if handle is not None else None
+
+    def _prepared_still_valid(self, prepared) -> bool:
+        seqs = prepared[0]
+        return (not self.scheduler.waiting and self.scheduler.running == seqs
+                and all(s.num_computed == s.length - 1 for s in seqs))
 
     def generate(self, prompts: dict[str, list[int]], params: SamplingParams) -> dict[str, list[int]]:
         """Run requests to completion; returns the generated token ids per request."""

@@ -190,8 +190,25 @@ class ModelRunner:
         )
         return ctx, dview(v_rows)
 
+    def prepare_decode(self, req_ids: list, positions: list[int], pad_to_seqs: int, table_width: int):
+        """Pack a decode step whose token ids are not known yet (they are being sampled on the
+        device right now) into a pinned buffer, without copying it.  Returns a handle for
+        :meth:`commit_prepared`, which fills in the tokens and starts the copy.  Every entry
+        wants its logits."""
+        entries = [StepEntry(r, [0], p, [0]) for r, p in zip(req_ids, positions)]
+        return self._build_decode_context(entries, pad_to_seqs, table_width, views=False, defer=True)
+
+    def commit_prepared(self, handle, tokens: list[int]) -> None:
+        turn, off, tok_at, count = handle
+        self._staging_host[turn][tok_at: tok_at + count] = self._torch.tensor(tokens, dtype=self._torch.int32)
+        self._staging_dev[:off].copy_(self._staging_host[turn][:off], non_blocking=True)
+        if self._staging_events[turn] is not None:
+            self._staging_events[turn].record()
+            self._staging_used[turn] = True
+        self.last_h2d_bytes = off * 4
+
     def _build_decode_context(self, entries: list[StepEntry], pad_to_seqs: int | None,
-                              table_width: int | None, views: bool = True):
+                              table_width: int | None, views: bool = True, defer: bool = False):
         """The same packing for a step of single tokens, without a Python loop over what the
         entries hold: block-table rows are gathered from the cache manager's dense copy."""
         import numpy as np
@@ -255,6 +272,8 @@ class ModelRunner:
                 block[real_b:, 0] = st.scratch_page
                 block[real_b:, 1:] = -1
                 buf[v_slots[g][0] + real_b: v_slots[g][0] + b] = st.scratch_page * ps
+        if defer:  # the tokens come later: see commit_prepared
+            return (turn, off, v_tok[0], real_b)
         self._staging_dev[:off].copy_(self._staging_host[turn][:off], non_blocking=True)
         if self._staging_events[turn] is not None:
             self._staging_events[turn].record()

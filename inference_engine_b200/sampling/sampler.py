@@ -32,6 +32,10 @@ class Sampler:
         ``seeds[r]``/``draws[r]``: its request's seed and the number of tokens it has already
         produced; ``histories[r]``: the ids the repetition penalty looks at.
         Returns ``(tokens, logprobs)``: a list of ints and a list of floats or None."""
+        return self.collect(self.launch(logits, params, seeds, draws, histories))
+
+    def launch(self, logits, params, seeds, draws, histories=None):
+        """Start the sampling kernel; :meth:`collect` waits for it and fetches the tokens."""
         torch = self.torch
         rows = logits.shape[0]
         out = self._out(rows)
@@ -57,6 +61,10 @@ class Sampler:
                 kwargs["penalty"] = f32([p.repetition_penalty for p in params])
                 kwargs["seen_bits"] = self._seen_bits(params, histories)
             self.ops.sample(logits, out, logprob=logprob, **kwargs)
+        return out, logprob
+
+    def collect(self, pending):
+        out, logprob = pending
         tokens = out.tolist()  # the step's one wait for the device
         return tokens, (logprob.tolist() if logprob is not None else None)
 

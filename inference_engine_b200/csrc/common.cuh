@@ -20,6 +20,7 @@ enum IeError {
     IE_ERR_PAGE = 2,       // a page or slot outside the cache
     IE_ERR_POSITION = 3,   // a position outside the rotary table
     IE_ERR_TABLE = 4,      // a block-table entry that was given back (-1) was read
+    IE_ERR_TIMEOUT = 5,    // a bounded wait inside a kernel ran out (value, where = block x, y)
 };
 
 // Every launch gets `err`, four ints in device memory owned by the caller:

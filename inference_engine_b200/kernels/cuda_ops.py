@@ -22,6 +22,7 @@ _ERRORS = {
     2: "a page or slot outside the cache",
     3: "a position outside the rotary table",
     4: "a block-table entry that was already given back",
+    5: "a bounded wait inside a kernel ran out (a copy never arrived)",
 }
 
 
@@ -66,6 +67,13 @@ class CudaOps:
         self._tickets = None
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.skinny_max_blocks = int(os.environ.get("IE_B200_SKINNY_MAX_BLOCKS", self.sm_count))
+        # which kernel takes few-row bfloat16 products: "tma" (TMA-fed ring), "cp" (cp.async
+        # rings per warp), "auto" (cp for few output features, the vendor library otherwise)
+        self.few_row_gemm = os.environ.get("IE_B200_FEW_ROW_GEMM", "tma")
+        # ... for matrices with fewer 128-feature tiles than half the SMs (they need their inner
+        # dimension cut to occupy the GPU, which the vendor library does not do); measured on
+        # the 1B shape: wider matrices stream faster through the library's kernel
+        self.tma_max_tiles = int(os.environ.get("IE_B200_TMA_MAX_TILES", self.sm_count // 2))
         self._device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self._raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
         self.launches = 0  # launches of this library's kernels (library matrix products not counted)
@@ -80,6 +88,7 @@ class CudaOps:
             "ie_argmax": [P, I, I, I, P, P, P],
             "ie_gemm_f32": [P, P, P, I, I, I, P],
             "ie_gemm_skinny_bf16": [P, P, P, I, I, I, I, I, I, P],
+            "ie_gemm_tma_bf16": [P, P, P, I, I, I, I, I, I, P, P],
             "ie_paged_attention_generic": [P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, F, I, P, P],
             "ie_sample": [P, I, I, P, P, P, P, P, P, I, P, P, P, P, P],
         }
@@ -148,6 +157,16 @@ class CudaOps:
         per = min(per, -(-k // 16) * 16)
         return per, -(-k // per)
 
+    def tma_split(self, n_out: int, k: int) -> tuple[int, int]:
+        """(64-wide k blocks per split, splits) for the TMA-fed few-row product: one block of
+        128 features per SM if there are enough features, else the inner dimension is cut so
+        that about every SM has a block; a block takes at most 32 k blocks."""
+        tiles = -(-n_out // 128)
+        total = -(-k // 64)
+        splits = max(1, min(total, self.sm_count // tiles))
+        per = min(-(-total // splits), 32)
+        return per, -(-total // per)
+
     def linear(self, x, w, out=None, *, ws=None, tag="linear", out_dtype=None, allow_split=False):
         """``x[M, K] @ w[N, K]^T``.  With ``out`` given the product is written there; otherwise a
         buffer named ``tag`` is taken from ``ws``.  With ``allow_split`` the result may come back
@@ -168,6 +187,18 @@ class CudaOps:
             return out
         # The weight-streaming kernel pays where the library leaves SMs idle: few output
         # features (fewer 16-feature blocks than SMs) and a long inner dimension to split.
+        few_rows = 0 < m <= self.SKINNY_ROWS and k % 8 == 0 and x.is_contiguous() and w.is_contiguous()
+        if (few_rows and self.few_row_gemm == "tma" and not self.force_skinny
+                and -(-n // 128) <= self.tma_max_tiles):
+            kbps, splits = self.tma_split(n, k) if allow_split and out is None else (-(-k // 64), 1)
+            if kbps <= 32:
+                if splits > 1:
+                    out = ws.buffer(tag, splits * m, n, torch.float32).view(splits, m, n)
+                elif out is None:
+                    out = ws.buffer(tag, m, n, out_dtype)
+                self._check(self._gemm_tma_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), _dtype_code(out),
+                                                m, n, k, kbps, splits, self._err_ptr, self._stream()), "gemm_tma")
+                return out
         skinny = (0 < m <= self.SKINNY_ROWS and k % 8 == 0 and x.is_contiguous() and w.is_contiguous()
                   and (self.force_skinny or (allow_split and out is None and -(-n // 16) <= self.skinny_max_blocks)))
         if skinny:

@@ -174,6 +174,34 @@ def test_skinny_gemm_streams_the_weights_for_few_rows(ops, m, n, k):
         ops.force_skinny = False
 
 
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("n,k", [(3072, 2048), (2048, 8192), (331, 80), (192, 64), (512, 96), (1000, 1032), (16384, 2048)])
+def test_tma_fed_gemm_for_few_rows(ops, m, n, k):
+    """The TMA-fed weight-streaming product: any N (tiles of 128 with a ragged edge), any K
+    that is a multiple of 8 (blocks of 64 with a ragged edge), with and without k splits."""
+    from inference_engine_b200.engine.workspace import Workspace
+
+    x = torch.randn(m, k, device="cuda").bfloat16()
+    w = (torch.randn(n, k, device="cuda") * 0.05).bfloat16()
+    want = x.double() @ w.double().t()
+    ws = Workspace("cuda")
+    saved, ops.few_row_gemm = ops.few_row_gemm, "tma"
+    try:
+        split = ops.linear(x, w, ws=ws, tag="t", out_dtype=torch.float32, allow_split=True)
+        per, splits = ops.tma_split(n, k)
+        assert split.shape == ((splits, m, n) if splits > 1 else (m, n))
+        total = split.sum(0) if split.dim() == 3 else split
+        torch.testing.assert_close(total.double(), want, atol=2e-4 * k ** 0.5, rtol=1e-5)
+        for out_dtype in DTYPES:
+            out = torch.empty(m, n, device="cuda", dtype=out_dtype)
+            assert ops.linear(x, w, out) is out
+            tol = dict(atol=2e-4 * k ** 0.5, rtol=1e-5) if out_dtype == torch.float32 else dict(atol=0.01 * k ** 0.5, rtol=1e-2)
+            torch.testing.assert_close(out.double(), want, **tol)
+        ops.check_errors()
+    finally:
+        ops.few_row_gemm = saved
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkv,hd,rd,ps", [(4, 2, 16, 16, 16), (3, 1, 32, 32, 8), (5, 5, 48, 48, 4),
                                              (32, 8, 64, 64, 16), (6, 2, 80, 32, 16), (2, 1, 128, 0, 32)])

@@ -15,7 +15,8 @@ Categories and what each must provide
                   applied to queries and keys, ``apply_to_embedding`` for additive ones.
 ``mixer``         ``cache_request()`` (what it keeps per request: pages of keys and values,
                   a fixed-size state, or nothing) and
-                  ``forward(x, ctx, binding) -> delta`` (32-bit ``[N, hidden]``).
+                  ``forward(x, ctx, binding) -> delta`` (32-bit ``[N, hidden]``, or
+                  ``[S, N, hidden]`` partial sums that the next norm adds in order).
 ``feed_forward``  ``forward(x, ctx) -> delta`` (32-bit ``[N, hidden]``).
 ``block``         the arrangement: ``forward(h, delta, ctx, binding) -> delta`` where ``h``
                   is the residual stream and ``delta`` the not-yet-added output of the

@@ -21,6 +21,12 @@ def _tol(dtype):
     return dict(atol=3e-5, rtol=1e-4) if dtype == "float32" else dict(atol=4e-2, rtol=4e-2)
 
 
+def _total(t):
+    """A part may hand back its output as partial sums ``[S, N, hidden]`` (the pieces of a
+    matrix product that was split along its inner dimension); the next norm adds them."""
+    return t.float().sum(0) if t.dim() == 3 else t.float()
+
+
 class _Ctx:
     """The least a part needs of a step: kernels, buffers and index vectors."""
 
@@ -116,7 +122,7 @@ def test_attention_mixer_over_the_paged_cache(cfg, dtype):
             cache.grow("a", pos, pos + n)
             ctx, _ = runner.build_context([StepEntry("a", [0] * n, pos, [])])
             out = mixer.forward(x[pos:pos + n].cuda().to(env.torch_dtype), ctx, CacheBinding(0, 0))
-            outs.append(out.float().cpu().clone())
+            outs.append(_total(out).cpu().clone())
             pos += n
         torch.testing.assert_close(torch.cat(outs), want, **_tol(dtype))
         cache.free("a")
@@ -135,7 +141,7 @@ def test_swiglu_part(dtype):
     ffn.bind({n: weights[n].cuda() for n in ffn.weights()}, env)
     x = (torch.randn(13, cfg["hidden_size"]) * 2).to(env.torch_dtype)
     out = ffn.forward(x.cuda(), _Ctx(dtype, 13))
-    torch.testing.assert_close(out.float().cpu(), P.swiglu(weights, p, x.float()), **_tol(dtype))
+    torch.testing.assert_close(_total(out).cpu(), P.swiglu(weights, p, x.float()), **_tol(dtype))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

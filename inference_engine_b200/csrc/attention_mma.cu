@@ -147,32 +147,16 @@ struct RowState {
     }
 };
 
-// One key tile for one warp: scores, mask, online softmax, weighted values.
-//   qf        : the warp's 16 query rows as A fragments
+// Online softmax of one 16-row tile over one key tile: mask, running maximum and sum, rescale of
+// the output so far; on return s holds the weights 2^(scale*s - m).
 //   qpos, qlo : for the thread's two rows (lane / 4 and lane / 4 + 8): position of the query
 //               and first key it may see; a row that does not exist has qpos < 0
 //   key_hi    : last key of the range this call may use (split end)
 template <int KT>
-__device__ __forceinline__ void process_tile(RowState& st, const unsigned (&qf)[KS][4],
-                                             const bf16* ktile, const bf16* vtile, int key0,
+__device__ __forceinline__ void softmax_rows(RowState& st, float (&s)[KT / 8][4], int key0,
                                              const int (&qpos)[2], const int (&qlo)[2], int key_hi,
                                              float scale_log2, int lane) {
-    constexpr int NT = KT / 8;  // 8-key score tiles per key tile
-    float s[NT][4];
-#pragma unroll
-    for (int n = 0; n < NT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
-#pragma unroll
-    for (int ks = 0; ks < KS; ++ks) {
-#pragma unroll
-        for (int n = 0; n < NT; n += 2) {
-            unsigned b[4];
-            int row = n * 8 + (lane & 7) + ((lane >> 4) << 3);
-            int c = ks * 2 + ((lane >> 3) & 1);
-            ldmatrix_x4(b, ktile + (row * C + swz(row, c)) * 8);
-            mma_bf16(s[n], qf[ks], b[0], b[1]);
-            mma_bf16(s[n + 1], qf[ks], b[2], b[3]);
-        }
-    }
+    constexpr int NT = KT / 8;
     float tile_max[2] = {-INFINITY, -INFINITY};
     int last = key0 + KT - 1;
     bool all_visible = last <= key_hi && last <= qpos[0] && last <= qpos[1] &&
@@ -181,11 +165,7 @@ __device__ __forceinline__ void process_tile(RowState& st, const unsigned (&qf)[
 #pragma unroll
         for (int n = 0; n < NT; ++n) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                float v = s[n][j] * scale_log2;
-                s[n][j] = v;
-                tile_max[j >> 1] = fmaxf(tile_max[j >> 1], v);
-            }
+            for (int j = 0; j < 4; ++j) tile_max[j >> 1] = fmaxf(tile_max[j >> 1], s[n][j]);
         }
     } else {
 #pragma unroll
@@ -195,7 +175,7 @@ __device__ __forceinline__ void process_tile(RowState& st, const unsigned (&qf)[
                 int r = j >> 1;
                 int kpos = key0 + n * 8 + (lane & 3) * 2 + (j & 1);
                 bool valid = kpos <= qpos[r] && kpos >= qlo[r] && kpos <= key_hi;
-                float v = valid ? s[n][j] * scale_log2 : -INFINITY;
+                float v = valid ? s[n][j] : -INFINITY;
                 s[n][j] = v;
                 tile_max[r] = fmaxf(tile_max[r], v);
             }
@@ -207,7 +187,7 @@ __device__ __forceinline__ void process_tile(RowState& st, const unsigned (&qf)[
         float t = tile_max[r];
         t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, 1));
         t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, 2));
-        float m_new = fmaxf(st.m[r], t);
+        float m_new = fmaxf(st.m[r], t * scale_log2);  // the scale is positive: max commutes
         m_safe[r] = (m_new == -INFINITY) ? 0.f : m_new;
         alpha[r] = fast_exp2(st.m[r] - m_safe[r]);  // 0 when nothing was seen before
         st.m[r] = m_new;
@@ -222,26 +202,67 @@ __device__ __forceinline__ void process_tile(RowState& st, const unsigned (&qf)[
     for (int n = 0; n < NT; ++n) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            float p = fast_exp2(s[n][j] - m_safe[j >> 1]);
+            float p = fast_exp2(fmaf(s[n][j], scale_log2, -m_safe[j >> 1]));  // -inf stays -inf -> 0
             s[n][j] = p;
             st.l[j >> 1] += p;
         }
     }
+}
+
+// One key tile for MT 16-row tiles of one warp: scores, softmax, weighted values.  The K and V
+// fragments read from shared memory are used by all MT row tiles (with MT = 2 shared-memory
+// traffic per multiply is halved, which is what bounds the prefill kernel otherwise).
+//   qf : the warp's query rows as A fragments
+template <int KT, int MT>
+__device__ __forceinline__ void process_tile(RowState (&st)[MT], const unsigned (&qf)[MT][KS][4],
+                                             const bf16* ktile, const bf16* vtile, int key0,
+                                             const int (&qpos)[MT][2], const int (&qlo)[MT][2], int key_hi,
+                                             float scale_log2, int lane) {
+    constexpr int NT = KT / 8;  // 8-key score tiles per key tile
+    float s[MT][NT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int n = 0; n < NT; ++n) s[mt][n][0] = s[mt][n][1] = s[mt][n][2] = s[mt][n][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+        for (int n = 0; n < NT; n += 2) {
+            unsigned b[4];
+            int row = n * 8 + (lane & 7) + ((lane >> 4) << 3);
+            int c = ks * 2 + ((lane >> 3) & 1);
+            ldmatrix_x4(b, ktile + (row * C + swz(row, c)) * 8);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                mma_bf16(s[mt][n], qf[mt][ks], b[0], b[1]);
+                mma_bf16(s[mt][n + 1], qf[mt][ks], b[2], b[3]);
+            }
+        }
+    }
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+        softmax_rows<KT>(st[mt], s[mt], key0, qpos[mt], qlo[mt], key_hi, scale_log2, lane);
 #pragma unroll
     for (int kk = 0; kk < KT / 16; ++kk) {
-        unsigned a[4];
-        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+        unsigned a[MT][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            a[mt][0] = pack_bf16(s[mt][2 * kk][0], s[mt][2 * kk][1]);
+            a[mt][1] = pack_bf16(s[mt][2 * kk][2], s[mt][2 * kk][3]);
+            a[mt][2] = pack_bf16(s[mt][2 * kk + 1][0], s[mt][2 * kk + 1][1]);
+            a[mt][3] = pack_bf16(s[mt][2 * kk + 1][2], s[mt][2 * kk + 1][3]);
+        }
 #pragma unroll
         for (int d = 0; d < DT; d += 2) {
             unsigned b[4];
             int row = kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
             int c = d + (lane >> 4);
             ldmatrix_x4_trans(b, vtile + (row * C + swz(row, c)) * 8);
-            mma_bf16(st.o[d], a, b[0], b[1]);
-            mma_bf16(st.o[d + 1], a, b[2], b[3]);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                mma_bf16(st[mt].o[d], a[mt], b[0], b[1]);
+                mma_bf16(st[mt].o[d + 1], a[mt], b[2], b[3]);
+            }
         }
     }
 }
@@ -332,25 +353,26 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
         cp_async_commit();
     }
     // 3. the queries (they needed cu_q) while those are in flight
-    int qpos[2], qlo[2];
-    unsigned qf[KS][4];
+    int qpos[1][2], qlo[1][2];
+    unsigned qf[1][KS][4];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         int row = (lane >> 2) + r * 8;
         bool exists = row < rows;
         int tok = exists ? row / G : 0, g = exists ? row - tok * G : 0;
-        qpos[r] = exists ? first_qpos + tok : -1;
-        qlo[r] = (window > 0 && qpos[r] - window + 1 > 0) ? qpos[r] - window + 1 : 0;
+        qpos[0][r] = exists ? first_qpos + tok : -1;
+        qlo[0][r] = (window > 0 && qpos[0][r] - window + 1 > 0) ? qpos[0][r] - window + 1 : 0;
         const bf16* qrow = q + ((size_t)(q0 + tok) * nh + kvh * G + g) * HD;
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
             int d = ks * 16 + (lane & 3) * 2;
-            qf[ks][r] = exists ? *reinterpret_cast<const unsigned*>(qrow + d) : 0u;
-            qf[ks][r + 2] = exists ? *reinterpret_cast<const unsigned*>(qrow + d + 8) : 0u;
+            qf[0][ks][r] = exists ? *reinterpret_cast<const unsigned*>(qrow + d) : 0u;
+            qf[0][ks][r + 2] = exists ? *reinterpret_cast<const unsigned*>(qrow + d + 8) : 0u;
         }
     }
-    RowState st;
-    st.init();
+    RowState sts[1];
+    sts[0].init();
+    RowState& st = sts[0];
     // 4. the ring: the copies of tile i+2 use block-table entries fetched one tile earlier, and
     //    the entries of tile i+3 are fetched now, so no lookup is waited for
     Pages next = pg[DSTAGES - 1];
@@ -368,7 +390,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
         cp_async_wait<DSTAGES - 1>();
         __syncwarp();
         const bf16* cur = ring + (size_t)(i % DSTAGES) * 2 * TILE_ELEMS;
-        process_tile<KT>(st, qf, cur, cur + TILE_ELEMS, lo + j * KT, qpos, qlo, hi, scale_log2, lane);
+        process_tile<KT, 1>(sts, qf, cur, cur + TILE_ELEMS, lo + j * KT, qpos, qlo, hi, scale_log2, lane);
         __syncwarp();
     }
     cp_async_wait<0>();
@@ -447,9 +469,11 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
 }
 
 // -------------------------------------------------------------------------------------------------
-// Prefill: portions with more than 16 rows.  grid = (64-token tiles over all requests, heads).
+// Prefill: portions with more than 16 rows.  grid = (128-token tiles over all requests, heads);
+// four warps of 32 rows (two 16-row tiles that share every K and V fragment).
 // -------------------------------------------------------------------------------------------------
-constexpr int BM = 64;
+constexpr int PMT = HD <= 64 ? 2 : 1;  // 16-row tiles per warp (registers allow two up to head size 64)
+constexpr int BM = WARPS * PMT * 16;   // query tokens per block
 
 __global__ void __launch_bounds__(WARPS * 32)
 attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache,
@@ -462,7 +486,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int head = blockIdx.y, G = nh / nkv, kvh = head / G;
-    // which request and which 64-token tile of it is this block's?
+    // which request and which query tile of it is this block's?
     ie_pdl_trigger();
     ie_pdl_wait();
     // late tiles of a portion see the most keys: they go first so the short ones fill the tail
@@ -483,30 +507,34 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
     int key_begin = (lo / KT) * KT;              // tiles are aligned to absolute position 0
     int n_tiles = (cta_qpos_hi - key_begin) / KT + 1;
 
-    int qpos[2], qlo[2];
-    unsigned qf[KS][4];
-    int warp_hi = -1;
+    constexpr int WROWS = PMT * 16;  // rows of one warp
+    int qpos[PMT][2], qlo[PMT][2];
+    unsigned qf[PMT][KS][4];
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        int row = warp * 16 + (lane >> 2) + r * 8;
-        bool exists = row < tile_rows;
-        qpos[r] = exists ? cta_qpos_lo + row : -1;
-        qlo[r] = (window > 0 && qpos[r] - window + 1 > 0) ? qpos[r] - window + 1 : 0;
-        const bf16* qrow = q + ((size_t)(q0 + t0 + (exists ? row : 0)) * nh + head) * HD;
+    for (int mt = 0; mt < PMT; ++mt) {
 #pragma unroll
-        for (int ks = 0; ks < KS; ++ks) {
-            int d = ks * 16 + (lane & 3) * 2;
-            qf[ks][r] = exists ? *reinterpret_cast<const unsigned*>(qrow + d) : 0u;
-            qf[ks][r + 2] = exists ? *reinterpret_cast<const unsigned*>(qrow + d + 8) : 0u;
+        for (int r = 0; r < 2; ++r) {
+            int row = warp * WROWS + mt * 16 + (lane >> 2) + r * 8;
+            bool exists = row < tile_rows;
+            qpos[mt][r] = exists ? cta_qpos_lo + row : -1;
+            qlo[mt][r] = (window > 0 && qpos[mt][r] - window + 1 > 0) ? qpos[mt][r] - window + 1 : 0;
+            const bf16* qrow = q + ((size_t)(q0 + t0 + (exists ? row : 0)) * nh + head) * HD;
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+                int d = ks * 16 + (lane & 3) * 2;
+                qf[mt][ks][r] = exists ? *reinterpret_cast<const unsigned*>(qrow + d) : 0u;
+                qf[mt][ks][r + 2] = exists ? *reinterpret_cast<const unsigned*>(qrow + d + 8) : 0u;
+            }
         }
     }
-    warp_hi = min(cta_qpos_lo + warp * 16 + 15, cta_qpos_hi);  // last position this warp's rows see
-    int warp_lo_pos = cta_qpos_lo + warp * 16;
+    int warp_hi = min(cta_qpos_lo + warp * WROWS + WROWS - 1, cta_qpos_hi);  // last position this warp's rows see
+    int warp_lo_pos = cta_qpos_lo + warp * WROWS;
     int warp_lo = (window > 0 && warp_lo_pos - window + 1 > 0) ? warp_lo_pos - window + 1 : 0;
-    bool warp_has_rows = warp * 16 < tile_rows;
+    bool warp_has_rows = warp * WROWS < tile_rows;
 
-    RowState st;
-    st.init();
+    RowState st[PMT];
+#pragma unroll
+    for (int mt = 0; mt < PMT; ++mt) st[mt].init();
     // Three stages of (K, V) tiles; the block-table entries of a tile are fetched one tile
     // before its copies are issued, so no lookup is waited for inside the loop.
     typedef TilePages<KT, WARPS * 32> Pages;
@@ -541,20 +569,23 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
                                         page_shift, threadIdx.x);
         const bf16* cur = smem + (size_t)(t % PSTAGES) * 2 * TILE_ELEMS;
         if (warp_has_rows && key0 <= warp_hi && key0 + KT - 1 >= warp_lo)
-            process_tile<KT>(st, qf, cur, cur + TILE_ELEMS, key0, qpos, qlo, cta_qpos_hi, scale_log2, lane);
+            process_tile<KT, PMT>(st, qf, cur, cur + TILE_ELEMS, key0, qpos, qlo, cta_qpos_hi, scale_log2, lane);
     }
     cp_async_wait<0>();
-    finish_rows(st);
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        int row = warp * 16 + (lane >> 2) + r * 8;
-        if (row >= tile_rows) continue;
-        float inv = st.l[r] > 0.f ? 1.0f / st.l[r] : 0.f;
-        bf16* orow = out + ((size_t)(q0 + t0 + row) * nh + head) * HD;
+    for (int mt = 0; mt < PMT; ++mt) {
+        finish_rows(st[mt]);
 #pragma unroll
-        for (int d = 0; d < DT; ++d) {
-            __nv_bfloat162 v = __floats2bfloat162_rn(st.o[d][r * 2] * inv, st.o[d][r * 2 + 1] * inv);
-            *reinterpret_cast<__nv_bfloat162*>(orow + d * 8 + (lane & 3) * 2) = v;
+        for (int r = 0; r < 2; ++r) {
+            int row = warp * WROWS + mt * 16 + (lane >> 2) + r * 8;
+            if (row >= tile_rows) continue;
+            float inv = st[mt].l[r] > 0.f ? 1.0f / st[mt].l[r] : 0.f;
+            bf16* orow = out + ((size_t)(q0 + t0 + row) * nh + head) * HD;
+#pragma unroll
+            for (int d = 0; d < DT; ++d) {
+                __nv_bfloat162 v = __floats2bfloat162_rn(st[mt].o[d][r * 2] * inv, st[mt].o[d][r * 2 + 1] * inv);
+                *reinterpret_cast<__nv_bfloat162*>(orow + d * 8 + (lane & 3) * 2) = v;
+            }
         }
     }
 }
@@ -566,6 +597,8 @@ constexpr size_t DECODE_SMEM = DECODE_SMEM_TILES > DECODE_MERGE_SMEM ? DECODE_SM
 }  // namespace
 
 IE_API int ie_attention_head_dim() { return HD; }
+// Query tokens one block of the prefill kernel takes (callers count tiles with it).
+IE_API int ie_attention_prefill_rows() { return BM; }
 IE_API void ie_set_pdl(int enabled) { ie_pdl_enabled() = enabled ? 1 : 0; }
 
 // Floats of scratch the decode kernel needs for `num_seqs` requests at `num_splits` splits:
@@ -607,8 +640,8 @@ IE_API int ie_attention_decode(const void* q, const void* k_cache, const void* v
                      scale * 1.4426950408889634f, window, num_splits, err);
 }
 
-// Requests with more than 16 rows.  `max_tiles` bounds the number of 64-token tiles over all
-// such requests (num_tokens / 64 + num_seqs always suffices).
+// Requests with more than 16 rows.  `max_tiles` bounds the number of query tiles over all
+// such requests, each tile being ie_attention_prefill_rows() tokens.
 IE_API int ie_attention_prefill(const void* q, const void* k_cache, const void* v_cache,
                                 const int* tables, int table_width, const int* cu_q,
                                 const int* ctx_lens, void* out, int num_seqs, int max_tiles,

@@ -294,7 +294,8 @@ class CudaOps:
                     self._ptr(scratch), self._ptr(tickets), ctx.num_seqs, nh, nkv, page_size,
                     total_pages, scale, window, splits, self._err_ptr, stream), "attention_decode")
             if not all(small):
-                tiles = sum(-(-ql // 64) for ql, s in zip(ctx.q_lens, small) if not s)
+                rows = lib.ie_attention_prefill_rows()
+                tiles = sum(-(-ql // rows) for ql, s in zip(ctx.q_lens, small) if not s)
                 self._check(lib.ie_attention_prefill(
                     q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
                     block_tables.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_lens.data_ptr(), out.data_ptr(),

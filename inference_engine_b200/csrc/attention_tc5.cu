@@ -1,0 +1,383 @@
+// Paged prefill attention on the fifth-generation tensor cores (tcgen05 + TMEM + TMA), bfloat16,
+// head size 64, pages of a multiple of 8 tokens.  One build per head size (-DIE_HD=64); for
+// other head sizes the file compiles to a stub that reports "not available".
+//
+// One block = 128 query tokens of one head (a tcgen05.mma of M = 128: TMEM lane = query row =
+// thread).  For every tile of 64 keys:
+//   1. one thread copies the tile's pages of K and V with TMA (cp.async.bulk.tensor, one box
+//      per page, 128-byte swizzle) into a two-stage ring, a tile ahead of use;
+//   2. S = Q K^T: four tcgen05.mma (k = 16 each) from shared-memory descriptors into 64 TMEM
+//      columns; tcgen05.commit signals an mbarrier;
+//   3. every thread reads its row of S from TMEM (tcgen05.ld 32x32b.x64), applies the causal /
+//      window mask, keeps the running maximum and sum (a row is private to a thread: no
+//      shuffles), rounds the weights to bfloat16 and stores them as the next product's A
+//      operand in shared memory (K-major, swizzled);
+//   4. PV = P V: four tcgen05.mma with V as an MN-major B operand into 64 more TMEM columns;
+//   5. every thread reads its row of PV and folds it into its 64 output registers with the
+//      rescaling factor of the running maximum.
+// All waits on mbarriers are bounded; a block that waits too long records IE_ERR_TIMEOUT, frees
+// its TMEM and leaves.  The reference's counterpart is the FlashAttention varlen call over
+// gathered keys and values (engine/model/layers.py:246-253).
+#include "common.cuh"
+#include <cuda.h>
+#include <math.h>
+
+#ifndef IE_HD
+#error "compile with -DIE_HD=<head size>"
+#endif
+
+#if IE_HD == 64
+
+namespace {
+typedef __nv_bfloat16 bf16;
+constexpr int HD = 64;
+constexpr int BM = 128;             // query rows per block
+constexpr int KT = 64;              // keys per tile
+constexpr int THREADS = 128;
+constexpr int Q_BYTES = BM * HD * 2;        // 16 KB
+constexpr int KV_BYTES = KT * HD * 2;       // 8 KB each
+constexpr int P_BYTES = BM * KT * 2;        // 16 KB
+constexpr int MAX_TABLE = 1024;             // block-table entries cached in shared memory
+constexpr int TMEM_COLS = 128;              // S: columns 0..63, PV: 64..127
+constexpr long long SPIN_LIMIT = 20000000;
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, int bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, int parity) {
+    unsigned addr = smem_u32(bar);
+    for (long long spin = 0; spin < SPIN_LIMIT; ++spin) {
+        unsigned done;
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, rows (or 8-key groups) 1024 bytes apart.
+__device__ __forceinline__ unsigned long long smem_desc(unsigned addr) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((addr >> 4) & 0x3FFF);   // start address, 16-byte units
+    d |= (unsigned long long)64 << 16;                 // leading byte offset (unused here): 1024 B
+    d |= (unsigned long long)64 << 32;                 // stride byte offset: 1024 B between 8-row groups
+    d |= (unsigned long long)1 << 46;                  // descriptor version of this architecture
+    d |= (unsigned long long)2 << 61;                  // layout: 128-byte swizzle
+    return d;
+}
+// Instruction descriptor: bfloat16 x bfloat16 -> float, M = 128, N = 64; b_mn: B is MN-major.
+__device__ __forceinline__ unsigned instr_desc(bool b_mn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
+}
+__device__ __forceinline__ void umma(unsigned tmem_d, unsigned long long a, unsigned long long b, unsigned idesc, unsigned accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                 " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}"
+                 ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// One row (this thread's TMEM lane) of 64 columns starting at `taddr`.
+__device__ __forceinline__ void tmem_ld64(float (&v)[64], unsigned taddr) {
+    unsigned* r = reinterpret_cast<unsigned*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,"
+        "%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,"
+        "%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%64];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]),
+          "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]),
+          "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]),
+          "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]),
+          "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct __align__(8) Barriers {
+    unsigned long long q_full, kv_full[2], s_done, o_done;
+    unsigned tmem_base;
+    int failed;
+};
+
+__global__ void __launch_bounds__(THREADS)
+attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
+                             const __grid_constant__ CUtensorMap v_map, const int* __restrict__ tables,
+                             int table_width, const int* __restrict__ cu_q, const int* __restrict__ ctx_lens,
+                             bf16* __restrict__ out, int num_seqs, int nh, int nkv, int page_shift,
+                             int total_pages, float scale_log2, int window, int* err) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    unsigned char* q_s = smem;                            // 16 KB
+    unsigned char* k_s = q_s + Q_BYTES;                   // 2 x 8 KB
+    unsigned char* v_s = k_s + 2 * KV_BYTES;              // 2 x 8 KB
+    unsigned char* p_s = v_s + 2 * KV_BYTES;              // 16 KB
+    int* table_s = reinterpret_cast<int*>(p_s + P_BYTES); // MAX_TABLE ints
+    Barriers* bars = reinterpret_cast<Barriers*>(table_s + MAX_TABLE);
+    int tid = threadIdx.x, warp = tid >> 5;
+    int head = blockIdx.y, G = nh / nkv, kvh = head / G;
+    ie_pdl_trigger();
+    ie_pdl_wait();
+    // which request and which 128-token tile of it is this block's?  (heavy tiles first)
+    int tile = gridDim.x - 1 - blockIdx.x, seq = -1, t0 = 0, q0 = 0, qlen = 0;
+    for (int s = 0; s < num_seqs; ++s) {
+        int a = cu_q[s], n = cu_q[s + 1] - a;
+        int tiles = (n * G > 16) ? (n + BM - 1) / BM : 0;
+        if (tile < tiles) { seq = s; t0 = tile * BM; q0 = a; qlen = n; break; }
+        tile -= tiles;
+    }
+    if (seq < 0) return;
+    int ctx = ctx_lens[seq];
+    const int* table = tables + (size_t)seq * table_width;
+    int first_qpos = ctx - qlen;
+    int tile_rows = min(BM, qlen - t0);
+    int qpos_lo = first_qpos + t0, qpos_hi = qpos_lo + tile_rows - 1;
+    int lo = (window > 0 && qpos_lo - window + 1 > 0) ? qpos_lo - window + 1 : 0;
+    int key_begin = (lo / KT) * KT;
+    int n_tiles = (qpos_hi - key_begin) / KT + 1;
+    int page_size = 1 << page_shift;
+    int pages_per_tile = KT >> page_shift;
+    int first_entry = key_begin >> page_shift;
+    int n_entries = min(n_tiles * pages_per_tile, MAX_TABLE);
+
+    if (tid == 0) {
+        mbar_init(&bars->q_full, 1);
+        mbar_init(&bars->kv_full[0], 1);
+        mbar_init(&bars->kv_full[1], 1);
+        mbar_init(&bars->s_done, 1);
+        mbar_init(&bars->o_done, 1);
+        bars->failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int i = tid; i < n_entries; i += THREADS) {
+        int e = first_entry + i;
+        int page = e < table_width ? table[e] : -1;
+        // a page that is not there lies beyond the context: its keys are masked, any page's
+        // (finite) contents will do
+        table_s[i] = (page >= 0 && page < total_pages) ? page : 0;
+    }
+    if (warp == 0) {  // one warp allocates the block's TMEM columns
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&bars->tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    unsigned tmem = bars->tmem_base;
+    unsigned tmem_s = tmem, tmem_o = tmem + KT;
+    unsigned lane_addr = (unsigned)(warp * 32) << 16;  // this warp's 32 TMEM lanes
+
+    auto issue_kv = [&](int t) {  // thread 0: the pages of key tile t into stage t % 2
+        int stage = t & 1;
+        mbar_expect_tx(&bars->kv_full[stage], 2 * KV_BYTES);
+        for (int p = 0; p < pages_per_tile; ++p) {
+            int page = table_s[min(t * pages_per_tile + p, MAX_TABLE - 1)];
+            int row = (page * nkv + kvh) << page_shift;
+            tma_load_2d(k_s + stage * KV_BYTES + p * page_size * 128, &k_map, 0, row, &bars->kv_full[stage]);
+            tma_load_2d(v_s + stage * KV_BYTES + p * page_size * 128, &v_map, 0, row, &bars->kv_full[stage]);
+        }
+    };
+    if (tid == 0) {
+        mbar_expect_tx(&bars->q_full, Q_BYTES);
+        tma_load_2d(q_s, &q_map, head * HD, q0 + t0, &bars->q_full);
+        issue_kv(0);
+    }
+
+    int row = tid;                       // this thread's query row
+    bool exists = row < tile_rows;
+    int qpos = exists ? qpos_lo + row : -1;
+    int qlo = (window > 0 && qpos - window + 1 > 0) ? qpos - window + 1 : 0;
+    float m = -INFINITY, l = 0.f;
+    float o[HD];
+#pragma unroll
+    for (int d = 0; d < HD; ++d) o[d] = 0.f;
+    bool ok = mbar_wait(&bars->q_full, 0);
+    unsigned idesc_qk = instr_desc(false), idesc_pv = instr_desc(true);
+
+    for (int t = 0; t < n_tiles && ok; ++t) {
+        int stage = t & 1;
+        int key0 = key_begin + t * KT;
+        if (tid == 0) {
+            if (t + 1 < n_tiles) issue_kv(t + 1);  // stage (t+1)%2 was released by tile t-1's PV
+            if (mbar_wait(&bars->kv_full[stage], (t >> 1) & 1)) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                unsigned qa = smem_u32(q_s), ka = smem_u32(k_s + stage * KV_BYTES);
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks)  // 32 bytes further along k per step
+                    umma(tmem_s, smem_desc(qa + ks * 32), smem_desc(ka + ks * 32), idesc_qk, ks > 0);
+                umma_commit(&bars->s_done);
+            } else {
+                bars->failed = 1;
+            }
+        }
+        if (!mbar_wait(&bars->s_done, t & 1)) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        float s[KT];
+        tmem_ld64(s, tmem_s + lane_addr);
+        float tile_max = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < KT; ++j) {
+            int kpos = key0 + j;
+            bool valid = kpos <= qpos && kpos >= qlo;
+            s[j] = valid ? s[j] : -INFINITY;
+            tile_max = fmaxf(tile_max, s[j]);
+        }
+        float m_new = fmaxf(m, tile_max * scale_log2);
+        float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+        float alpha = fast_exp2(m - m_safe);
+        m = m_new;
+        l *= alpha;
+        // weights, rounded to bfloat16, into the A operand tile: row `row`, 16-byte chunk c at
+        // chunk position c ^ (row & 7) of the row's 128 bytes
+        unsigned char* prow = p_s + row * 128;
+#pragma unroll
+        for (int c = 0; c < KT / 8; ++c) {
+            unsigned w[4];
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+                float p0 = fast_exp2(fmaf(s[c * 8 + 2 * h], scale_log2, -m_safe));
+                float p1 = fast_exp2(fmaf(s[c * 8 + 2 * h + 1], scale_log2, -m_safe));
+                l += p0 + p1;
+                __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+                w[h] = *reinterpret_cast<unsigned*>(&pk);
+            }
+            *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic stores -> the tensor core's reads
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        if (tid == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            unsigned pa = smem_u32(p_s), va = smem_u32(v_s + stage * KV_BYTES);
+#pragma unroll
+            for (int ks = 0; ks < KT / 16; ++ks)  // P: 32 bytes along k; V: 16 keys = 2048 bytes
+                umma(tmem_o, smem_desc(pa + ks * 32), smem_desc(va + ks * 2048), idesc_pv, ks > 0);
+            umma_commit(&bars->o_done);
+        }
+        if (!mbar_wait(&bars->o_done, t & 1)) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        float pv[HD];
+        tmem_ld64(pv, tmem_o + lane_addr);
+#pragma unroll
+        for (int d = 0; d < HD; ++d) o[d] = fmaf(o[d], alpha, pv[d]);
+        // the next tile's S overwrites TMEM and P: everybody must have read theirs
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+    }
+    if (!ok) bars->failed = 1;
+    if (exists && ok) {
+        float inv = l > 0.f ? 1.0f / l : 0.f;
+        bf16* orow = out + ((size_t)(q0 + t0 + row) * nh + head) * HD;
+#pragma unroll
+        for (int c = 0; c < HD / 8; ++c) {
+            unsigned w[4];
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+                __nv_bfloat162 pk = __floats2bfloat162_rn(o[c * 8 + 2 * h] * inv, o[c * 8 + 2 * h + 1] * inv);
+                w[h] = *reinterpret_cast<unsigned*>(&pk);
+            }
+            *reinterpret_cast<uint4*>(orow + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    if (tid == 0 && bars->failed) ie_report(err, IE_ERR_TIMEOUT, blockIdx.x, blockIdx.y);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+// Row-major [rows, cols] bfloat16 as a 2-D map with boxes of box_rows x 64 columns, 128-byte swizzle.
+bool make_map(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+constexpr size_t SMEM_BYTES = Q_BYTES + 4 * KV_BYTES + P_BYTES + MAX_TABLE * 4 + sizeof(Barriers) + 1024;
+}  // namespace
+
+// 1 if the tcgen05 prefill kernel can take this geometry: pages of 8..64 tokens, at most
+// `MAX_TABLE` pages per 128-token tile's key range.
+IE_API int ie_attention_prefill_tc5_ok(int page_size, int max_ctx) {
+    if (encode_fn() == nullptr) return 0;
+    if (page_size < 8 || page_size > KT || (page_size & (page_size - 1)) != 0) return 0;
+    return (max_ctx + KT) / page_size <= MAX_TABLE ? 1 : 0;
+}
+
+IE_API int ie_attention_prefill_tc5(const void* q, const void* k_cache, const void* v_cache, const int* tables,
+                                    int table_width, const int* cu_q, const int* ctx_lens, void* out,
+                                    int num_tokens, int num_seqs, int max_tiles, int nh, int nkv,
+                                    int page_size, int total_pages, float scale, int window, int* err,
+                                    void* stream) {
+    if (num_seqs <= 0 || max_tiles <= 0) return 0;
+    if (nkv <= 0 || nh % nkv != 0 || (page_size & (page_size - 1)) != 0 || page_size < 8 || page_size > KT)
+        return (int)cudaErrorInvalidValue;
+    int page_shift = 0;
+    while ((1 << page_shift) < page_size) ++page_shift;
+    CUtensorMap qm, km, vm;
+    long long kv_rows = (long long)total_pages * nkv * page_size;
+    if (!make_map(&qm, q, num_tokens, (long long)nh * HD, BM) || !make_map(&km, k_cache, kv_rows, HD, page_size) ||
+        !make_map(&vm, v_cache, kv_rows, HD, page_size))
+        return (int)cudaErrorNotSupported;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc5_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    return ie_launch(attention_prefill_tc5_kernel, dim3(max_tiles, nh), dim3(THREADS), SMEM_BYTES,
+                     (cudaStream_t)stream, qm, km, vm, tables, table_width, cu_q, ctx_lens, (bf16*)out, num_seqs,
+                     nh, nkv, page_shift, total_pages, scale * 1.4426950408889634f, window, err);
+}
+
+#else  // other head sizes: the mma.sync kernels of attention_mma.cu serve them
+
+IE_API int ie_attention_prefill_tc5_ok(int, int) { return 0; }
+IE_API int ie_attention_prefill_tc5(const void*, const void*, const void*, const int*, int, const int*,
+                                    const int*, void*, int, int, int, int, int, int, int, float, int, int*,
+                                    void*) {
+    return (int)cudaErrorNotSupported;
+}
+
+#endif

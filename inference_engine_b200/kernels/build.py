@@ -137,7 +137,8 @@ def build_attention(head_dim: int) -> Path:
     for the head size the loaded model has)."""
     if head_dim not in ATTENTION_HEAD_DIMS:
         raise BuildError(f"the tensor-core attention takes head sizes {ATTENTION_HEAD_DIMS}, not {head_dim}")
-    return build_library(f"ie_b200_attn_hd{head_dim}", ["attention_mma.cu"], [f"-DIE_HD={head_dim}"])
+    return build_library(f"ie_b200_attn_hd{head_dim}", ["attention_mma.cu", "attention_tc5.cu"],
+                         [f"-DIE_HD={head_dim}"])
 
 
 def build_all() -> list[Path]:

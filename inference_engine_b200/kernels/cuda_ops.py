@@ -69,6 +69,7 @@ class CudaOps:
         self.skinny_max_blocks = int(os.environ.get("IE_B200_SKINNY_MAX_BLOCKS", self.sm_count))
         # which kernel takes few-row bfloat16 products: "tma" (TMA-fed ring), "cp" (cp.async
         # rings per warp), "auto" (cp for few output features, the vendor library otherwise)
+        self.attn_tc5 = os.environ.get("IE_B200_ATTN_TC5", "1") != "0"  # tcgen05 prefill attention
         self.few_row_gemm = os.environ.get("IE_B200_FEW_ROW_GEMM", "tma")
         # ... for matrices with fewer 128-feature tiles than half the SMs (they need their inner
         # dimension cut to occupy the GPU, which the vendor library does not do); measured on
@@ -242,6 +243,8 @@ class CudaOps:
             P, I, F = c_void_p, c_int, c_float
             lib.ie_attention_decode.argtypes = [P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, F, I, I, P, P]
             lib.ie_attention_prefill.argtypes = [P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P, P]
+            lib.ie_attention_prefill_tc5.argtypes = [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, P]
+            lib.ie_attention_prefill_tc5_ok.argtypes = [I, I]
             lib.ie_attention_decode_scratch_floats.argtypes = [I, I, I]
             lib.ie_attention_decode_scratch_floats.restype = ctypes.c_longlong
             self._attn_libs[hd] = lib
@@ -296,6 +299,14 @@ class CudaOps:
             if not all(small):
                 rows = lib.ie_attention_prefill_rows()
                 tiles = sum(-(-ql // rows) for ql, s in zip(ctx.q_lens, small) if not s)
+                if self.attn_tc5 and lib.ie_attention_prefill_tc5_ok(page_size, ctx.max_ctx_len):
+                    # head size 64, pages of 8 tokens or more: the tcgen05 / TMEM / TMA kernel
+                    self._check(lib.ie_attention_prefill_tc5(
+                        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
+                        block_tables.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_lens.data_ptr(), out.data_ptr(),
+                        ctx.num_tokens, ctx.num_seqs, tiles, nh, nkv, page_size, total_pages, scale, window,
+                        self._err_ptr, stream), "attention_prefill_tc5")
+                    return
                 self._check(lib.ie_attention_prefill(
                     q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
                     block_tables.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_lens.data_ptr(), out.data_ptr(),

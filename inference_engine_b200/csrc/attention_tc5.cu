@@ -3,21 +3,26 @@
 // other head sizes the file compiles to a stub that reports "not available".
 //
 // One block = 128 query tokens of one head (a tcgen05.mma of M = 128: TMEM lane = query row =
-// thread).  For every tile of 64 keys:
-//   1. one thread copies the tile's pages of K and V with TMA (cp.async.bulk.tensor, one box
-//      per page, 128-byte swizzle) into a two-stage ring, a tile ahead of use;
-//   2. S = Q K^T: four tcgen05.mma (k = 16 each) from shared-memory descriptors into 64 TMEM
-//      columns; tcgen05.commit signals an mbarrier;
-//   3. every thread reads its row of S from TMEM (tcgen05.ld 32x32b.x64), applies the causal /
-//      window mask, keeps the running maximum and sum (a row is private to a thread: no
-//      shuffles), rounds the weights to bfloat16 and stores them as the next product's A
-//      operand in shared memory (K-major, swizzled);
-//   4. PV = P V: four tcgen05.mma with V as an MN-major B operand into 64 more TMEM columns;
-//   5. every thread reads its row of PV and folds it into its 64 output registers with the
-//      rescaling factor of the running maximum.
-// All waits on mbarriers are bounded; a block that waits too long records IE_ERR_TIMEOUT, frees
-// its TMEM and leaves.  The reference's counterpart is the FlashAttention varlen call over
-// gathered keys and values (engine/model/layers.py:246-253).
+// thread of the softmax warps).  Six warps in three roles, decoupled by mbarriers:
+//   * warp 4, one thread: copies the pages of every 64-key tile of K and V with TMA
+//     (cp.async.bulk.tensor, one box per page, 128-byte swizzle) into a three-stage ring;
+//   * warp 5, one thread: issues S(t) = Q K(t)^T (four tcgen05.mma of k = 16, A = Q from tensor
+//     memory, B = K from shared memory) into one of two 64-column TMEM buffers, one tile ahead
+//     of the softmax, and O += P(t) V(t) (A = P from tensor memory, V as an MN-major B operand)
+//     as soon as the weights of tile t are written; tcgen05.commit signals the softmax warps
+//     and frees the ring stage;
+//   * warps 0-3: every thread puts its row of Q into tensor memory once, then for every tile
+//     reads its row of S (tcgen05.ld 32x32b), masks (diagonal and window tiles only), keeps the
+//     running maximum and sum -- a row is private to a thread, no shuffles -- rounds the weights
+//     to bfloat16 and writes them, two to a column, over the row of S (tcgen05.st).
+// The output accumulator stays in tensor memory for the whole key range.  The maximum that the
+// weights are taken against follows the running maximum only when that has grown by more than
+// 2^8; only then is the accumulator read, rescaled and written back.
+// While the softmax of tile t runs, the tensor core computes S(t+1) and P(t-1) V(t-1), and the
+// copies of tile t+2 are in flight; shared memory carries K and V only.  All waits on mbarriers
+// are bounded; a block that waits too long records IE_ERR_TIMEOUT, frees its TMEM and leaves.
+// The reference's counterpart is the FlashAttention varlen call over gathered keys and values
+// (engine/model/layers.py:246-253).
 #include "common.cuh"
 #include <cuda.h>
 #include <math.h>
@@ -33,13 +38,14 @@ typedef __nv_bfloat16 bf16;
 constexpr int HD = 64;
 constexpr int BM = 128;             // query rows per block
 constexpr int KT = 64;              // keys per tile
-constexpr int THREADS = 128;
-constexpr int Q_BYTES = BM * HD * 2;        // 16 KB
-constexpr int KV_BYTES = KT * HD * 2;       // 8 KB each
-constexpr int P_BYTES = BM * KT * 2;        // 16 KB
+constexpr int SOFTMAX_THREADS = 128;
+constexpr int THREADS = 192;                // + the copy warp and the tensor-core warp
+constexpr int KV_STAGES = 3;
+constexpr int KV_BYTES = KT * HD * 2;       // 8 KB each (K and V of a stage)
 constexpr int MAX_TABLE = 1024;             // block-table entries cached in shared memory
-constexpr int TMEM_COLS = 128;              // S: columns 0..63, PV: 64..127
+constexpr int TMEM_COLS = 256;              // S (then P, packed): columns 0..63 and 64..127; O: 128..191; Q: 192..223
 constexpr long long SPIN_LIMIT = 20000000;
+constexpr float RESCALE_LAG = 8.0f;         // in powers of two
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
@@ -47,6 +53,9 @@ __device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, int bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, int parity) {
     unsigned addr = smem_u32(bar);
@@ -82,10 +91,11 @@ __device__ __forceinline__ unsigned long long smem_desc(unsigned addr) {
 __device__ __forceinline__ unsigned instr_desc(bool b_mn) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
 }
-__device__ __forceinline__ void umma(unsigned tmem_d, unsigned long long a, unsigned long long b, unsigned idesc, unsigned accumulate) {
+// D (TMEM) = or += A B; A in tensor memory: lane = row, a 32-bit column = two consecutive k.
+__device__ __forceinline__ void umma_ta(unsigned tmem_d, unsigned tmem_a, unsigned long long b, unsigned idesc, unsigned accumulate) {
     asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-                 " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}"
-                 ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+                 " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void umma_commit(unsigned long long* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -111,27 +121,53 @@ __device__ __forceinline__ void tmem_ld64(float (&v)[64], unsigned taddr) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tmem_ld32(float (&v)[32], unsigned taddr) {
+    unsigned* r = reinterpret_cast<unsigned*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_st32(const float (&v)[32], unsigned taddr) {
+    const unsigned* r = reinterpret_cast<const unsigned*>(v);
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31};"
+        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]),
+          "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 struct __align__(8) Barriers {
-    unsigned long long q_full, kv_full[2], s_done, o_done;
+    unsigned long long q_full, kv_full[KV_STAGES], kv_empty[KV_STAGES], s_done[2], p_ready[2], o_done;
     unsigned tmem_base;
     int failed;
 };
 
-__global__ void __launch_bounds__(THREADS)
-attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
+__global__ void __launch_bounds__(THREADS, 2)
+attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__ CUtensorMap k_map,
                              const __grid_constant__ CUtensorMap v_map, const int* __restrict__ tables,
                              int table_width, const int* __restrict__ cu_q, const int* __restrict__ ctx_lens,
                              bf16* __restrict__ out, int num_seqs, int nh, int nkv, int page_shift,
                              int total_pages, float scale_log2, int window, int* err) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    unsigned char* q_s = smem;                            // 16 KB
-    unsigned char* k_s = q_s + Q_BYTES;                   // 2 x 8 KB
-    unsigned char* v_s = k_s + 2 * KV_BYTES;              // 2 x 8 KB
-    unsigned char* p_s = v_s + 2 * KV_BYTES;              // 16 KB
-    int* table_s = reinterpret_cast<int*>(p_s + P_BYTES); // MAX_TABLE ints
+    unsigned char* k_s = smem;                                  // stages x 8 KB
+    unsigned char* v_s = k_s + KV_STAGES * KV_BYTES;            // stages x 8 KB
+    int* table_s = reinterpret_cast<int*>(v_s + KV_STAGES * KV_BYTES);  // MAX_TABLE ints
     Barriers* bars = reinterpret_cast<Barriers*>(table_s + MAX_TABLE);
-    int tid = threadIdx.x, warp = tid >> 5;
+    int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     int head = blockIdx.y, G = nh / nkv, kvh = head / G;
     ie_pdl_trigger();
     ie_pdl_wait();
@@ -158,10 +194,9 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap q_map, const __
     int n_entries = min(n_tiles * pages_per_tile, MAX_TABLE);
 
     if (tid == 0) {
-        mbar_init(&bars->q_full, 1);
-        mbar_init(&bars->kv_full[0], 1);
-        mbar_init(&bars->kv_full[1], 1);
-        mbar_init(&bars->s_done, 1);
+        mbar_init(&bars->q_full, SOFTMAX_THREADS);
+        for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&bars->kv_full[s], 1); mbar_init(&bars->kv_empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&bars->s_done[b], 1); mbar_init(&bars->p_ready[b], SOFTMAX_THREADS); }
         mbar_init(&bars->o_done, 1);
         bars->failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -182,119 +217,171 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap q_map, const __
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     unsigned tmem = bars->tmem_base;
-    unsigned tmem_s = tmem, tmem_o = tmem + KT;
-    unsigned lane_addr = (unsigned)(warp * 32) << 16;  // this warp's 32 TMEM lanes
+    unsigned tmem_o = tmem + 2 * KT, tmem_q = tmem + 2 * KT + HD;
 
-    auto issue_kv = [&](int t) {  // thread 0: the pages of key tile t into stage t % 2
-        int stage = t & 1;
-        mbar_expect_tx(&bars->kv_full[stage], 2 * KV_BYTES);
-        for (int p = 0; p < pages_per_tile; ++p) {
-            int page = table_s[min(t * pages_per_tile + p, MAX_TABLE - 1)];
-            int row = (page * nkv + kvh) << page_shift;
-            tma_load_2d(k_s + stage * KV_BYTES + p * page_size * 128, &k_map, 0, row, &bars->kv_full[stage]);
-            tma_load_2d(v_s + stage * KV_BYTES + p * page_size * 128, &v_map, 0, row, &bars->kv_full[stage]);
+    if (warp == 4) {
+        // ---- copies: one thread ----
+        if (lane == 0) {
+            for (int t = 0; t < n_tiles; ++t) {
+                int stage = t % KV_STAGES;
+                if (t >= KV_STAGES && !mbar_wait(&bars->kv_empty[stage], (t / KV_STAGES - 1) & 1)) {
+                    bars->failed = 1;
+                    break;
+                }
+                mbar_expect_tx(&bars->kv_full[stage], 2 * KV_BYTES);
+                for (int p = 0; p < pages_per_tile; ++p) {
+                    int page = table_s[min(t * pages_per_tile + p, MAX_TABLE - 1)];
+                    int row = (page * nkv + kvh) << page_shift;
+                    tma_load_2d(k_s + stage * KV_BYTES + p * page_size * 128, &k_map, 0, row, &bars->kv_full[stage]);
+                    tma_load_2d(v_s + stage * KV_BYTES + p * page_size * 128, &v_map, 0, row, &bars->kv_full[stage]);
+                }
+            }
         }
-    };
-    if (tid == 0) {
-        mbar_expect_tx(&bars->q_full, Q_BYTES);
-        tma_load_2d(q_s, &q_map, head * HD, q0 + t0, &bars->q_full);
-        issue_kv(0);
-    }
-
-    int row = tid;                       // this thread's query row
-    bool exists = row < tile_rows;
-    int qpos = exists ? qpos_lo + row : -1;
-    int qlo = (window > 0 && qpos - window + 1 > 0) ? qpos - window + 1 : 0;
-    float m = -INFINITY, l = 0.f;
-    float o[HD];
-#pragma unroll
-    for (int d = 0; d < HD; ++d) o[d] = 0.f;
-    bool ok = mbar_wait(&bars->q_full, 0);
-    unsigned idesc_qk = instr_desc(false), idesc_pv = instr_desc(true);
-
-    for (int t = 0; t < n_tiles && ok; ++t) {
-        int stage = t & 1;
-        int key0 = key_begin + t * KT;
-        if (tid == 0) {
-            if (t + 1 < n_tiles) issue_kv(t + 1);  // stage (t+1)%2 was released by tile t-1's PV
-            if (mbar_wait(&bars->kv_full[stage], (t >> 1) & 1)) {
+    } else if (warp == 5) {
+        // ---- tensor core: one thread ----
+        if (lane == 0) {
+            unsigned idesc_qk = instr_desc(false), idesc_pv = instr_desc(true);
+            bool ok = mbar_wait(&bars->q_full, 0);
+            auto issue_s = [&](int t) {  // S(t) = Q K(t)^T into S buffer t & 1
+                int stage = t % KV_STAGES;
+                if (!mbar_wait(&bars->kv_full[stage], (t / KV_STAGES) & 1)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                unsigned qa = smem_u32(q_s), ka = smem_u32(k_s + stage * KV_BYTES);
+                unsigned ka = smem_u32(k_s + stage * KV_BYTES);
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks)  // 32 bytes further along k per step
-                    umma(tmem_s, smem_desc(qa + ks * 32), smem_desc(ka + ks * 32), idesc_qk, ks > 0);
-                umma_commit(&bars->s_done);
-            } else {
-                bars->failed = 1;
+                    umma_ta(tmem + (t & 1) * KT, tmem_q + ks * 8, smem_desc(ka + ks * 32), idesc_qk, ks > 0);
+                umma_commit(&bars->s_done[t & 1]);
+                return true;
+            };
+            ok = ok && issue_s(0);
+            for (int t = 0; t < n_tiles && ok; ++t) {
+                if (t + 1 < n_tiles) {
+                    // its S buffer held the weights of tile t - 1: that product must have read them
+                    if (t > 0 && !mbar_wait(&bars->o_done, (t - 1) & 1)) { ok = false; break; }
+                    ok = issue_s(t + 1);
+                }
+                if (!ok || !mbar_wait(&bars->p_ready[t & 1], (t >> 1) & 1)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                int stage = t % KV_STAGES;
+                unsigned va = smem_u32(v_s + stage * KV_BYTES);
+#pragma unroll
+                for (int ks = 0; ks < KT / 16; ++ks)  // P: 8 columns of two keys each; V: 16 keys = 2048 bytes
+                    umma_ta(tmem_o, tmem + (t & 1) * KT + ks * 8, smem_desc(va + ks * 2048), idesc_pv, (t > 0 || ks > 0) ? 1u : 0u);
+                umma_commit(&bars->o_done);
+                umma_commit(&bars->kv_empty[stage]);
             }
+            if (!ok) bars->failed = 1;
         }
-        if (!mbar_wait(&bars->s_done, t & 1)) { ok = false; break; }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        float s[KT];
-        tmem_ld64(s, tmem_s + lane_addr);
-        float tile_max = -INFINITY;
+    } else {
+        // ---- softmax: thread = query row = TMEM lane ----
+        int row = tid;
+        unsigned lane_addr = (unsigned)(warp * 32) << 16;  // this warp's 32 TMEM lanes
+        bool exists = row < tile_rows;
+        int qpos = exists ? qpos_lo + row : -1;
+        int qlo = (window > 0 && qpos - window + 1 > 0) ? qpos - window + 1 : 0;
+        // m: the maximum that the weights are taken against.  It follows the running maximum
+        // only when that has grown by more than 2^RESCALE_LAG (for any row of the warp), so
+        // that the accumulator in TMEM is rescaled on few tiles; weights stay below 2^RESCALE_LAG
+        // and the quotient of accumulator and sum is the same.
+        float m = -INFINITY, l = 0.f;
+        {   // this row of Q, two features to a column, as the first product's A operand
+            float qw[32];
+            uint4* q4 = reinterpret_cast<uint4*>(qw);
+            const uint4* src = reinterpret_cast<const uint4*>(q + ((size_t)(q0 + t0 + row) * nh + head) * HD);
 #pragma unroll
-        for (int j = 0; j < KT; ++j) {
-            int kpos = key0 + j;
-            bool valid = kpos <= qpos && kpos >= qlo;
-            s[j] = valid ? s[j] : -INFINITY;
-            tile_max = fmaxf(tile_max, s[j]);
+            for (int c = 0; c < HD / 8; ++c) q4[c] = exists ? src[c] : make_uint4(0u, 0u, 0u, 0u);
+            tmem_st32(qw, tmem_q + lane_addr);
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(&bars->q_full);
         }
-        float m_new = fmaxf(m, tile_max * scale_log2);
-        float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
-        float alpha = fast_exp2(m - m_safe);
-        m = m_new;
-        l *= alpha;
-        // weights, rounded to bfloat16, into the A operand tile: row `row`, 16-byte chunk c at
-        // chunk position c ^ (row & 7) of the row's 128 bytes
-        unsigned char* prow = p_s + row * 128;
-#pragma unroll
-        for (int c = 0; c < KT / 8; ++c) {
-            unsigned w[4];
-#pragma unroll
-            for (int h = 0; h < 4; ++h) {
-                float p0 = fast_exp2(fmaf(s[c * 8 + 2 * h], scale_log2, -m_safe));
-                float p1 = fast_exp2(fmaf(s[c * 8 + 2 * h + 1], scale_log2, -m_safe));
-                l += p0 + p1;
-                __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-                w[h] = *reinterpret_cast<unsigned*>(&pk);
-            }
-            *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic stores -> the tensor core's reads
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
-        if (tid == 0) {
+        bool ok = true;
+        for (int t = 0; t < n_tiles; ++t) {
+            int key0 = key_begin + t * KT;
+            if (!mbar_wait(&bars->s_done[t & 1], (t >> 1) & 1)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            unsigned pa = smem_u32(p_s), va = smem_u32(v_s + stage * KV_BYTES);
+            float s[KT];
+            tmem_ld64(s, tmem + (t & 1) * KT + lane_addr);
+            // inner tiles (every key visible to every row of the block) need no mask
+            bool inner = key0 + KT - 1 <= qpos_lo && (window <= 0 || key0 >= qpos_hi - window + 1);
+            if (!inner) {
 #pragma unroll
-            for (int ks = 0; ks < KT / 16; ++ks)  // P: 32 bytes along k; V: 16 keys = 2048 bytes
-                umma(tmem_o, smem_desc(pa + ks * 32), smem_desc(va + ks * 2048), idesc_pv, ks > 0);
-            umma_commit(&bars->o_done);
-        }
-        if (!mbar_wait(&bars->o_done, t & 1)) { ok = false; break; }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        float pv[HD];
-        tmem_ld64(pv, tmem_o + lane_addr);
-#pragma unroll
-        for (int d = 0; d < HD; ++d) o[d] = fmaf(o[d], alpha, pv[d]);
-        // the next tile's S overwrites TMEM and P: everybody must have read theirs
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
-    }
-    if (!ok) bars->failed = 1;
-    if (exists && ok) {
-        float inv = l > 0.f ? 1.0f / l : 0.f;
-        bf16* orow = out + ((size_t)(q0 + t0 + row) * nh + head) * HD;
-#pragma unroll
-        for (int c = 0; c < HD / 8; ++c) {
-            unsigned w[4];
-#pragma unroll
-            for (int h = 0; h < 4; ++h) {
-                __nv_bfloat162 pk = __floats2bfloat162_rn(o[c * 8 + 2 * h] * inv, o[c * 8 + 2 * h + 1] * inv);
-                w[h] = *reinterpret_cast<unsigned*>(&pk);
+                for (int j = 0; j < KT; ++j) {
+                    int kpos = key0 + j;
+                    s[j] = (kpos <= qpos && kpos >= qlo) ? s[j] : -INFINITY;
+                }
             }
-            *reinterpret_cast<uint4*>(orow + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+            float mx[8];  // eight independent chains: a warp has a scheduler to itself most of the time
+#pragma unroll
+            for (int j = 0; j < 8; ++j) mx[j] = s[j];
+#pragma unroll
+            for (int j = 8; j < KT; ++j) mx[j & 7] = fmaxf(mx[j & 7], s[j]);
+            float tile_max = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+            float m_cand = fmaxf(m, tile_max * scale_log2);
+            bool rescale = __any_sync(0xffffffffu, m_cand > m + RESCALE_LAG);
+            float alpha = 1.f;
+            if (rescale) {
+                alpha = fast_exp2(m - ((m_cand == -INFINITY) ? 0.f : m_cand));
+                m = m_cand;
+                l *= alpha;
+            }
+            float m_safe = (m == -INFINITY) ? 0.f : m;
+            // weights, rounded to bfloat16 and packed two to a column, over this row of S: the
+            // second product's A operand
+            float pw[32];
+            unsigned* w = reinterpret_cast<unsigned*>(pw);
+            float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int c = 0; c < KT / 2; ++c) {
+                float p0 = fast_exp2(fmaf(s[2 * c], scale_log2, -m_safe));
+                float p1 = fast_exp2(fmaf(s[2 * c + 1], scale_log2, -m_safe));
+                ls[c & 3] += p0 + p1;
+                __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+                w[c] = *reinterpret_cast<unsigned*>(&pk);
+            }
+            l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+            tmem_st32(pw, tmem + (t & 1) * KT + lane_addr);
+            if (t > 0) {
+                // the previous tile's product has had this tile's softmax to finish; waiting for
+                // it here every tile also keeps this barrier's phase in step
+                if (!mbar_wait(&bars->o_done, (t - 1) & 1)) { ok = false; break; }
+                if (rescale) {
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        float acc[32];
+                        tmem_ld32(acc, tmem_o + half * 32 + lane_addr);
+#pragma unroll
+                        for (int d = 0; d < 32; ++d) acc[d] *= alpha;
+                        tmem_st32(acc, tmem_o + half * 32 + lane_addr);
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(&bars->p_ready[t & 1]);
+        }
+        if (ok && n_tiles > 0 && !mbar_wait(&bars->o_done, (n_tiles - 1) & 1)) ok = false;
+        if (!ok) bars->failed = 1;
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            float inv = l > 0.f ? 1.0f / l : 0.f;
+            bf16* orow = out + ((size_t)(q0 + t0 + row) * nh + head) * HD;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                float acc[32];
+                tmem_ld32(acc, tmem_o + half * 32 + lane_addr);
+                if (exists) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        unsigned w[4];
+#pragma unroll
+                        for (int h = 0; h < 4; ++h) {
+                            __nv_bfloat162 pk = __floats2bfloat162_rn(acc[c * 8 + 2 * h] * inv, acc[c * 8 + 2 * h + 1] * inv);
+                            w[h] = *reinterpret_cast<unsigned*>(&pk);
+                        }
+                        *reinterpret_cast<uint4*>(orow + half * 32 + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -333,7 +420,7 @@ bool make_map(CUtensorMap* map, const void* base, long long rows, long long cols
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
-constexpr size_t SMEM_BYTES = Q_BYTES + 4 * KV_BYTES + P_BYTES + MAX_TABLE * 4 + sizeof(Barriers) + 1024;
+constexpr size_t SMEM_BYTES = 2 * KV_STAGES * KV_BYTES + MAX_TABLE * 4 + sizeof(Barriers) + 1024;
 }  // namespace
 
 // 1 if the tcgen05 prefill kernel can take this geometry: pages of 8..64 tokens, at most
@@ -354,9 +441,9 @@ IE_API int ie_attention_prefill_tc5(const void* q, const void* k_cache, const vo
         return (int)cudaErrorInvalidValue;
     int page_shift = 0;
     while ((1 << page_shift) < page_size) ++page_shift;
-    CUtensorMap qm, km, vm;
+    CUtensorMap km, vm;
     long long kv_rows = (long long)total_pages * nkv * page_size;
-    if (!make_map(&qm, q, num_tokens, (long long)nh * HD, BM) || !make_map(&km, k_cache, kv_rows, HD, page_size) ||
+    if (!make_map(&km, k_cache, kv_rows, HD, page_size) ||
         !make_map(&vm, v_cache, kv_rows, HD, page_size))
         return (int)cudaErrorNotSupported;
     static bool configured = false;
@@ -367,7 +454,7 @@ IE_API int ie_attention_prefill_tc5(const void* q, const void* k_cache, const vo
         configured = true;
     }
     return ie_launch(attention_prefill_tc5_kernel, dim3(max_tiles, nh), dim3(THREADS), SMEM_BYTES,
-                     (cudaStream_t)stream, qm, km, vm, tables, table_width, cu_q, ctx_lens, (bf16*)out, num_seqs,
+                     (cudaStream_t)stream, (const bf16*)q, km, vm, tables, table_width, cu_q, ctx_lens, (bf16*)out, num_seqs,
                      nh, nkv, page_shift, total_pages, scale * 1.4426950408889634f, window, err);
 }
 

@@ -141,9 +141,18 @@ def build_attention(head_dim: int) -> Path:
                          [f"-DIE_HD={head_dim}"])
 
 
-def build_all() -> list[Path]:
-    """Every library the package can load (the build check compiles them all)."""
+def build_all(prune: bool = True) -> list[Path]:
+    """Every library the package can load (the build check compiles them all).  With `prune`,
+    libraries of this package in the build folder that belong to older sources are removed."""
     libs = [build_core()]
     with ThreadPoolExecutor(max_workers=os.cpu_count() or 2) as pool:
         libs += list(pool.map(build_attention, ATTENTION_HEAD_DIMS))
+    if prune:
+        keep = {lib.name for lib in libs}
+        for old in build_dir().glob("libie_b200_*.so"):
+            if old.name not in keep:
+                try:
+                    old.unlink()
+                except OSError:
+                    pass
     return libs

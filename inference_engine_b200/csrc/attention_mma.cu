@@ -112,6 +112,36 @@ __device__ __forceinline__ int issue_kv(bf16* ktile, bf16* vtile, const TilePage
                                         const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                                         int key0, int lo, int hi, int kvh, int nkv, int page_shift,
                                         int total_pages, int tid, int* err) {
+    if constexpr (REPORT && NTHREADS == 32 && 32 % C == 0) {
+        // A warp's own tile (the decode kernel): every instruction copies R whole rows, so the
+        // shared-memory offsets are constants of the lane and the unrolled iteration, and the
+        // global offset needs one 64-bit product per page.  (The decode kernel is bound by
+        // the issue of these copies; the general form below costs twice the instructions.)
+        constexpr int R = 32 / C;                 // rows per instruction
+        constexpr int V = R >= 8 ? 1 : 8 / R;     // distinct (row & 7) patterns over iterations
+        const int sub = tid / C, c = tid % C;
+        const int page_mask = (1 << page_shift) - 1;
+        const unsigned ks = (unsigned)__cvta_generic_to_shared(ktile), vs = (unsigned)__cvta_generic_to_shared(vtile);
+        unsigned dst_lane[V];
+#pragma unroll
+        for (int v = 0; v < V; ++v) dst_lane[v] = (unsigned)((sub * C + swz(sub + v * R, c)) * 16);
+#pragma unroll
+        for (int i = 0; i < KT / R; ++i) {
+            int kpos = key0 + sub + i * R;
+            int page = pg.page[i];
+            bool in_range = kpos >= lo && kpos <= hi;
+            bool valid = in_range && (unsigned)page < (unsigned)total_pages;
+            if (in_range && !valid) ie_report(err, page < 0 ? IE_ERR_TABLE : IE_ERR_PAGE, page, kpos);
+            size_t off = valid ? (((size_t)(page * nkv + kvh)) << page_shift) * HD +
+                                     (size_t)((kpos & page_mask) * HD + c * 8)
+                               : 0;
+            unsigned dst = (unsigned)(i * R * C * 16) + dst_lane[((i * R) & 7) / R % V];
+            int bytes = valid ? 16 : 0;  // 0: nothing is read, the 16 bytes are zero-filled
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(ks + dst), "l"(k_cache + off), "r"(bytes));
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(vs + dst), "l"(v_cache + off), "r"(bytes));
+        }
+        return 0x7fffffff;
+    }
     int page_mask = (1 << page_shift) - 1;
     int bad = 0x7fffffff;
 #pragma unroll
@@ -293,17 +323,107 @@ __device__ __forceinline__ void finish_rows(RowState& st) {
 // Partials for splits > 1: part_o[((seq * nkv + kvh) * splits + split) * 16 + row][HD],
 // part_ml[... ][2] = (maximum in log2 units, sum).
 // -------------------------------------------------------------------------------------------------
-constexpr int DWARPS = 8;
+constexpr int DWARPS = 8;   // warps of a block that has an SM to itself (192 KB of tiles in flight)
+constexpr int DWARPS_SHARED = 4;  // warps of a block when more blocks than SMs run: two blocks share an SM
 constexpr int DSTAGES = 3;
+template <int NWARPS>
+__device__ __forceinline__ void decode_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(NWARPS * 32) : "memory"); }
 
-__global__ void __launch_bounds__(DWARPS * 32)
+// The end of a decode block (its 8 x 32 compute threads call this together): the warps' partial
+// results are merged through shared memory; with one split the block writes the output, with
+// more it writes its partial result and the block that finishes last for this (request,
+// key/value head) merges all splits, always in the order 0, 1, 2, ...  The ticket counter goes
+// back to zero for the next launch.  Barrier 1 is used, so that other warps of the block need
+// not take part.
+template <int NWARPS>
+__device__ __forceinline__ void decode_merge_store(RowState& st, unsigned char* smem_raw, int* is_last, int warp,
+                                                   int lane, int rows, int G, int q0, int seq, int kvh, int split,
+                                                   int num_splits, int nh, int nkv, bf16* __restrict__ out,
+                                                   float* __restrict__ part_o, float* __restrict__ part_ml,
+                                                   int* __restrict__ tickets) {
+    constexpr int WARPS = NWARPS;
+    int tid = warp * 32 + lane;
+    finish_rows(st);
+    decode_barrier<NWARPS>();  // every warp is done with its tiles: the shared memory is reused below
+    // [warp][row] m, l and [warp][row][HD] o in shared memory
+    float* sm_ml = reinterpret_cast<float*>(smem_raw);            // [WARPS][16][2]
+    float* sm_o = sm_ml + WARPS * MAX_ROWS * 2;                   // [WARPS][16][HD]
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        int row = (lane >> 2) + r * 8;
+        if ((lane & 3) == 0) {
+            sm_ml[(warp * MAX_ROWS + row) * 2] = st.m[r];
+            sm_ml[(warp * MAX_ROWS + row) * 2 + 1] = st.l[r];
+        }
+#pragma unroll
+        for (int d = 0; d < DT; ++d) {
+            float* dst = sm_o + ((size_t)(warp * MAX_ROWS + row)) * HD + d * 8 + (lane & 3) * 2;
+            dst[0] = st.o[d][r * 2];
+            dst[1] = st.o[d][r * 2 + 1];
+        }
+    }
+    decode_barrier<NWARPS>();
+    for (int idx = tid; idx < rows * HD; idx += WARPS * 32) {
+        int row = idx / HD, d = idx - row * HD;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) m = fmaxf(m, sm_ml[(w * MAX_ROWS + row) * 2]);
+        float m_safe = (m == -INFINITY) ? 0.f : m;
+        float l = 0.f, o = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+            float f = exp2f(sm_ml[(w * MAX_ROWS + row) * 2] - m_safe);
+            l += sm_ml[(w * MAX_ROWS + row) * 2 + 1] * f;
+            o += sm_o[((size_t)(w * MAX_ROWS + row)) * HD + d] * f;
+        }
+        if (num_splits == 1) {
+            int tok = row / G, g = row - tok * G;
+            out[((size_t)(q0 + tok) * nh + kvh * G + g) * HD + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+        } else {
+            size_t p = (((size_t)seq * nkv + kvh) * num_splits + split) * MAX_ROWS + row;
+            part_o[p * HD + d] = o;
+            if (d == 0) { part_ml[p * 2] = m; part_ml[p * 2 + 1] = l; }
+        }
+    }
+    if (num_splits == 1) return;
+    __threadfence();
+    decode_barrier<NWARPS>();
+    if (tid == 0) {
+        int ticket = atomicAdd(&tickets[seq * nkv + kvh], 1);
+        *is_last = (ticket == num_splits - 1);
+        if (*is_last) tickets[seq * nkv + kvh] = 0;
+    }
+    decode_barrier<NWARPS>();
+    if (!*is_last) return;
+    __threadfence();
+    size_t base = ((size_t)seq * nkv + kvh) * num_splits * MAX_ROWS;
+    for (int idx = tid; idx < rows * HD; idx += WARPS * 32) {
+        int row = idx / HD, d = idx - row * HD;
+        float m = -INFINITY;
+        for (int s = 0; s < num_splits; ++s) m = fmaxf(m, __ldcg(part_ml + (base + (size_t)s * MAX_ROWS + row) * 2));
+        float m_safe = (m == -INFINITY) ? 0.f : m;
+        float l = 0.f, o = 0.f;
+        for (int s = 0; s < num_splits; ++s) {
+            size_t p = base + (size_t)s * MAX_ROWS + row;
+            float f = exp2f(__ldcg(part_ml + p * 2) - m_safe);
+            l += __ldcg(part_ml + p * 2 + 1) * f;
+            o += __ldcg(part_o + p * HD + d) * f;
+        }
+        int tok = row / G, g = row - tok * G;
+        out[((size_t)(q0 + tok) * nh + kvh * G + g) * HD + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+    }
+}
+
+
+template <int NWARPS>
+__global__ void __launch_bounds__(NWARPS * 32)
 attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache,
                         const bf16* __restrict__ v_cache, const int* __restrict__ tables,
                         int table_width, const int* __restrict__ cu_q, const int* __restrict__ ctx_lens,
                         bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                         int* __restrict__ tickets, int nh, int nkv, int page_shift, int total_pages,
                         float scale_log2, int window, int num_splits, int* err) {
-    constexpr int KT = KT_DECODE, TILE_ELEMS = KT * HD, WARPS = DWARPS;
+    constexpr int KT = KT_DECODE, TILE_ELEMS = KT * HD, WARPS = NWARPS;
     __shared__ int is_last;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
@@ -329,28 +449,51 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
         for (int s = 0; s < DSTAGES; ++s)
             fetch_pages<KT, 32>(pg[s], table, table_width, (j0 + s * stride) * KT, 0, 0x7fffffff, page_shift, lane);
     }
-    ie_pdl_wait();
     int qlen = q1 - q0;
     int rows = qlen * G;
-    if (rows > MAX_ROWS || qlen <= 0) return;  // the prefill kernel takes this request
     int first_qpos = ctx - qlen, hi = ctx - 1;
     int lo = (window > 0 && first_qpos - window + 1 > 0) ? first_qpos - window + 1 : 0;
     int n_tiles = (hi - lo) / KT + 1;         // tiles of the whole request
+    // 2. the first tiles' keys and values.  Tiles that lie wholly before this step's tokens
+    //    were written by earlier steps: their copies start before the wait for the previous
+    //    kernel and overlap it.  A warp whose first tiles reach this step's tokens (short
+    //    contexts) starts its copies after the wait.
+    bool ahead = early && qlen > 0 && rows <= MAX_ROWS;
+#pragma unroll
+    for (int s = 0; s < DSTAGES - 1; ++s) {
+        int j = j0 + s * stride;
+        ahead = ahead && (j >= n_tiles || (j + 1) * KT <= first_qpos);
+    }
+    if (ahead) {
+#pragma unroll
+        for (int s = 0; s < DSTAGES - 1; ++s) {
+            int j = j0 + s * stride;
+            if (j < n_tiles) {
+                bf16* st_k = ring + (size_t)s * 2 * TILE_ELEMS;
+                issue_kv<KT, 32, true>(st_k, st_k + TILE_ELEMS, pg[s], k_cache, v_cache, lo + j * KT, lo, hi,
+                                       kvh, nkv, page_shift, total_pages, lane, err);
+            }
+            cp_async_commit();
+        }
+    }
+    ie_pdl_wait();
+    if (rows > MAX_ROWS || qlen <= 0) return;  // the prefill kernel takes this request
     if (!early) {
 #pragma unroll
         for (int s = 0; s < DSTAGES; ++s)
             fetch_pages<KT, 32>(pg[s], table, table_width, lo + (j0 + s * stride) * KT, lo, hi, page_shift, lane);
     }
-    // 2. the first tiles' keys and values
+    if (!ahead) {
 #pragma unroll
-    for (int s = 0; s < DSTAGES - 1; ++s) {
-        int j = j0 + s * stride;
-        if (j < n_tiles) {
-            bf16* st_k = ring + (size_t)s * 2 * TILE_ELEMS;
-            issue_kv<KT, 32, true>(st_k, st_k + TILE_ELEMS, pg[s], k_cache, v_cache, lo + j * KT, lo, hi,
-                                   kvh, nkv, page_shift, total_pages, lane, err);
+        for (int s = 0; s < DSTAGES - 1; ++s) {
+            int j = j0 + s * stride;
+            if (j < n_tiles) {
+                bf16* st_k = ring + (size_t)s * 2 * TILE_ELEMS;
+                issue_kv<KT, 32, true>(st_k, st_k + TILE_ELEMS, pg[s], k_cache, v_cache, lo + j * KT, lo, hi,
+                                       kvh, nkv, page_shift, total_pages, lane, err);
+            }
+            cp_async_commit();
         }
-        cp_async_commit();
     }
     // 3. the queries (they needed cu_q) while those are in flight
     int qpos[1][2], qlo[1][2];
@@ -394,78 +537,8 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
         __syncwarp();
     }
     cp_async_wait<0>();
-    finish_rows(st);
-    __syncthreads();  // every warp is done with its tiles: the shared memory is reused below
-
-    // merge the warps: [warp][row] m, l and [warp][row][HD] o in shared memory
-    float* sm_ml = reinterpret_cast<float*>(smem_raw);            // [WARPS][16][2]
-    float* sm_o = sm_ml + WARPS * MAX_ROWS * 2;                   // [WARPS][16][HD]
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        int row = (lane >> 2) + r * 8;
-        if ((lane & 3) == 0) {
-            sm_ml[(warp * MAX_ROWS + row) * 2] = st.m[r];
-            sm_ml[(warp * MAX_ROWS + row) * 2 + 1] = st.l[r];
-        }
-#pragma unroll
-        for (int d = 0; d < DT; ++d) {
-            float* dst = sm_o + ((size_t)(warp * MAX_ROWS + row)) * HD + d * 8 + (lane & 3) * 2;
-            dst[0] = st.o[d][r * 2];
-            dst[1] = st.o[d][r * 2 + 1];
-        }
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < rows * HD; idx += WARPS * 32) {
-        int row = idx / HD, d = idx - row * HD;
-        float m = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < WARPS; ++w) m = fmaxf(m, sm_ml[(w * MAX_ROWS + row) * 2]);
-        float m_safe = (m == -INFINITY) ? 0.f : m;
-        float l = 0.f, o = 0.f;
-#pragma unroll
-        for (int w = 0; w < WARPS; ++w) {
-            float f = exp2f(sm_ml[(w * MAX_ROWS + row) * 2] - m_safe);
-            l += sm_ml[(w * MAX_ROWS + row) * 2 + 1] * f;
-            o += sm_o[((size_t)(w * MAX_ROWS + row)) * HD + d] * f;
-        }
-        if (num_splits == 1) {
-            int tok = row / G, g = row - tok * G;
-            out[((size_t)(q0 + tok) * nh + kvh * G + g) * HD + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
-        } else {
-            size_t p = (((size_t)seq * nkv + kvh) * num_splits + split) * MAX_ROWS + row;
-            part_o[p * HD + d] = o;
-            if (d == 0) { part_ml[p * 2] = m; part_ml[p * 2 + 1] = l; }
-        }
-    }
-    if (num_splits == 1) return;
-    // The block that finishes last for this (request, key/value head) merges all splits, always
-    // in the order 0, 1, 2, ...  The ticket counter goes back to zero for the next launch.
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int ticket = atomicAdd(&tickets[seq * nkv + kvh], 1);
-        is_last = (ticket == num_splits - 1);
-        if (is_last) tickets[seq * nkv + kvh] = 0;
-    }
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    size_t base = ((size_t)seq * nkv + kvh) * num_splits * MAX_ROWS;
-    for (int idx = threadIdx.x; idx < rows * HD; idx += WARPS * 32) {
-        int row = idx / HD, d = idx - row * HD;
-        float m = -INFINITY;
-        for (int s = 0; s < num_splits; ++s) m = fmaxf(m, __ldcg(part_ml + (base + (size_t)s * MAX_ROWS + row) * 2));
-        float m_safe = (m == -INFINITY) ? 0.f : m;
-        float l = 0.f, o = 0.f;
-        for (int s = 0; s < num_splits; ++s) {
-            size_t p = base + (size_t)s * MAX_ROWS + row;
-            float f = exp2f(__ldcg(part_ml + p * 2) - m_safe);
-            l += __ldcg(part_ml + p * 2 + 1) * f;
-            o += __ldcg(part_o + p * HD + d) * f;
-        }
-        int tok = row / G, g = row - tok * G;
-        out[((size_t)(q0 + tok) * nh + kvh * G + g) * HD + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
-    }
+    decode_merge_store<NWARPS>(st, smem_raw, &is_last, warp, lane, rows, G, q0, seq, kvh, split, num_splits, nh, nkv, out,
+                       part_o, part_ml, tickets);
 }
 
 // -------------------------------------------------------------------------------------------------
@@ -590,10 +663,12 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
     }
 }
 
-constexpr size_t DECODE_SMEM_TILES = (size_t)DWARPS * DSTAGES * 2 * KT_DECODE * HD * sizeof(bf16);
-constexpr size_t DECODE_MERGE_SMEM = (size_t)DWARPS * MAX_ROWS * (2 + HD) * sizeof(float);
+constexpr size_t decode_smem(int warps) {
+    size_t tiles = (size_t)warps * DSTAGES * 2 * KT_DECODE * HD * sizeof(bf16);
+    size_t merge = (size_t)warps * MAX_ROWS * (2 + HD) * sizeof(float);
+    return tiles > merge ? tiles : merge;
+}
 constexpr size_t PREFILL_SMEM = (size_t)3 * 2 * KT_PREFILL * HD * sizeof(bf16);
-constexpr size_t DECODE_SMEM = DECODE_SMEM_TILES > DECODE_MERGE_SMEM ? DECODE_SMEM_TILES : DECODE_MERGE_SMEM;
 }  // namespace
 
 IE_API int ie_attention_head_dim() { return HD; }
@@ -607,6 +682,51 @@ IE_API long long ie_attention_decode_scratch_floats(int num_seqs, int nkv, int n
     if (num_splits <= 1) return 0;
     return (long long)num_seqs * nkv * num_splits * MAX_ROWS * (HD + 2);
 }
+
+namespace {
+template <int NWARPS>
+int launch_decode_as(const void* q, const void* k_cache, const void* v_cache, const int* tables, int table_width,
+                     const int* cu_q, const int* ctx_lens, void* out, float* part_o, float* part_ml, int* tickets,
+                     int num_seqs, int nh, int nkv, int page_shift, int total_pages, float scale, int window,
+                     int num_splits, int* err, cudaStream_t s) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<NWARPS>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(NWARPS));
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid(num_seqs, nkv, num_splits);
+    return ie_launch(attention_decode_kernel<NWARPS>, grid, dim3(NWARPS * 32), decode_smem(NWARPS), s,
+                     (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, tables, table_width, cu_q,
+                     ctx_lens, (bf16*)out, part_o, part_ml, tickets, nh, nkv, page_shift, total_pages,
+                     scale * 1.4426950408889634f, window, num_splits, err);
+}
+
+// With at most one block per SM a block takes the SM's whole shared memory for tiles in flight;
+// with more blocks than SMs, blocks of half the size run two to an SM, so that one block's
+// start-up and merge overlap the other's streaming.  The choice depends on the grid alone.
+int launch_decode(const void* q, const void* k_cache, const void* v_cache, const int* tables, int table_width,
+                  const int* cu_q, const int* ctx_lens, void* out, float* part_o, float* part_ml, int* tickets,
+                  int num_seqs, int nh, int nkv, int page_shift, int total_pages, float scale, int window,
+                  int num_splits, int* err, cudaStream_t s) {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+    }
+    long long blocks = (long long)num_seqs * nkv * num_splits;
+    if (blocks > sms)
+        return launch_decode_as<DWARPS_SHARED>(q, k_cache, v_cache, tables, table_width, cu_q, ctx_lens, out, part_o,
+                                               part_ml, tickets, num_seqs, nh, nkv, page_shift, total_pages, scale,
+                                               window, num_splits, err, s);
+    return launch_decode_as<DWARPS>(q, k_cache, v_cache, tables, table_width, cu_q, ctx_lens, out, part_o, part_ml,
+                                    tickets, num_seqs, nh, nkv, page_shift, total_pages, scale, window, num_splits,
+                                    err, s);
+}
+}  // namespace
 
 // Requests with (tokens x group size) <= 16 rows.  With num_splits > 1 the kernel needs
 // `scratch` (ie_attention_decode_scratch_floats floats; contents do not matter) and `tickets`
@@ -623,21 +743,11 @@ IE_API int ie_attention_decode(const void* q, const void* k_cache, const void* v
         return (int)cudaErrorInvalidValue;
     int page_shift = 0;
     while ((1 << page_shift) < page_size) ++page_shift;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_SMEM);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
-    cudaStream_t s = (cudaStream_t)stream;
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)num_seqs * nkv * num_splits * MAX_ROWS * HD : nullptr;
-    dim3 grid(num_seqs, nkv, num_splits);
-    return ie_launch(attention_decode_kernel, grid, dim3(DWARPS * 32), DECODE_SMEM, s,
-                     (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, tables, table_width, cu_q,
-                     ctx_lens, (bf16*)out, part_o, part_ml, tickets, nh, nkv, page_shift, total_pages,
-                     scale * 1.4426950408889634f, window, num_splits, err);
+    return launch_decode(q, k_cache, v_cache, tables, table_width, cu_q, ctx_lens, out, part_o, part_ml, tickets,
+                         num_seqs, nh, nkv, page_shift, total_pages, scale, window, num_splits, err,
+                         (cudaStream_t)stream);
 }
 
 // Requests with more than 16 rows.  `max_tiles` bounds the number of query tiles over all

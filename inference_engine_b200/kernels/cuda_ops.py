@@ -70,6 +70,8 @@ class CudaOps:
         # which kernel takes few-row bfloat16 products: "tma" (TMA-fed ring), "cp" (cp.async
         # rings per warp), "auto" (cp for few output features, the vendor library otherwise)
         self.attn_tc5 = os.environ.get("IE_B200_ATTN_TC5", "1") != "0"  # tcgen05 prefill attention
+        # the decode kernel cuts contexts until about this many blocks run (one block per SM)
+        self.decode_split_target = int(os.environ.get("IE_B200_DECODE_SPLIT_TARGET", 128))
         self.few_row_gemm = os.environ.get("IE_B200_FEW_ROW_GEMM", "tma")
         # ... for matrices with fewer 128-feature tiles than half the SMs (they need their inner
         # dimension cut to occupy the GPU, which the vendor library does not do); measured on
@@ -262,7 +264,7 @@ class CudaOps:
         few such blocks (small batches); the number depends on the batch alone, never on the
         contexts' lengths, so that a captured launch stays valid."""
         blocks = max(num_seqs * nkv, 1)
-        return max(1, min(64 // blocks, 32))
+        return max(1, min(self.decode_split_target // blocks, 32))
 
     def paged_attention(self, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, page_size,
                         scale, window, out) -> None:

@@ -52,8 +52,9 @@ class DecodeGraphs:
             return None
         return (bucket, handle)
 
-    def run_prepared(self, prepared, tokens: list[int]):
-        """Fill the sampled tokens into a step packed by :meth:`prepare` and replay it."""
+    def run_prepared(self, prepared, tokens, count: int | None = None):
+        """Fill the sampled tokens (a list, or a device tensor of which the first ``count`` are
+        taken) into a step packed by :meth:`prepare` and replay it."""
         bucket, handle = prepared
         if bucket not in self._graphs or self._version != self.runner.ws.version:
             return None
@@ -61,7 +62,7 @@ class DecodeGraphs:
         graph, logits, _ = self._graphs[bucket]
         graph.replay()
         self.replays += 1
-        return logits[: len(tokens)]
+        return logits[: len(tokens) if count is None else count]
 
     def can_run(self, entries) -> bool:
         if not entries or any(len(e.tokens) != 1 for e in entries):

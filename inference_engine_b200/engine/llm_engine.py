@@ -15,6 +15,7 @@ and only used for text deltas and stop strings.  Not thread-safe.
 from __future__ import annotations
 
 import itertools
+import os
 import random
 import time
 from collections import deque
@@ -74,6 +75,8 @@ class LLMEngine:
         self._requests: dict[str, Sequence] = {}
         self._rng = random.Random()
         self._prepared = None
+        self._ahead = None  # a decode step launched before the previous step's tokens were fetched
+        self.launch_ahead = os.environ.get("IE_B200_LAUNCH_AHEAD", "1") != "0"
         self.step_log: deque[dict] = deque(maxlen=240)
         self.steps_total = self.generated_total = self.finished_total = 0
         self.prompt_tokens_total = 0
@@ -153,12 +156,19 @@ class LLMEngine:
         started = time.perf_counter()
         preempted_before = self.scheduler.num_preemptions
         logits = None
+        ahead, self._ahead = self._ahead, None
         prepared, self._prepared = self._prepared, None
-        if prepared is not None and self._prepared_still_valid(prepared):
+        if ahead is not None:
+            # This step is already running on the device (see _launch_ahead).
+            seqs, pending, logits = ahead
+            sampled, counts, used_graph, decode_tokens = seqs, [0] * len(seqs), True, len(seqs)
+        elif prepared is not None and self._prepared_still_valid(prepared):
             # Steady decoding: this step was packed while the device worked on the last one.
             seqs = prepared[0]
             logits = self.graphs.run_prepared(prepared[1], [s.output_ids[-1] for s in seqs])
-        if logits is not None:
+        if ahead is not None:
+            pass
+        elif logits is not None:
             sampled, counts, used_graph = seqs, [1] * len(seqs), True
             decode_tokens = len(seqs)
         else:
@@ -199,15 +209,22 @@ class LLMEngine:
 
         outputs: list[RequestOutput] = []
         if sampled:
-            params = [s.params for s in sampled]
-            needs_history = any(p.repetition_penalty != 1.0 for p in params)
-            pending = self.sampler.launch(
-                logits, params, [s.seed for s in sampled], [len(s.output_ids) for s in sampled],
-                [s.all_ids for s in sampled] if needs_history else None)
+            if ahead is None:
+                params = [s.params for s in sampled]
+                needs_history = any(p.repetition_penalty != 1.0 for p in params)
+                pending = self.sampler.launch(
+                    logits, params, [s.seed for s in sampled], [len(s.output_ids) for s in sampled],
+                    [s.all_ids for s in sampled] if needs_history else None)
             if used_graph and len(sampled) == len(seqs):
-                self._prepared = self._prepare_next(seqs)  # while the device is busy
+                # while the device is busy: start the next step on the tokens it is sampling,
+                # or at least pack that step's index data
+                self._ahead = self._launch_ahead(seqs, pending)
+                if self._ahead is None:
+                    self._prepared = self._prepare_next(seqs)
             tokens, logprobs = self.sampler.collect(pending)
             for row, (seq, token) in enumerate(zip(sampled, tokens)):
+                if self._requests.get(seq.request_id) is not seq:
+                    continue  # it ended or was aborted after this step had been launched ahead
                 seq.output_ids.append(token)
                 text, finished, reason = seq.processor.process(token)
                 out = RequestOutput(seq.request_id, token, text, finished, reason,
@@ -220,6 +237,9 @@ class LLMEngine:
                     self.scheduler.finish(seq, reason)
                     self._requests.pop(seq.request_id, None)
                 outputs.append(out)
+            if self._ahead is not None and not any(
+                    self._requests.get(s.request_id) is s for s in self._ahead[0]):
+                self._ahead = None  # nobody is left to take that step's tokens
         if self.debug_checks:
             self.cache.check_invariants()
             self.ops.check_errors()
@@ -256,6 +276,31 @@ class LLMEngine:
             positions.append(pos)
         handle = self.graphs.prepare([s.seq_id for s in seqs], positions)
         return (list(seqs), handle) if handle is not None else None
+
+    # One step further: with greedy or seeded sampling that needs nothing from the host (no
+    # repetition penalty, no log-probabilities) the next decode step can run on the tokens the
+    # device is sampling right now.  It is launched before those tokens are fetched, so the
+    # device never waits for the host between decode steps.  What the host learns too late (a
+    # stop token, an abort) costs one row of that step, which is dropped; its cache page goes
+    # back with the request's other pages, and everything is ordered on one stream.
+
+    def _launch_ahead(self, seqs: list[Sequence], pending):
+        if not self.launch_ahead or self.graphs is None:
+            return None
+        if any(s.params.repetition_penalty != 1.0 or s.params.logprobs for s in seqs):
+            return None
+        prepared = self._prepare_next(seqs)
+        if prepared is None:
+            return None
+        logits = self.graphs.run_prepared(prepared[1], pending[0], count=len(seqs))
+        if logits is None:
+            return None
+        for seq in seqs:
+            seq.num_computed += 1
+            self.cache.release_behind_window(seq.seq_id, seq.num_computed)
+        nxt = self.sampler.launch(logits, [s.params for s in seqs], [s.seed for s in seqs],
+                                  [len(s.output_ids) + 1 for s in seqs], None)
+        return (list(seqs), nxt, logits)
 
     def _prepared_still_valid(self, prepared) -> bool:
         seqs = prepared[0]

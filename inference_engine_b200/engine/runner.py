@@ -198,10 +198,16 @@ class ModelRunner:
         entries = [StepEntry(r, [0], p, [0]) for r, p in zip(req_ids, positions)]
         return self._build_decode_context(entries, pad_to_seqs, table_width, views=False, defer=True)
 
-    def commit_prepared(self, handle, tokens: list[int]) -> None:
+    def commit_prepared(self, handle, tokens) -> None:
+        """``tokens``: the step's token ids as a list, or as a 32-bit device tensor (the ids a
+        sampling kernel is still writing: they go from device to device, in stream order)."""
         turn, off, tok_at, count = handle
-        self._staging_host[turn][tok_at: tok_at + count] = self._torch.tensor(tokens, dtype=self._torch.int32)
+        on_device = not isinstance(tokens, (list, tuple))
+        if not on_device:
+            self._staging_host[turn][tok_at: tok_at + count] = self._torch.tensor(tokens, dtype=self._torch.int32)
         self._staging_dev[:off].copy_(self._staging_host[turn][:off], non_blocking=True)
+        if on_device:
+            self._staging_dev[tok_at: tok_at + count].copy_(tokens[:count], non_blocking=True)
         if self._staging_events[turn] is not None:
             self._staging_events[turn].record()
             self._staging_used[turn] = True

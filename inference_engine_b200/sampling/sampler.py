@@ -19,12 +19,23 @@ class Sampler:
         import torch
 
         self.ops, self.device, self.vocab_size, self.torch = ops, device, vocab_size, torch
-        self._tokens = torch.empty(0, dtype=torch.int32, device=device)
+        # Two sets of output buffers in turn: the engine may start the next step, which reads
+        # this step's tokens on the device, and its sampling before it has fetched these.
+        self._tokens = [torch.empty(0, dtype=torch.int32, device=device) for _ in range(2)]
+        self._host = [None, None]     # pinned copies of the tokens
+        self._events = [None, None]
+        self._turn = 0
 
     def _out(self, rows: int):
-        if self._tokens.numel() < rows:
-            self._tokens = self.torch.empty(max(rows, 64), dtype=self.torch.int32, device=self.device)
-        return self._tokens[:rows]
+        i = self._turn = 1 - self._turn
+        if self._tokens[i].numel() < rows:
+            torch = self.torch
+            n = max(rows, 64)
+            self._tokens[i] = torch.empty(n, dtype=torch.int32, device=self.device)
+            pinned = torch.device(self.device).type == "cuda"
+            self._host[i] = torch.empty(n, dtype=torch.int32, pin_memory=pinned)
+            self._events[i] = torch.cuda.Event() if pinned else None
+        return i, self._tokens[i][:rows]
 
     def sample(self, logits, params: Seq[Any], seeds: Seq[int], draws: Seq[int],
                histories: Seq[Seq[int]] | None = None):
@@ -38,7 +49,7 @@ class Sampler:
         """Start the sampling kernel; :meth:`collect` waits for it and fetches the tokens."""
         torch = self.torch
         rows = logits.shape[0]
-        out = self._out(rows)
+        turn, out = self._out(rows)
         want_logprobs = any(p.logprobs for p in params)
         logprob = torch.empty(rows, dtype=torch.float32, device=self.device) if want_logprobs else None
         if all(p.greedy and p.repetition_penalty == 1.0 for p in params):
@@ -61,11 +72,18 @@ class Sampler:
                 kwargs["penalty"] = f32([p.repetition_penalty for p in params])
                 kwargs["seen_bits"] = self._seen_bits(params, histories)
             self.ops.sample(logits, out, logprob=logprob, **kwargs)
-        return out, logprob
+        # the tokens start on their way to the host right behind the kernel
+        host = self._host[turn][:rows]
+        host.copy_(out, non_blocking=True)
+        if self._events[turn] is not None:
+            self._events[turn].record()
+        return out, logprob, host, self._events[turn]
 
     def collect(self, pending):
-        out, logprob = pending
-        tokens = out.tolist()  # the step's one wait for the device
+        out, logprob, host, event = pending
+        if event is not None:
+            event.synchronize()  # the step's one wait for the device: until its tokens have arrived
+        tokens = host.tolist()
         return tokens, (logprob.tolist() if logprob is not None else None)
 
     def _seen_bits(self, params, histories):

@@ -110,6 +110,51 @@ def test_preemption_with_few_pages_gives_the_same_tokens():
     assert tight.cache.num_free_pages == [24]
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_launched_ahead_give_the_same_tokens(dtype):
+    """A decode step may start on the tokens the device is still sampling, before the host has
+    seen them.  Requests that stop at a stop id or at their own limit, one that is aborted and
+    one that arrives late, with greedy and with seeded sampling: the tokens and the reasons are
+    those of an engine that fetches every token before it launches the next step."""
+    from inference_engine_b200 import SamplingParams
+
+    cfg, weights = TINY_B, H.make_weights(TINY_B, seed=11)
+    prompts = [H.random_tokens(cfg, n, 90 + i) for i, n in enumerate([3, 21, 40, 9, 17])]
+    limits = [30, 11, 24, 30, 16]
+
+    def run(ahead: bool, stop_ids):
+        engine = _engine(cfg, weights, dtype, num_blocks=64, block_size=8, max_num_seqs=4,
+                         max_num_batched_tokens=24, stop_token_ids=stop_ids)
+        engine.launch_ahead = ahead
+        for i in range(4):
+            sampling = dict(temperature=0) if i % 2 == 0 else dict(temperature=0.7, seed=50 + i, top_k=20)
+            engine.add_request(f"r{i}", prompts[i], SamplingParams(max_tokens=limits[i], **sampling))
+        got, steps, ahead_steps = {}, 0, 0
+        while engine.has_unfinished():
+            steps += 1
+            if steps == 9:
+                assert engine.abort("r3")
+            if steps == 14:
+                engine.add_request("r4", prompts[4], SamplingParams(temperature=0, max_tokens=limits[4]))
+            ahead_steps += engine._ahead is not None
+            for out in engine.step():
+                got.setdefault(out.request_id, []).append((out.token_id, out.finished, out.finish_reason))
+        assert engine.cache.num_free_pages == [64]
+        return got, ahead_steps
+
+    plain, none_ahead = run(False, ())
+    assert none_ahead == 0
+    # a stop id that the longest greedy request produces in mid-course
+    stop = plain["r0"][12][0]
+    want, _ = run(False, (stop,))
+    got, ahead_steps = run(True, (stop,))
+    assert ahead_steps > 10
+    assert got == want
+    assert any(reason == "stop" for _, _, reason in (v[-1] for v in got.values()))
+    assert len(got["r3"]) < limits[3] and not got["r3"][-1][1]  # aborted
+    assert len(got["r4"]) == limits[4] or got["r4"][-1][2] == "stop"
+
+
 def test_seeded_sampling_does_not_depend_on_the_batch():
     from inference_engine_b200 import SamplingParams
 

@@ -2,13 +2,18 @@
 //   C[M, N] = X[M, K] * W[N, K]^T,  bfloat16 in, 32-bit accumulation, M <= 16.
 //
 // A decode step is a stream of weights through the SMs.  Here one elected thread per block
-// issues cp.async.bulk.tensor (TMA) copies of 128-feature x 64-k tiles of W into a deep ring
-// in shared memory (128-byte swizzle, so ldmatrix reads them without bank conflicts); four
-// consumer warps wait on the tiles' mbarriers, multiply with mma.m16n8k16 (the 16 output
-// features of a tile row are the rows of the instruction, the step's tokens its columns) and
-// hand the slots back through a second set of mbarriers.  Issuing a 16 KB tile costs one
-// instruction instead of a thousand 16-byte copies, which is what lets a block keep about
-// 150 KB in flight and the SM stream at its full rate.
+// issues cp.async.bulk.tensor (TMA) copies of W into a ring in shared memory (128-byte
+// swizzle, so ldmatrix reads the tiles without bank conflicts); four consumer warps wait on
+// the copies' mbarriers, multiply with mma.m16n8k16 (the 16 output features of a tile row are
+// the rows of the instruction, the step's tokens its columns) and hand the slots back through
+// a second set of mbarriers.
+//
+// The copy engine spends a fixed time on every copy before it streams (measured on this part:
+// 16 KB boxes of a 2-D map reach 5.0 TB/s over all SMs, 64 KB boxes of a 3-D map 6.7 TB/s, the
+// rate of a plain copy).  So W[N, K] is described as a 3-D tensor (64 k, N features, K/64 k
+// blocks) and one copy brings 128 features x up to four k blocks, which land as consecutive
+// 128 x 64 tiles of the ring.  When K is no multiple of 64 the 2-D form with one k block per
+// copy is used.
 //
 // The weights do not depend on the kernel that runs before this one, so under programmatic
 // dependent launch the producer fills the ring before it waits for that kernel; only the copy
@@ -28,11 +33,12 @@ constexpr int CWARPS = 4;                 // consumer warps
 constexpr int THREADS = (CWARPS + 1) * 32;  // + one producer warp
 constexpr int BN = 128;                   // features per block (32 per consumer warp)
 constexpr int BK = 64;                    // k per stage: 128 bytes per row, one swizzle atom
-constexpr int XROWS = 16;                 // rows of X staged (M <= 16; missing rows read as zero)
-constexpr int STAGE_BYTES = BN * BK * 2;  // 16 KB
-constexpr int XBOX_BYTES = XROWS * BK * 2;  // 2 KB per 64 k
+constexpr int STAGE_BYTES = BN * BK * 2;  // 16 KB: one k block of 128 features
 constexpr int MAX_KBLOCKS = 32;           // k-slice of a block: at most 2048
-constexpr int MAX_STAGES = 9;
+constexpr int MAX_OPS = 12;               // copies in flight (ring slots)
+constexpr int MAX_KPO = 4;                // k blocks per copy
+// Shared memory for tiles: what the 227 KB of an SM leave beside X (8 NT rows x 2048 k)
+__host__ __device__ constexpr int ring_bytes(int nt) { return nt == 1 ? 192 * 1024 : 160 * 1024; }
 constexpr long long SPIN_LIMIT = 20000000;  // about ten milliseconds of polling
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -60,6 +66,10 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], unsigned addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -70,11 +80,15 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// Shared memory: [ring: stages x 16 KB][X: kblocks x 2 KB][barriers], 1024-byte aligned.
+// Shared memory: [ring: ops x kpo x 16 KB][X: kblocks x (8 NT rows x 128 B)][barriers], 1024-byte aligned.
+// NT: 8-token column tiles (1: M <= 8, 2: M <= 16).  `kpo` k blocks per copy (3-D map) or 1 (2-D map).
 template <int NT, typename OutT>
 __global__ void __launch_bounds__(THREADS)
 gemm_tma_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
-                OutT* __restrict__ out, int M, int N, int K, int kblocks_per_split, int stages, int* err) {
+                OutT* __restrict__ out, int M, int N, int K, int kblocks_per_split, int ops, int kpo, int w3d,
+                int* err) {
+    constexpr int XR = 8 * NT;                 // rows of X staged (missing rows read as zero)
+    constexpr int XBOX_BYTES = XR * BK * 2;
     extern __shared__ unsigned char smem_raw[];
     // swizzled TMA tiles want 1024-byte alignment; the launch reserves the slack
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -85,16 +99,18 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
     int kb0 = split * kblocks_per_split;
     int nkb = min(kblocks_per_split, total_kblocks - kb0);
     if (nkb < 0) nkb = 0;
+    int nops = (nkb + kpo - 1) / kpo;          // copies this block asks for
+    int op_bytes = kpo * STAGE_BYTES;
     unsigned char* ring = smem;
-    unsigned char* xs = smem + (size_t)stages * STAGE_BYTES;
+    unsigned char* xs = smem + (size_t)ring_bytes(NT);
     unsigned long long* full = reinterpret_cast<unsigned long long*>(xs + (size_t)MAX_KBLOCKS * XBOX_BYTES);
-    unsigned long long* empty = full + MAX_STAGES;
-    unsigned long long* x_full = empty + MAX_STAGES;
+    unsigned long long* empty = full + MAX_OPS;
+    unsigned long long* x_full = empty + MAX_OPS;
     __shared__ int failed;
 
     if (threadIdx.x == 0) {
         failed = 0;
-        for (int s = 0; s < stages; ++s) {
+        for (int s = 0; s < ops; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], CWARPS);
         }
@@ -107,24 +123,27 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
     if (warp == CWARPS) {
         // ---- producer: one thread ----
         if (lane == 0) {
+            auto copy_w = [&](int o) {  // copy o of this block into slot o % ops
+                int s = o % ops;
+                mbar_expect_tx(&full[s], op_bytes);
+                if (w3d)
+                    tma_load_3d(ring + (size_t)s * op_bytes, &w_map, 0, n0, kb0 + o * kpo, &full[s]);
+                else
+                    tma_load_2d(ring + (size_t)s * op_bytes, &w_map, (kb0 + o) * BK, n0, &full[s]);
+            };
             int issued = 0;
             // the weights need nobody's results: fill the ring right away
-            for (; issued < nkb && issued < stages; ++issued) {
-                mbar_expect_tx(&full[issued], STAGE_BYTES);
-                tma_load_2d(ring + (size_t)issued * STAGE_BYTES, &w_map, (kb0 + issued) * BK, n0, &full[issued]);
-            }
+            for (; issued < nops && issued < ops; ++issued) copy_w(issued);
             ie_pdl_wait();  // X is the previous kernel's output
             if (nkb > 0) {
                 mbar_expect_tx(x_full, nkb * XBOX_BYTES);
                 for (int kb = 0; kb < nkb; ++kb)
                     tma_load_2d(xs + (size_t)kb * XBOX_BYTES, &x_map, (kb0 + kb) * BK, 0, x_full);
             }
-            for (; issued < nkb; ++issued) {
-                int s = issued % stages;
-                int round = issued / stages;  // this slot's round-th reuse: wait for its release
-                if (!mbar_wait(&empty[s], (round - 1) & 1)) { failed = 1; break; }
-                mbar_expect_tx(&full[s], STAGE_BYTES);
-                tma_load_2d(ring + (size_t)s * STAGE_BYTES, &w_map, (kb0 + issued) * BK, n0, &full[s]);
+            for (; issued < nops; ++issued) {
+                int round = issued / ops;  // this slot's round-th reuse: wait for its release
+                if (!mbar_wait(&empty[issued % ops], (round - 1) & 1)) { failed = 1; break; }
+                copy_w(issued);
             }
         } else {
             ie_pdl_wait();
@@ -139,27 +158,45 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
             for (int n = 0; n < NT; ++n) acc[mt][n][0] = acc[mt][n][1] = acc[mt][n][2] = acc[mt][n][3] = 0.f;
         bool ok = nkb == 0 || mbar_wait(x_full, 0);
         unsigned ring_addr = smem_u32(ring), xs_addr = smem_u32(xs);
-        for (int kb = 0; kb < nkb && ok; ++kb) {
-            int s = kb % stages;
-            if (!mbar_wait(&full[s], (kb / stages) & 1)) { ok = false; break; }
-            unsigned wt = ring_addr + s * STAGE_BYTES;
-            unsigned xt = xs_addr + kb * XBOX_BYTES;
+        for (int o = 0; o < nops && ok; ++o) {
+            int s = o % ops;
+            if (!mbar_wait(&full[s], (o / ops) & 1)) { ok = false; break; }
+            int kbs = min(kpo, nkb - o * kpo);  // a copy may reach beyond the block's slice of k
+            for (int j = 0; j < kbs; ++j) {
+                unsigned wt = ring_addr + s * op_bytes + j * STAGE_BYTES;
+                unsigned xt = xs_addr + (o * kpo + j) * XBOX_BYTES;
 #pragma unroll
-            for (int ks = 0; ks < BK / 16; ++ks) {
-                unsigned xb[4];
-                {   // tokens (lane & 7) + 8 (lane >> 4), k chunk ks*2 + ((lane >> 3) & 1)
-                    int r = (lane & 7) + ((lane >> 4) << 3);
-                    int c = ks * 2 + ((lane >> 3) & 1);
-                    ldmatrix_x4(xb, xt + r * 128 + ((c ^ (r & 7)) << 4));
-                }
+                for (int ks2 = 0; ks2 < BK / 32; ++ks2) {
+                    // X as B fragments of two 16-wide k steps
+                    unsigned xb[2][2 * NT];
+                    if (NT == 1) {  // 8 tokens: one ldmatrix brings both steps (k chunks 4 ks2 .. + 3)
+                        unsigned t[4];
+                        int r = lane & 7, c = ks2 * 4 + (lane >> 3);
+                        ldmatrix_x4(t, xt + r * 128 + ((c ^ (r & 7)) << 4));
+                        xb[0][0] = t[0]; xb[0][1] = t[1]; xb[1][0] = t[2]; xb[1][1] = t[3];
+                    } else {        // 16 tokens: tokens (lane & 7) + 8 (lane >> 4), k chunk + ((lane >> 3) & 1)
 #pragma unroll
-                for (int mt = 0; mt < 2; ++mt) {
-                    unsigned a[4];
-                    int r = warp * 32 + mt * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
-                    int c = ks * 2 + (lane >> 4);
-                    ldmatrix_x4(a, wt + r * 128 + ((c ^ (r & 7)) << 4));
-                    mma_bf16(acc[mt][0], a, xb[0], xb[1]);
-                    if (NT == 2) mma_bf16(acc[mt][NT - 1], a, xb[2], xb[3]);
+                        for (int h = 0; h < 2; ++h) {
+                            unsigned t[4];
+                            int r = (lane & 7) + ((lane >> 4) << 3);
+                            int c = (ks2 * 2 + h) * 2 + ((lane >> 3) & 1);
+                            ldmatrix_x4(t, xt + r * 128 + ((c ^ (r & 7)) << 4));
+                            xb[h][0] = t[0]; xb[h][1] = t[1]; xb[h][2 * NT - 2] = t[2]; xb[h][2 * NT - 1] = t[3];
+                        }
+                    }
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        int ks = ks2 * 2 + h;
+#pragma unroll
+                        for (int mt = 0; mt < 2; ++mt) {
+                            unsigned a[4];
+                            int r = warp * 32 + mt * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+                            int c = ks * 2 + (lane >> 4);
+                            ldmatrix_x4(a, wt + r * 128 + ((c ^ (r & 7)) << 4));
+                            mma_bf16(acc[mt][0], a, xb[h][0], xb[h][1]);
+                            if (NT == 2) mma_bf16(acc[mt][NT - 1], a, xb[h][2 * NT - 2], xb[h][2 * NT - 1]);
+                        }
+                    }
                 }
             }
             __syncwarp();
@@ -216,11 +253,39 @@ bool make_map(CUtensorMap* map, const void* base, long long rows, long long cols
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// W[rows, cols] (cols a multiple of 64) as a 3-D tensor (64 k, rows, cols / 64 k blocks) with
+// boxes of 64 x 128 features x kpo k blocks: in shared memory kpo consecutive 128 x 64 tiles.
+bool make_map_3d(CUtensorMap* map, const void* base, long long rows, long long cols, int kpo) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr || cols % BK != 0) return false;
+    cuuint64_t dims[3] = {(cuuint64_t)BK, (cuuint64_t)rows, (cuuint64_t)(cols / BK)};
+    cuuint64_t strides[2] = {(cuuint64_t)cols * 2, (cuuint64_t)BK * 2};
+    cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)BN, (cuuint32_t)kpo};
+    cuuint32_t elem[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int NT, typename OutT>
-int launch(const CUtensorMap& wm, const CUtensorMap& xm, OutT* out, int M, int N, int K, int kblocks_per_split,
-           int splits, int* err, cudaStream_t s) {
-    int stages = MAX_STAGES;
-    size_t smem = (size_t)stages * STAGE_BYTES + (size_t)MAX_KBLOCKS * XBOX_BYTES + (2 * MAX_STAGES + 1) * 8 + 1024;
+int launch(const void* X, const void* W, OutT* out, int M, int N, int K, int kblocks_per_split, int splits,
+           int* err, cudaStream_t s) {
+    // k blocks per copy: as many as divide the block's slice (a copy must not reach into the
+    // next block's slice: that would read those bytes twice)
+    int kpo = 1, w3d = 0;
+    CUtensorMap wm, xm;
+    if (K % BK == 0) {
+        // (16 tokens leave room for 160 KB of tiles: 32 KB copies keep five of them in flight)
+        for (kpo = NT == 1 ? MAX_KPO : 2; kpo > 1 && kblocks_per_split % kpo != 0; kpo >>= 1) {}
+        w3d = 1;
+        if (!make_map_3d(&wm, W, N, K, kpo)) return (int)cudaErrorNotSupported;
+    } else if (!make_map(&wm, W, N, K, BN)) {
+        return (int)cudaErrorNotSupported;
+    }
+    if (!make_map(&xm, X, M, K, 8 * NT)) return (int)cudaErrorNotSupported;
+    int ops = ring_bytes(NT) / (kpo * STAGE_BYTES);
+    if (ops > MAX_OPS) ops = MAX_OPS;
+    size_t smem = (size_t)ring_bytes(NT) + (size_t)MAX_KBLOCKS * 8 * NT * BK * 2 + (2 * MAX_OPS + 1) * 8 + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tma_kernel<NT, OutT>,
@@ -230,7 +295,7 @@ int launch(const CUtensorMap& wm, const CUtensorMap& xm, OutT* out, int M, int N
     }
     dim3 grid((N + BN - 1) / BN, splits);
     return ie_launch(gemm_tma_kernel<NT, OutT>, grid, dim3(THREADS), smem, s, wm, xm, out, M, N, K,
-                     kblocks_per_split, stages, err);
+                     kblocks_per_split, ops, kpo, w3d, err);
 }
 }  // namespace
 
@@ -244,16 +309,14 @@ IE_API int ie_gemm_tma_bf16(const void* X, const void* W, void* out, int out_dty
                             int kblocks_per_split, int splits, int* err, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     int total_kblocks = (K + BK - 1) / BK;
-    if (M > XROWS || K % 8 != 0 || splits < 1 || kblocks_per_split < 1 || kblocks_per_split > MAX_KBLOCKS ||
+    if (M > 16 || K % 8 != 0 || splits < 1 || kblocks_per_split < 1 || kblocks_per_split > MAX_KBLOCKS ||
         (long long)kblocks_per_split * splits < total_kblocks || (splits > 1 && out_dtype != IE_F32) ||
         ((uintptr_t)X & 15) != 0 || ((uintptr_t)W & 15) != 0)
         return (int)cudaErrorInvalidValue;
-    CUtensorMap wm, xm;
-    if (!make_map(&wm, W, N, K, BN) || !make_map(&xm, X, M, K, XROWS)) return (int)cudaErrorNotSupported;
     cudaStream_t s = (cudaStream_t)stream;
     if (out_dtype == IE_F32)
-        return M <= 8 ? launch<1, float>(wm, xm, (float*)out, M, N, K, kblocks_per_split, splits, err, s)
-                      : launch<2, float>(wm, xm, (float*)out, M, N, K, kblocks_per_split, splits, err, s);
-    return M <= 8 ? launch<1, bf16>(wm, xm, (bf16*)out, M, N, K, kblocks_per_split, splits, err, s)
-                  : launch<2, bf16>(wm, xm, (bf16*)out, M, N, K, kblocks_per_split, splits, err, s);
+        return M <= 8 ? launch<1, float>(X, W, (float*)out, M, N, K, kblocks_per_split, splits, err, s)
+                      : launch<2, float>(X, W, (float*)out, M, N, K, kblocks_per_split, splits, err, s);
+    return M <= 8 ? launch<1, bf16>(X, W, (bf16*)out, M, N, K, kblocks_per_split, splits, err, s)
+                  : launch<2, bf16>(X, W, (bf16*)out, M, N, K, kblocks_per_split, splits, err, s);
 }

@@ -73,10 +73,12 @@ class CudaOps:
         # the decode kernel cuts contexts until about this many blocks run (one block per SM)
         self.decode_split_target = int(os.environ.get("IE_B200_DECODE_SPLIT_TARGET", 128))
         self.few_row_gemm = os.environ.get("IE_B200_FEW_ROW_GEMM", "tma")
-        # ... for matrices with fewer 128-feature tiles than half the SMs (they need their inner
-        # dimension cut to occupy the GPU, which the vendor library does not do); measured on
-        # the 1B shape: wider matrices stream faster through the library's kernel
-        self.tma_max_tiles = int(os.environ.get("IE_B200_TMA_MAX_TILES", self.sm_count // 2))
+        # ... up to this many 128-feature tiles (measured on the 1B shape: up to 8 rows the kernel
+        # streams 67 MB in 12.0 us where the vendor library takes 12.7, and the 525 MB of the
+        # head in 82 us against 79.5; from 9 rows on its second column tile makes it slower on
+        # wide matrices, so only those that must be cut along k to fill the GPU go to it)
+        self.tma_max_tiles = int(os.environ.get("IE_B200_TMA_MAX_TILES", 256))
+        self.tma_max_tiles_wide = min(self.tma_max_tiles, self.sm_count // 2)  # 9 to 16 rows
         self._device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self._raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
         self.launches = 0  # launches of this library's kernels (library matrix products not counted)
@@ -168,6 +170,15 @@ class CudaOps:
         total = -(-k // 64)
         splits = max(1, min(total, self.sm_count // tiles))
         per = min(-(-total // splits), 32)
+        # one copy brings up to four k blocks when they divide the slice: round the slice up to
+        # a multiple of 4 (or 2) unless that leaves many SMs without a block
+        for multiple in (4, 2):
+            rounded = min(-(-per // multiple) * multiple, 32)
+            if rounded != per and -(-total // rounded) * tiles * 10 >= -(-total // per) * tiles * 8:
+                per = rounded
+                break
+            if rounded == per:
+                break
         return per, -(-total // per)
 
     def linear(self, x, w, out=None, *, ws=None, tag="linear", out_dtype=None, allow_split=False):
@@ -192,7 +203,7 @@ class CudaOps:
         # features (fewer 16-feature blocks than SMs) and a long inner dimension to split.
         few_rows = 0 < m <= self.SKINNY_ROWS and k % 8 == 0 and x.is_contiguous() and w.is_contiguous()
         if (few_rows and self.few_row_gemm == "tma" and not self.force_skinny
-                and -(-n // 128) <= self.tma_max_tiles):
+                and -(-n // 128) <= (self.tma_max_tiles if m <= 8 else self.tma_max_tiles_wide)):
             kbps, splits = self.tma_split(n, k) if allow_split and out is None else (-(-k // 64), 1)
             if kbps <= 32:
                 if splits > 1:

@@ -79,6 +79,16 @@ class CudaOps:
         # wide matrices, so only those that must be cut along k to fill the GPU go to it)
         self.tma_max_tiles = int(os.environ.get("IE_B200_TMA_MAX_TILES", 256))
         self.tma_max_tiles_wide = min(self.tma_max_tiles, self.sm_count // 2)  # 9 to 16 rows
+        # Products of 17 to `batch_gemm_rows` rows with a long inner dimension: the tcgen05
+        # weight-streaming kernel (IE_B200_BATCH_GEMM=0: the vendor library).  Measured on the 1B
+        # shape at 64 rows: the down projection (K = 8192) 11.0 us against the library's 13.0,
+        # but QKV, output and gate-up (K = 2048) 7.3 / 6.3 / 16.3 against 5.7 / 5.5 / 13.5: every
+        # block copies all tokens' activations through its SM's copy engine beside the weights,
+        # which the library's kernels share within a cluster.  So only long inner dimensions.
+        self.batch_gemm = os.environ.get("IE_B200_BATCH_GEMM", "1") != "0"
+        self.batch_gemm_rows = int(os.environ.get("IE_B200_BATCH_GEMM_ROWS", 64))
+        self.batch_gemm_max_tiles = int(os.environ.get("IE_B200_BATCH_GEMM_MAX_TILES", 256))
+        self.batch_gemm_min_k = int(os.environ.get("IE_B200_BATCH_GEMM_MIN_K", 4096))
         self._device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self._raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
         self.launches = 0  # launches of this library's kernels (library matrix products not counted)
@@ -94,6 +104,8 @@ class CudaOps:
             "ie_gemm_f32": [P, P, P, I, I, I, P],
             "ie_gemm_skinny_bf16": [P, P, P, I, I, I, I, I, I, P],
             "ie_gemm_tma_bf16": [P, P, P, I, I, I, I, I, I, P, P],
+            "ie_gemm_tc5_bf16": [P, P, P, I, I, I, I, I, I, P, P],
+            "ie_gemm_tc5_ok": [I, I, I],
             "ie_paged_attention_generic": [P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, F, I, P, P],
             "ie_sample": [P, I, I, P, P, P, P, P, P, I, P, P, P, P, P],
         }
@@ -213,6 +225,19 @@ class CudaOps:
                 self._check(self._gemm_tma_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), _dtype_code(out),
                                                 m, n, k, kbps, splits, self._err_ptr, self._stream()), "gemm_tma")
                 return out
+        # A batch of decode tokens (17 to 256 rows): still a stream of weights; the tcgen05
+        # kernel with the operands' roles swapped, cut along k like the few-row kernel.
+        if (self.batch_gemm and self.SKINNY_ROWS < m <= self.batch_gemm_rows and x.is_contiguous()
+                and w.is_contiguous() and self._gemm_tc5_ok(m, n, k)
+                and -(-n // 128) <= self.batch_gemm_max_tiles and k >= self.batch_gemm_min_k):
+            per, splits = self.tma_split(n, k) if allow_split and out is None else (k // 64, 1)
+            if splits > 1:
+                out = ws.buffer(tag, splits * m, n, torch.float32).view(splits, m, n)
+            elif out is None:
+                out = ws.buffer(tag, m, n, out_dtype)
+            self._check(self._gemm_tc5_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), _dtype_code(out),
+                                            m, n, k, per, splits, self._err_ptr, self._stream()), "gemm_tc5")
+            return out
         skinny = (0 < m <= self.SKINNY_ROWS and k % 8 == 0 and x.is_contiguous() and w.is_contiguous()
                   and (self.force_skinny or (allow_split and out is None and -(-n // 16) <= self.skinny_max_blocks)))
         if skinny:

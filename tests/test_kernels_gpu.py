@@ -202,6 +202,40 @@ def test_tma_fed_gemm_for_few_rows(ops, m, n, k):
         ops.few_row_gemm = saved
 
 
+@pytest.mark.parametrize("m", [17, 33, 64, 100, 128, 200, 256])
+@pytest.mark.parametrize("n,k", [(3072, 2048), (2048, 8192), (328, 128), (192, 64), (1000, 1024), (16384, 2048)])
+def test_tcgen05_gemm_for_a_batch_of_decode_tokens(ops, m, n, k):
+    """17 to 256 rows: features are the rows of tcgen05.mma, tokens its columns; any N (tiles of
+    128 with a ragged edge), K a multiple of 64, with and without k splits, 32-bit and bfloat16
+    results; twice, so that tensor memory must have been given back."""
+    from inference_engine_b200.engine.workspace import Workspace
+
+    g = torch.Generator(device="cuda").manual_seed(m + n + k)
+    x = torch.randn(m, k, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(n, k, device="cuda", generator=g) * 0.05).bfloat16()
+    want = x.double() @ w.double().t()
+    ws = Workspace("cuda")
+    saved = ops.batch_gemm, ops.batch_gemm_rows, ops.batch_gemm_max_tiles, ops.batch_gemm_min_k
+    ops.batch_gemm, ops.batch_gemm_rows, ops.batch_gemm_max_tiles, ops.batch_gemm_min_k = True, 256, 1 << 20, 0
+    launches = ops.launches
+    try:
+        for _ in range(2):
+            split = ops.linear(x, w, ws=ws, tag="t", out_dtype=torch.float32, allow_split=True)
+            per, splits = ops.tma_split(n, k)
+            assert split.shape == ((splits, m, n) if splits > 1 else (m, n))
+            total = split.sum(0) if split.dim() == 3 else split
+            torch.testing.assert_close(total.double(), want, atol=2e-4 * k ** 0.5, rtol=1e-5)
+            for out_dtype in DTYPES:
+                out = torch.empty(m, n, device="cuda", dtype=out_dtype)
+                assert ops.linear(x, w, out) is out
+                tol = dict(atol=2e-4 * k ** 0.5, rtol=1e-5) if out_dtype == torch.float32 else dict(atol=0.01 * k ** 0.5, rtol=1e-2)
+                torch.testing.assert_close(out.double(), want, **tol)
+        assert ops.launches - launches == 6  # every product ran this kernel, none the vendor library
+        ops.check_errors()
+    finally:
+        ops.batch_gemm, ops.batch_gemm_rows, ops.batch_gemm_max_tiles, ops.batch_gemm_min_k = saved
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkv,hd,rd,ps", [(4, 2, 16, 16, 16), (3, 1, 32, 32, 8), (5, 5, 48, 48, 4),
                                              (32, 8, 64, 64, 16), (6, 2, 80, 32, 16), (2, 1, 128, 0, 32)])

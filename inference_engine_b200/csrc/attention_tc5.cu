@@ -160,7 +160,7 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
                              const __grid_constant__ CUtensorMap v_map, const int* __restrict__ tables,
                              int table_width, const int* __restrict__ cu_q, const int* __restrict__ ctx_lens,
                              bf16* __restrict__ out, int num_seqs, int nh, int nkv, int page_shift,
-                             int total_pages, float scale_log2, int window, int* err) {
+                             int total_pages, float scale_log2, int window, int paired, int* err) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     unsigned char* k_s = smem;                                  // stages x 8 KB
@@ -171,27 +171,51 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
     int head = blockIdx.y, G = nh / nkv, kvh = head / G;
     ie_pdl_trigger();
     ie_pdl_wait();
-    // which request and which 128-token tile of it is this block's?  (heavy tiles first)
-    int tile = gridDim.x - 1 - blockIdx.x, seq = -1, t0 = 0, q0 = 0, qlen = 0;
+    // Which request and which of its 128-token tiles are this block's?  Tile i of a request of n
+    // tiles needs about i + 1 key tiles.  With few blocks (`paired`) a block takes the pair
+    // (n - 1 - p, p), one after the other, so that every block of a request has the same amount
+    // of work and all run at once; with many blocks each takes one tile, the heavy ones first.
+    int item = paired ? blockIdx.x : gridDim.x - 1 - blockIdx.x;
+    int seq = -1, q0 = 0, qlen = 0, tile_a = 0, tile_b = 0;
     for (int s = 0; s < num_seqs; ++s) {
         int a = cu_q[s], n = cu_q[s + 1] - a;
         int tiles = (n * G > 16) ? (n + BM - 1) / BM : 0;
-        if (tile < tiles) { seq = s; t0 = tile * BM; q0 = a; qlen = n; break; }
-        tile -= tiles;
+        int items = paired ? (tiles + 1) / 2 : tiles;
+        if (item < items) {
+            seq = s; q0 = a; qlen = n;
+            tile_a = paired ? tiles - 1 - item : item;
+            tile_b = item;  // unpaired: the same tile, one part
+            break;
+        }
+        item -= items;
     }
     if (seq < 0) return;
     int ctx = ctx_lens[seq];
     const int* table = tables + (size_t)seq * table_width;
     int first_qpos = ctx - qlen;
-    int tile_rows = min(BM, qlen - t0);
-    int qpos_lo = first_qpos + t0, qpos_hi = qpos_lo + tile_rows - 1;
-    int lo = (window > 0 && qpos_lo - window + 1 > 0) ? qpos_lo - window + 1 : 0;
-    int key_begin = (lo / KT) * KT;
-    int n_tiles = (qpos_hi - key_begin) / KT + 1;
+    struct Part { int t0, rows, qpos_lo, qpos_hi, key_begin, n_tiles; };
+    auto make_part = [&](int tile) {
+        Part p;
+        p.t0 = tile * BM;
+        p.rows = min(BM, qlen - p.t0);
+        p.qpos_lo = first_qpos + p.t0;
+        p.qpos_hi = p.qpos_lo + p.rows - 1;
+        int lo = (window > 0 && p.qpos_lo - window + 1 > 0) ? p.qpos_lo - window + 1 : 0;
+        p.key_begin = (lo / KT) * KT;
+        p.n_tiles = (p.qpos_hi - p.key_begin) / KT + 1;
+        return p;
+    };
+    Part parts[2];
+    int nparts = tile_b < tile_a ? 2 : 1;
+    parts[0] = make_part(tile_a);
+    parts[1] = make_part(nparts == 2 ? tile_b : tile_a);
     int page_size = 1 << page_shift;
     int pages_per_tile = KT >> page_shift;
-    int first_entry = key_begin >> page_shift;
-    int n_entries = min(n_tiles * pages_per_tile, MAX_TABLE);
+    // block-table entries of both parts' key ranges, once
+    int first_entry = min(parts[0].key_begin, parts[1].key_begin) >> page_shift;
+    int last_entry = max(parts[0].key_begin + parts[0].n_tiles * KT, parts[1].key_begin + parts[1].n_tiles * KT) - 1;
+    last_entry >>= page_shift;
+    int n_entries = min(last_entry - first_entry + 1, MAX_TABLE);
 
     if (tid == 0) {
         mbar_init(&bars->q_full, SOFTMAX_THREADS);
@@ -218,57 +242,69 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     unsigned tmem = bars->tmem_base;
     unsigned tmem_o = tmem + 2 * KT, tmem_q = tmem + 2 * KT + HD;
+    // In all three roles g counts the key tiles over both parts: ring stage g % 3, S buffer
+    // g & 1 and the barriers' phases go on from the first part into the second.
 
     if (warp == 4) {
         // ---- copies: one thread ----
         if (lane == 0) {
-            for (int t = 0; t < n_tiles; ++t) {
-                int stage = t % KV_STAGES;
-                if (t >= KV_STAGES && !mbar_wait(&bars->kv_empty[stage], (t / KV_STAGES - 1) & 1)) {
-                    bars->failed = 1;
-                    break;
-                }
-                mbar_expect_tx(&bars->kv_full[stage], 2 * KV_BYTES);
-                for (int p = 0; p < pages_per_tile; ++p) {
-                    int page = table_s[min(t * pages_per_tile + p, MAX_TABLE - 1)];
-                    int row = (page * nkv + kvh) << page_shift;
-                    tma_load_2d(k_s + stage * KV_BYTES + p * page_size * 128, &k_map, 0, row, &bars->kv_full[stage]);
-                    tma_load_2d(v_s + stage * KV_BYTES + p * page_size * 128, &v_map, 0, row, &bars->kv_full[stage]);
+            int g = 0;
+            bool ok = true;
+            for (int pi = 0; pi < nparts && ok; ++pi) {
+                const Part& pt = parts[pi];
+                for (int t = 0; t < pt.n_tiles; ++t, ++g) {
+                    int stage = g % KV_STAGES;
+                    if (g >= KV_STAGES && !mbar_wait(&bars->kv_empty[stage], (g / KV_STAGES - 1) & 1)) { ok = false; break; }
+                    mbar_expect_tx(&bars->kv_full[stage], 2 * KV_BYTES);
+                    int entry = ((pt.key_begin + t * KT) >> page_shift) - first_entry;
+                    for (int p = 0; p < pages_per_tile; ++p) {
+                        int page = table_s[min(entry + p, MAX_TABLE - 1)];
+                        int row = (page * nkv + kvh) << page_shift;
+                        tma_load_2d(k_s + stage * KV_BYTES + p * page_size * 128, &k_map, 0, row, &bars->kv_full[stage]);
+                        tma_load_2d(v_s + stage * KV_BYTES + p * page_size * 128, &v_map, 0, row, &bars->kv_full[stage]);
+                    }
                 }
             }
+            if (!ok) bars->failed = 1;
         }
     } else if (warp == 5) {
         // ---- tensor core: one thread ----
         if (lane == 0) {
             unsigned idesc_qk = instr_desc(false), idesc_pv = instr_desc(true);
-            bool ok = mbar_wait(&bars->q_full, 0);
-            auto issue_s = [&](int t) {  // S(t) = Q K(t)^T into S buffer t & 1
-                int stage = t % KV_STAGES;
-                if (!mbar_wait(&bars->kv_full[stage], (t / KV_STAGES) & 1)) return false;
+            bool ok = true;
+            auto issue_s = [&](int g) {  // S = Q K^T of key tile g into S buffer g & 1
+                int stage = g % KV_STAGES;
+                if (!mbar_wait(&bars->kv_full[stage], (g / KV_STAGES) & 1)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 unsigned ka = smem_u32(k_s + stage * KV_BYTES);
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks)  // 32 bytes further along k per step
-                    umma_ta(tmem + (t & 1) * KT, tmem_q + ks * 8, smem_desc(ka + ks * 32), idesc_qk, ks > 0);
-                umma_commit(&bars->s_done[t & 1]);
+                    umma_ta(tmem + (g & 1) * KT, tmem_q + ks * 8, smem_desc(ka + ks * 32), idesc_qk, ks > 0);
+                umma_commit(&bars->s_done[g & 1]);
                 return true;
             };
-            ok = ok && issue_s(0);
-            for (int t = 0; t < n_tiles && ok; ++t) {
-                if (t + 1 < n_tiles) {
-                    // its S buffer held the weights of tile t - 1: that product must have read them
-                    if (t > 0 && !mbar_wait(&bars->o_done, (t - 1) & 1)) { ok = false; break; }
-                    ok = issue_s(t + 1);
-                }
-                if (!ok || !mbar_wait(&bars->p_ready[t & 1], (t >> 1) & 1)) { ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                int stage = t % KV_STAGES;
-                unsigned va = smem_u32(v_s + stage * KV_BYTES);
+            int g = 0;
+            for (int pi = 0; pi < nparts && ok; ++pi) {
+                int n_tiles = parts[pi].n_tiles;
+                // the part's Q is in tensor memory (and the softmax warps are done with the
+                // accumulator of the part before)
+                ok = mbar_wait(&bars->q_full, pi & 1) && issue_s(g);
+                for (int t = 0; t < n_tiles && ok; ++t, ++g) {
+                    if (t + 1 < n_tiles) {
+                        // its S buffer held the weights of tile g - 1: that product must have read them
+                        if (g > 0 && !mbar_wait(&bars->o_done, (g - 1) & 1)) { ok = false; break; }
+                        ok = issue_s(g + 1);
+                    }
+                    if (!ok || !mbar_wait(&bars->p_ready[g & 1], (g >> 1) & 1)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    int stage = g % KV_STAGES;
+                    unsigned va = smem_u32(v_s + stage * KV_BYTES);
 #pragma unroll
-                for (int ks = 0; ks < KT / 16; ++ks)  // P: 8 columns of two keys each; V: 16 keys = 2048 bytes
-                    umma_ta(tmem_o, tmem + (t & 1) * KT + ks * 8, smem_desc(va + ks * 2048), idesc_pv, (t > 0 || ks > 0) ? 1u : 0u);
-                umma_commit(&bars->o_done);
-                umma_commit(&bars->kv_empty[stage]);
+                    for (int ks = 0; ks < KT / 16; ++ks)  // P: 8 columns of two keys each; V: 16 keys = 2048 bytes
+                        umma_ta(tmem_o, tmem + (g & 1) * KT + ks * 8, smem_desc(va + ks * 2048), idesc_pv, (t > 0 || ks > 0) ? 1u : 0u);
+                    umma_commit(&bars->o_done);
+                    umma_commit(&bars->kv_empty[stage]);
+                }
             }
             if (!ok) bars->failed = 1;
         }
@@ -276,113 +312,119 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
         // ---- softmax: thread = query row = TMEM lane ----
         int row = tid;
         unsigned lane_addr = (unsigned)(warp * 32) << 16;  // this warp's 32 TMEM lanes
-        bool exists = row < tile_rows;
-        int qpos = exists ? qpos_lo + row : -1;
-        int qlo = (window > 0 && qpos - window + 1 > 0) ? qpos - window + 1 : 0;
-        // m: the maximum that the weights are taken against.  It follows the running maximum
-        // only when that has grown by more than 2^RESCALE_LAG (for any row of the warp), so
-        // that the accumulator in TMEM is rescaled on few tiles; weights stay below 2^RESCALE_LAG
-        // and the quotient of accumulator and sum is the same.
-        float m = -INFINITY, l = 0.f;
-        {   // this row of Q, two features to a column, as the first product's A operand
-            float qw[32];
-            uint4* q4 = reinterpret_cast<uint4*>(qw);
-            const uint4* src = reinterpret_cast<const uint4*>(q + ((size_t)(q0 + t0 + row) * nh + head) * HD);
-#pragma unroll
-            for (int c = 0; c < HD / 8; ++c) q4[c] = exists ? src[c] : make_uint4(0u, 0u, 0u, 0u);
-            tmem_st32(qw, tmem_q + lane_addr);
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(&bars->q_full);
-        }
         bool ok = true;
-        for (int t = 0; t < n_tiles; ++t) {
-            int key0 = key_begin + t * KT;
-            if (!mbar_wait(&bars->s_done[t & 1], (t >> 1) & 1)) { ok = false; break; }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            float s[KT];
-            tmem_ld64(s, tmem + (t & 1) * KT + lane_addr);
-            // inner tiles (every key visible to every row of the block) need no mask
-            bool inner = key0 + KT - 1 <= qpos_lo && (window <= 0 || key0 >= qpos_hi - window + 1);
-            if (!inner) {
+        int g = 0;
+        for (int pi = 0; pi < nparts && ok; ++pi) {
+            const Part& pt = parts[pi];
+            int n_tiles = pt.n_tiles, qpos_lo = pt.qpos_lo, qpos_hi = pt.qpos_hi;
+            bool exists = row < pt.rows;
+            int qpos = exists ? qpos_lo + row : -1;
+            int qlo = (window > 0 && qpos - window + 1 > 0) ? qpos - window + 1 : 0;
+            // m: the maximum that the weights are taken against.  It follows the running maximum
+            // only when that has grown by more than 2^RESCALE_LAG (for any row of the warp), so
+            // that the accumulator in TMEM is rescaled on few tiles; weights stay below 2^RESCALE_LAG
+            // and the quotient of accumulator and sum is the same.
+            float m = -INFINITY, l = 0.f;
+            {   // this row of Q, two features to a column, as the first product's A operand (the
+                // products of the part before have all been waited for)
+                float qw[32];
+                uint4* q4 = reinterpret_cast<uint4*>(qw);
+                const uint4* src = reinterpret_cast<const uint4*>(q + ((size_t)(q0 + pt.t0 + row) * nh + head) * HD);
 #pragma unroll
-                for (int j = 0; j < KT; ++j) {
-                    int kpos = key0 + j;
-                    s[j] = (kpos <= qpos && kpos >= qlo) ? s[j] : -INFINITY;
+                for (int c = 0; c < HD / 8; ++c) q4[c] = exists ? src[c] : make_uint4(0u, 0u, 0u, 0u);
+                tmem_st32(qw, tmem_q + lane_addr);
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(&bars->q_full);
+            }
+            for (int t = 0; t < n_tiles; ++t, ++g) {
+                int key0 = pt.key_begin + t * KT;
+                if (!mbar_wait(&bars->s_done[g & 1], (g >> 1) & 1)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                float s[KT];
+                tmem_ld64(s, tmem + (g & 1) * KT + lane_addr);
+                // inner tiles (every key visible to every row of the block) need no mask
+                bool inner = key0 + KT - 1 <= qpos_lo && (window <= 0 || key0 >= qpos_hi - window + 1);
+                if (!inner) {
+#pragma unroll
+                    for (int j = 0; j < KT; ++j) {
+                        int kpos = key0 + j;
+                        s[j] = (kpos <= qpos && kpos >= qlo) ? s[j] : -INFINITY;
+                    }
                 }
-            }
-            float mx[8];  // eight independent chains: a warp has a scheduler to itself most of the time
+                float mx[8];  // eight independent chains: a warp has a scheduler to itself most of the time
 #pragma unroll
-            for (int j = 0; j < 8; ++j) mx[j] = s[j];
+                for (int j = 0; j < 8; ++j) mx[j] = s[j];
 #pragma unroll
-            for (int j = 8; j < KT; ++j) mx[j & 7] = fmaxf(mx[j & 7], s[j]);
-            float tile_max = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
-            float m_cand = fmaxf(m, tile_max * scale_log2);
-            bool rescale = __any_sync(0xffffffffu, m_cand > m + RESCALE_LAG);
-            float alpha = 1.f;
-            if (rescale) {
-                alpha = fast_exp2(m - ((m_cand == -INFINITY) ? 0.f : m_cand));
-                m = m_cand;
-                l *= alpha;
-            }
-            float m_safe = (m == -INFINITY) ? 0.f : m;
-            // weights, rounded to bfloat16 and packed two to a column, over this row of S: the
-            // second product's A operand
-            float pw[32];
-            unsigned* w = reinterpret_cast<unsigned*>(pw);
-            float ls[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int c = 0; c < KT / 2; ++c) {
-                float p0 = fast_exp2(fmaf(s[2 * c], scale_log2, -m_safe));
-                float p1 = fast_exp2(fmaf(s[2 * c + 1], scale_log2, -m_safe));
-                ls[c & 3] += p0 + p1;
-                __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-                w[c] = *reinterpret_cast<unsigned*>(&pk);
-            }
-            l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
-            tmem_st32(pw, tmem + (t & 1) * KT + lane_addr);
-            if (t > 0) {
-                // the previous tile's product has had this tile's softmax to finish; waiting for
-                // it here every tile also keeps this barrier's phase in step
-                if (!mbar_wait(&bars->o_done, (t - 1) & 1)) { ok = false; break; }
+                for (int j = 8; j < KT; ++j) mx[j & 7] = fmaxf(mx[j & 7], s[j]);
+                float tile_max = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+                float m_cand = fmaxf(m, tile_max * scale_log2);
+                bool rescale = __any_sync(0xffffffffu, m_cand > m + RESCALE_LAG);
+                float alpha = 1.f;
                 if (rescale) {
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        float acc[32];
-                        tmem_ld32(acc, tmem_o + half * 32 + lane_addr);
-#pragma unroll
-                        for (int d = 0; d < 32; ++d) acc[d] *= alpha;
-                        tmem_st32(acc, tmem_o + half * 32 + lane_addr);
-                    }
+                    alpha = fast_exp2(m - ((m_cand == -INFINITY) ? 0.f : m_cand));
+                    m = m_cand;
+                    l *= alpha;
                 }
-            }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(&bars->p_ready[t & 1]);
-        }
-        if (ok && n_tiles > 0 && !mbar_wait(&bars->o_done, (n_tiles - 1) & 1)) ok = false;
-        if (!ok) bars->failed = 1;
-        if (ok) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            float inv = l > 0.f ? 1.0f / l : 0.f;
-            bf16* orow = out + ((size_t)(q0 + t0 + row) * nh + head) * HD;
+                float m_safe = (m == -INFINITY) ? 0.f : m;
+                // weights, rounded to bfloat16 and packed two to a column, over this row of S: the
+                // second product's A operand
+                float pw[32];
+                unsigned* w = reinterpret_cast<unsigned*>(pw);
+                float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                float acc[32];
-                tmem_ld32(acc, tmem_o + half * 32 + lane_addr);
-                if (exists) {
+                for (int c = 0; c < KT / 2; ++c) {
+                    float p0 = fast_exp2(fmaf(s[2 * c], scale_log2, -m_safe));
+                    float p1 = fast_exp2(fmaf(s[2 * c + 1], scale_log2, -m_safe));
+                    ls[c & 3] += p0 + p1;
+                    __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+                    w[c] = *reinterpret_cast<unsigned*>(&pk);
+                }
+                l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+                tmem_st32(pw, tmem + (g & 1) * KT + lane_addr);
+                if (t > 0) {
+                    // the previous tile's product has had this tile's softmax to finish; waiting for
+                    // it here every tile also keeps this barrier's phase in step
+                    if (!mbar_wait(&bars->o_done, (g - 1) & 1)) { ok = false; break; }
+                    if (rescale) {
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        unsigned w[4];
+                        for (int half = 0; half < 2; ++half) {
+                            float acc[32];
+                            tmem_ld32(acc, tmem_o + half * 32 + lane_addr);
 #pragma unroll
-                        for (int h = 0; h < 4; ++h) {
-                            __nv_bfloat162 pk = __floats2bfloat162_rn(acc[c * 8 + 2 * h] * inv, acc[c * 8 + 2 * h + 1] * inv);
-                            w[h] = *reinterpret_cast<unsigned*>(&pk);
+                            for (int d = 0; d < 32; ++d) acc[d] *= alpha;
+                            tmem_st32(acc, tmem_o + half * 32 + lane_addr);
                         }
-                        *reinterpret_cast<uint4*>(orow + half * 32 + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(&bars->p_ready[g & 1]);
+            }
+            if (ok && !mbar_wait(&bars->o_done, (g - 1) & 1)) ok = false;
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                float inv = l > 0.f ? 1.0f / l : 0.f;
+                bf16* orow = out + ((size_t)(q0 + pt.t0 + row) * nh + head) * HD;
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    float acc[32];
+                    tmem_ld32(acc, tmem_o + half * 32 + lane_addr);
+                    if (exists) {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            unsigned w[4];
+#pragma unroll
+                            for (int h = 0; h < 4; ++h) {
+                                __nv_bfloat162 pk = __floats2bfloat162_rn(acc[c * 8 + 2 * h] * inv, acc[c * 8 + 2 * h + 1] * inv);
+                                w[h] = *reinterpret_cast<unsigned*>(&pk);
+                            }
+                            *reinterpret_cast<uint4*>(orow + half * 32 + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
                     }
                 }
             }
         }
+        if (!ok) bars->failed = 1;
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -433,10 +475,10 @@ IE_API int ie_attention_prefill_tc5_ok(int page_size, int max_ctx) {
 
 IE_API int ie_attention_prefill_tc5(const void* q, const void* k_cache, const void* v_cache, const int* tables,
                                     int table_width, const int* cu_q, const int* ctx_lens, void* out,
-                                    int num_tokens, int num_seqs, int max_tiles, int nh, int nkv,
+                                    int num_tokens, int num_seqs, int max_items, int paired, int nh, int nkv,
                                     int page_size, int total_pages, float scale, int window, int* err,
                                     void* stream) {
-    if (num_seqs <= 0 || max_tiles <= 0) return 0;
+    if (num_seqs <= 0 || max_items <= 0) return 0;
     if (nkv <= 0 || nh % nkv != 0 || (page_size & (page_size - 1)) != 0 || page_size < 8 || page_size > KT)
         return (int)cudaErrorInvalidValue;
     int page_shift = 0;
@@ -453,16 +495,16 @@ IE_API int ie_attention_prefill_tc5(const void* q, const void* k_cache, const vo
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    return ie_launch(attention_prefill_tc5_kernel, dim3(max_tiles, nh), dim3(THREADS), SMEM_BYTES,
+    return ie_launch(attention_prefill_tc5_kernel, dim3(max_items, nh), dim3(THREADS), SMEM_BYTES,
                      (cudaStream_t)stream, (const bf16*)q, km, vm, tables, table_width, cu_q, ctx_lens, (bf16*)out, num_seqs,
-                     nh, nkv, page_shift, total_pages, scale * 1.4426950408889634f, window, err);
+                     nh, nkv, page_shift, total_pages, scale * 1.4426950408889634f, window, paired, err);
 }
 
 #else  // other head sizes: the mma.sync kernels of attention_mma.cu serve them
 
 IE_API int ie_attention_prefill_tc5_ok(int, int) { return 0; }
 IE_API int ie_attention_prefill_tc5(const void*, const void*, const void*, const int*, int, const int*,
-                                    const int*, void*, int, int, int, int, int, int, int, float, int, int*,
+                                    const int*, void*, int, int, int, int, int, int, int, int, float, int, int*,
                                     void*) {
     return (int)cudaErrorNotSupported;
 }

@@ -281,7 +281,7 @@ class CudaOps:
             P, I, F = c_void_p, c_int, c_float
             lib.ie_attention_decode.argtypes = [P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, F, I, I, P, P]
             lib.ie_attention_prefill.argtypes = [P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P, P]
-            lib.ie_attention_prefill_tc5.argtypes = [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, P]
+            lib.ie_attention_prefill_tc5.argtypes = [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P]
             lib.ie_attention_prefill_tc5_ok.argtypes = [I, I]
             lib.ie_attention_decode_scratch_floats.argtypes = [I, I, I]
             lib.ie_attention_decode_scratch_floats.restype = ctypes.c_longlong
@@ -338,12 +338,17 @@ class CudaOps:
                 rows = lib.ie_attention_prefill_rows()
                 tiles = sum(-(-ql // rows) for ql, s in zip(ctx.q_lens, small) if not s)
                 if self.attn_tc5 and lib.ie_attention_prefill_tc5_ok(page_size, ctx.max_ctx_len):
-                    # head size 64, pages of 8 tokens or more: the tcgen05 / TMEM / TMA kernel
+                    # head size 64, pages of 8 tokens or more: the tcgen05 / TMEM / TMA kernel.
+                    # While the blocks would fill the GPU less than about twice, a block takes two
+                    # tiles of a request, a late (long) and an early (short) one.
+                    paired = tiles * nh <= 4 * self.sm_count
+                    if paired:
+                        tiles = sum(-(-(-(-ql // rows)) // 2) for ql, s in zip(ctx.q_lens, small) if not s)
                     self._check(lib.ie_attention_prefill_tc5(
                         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
                         block_tables.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_lens.data_ptr(), out.data_ptr(),
-                        ctx.num_tokens, ctx.num_seqs, tiles, nh, nkv, page_size, total_pages, scale, window,
-                        self._err_ptr, stream), "attention_prefill_tc5")
+                        ctx.num_tokens, ctx.num_seqs, tiles, 1 if paired else 0, nh, nkv, page_size, total_pages,
+                        scale, window, self._err_ptr, stream), "attention_prefill_tc5")
                     return
                 self._check(lib.ie_attention_prefill(
                     q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),

@@ -89,7 +89,9 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
 // thread keeps its part of the row in registers, so the row is read once and all loads are in
 // flight together (a decode step's few rows are bound by latency, not bandwidth).  The order
 // in which a row's squares are added depends only on the row's width.
-template <typename OutT, int THREADS, int VPT>
+// PCH: how many parts of `delta` are loaded at a time (1 when it is a single array: a prefill
+// step's thousands of rows want the registers for occupancy instead).
+template <typename OutT, int THREADS, int VPT, int PCH>
 __global__ void __launch_bounds__(THREADS)
 rmsnorm_vec_kernel(float* __restrict__ h, const float* __restrict__ delta, int num_partials,
                    size_t partial_stride, const float* __restrict__ weight, float eps,
@@ -116,15 +118,27 @@ rmsnorm_vec_kernel(float* __restrict__ h, const float* __restrict__ delta, int n
         if (i < hidden) x[v] = *reinterpret_cast<const float4*>(h + src + i);
     }
     if (delta) {
-        for (int p = 0; p < num_partials; ++p) {
+        // The parts are added in order, but their loads are issued several parts at a time:
+        // one part after the other, every part would cost a trip to memory.
+        for (int p0 = 0; p0 < num_partials; p0 += PCH) {
+            float4 d[PCH][VPT];
 #pragma unroll
-            for (int v = 0; v < VPT; ++v) {
-                int i = (v * THREADS + threadIdx.x) * 4;
-                if (i < hidden) {
-                    float4 d = *reinterpret_cast<const float4*>(delta + p * partial_stride + src + i);
-                    x[v].x += d.x; x[v].y += d.y; x[v].z += d.z; x[v].w += d.w;
+            for (int j = 0; j < PCH; ++j)
+#pragma unroll
+                for (int v = 0; v < VPT; ++v) {
+                    int i = (v * THREADS + threadIdx.x) * 4;
+                    d[j][v] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (p0 + j < num_partials && i < hidden)
+                        d[j][v] = *reinterpret_cast<const float4*>(delta + (p0 + j) * partial_stride + src + i);
                 }
-            }
+#pragma unroll
+            for (int j = 0; j < PCH; ++j)
+                if (p0 + j < num_partials) {
+#pragma unroll
+                    for (int v = 0; v < VPT; ++v) {
+                        x[v].x += d[j][v].x; x[v].y += d[j][v].y; x[v].z += d[j][v].z; x[v].w += d[j][v].w;
+                    }
+                }
         }
     }
 #pragma unroll
@@ -162,12 +176,18 @@ template <typename OutT>
 static int launch_rmsnorm(float* h, const float* delta, int num_partials, size_t partial_stride,
                           const float* weight, float eps, OutT* out, const int* rows, int num_rows,
                           int hidden, cudaStream_t s) {
+#define IE_NORM_ARGS s, h, delta, num_partials, partial_stride, weight, eps, out, rows, hidden
+    bool multi = delta != nullptr && num_partials > 1;
     if (hidden % 4 == 0 && hidden <= 128 * 4 * 2)
-        return ie_launch(rmsnorm_vec_kernel<OutT, 128, 2>, dim3(num_rows), dim3(128), 0, s, h, delta, num_partials, partial_stride, weight, eps, out, rows, hidden);
+        return multi ? ie_launch(rmsnorm_vec_kernel<OutT, 128, 2, 8>, dim3(num_rows), dim3(128), 0, IE_NORM_ARGS)
+                     : ie_launch(rmsnorm_vec_kernel<OutT, 128, 2, 1>, dim3(num_rows), dim3(128), 0, IE_NORM_ARGS);
     if (hidden % 4 == 0 && hidden <= 256 * 4 * 2)
-        return ie_launch(rmsnorm_vec_kernel<OutT, 256, 2>, dim3(num_rows), dim3(256), 0, s, h, delta, num_partials, partial_stride, weight, eps, out, rows, hidden);
+        return multi ? ie_launch(rmsnorm_vec_kernel<OutT, 256, 2, 8>, dim3(num_rows), dim3(256), 0, IE_NORM_ARGS)
+                     : ie_launch(rmsnorm_vec_kernel<OutT, 256, 2, 1>, dim3(num_rows), dim3(256), 0, IE_NORM_ARGS);
     if (hidden % 4 == 0 && hidden <= 512 * 4 * 4)
-        return ie_launch(rmsnorm_vec_kernel<OutT, 512, 4>, dim3(num_rows), dim3(512), 0, s, h, delta, num_partials, partial_stride, weight, eps, out, rows, hidden);
+        return multi ? ie_launch(rmsnorm_vec_kernel<OutT, 512, 4, 4>, dim3(num_rows), dim3(512), 0, IE_NORM_ARGS)
+                     : ie_launch(rmsnorm_vec_kernel<OutT, 512, 4, 1>, dim3(num_rows), dim3(512), 0, IE_NORM_ARGS);
+#undef IE_NORM_ARGS
     return ie_launch(rmsnorm_kernel<OutT, 256>, dim3(num_rows), dim3(256), 0, s, h, delta, num_partials, partial_stride, weight, eps, out, rows, hidden);
 }
 
@@ -243,7 +263,7 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const int* _
 // takes four neighbouring dims of a head's low half and the four that pair with them in the
 // high half, so all its loads are independent 16-byte loads.  `qkv` may be the sum of
 // `num_partials` arrays (the parts of a matrix product split along its inner dimension).
-template <typename T>
+template <typename T, int PCH>
 __global__ void __launch_bounds__(128)
 rope_kv_write_vec_kernel(const float* __restrict__ qkv, int num_partials, size_t partial_stride,
                          const int* __restrict__ positions, const float* __restrict__ table,
@@ -267,11 +287,24 @@ rope_kv_write_vec_kernel(const float* __restrict__ qkv, int num_partials, size_t
     size_t base = (size_t)n * (nh + 2 * nkv) * hd + (size_t)head * hd + d;
     float4 lo = *reinterpret_cast<const float4*>(qkv + base);
     float4 hi = *reinterpret_cast<const float4*>(qkv + base + half);
-    for (int p = 1; p < num_partials; ++p) {
-        float4 a = *reinterpret_cast<const float4*>(qkv + p * partial_stride + base);
-        float4 b = *reinterpret_cast<const float4*>(qkv + p * partial_stride + base + half);
-        lo.x += a.x; lo.y += a.y; lo.z += a.z; lo.w += a.w;
-        hi.x += b.x; hi.y += b.y; hi.z += b.z; hi.w += b.w;
+    // further parts: added in order, loaded PCH at a time (one after the other, every part
+    // would cost a trip to memory)
+    for (int p0 = 1; p0 < num_partials; p0 += PCH) {
+        float4 a[PCH], b[PCH];
+#pragma unroll
+        for (int j = 0; j < PCH; ++j) {
+            a[j] = b[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (p0 + j < num_partials) {
+                a[j] = *reinterpret_cast<const float4*>(qkv + (p0 + j) * partial_stride + base);
+                b[j] = *reinterpret_cast<const float4*>(qkv + (p0 + j) * partial_stride + base + half);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < PCH; ++j)
+            if (p0 + j < num_partials) {
+                lo.x += a[j].x; lo.y += a[j].y; lo.z += a[j].z; lo.w += a[j].w;
+                hi.x += b[j].x; hi.y += b[j].y; hi.z += b[j].z; hi.w += b[j].w;
+            }
     }
     if (rotate) {
         float4 c = *reinterpret_cast<const float4*>(table + (size_t)pos * hd + d);
@@ -309,7 +342,11 @@ static int launch_rope(const float* qkv, int num_partials, size_t partial_stride
     if (hd % 8 == 0 && (!rotates || rotary_dim == hd)) {
         int heads = slot_mapping ? nh + 2 * nkv : nh;
         dim3 grid(num_tokens, (heads * (hd / 8) + 127) / 128);
-        return ie_launch(rope_kv_write_vec_kernel<T>, grid, dim3(128), 0, s, qkv, num_partials, partial_stride,
+        if (num_partials > 1)
+            return ie_launch(rope_kv_write_vec_kernel<T, 8>, grid, dim3(128), 0, s, qkv, num_partials, partial_stride,
+                             positions, rotates ? table : (const float*)nullptr, table_rows, q_out, k_cache,
+                             v_cache, slot_mapping, nh, nkv, hd, page_size, total_pages, err);
+        return ie_launch(rope_kv_write_vec_kernel<T, 1>, grid, dim3(128), 0, s, qkv, num_partials, partial_stride,
                          positions, rotates ? table : (const float*)nullptr, table_rows, q_out, k_cache, v_cache,
                          slot_mapping, nh, nkv, hd, page_size, total_pages, err);
     } else {

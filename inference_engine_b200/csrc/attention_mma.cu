@@ -399,15 +399,36 @@ __device__ __forceinline__ void decode_merge_store(RowState& st, unsigned char* 
     size_t base = ((size_t)seq * nkv + kvh) * num_splits * MAX_ROWS;
     for (int idx = tid; idx < rows * HD; idx += WARPS * 32) {
         int row = idx / HD, d = idx - row * HD;
+        // the splits' partial results: loaded eight at a time, merged in the order 0, 1, 2, ...
         float m = -INFINITY;
-        for (int s = 0; s < num_splits; ++s) m = fmaxf(m, __ldcg(part_ml + (base + (size_t)s * MAX_ROWS + row) * 2));
+        for (int s0 = 0; s0 < num_splits; s0 += 8) {
+            float t[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                t[j] = s0 + j < num_splits ? __ldcg(part_ml + (base + (size_t)(s0 + j) * MAX_ROWS + row) * 2) : -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) m = fmaxf(m, t[j]);
+        }
         float m_safe = (m == -INFINITY) ? 0.f : m;
         float l = 0.f, o = 0.f;
-        for (int s = 0; s < num_splits; ++s) {
-            size_t p = base + (size_t)s * MAX_ROWS + row;
-            float f = exp2f(__ldcg(part_ml + p * 2) - m_safe);
-            l += __ldcg(part_ml + p * 2 + 1) * f;
-            o += __ldcg(part_o + p * HD + d) * f;
+        for (int s0 = 0; s0 < num_splits; s0 += 8) {
+            float tm[8], tl[8], to[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                bool in = s0 + j < num_splits;
+                size_t p = base + (size_t)(in ? s0 + j : 0) * MAX_ROWS + row;
+                tm[j] = in ? __ldcg(part_ml + p * 2) : -INFINITY;
+                tl[j] = in ? __ldcg(part_ml + p * 2 + 1) : 0.f;
+                to[j] = in ? __ldcg(part_o + p * HD + d) : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (s0 + j < num_splits) {
+                    float f = exp2f(tm[j] - m_safe);
+                    l += tl[j] * f;
+                    o += to[j] * f;
+                }
+            }
         }
         int tok = row / G, g = row - tok * G;
         out[((size_t)(q0 + tok) * nh + kvh * G + g) * HD + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);

@@ -170,7 +170,8 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
     int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     int head = blockIdx.y, G = nh / nkv, kvh = head / G;
     ie_pdl_trigger();
-    ie_pdl_wait();
+    // (lengths and block tables are the step's inputs; queries, keys and values are the previous
+    // kernel's output: the roles wait for it below, after the set-up)
     // Which request and which of its 128-token tiles are this block's?  Tile i of a request of n
     // tiles needs about i + 1 key tiles.  With few blocks (`paired`) a block takes the pair
     // (n - 1 - p, p), one after the other, so that every block of a request has the same amount
@@ -247,6 +248,7 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
 
     if (warp == 4) {
         // ---- copies: one thread ----
+        ie_pdl_wait();
         if (lane == 0) {
             int g = 0;
             bool ok = true;
@@ -314,6 +316,7 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
         unsigned lane_addr = (unsigned)(warp * 32) << 16;  // this warp's 32 TMEM lanes
         bool ok = true;
         int g = 0;
+        ie_pdl_wait();
         for (int pi = 0; pi < nparts && ok; ++pi) {
             const Part& pt = parts[pi];
             int n_tiles = pt.n_tiles, qpos_lo = pt.qpos_lo, qpos_hi = pt.qpos_hi;

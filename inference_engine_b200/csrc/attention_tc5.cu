@@ -1,6 +1,8 @@
 // Paged prefill attention on the fifth-generation tensor cores (tcgen05 + TMEM + TMA), bfloat16,
-// head size 64, pages of a multiple of 8 tokens.  One build per head size (-DIE_HD=64); for
-// other head sizes the file compiles to a stub that reports "not available".
+// head sizes 64 and 128, pages of 8 to 64 tokens.  One build per head size (-DIE_HD=64 or 128);
+// for other head sizes the file compiles to a stub that reports "not available".  With head
+// size 128 a row of K or V is two 128-byte halves (two TMA boxes, two products of 64 output
+// dims) and a block takes 320 columns of tensor memory, so one block runs per SM instead of two.
 //
 // One block = 128 query tokens of one head (a tcgen05.mma of M = 128: TMEM lane = query row =
 // thread of the softmax warps).  Six warps in three roles, decoupled by mbarriers:
@@ -31,19 +33,24 @@
 #error "compile with -DIE_HD=<head size>"
 #endif
 
-#if IE_HD == 64
+#if IE_HD == 64 || IE_HD == 128
 
 namespace {
 typedef __nv_bfloat16 bf16;
-constexpr int HD = 64;
+constexpr int HD = IE_HD;
+constexpr int HALVES = HD / 64;           // 64-wide column halves of a K or V row (128 bytes, one swizzle atom)
 constexpr int BM = 128;             // query rows per block
 constexpr int KT = 64;              // keys per tile
 constexpr int SOFTMAX_THREADS = 128;
 constexpr int THREADS = 192;                // + the copy warp and the tensor-core warp
-constexpr int KV_STAGES = 3;
-constexpr int KV_BYTES = KT * HD * 2;       // 8 KB each (K and V of a stage)
+constexpr int KV_STAGES = HD == 64 ? 3 : 4;   // head size 128: 132 KB of shared memory, one block per SM as its tensor memory asks
+constexpr int KV_BYTES = KT * HD * 2;       // K (and as much V) of a stage: HALVES tiles of 64 keys x 64 dims, 8 KB each
+constexpr int HALF_BYTES = KT * 128;
 constexpr int MAX_TABLE = 1024;             // block-table entries cached in shared memory
-constexpr int TMEM_COLS = 256;              // S (then P, packed): columns 0..63 and 64..127; O: 128..191; Q: 192..223
+// tensor memory: S (then P, packed) in columns 0..63 and 64..127, O in the next HD, Q (two dims to a
+// column) in the next HD / 2: 224 columns for head size 64 (two blocks per SM), 320 for 128 (one)
+constexpr int TMEM_COLS = HD == 64 ? 256 : 512;
+constexpr int BLOCKS_PER_SM = HD == 64 ? 2 : 1;
 constexpr long long SPIN_LIMIT = 20000000;
 constexpr float RESCALE_LAG = 8.0f;         // in powers of two
 
@@ -155,7 +162,7 @@ struct __align__(8) Barriers {
     int failed;
 };
 
-__global__ void __launch_bounds__(THREADS, 2)
+__global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM)
 attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__ CUtensorMap k_map,
                              const __grid_constant__ CUtensorMap v_map, const int* __restrict__ tables,
                              int table_width, const int* __restrict__ cu_q, const int* __restrict__ ctx_lens,
@@ -164,7 +171,7 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     unsigned char* k_s = smem;                                  // stages x 8 KB
-    unsigned char* v_s = k_s + KV_STAGES * KV_BYTES;            // stages x 8 KB
+    unsigned char* v_s = k_s + KV_STAGES * KV_BYTES;
     int* table_s = reinterpret_cast<int*>(v_s + KV_STAGES * KV_BYTES);  // MAX_TABLE ints
     Barriers* bars = reinterpret_cast<Barriers*>(table_s + MAX_TABLE);
     int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -262,8 +269,12 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
                     for (int p = 0; p < pages_per_tile; ++p) {
                         int page = table_s[min(entry + p, MAX_TABLE - 1)];
                         int row = (page * nkv + kvh) << page_shift;
-                        tma_load_2d(k_s + stage * KV_BYTES + p * page_size * 128, &k_map, 0, row, &bars->kv_full[stage]);
-                        tma_load_2d(v_s + stage * KV_BYTES + p * page_size * 128, &v_map, 0, row, &bars->kv_full[stage]);
+#pragma unroll
+                        for (int h = 0; h < HALVES; ++h) {  // 64 dims to a box
+                            int at = stage * KV_BYTES + h * HALF_BYTES + p * page_size * 128;
+                            tma_load_2d(k_s + at, &k_map, h * 64, row, &bars->kv_full[stage]);
+                            tma_load_2d(v_s + at, &v_map, h * 64, row, &bars->kv_full[stage]);
+                        }
                     }
                 }
             }
@@ -280,8 +291,9 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 unsigned ka = smem_u32(k_s + stage * KV_BYTES);
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ++ks)  // 32 bytes further along k per step
-                    umma_ta(tmem + (g & 1) * KT, tmem_q + ks * 8, smem_desc(ka + ks * 32), idesc_qk, ks > 0);
+                for (int ks = 0; ks < HD / 16; ++ks)  // 32 bytes further along k per step, 4 steps to a half
+                    umma_ta(tmem + (g & 1) * KT, tmem_q + ks * 8, smem_desc(ka + (ks >> 2) * HALF_BYTES + (ks & 3) * 32),
+                            idesc_qk, ks > 0);
                 umma_commit(&bars->s_done[g & 1]);
                 return true;
             };
@@ -302,8 +314,11 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
                     int stage = g % KV_STAGES;
                     unsigned va = smem_u32(v_s + stage * KV_BYTES);
 #pragma unroll
-                    for (int ks = 0; ks < KT / 16; ++ks)  // P: 8 columns of two keys each; V: 16 keys = 2048 bytes
-                        umma_ta(tmem_o, tmem + (g & 1) * KT + ks * 8, smem_desc(va + ks * 2048), idesc_pv, (t > 0 || ks > 0) ? 1u : 0u);
+                    for (int h = 0; h < HALVES; ++h)  // 64 output dims per product
+#pragma unroll
+                        for (int ks = 0; ks < KT / 16; ++ks)  // P: 8 columns of two keys each; V: 16 keys = 2048 bytes
+                            umma_ta(tmem_o + h * 64, tmem + (g & 1) * KT + ks * 8,
+                                    smem_desc(va + h * HALF_BYTES + ks * 2048), idesc_pv, (t > 0 || ks > 0) ? 1u : 0u);
                     umma_commit(&bars->o_done);
                     umma_commit(&bars->kv_empty[stage]);
                 }
@@ -330,12 +345,15 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
             float m = -INFINITY, l = 0.f;
             {   // this row of Q, two features to a column, as the first product's A operand (the
                 // products of the part before have all been waited for)
-                float qw[32];
-                uint4* q4 = reinterpret_cast<uint4*>(qw);
                 const uint4* src = reinterpret_cast<const uint4*>(q + ((size_t)(q0 + pt.t0 + row) * nh + head) * HD);
 #pragma unroll
-                for (int c = 0; c < HD / 8; ++c) q4[c] = exists ? src[c] : make_uint4(0u, 0u, 0u, 0u);
-                tmem_st32(qw, tmem_q + lane_addr);
+                for (int h = 0; h < HALVES; ++h) {
+                    float qw[32];
+                    uint4* q4 = reinterpret_cast<uint4*>(qw);
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) q4[c] = exists ? src[h * 8 + c] : make_uint4(0u, 0u, 0u, 0u);
+                    tmem_st32(qw, tmem_q + h * 32 + lane_addr);
+                }
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 mbar_arrive(&bars->q_full);
             }
@@ -391,7 +409,7 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
                     if (rescale) {
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-                        for (int half = 0; half < 2; ++half) {
+                        for (int half = 0; half < HD / 32; ++half) {
                             float acc[32];
                             tmem_ld32(acc, tmem_o + half * 32 + lane_addr);
 #pragma unroll
@@ -409,7 +427,7 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
                 float inv = l > 0.f ? 1.0f / l : 0.f;
                 bf16* orow = out + ((size_t)(q0 + pt.t0 + row) * nh + head) * HD;
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
+                for (int half = 0; half < HD / 32; ++half) {
                     float acc[32];
                     tmem_ld32(acc, tmem_o + half * 32 + lane_addr);
                     if (exists) {

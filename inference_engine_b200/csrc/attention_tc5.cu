@@ -25,8 +25,7 @@
 // are bounded; a block that waits too long records IE_ERR_TIMEOUT, frees its TMEM and leaves.
 // The reference's counterpart is the FlashAttention varlen call over gathered keys and values
 // (engine/model/layers.py:246-253).
-#include "common.cuh"
-#include <cuda.h>
+#include "tma.cuh"
 #include <math.h>
 
 #ifndef IE_HD
@@ -35,8 +34,9 @@
 
 #if IE_HD == 64 || IE_HD == 128
 
+using namespace ie_tma;
+
 namespace {
-typedef __nv_bfloat16 bf16;
 constexpr int HD = IE_HD;
 constexpr int HALVES = HD / 64;           // 64-wide column halves of a K or V row (128 bytes, one swizzle atom)
 constexpr int BM = 128;             // query rows per block
@@ -51,49 +51,14 @@ constexpr int MAX_TABLE = 1024;             // block-table entries cached in sha
 // column) in the next HD / 2: 224 columns for head size 64 (two blocks per SM), 320 for 128 (one)
 constexpr int TMEM_COLS = HD == 64 ? 256 : 512;
 constexpr int BLOCKS_PER_SM = HD == 64 ? 2 : 1;
-constexpr long long SPIN_LIMIT = 20000000;
 constexpr float RESCALE_LAG = 8.0f;         // in powers of two
 
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, int bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, int parity) {
-    unsigned addr = smem_u32(bar);
-    for (long long spin = 0; spin < SPIN_LIMIT; ++spin) {
-        unsigned done;
-        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-                     : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
-}
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
 }
 
-// Shared-memory matrix descriptor, 128-byte swizzle, rows (or 8-key groups) 1024 bytes apart.
-__device__ __forceinline__ unsigned long long smem_desc(unsigned addr) {
-    unsigned long long d = 0;
-    d |= (unsigned long long)((addr >> 4) & 0x3FFF);   // start address, 16-byte units
-    d |= (unsigned long long)64 << 16;                 // leading byte offset (unused here): 1024 B
-    d |= (unsigned long long)64 << 32;                 // stride byte offset: 1024 B between 8-row groups
-    d |= (unsigned long long)1 << 46;                  // descriptor version of this architecture
-    d |= (unsigned long long)2 << 61;                  // layout: 128-byte swizzle
-    return d;
-}
 // Instruction descriptor: bfloat16 x bfloat16 -> float, M = 128, N = 64; b_mn: B is MN-major.
 __device__ __forceinline__ unsigned instr_desc(bool b_mn) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
@@ -103,9 +68,6 @@ __device__ __forceinline__ void umma_ta(unsigned tmem_d, unsigned tmem_a, unsign
     asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
                  " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
                  ::"r"(tmem_d), "r"(tmem_a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 // One row (this thread's TMEM lane) of 64 columns starting at `taddr`.
 __device__ __forceinline__ void tmem_ld64(float (&v)[64], unsigned taddr) {
@@ -292,7 +254,7 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
                 unsigned ka = smem_u32(k_s + stage * KV_BYTES);
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks)  // 32 bytes further along k per step, 4 steps to a half
-                    umma_ta(tmem + (g & 1) * KT, tmem_q + ks * 8, smem_desc(ka + (ks >> 2) * HALF_BYTES + (ks & 3) * 32),
+                    umma_ta(tmem + (g & 1) * KT, tmem_q + ks * 8, umma_desc_sw128(ka + (ks >> 2) * HALF_BYTES + (ks & 3) * 32),
                             idesc_qk, ks > 0);
                 umma_commit(&bars->s_done[g & 1]);
                 return true;
@@ -318,7 +280,7 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
 #pragma unroll
                         for (int ks = 0; ks < KT / 16; ++ks)  // P: 8 columns of two keys each; V: 16 keys = 2048 bytes
                             umma_ta(tmem_o + h * 64, tmem + (g & 1) * KT + ks * 8,
-                                    smem_desc(va + h * HALF_BYTES + ks * 2048), idesc_pv, (t > 0 || ks > 0) ? 1u : 0u);
+                                    umma_desc_sw128(va + h * HALF_BYTES + ks * 2048), idesc_pv, (t > 0 || ks > 0) ? 1u : 0u);
                     umma_commit(&bars->o_done);
                     umma_commit(&bars->kv_empty[stage]);
                 }
@@ -454,35 +416,6 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
     if (tid == 0 && bars->failed) ie_report(err, IE_ERR_TIMEOUT, blockIdx.x, blockIdx.y);
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    }
-    return fn;
-}
-// Row-major [rows, cols] bfloat16 as a 2-D map with boxes of box_rows x 64 columns, 128-byte swizzle.
-bool make_map(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (fn == nullptr) return false;
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
 constexpr size_t SMEM_BYTES = 2 * KV_STAGES * KV_BYTES + MAX_TABLE * 4 + sizeof(Barriers) + 1024;
 }  // namespace
 
@@ -506,8 +439,8 @@ IE_API int ie_attention_prefill_tc5(const void* q, const void* k_cache, const vo
     while ((1 << page_shift) < page_size) ++page_shift;
     CUtensorMap km, vm;
     long long kv_rows = (long long)total_pages * nkv * page_size;
-    if (!make_map(&km, k_cache, kv_rows, HD, page_size) ||
-        !make_map(&vm, v_cache, kv_rows, HD, page_size))
+    if (!make_map_bf16(&km, k_cache, kv_rows, HD, page_size) ||
+        !make_map_bf16(&vm, v_cache, kv_rows, HD, page_size))
         return (int)cudaErrorNotSupported;
     static bool configured = false;
     if (!configured) {

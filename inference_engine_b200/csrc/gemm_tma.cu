@@ -24,11 +24,11 @@
 // them in order.  Every wait on an mbarrier is bounded: a block that waits too long sets the
 // error word, drains and leaves.
 // The reference uses cuBLAS here (nn.Linear, engine/model/layers.py:126-129, 273-275).
-#include "common.cuh"
-#include <cuda.h>
+#include "tma.cuh"
+
+using namespace ie_tma;
 
 namespace {
-typedef __nv_bfloat16 bf16;
 constexpr int CWARPS = 4;                 // consumer warps
 constexpr int THREADS = (CWARPS + 1) * 32;  // + one producer warp
 constexpr int BN = 128;                   // features per block (32 per consumer warp)
@@ -39,46 +39,6 @@ constexpr int MAX_OPS = 12;               // copies in flight (ring slots)
 constexpr int MAX_KPO = 4;                // k blocks per copy
 // Shared memory for tiles: what the 227 KB of an SM leave beside X (8 NT rows x 2048 k)
 __host__ __device__ constexpr int ring_bytes(int nt) { return nt == 1 ? 192 * 1024 : 160 * 1024; }
-constexpr long long SPIN_LIMIT = 20000000;  // about ten milliseconds of polling
-
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, int bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-// Bounded wait: false when the phase did not complete within SPIN_LIMIT polls.
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, int parity) {
-    unsigned addr = smem_u32(bar);
-    for (long long spin = 0; spin < SPIN_LIMIT; ++spin) {
-        unsigned done;
-        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-                     : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, unsigned long long* bar) {
-    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], unsigned addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-__device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
 
 // Shared memory: [ring: ops x kpo x 16 KB][X: kblocks x (8 NT rows x 128 B)][barriers], 1024-byte aligned.
 // NT: 8-token column tiles (1: M <= 8, 2: M <= 16).  `kpo` k blocks per copy (3-D map) or 1 (2-D map).
@@ -220,53 +180,6 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
     if (threadIdx.x == 0 && failed) ie_report(err, IE_ERR_TIMEOUT, blockIdx.x, blockIdx.y);
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    }
-    return fn;
-}
-
-// A row-major [rows, cols] bfloat16 matrix as a 2-D tensor map with boxes of box_rows x 64
-// columns and the 128-byte swizzle; out-of-range elements read as zero.
-bool make_map(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (fn == nullptr) return false;
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-// W[rows, cols] (cols a multiple of 64) as a 3-D tensor (64 k, rows, cols / 64 k blocks) with
-// boxes of 64 x 128 features x kpo k blocks: in shared memory kpo consecutive 128 x 64 tiles.
-bool make_map_3d(CUtensorMap* map, const void* base, long long rows, long long cols, int kpo) {
-    EncodeTiledFn fn = encode_fn();
-    if (fn == nullptr || cols % BK != 0) return false;
-    cuuint64_t dims[3] = {(cuuint64_t)BK, (cuuint64_t)rows, (cuuint64_t)(cols / BK)};
-    cuuint64_t strides[2] = {(cuuint64_t)cols * 2, (cuuint64_t)BK * 2};
-    cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)BN, (cuuint32_t)kpo};
-    cuuint32_t elem[3] = {1, 1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 template <int NT, typename OutT>
 int launch(const void* X, const void* W, OutT* out, int M, int N, int K, int kblocks_per_split, int splits,
            int* err, cudaStream_t s) {
@@ -278,11 +191,11 @@ int launch(const void* X, const void* W, OutT* out, int M, int N, int K, int kbl
         // (16 tokens leave room for 160 KB of tiles: 32 KB copies keep five of them in flight)
         for (kpo = NT == 1 ? MAX_KPO : 2; kpo > 1 && kblocks_per_split % kpo != 0; kpo >>= 1) {}
         w3d = 1;
-        if (!make_map_3d(&wm, W, N, K, kpo)) return (int)cudaErrorNotSupported;
-    } else if (!make_map(&wm, W, N, K, BN)) {
+        if (!make_map_bf16_3d(&wm, W, N, K, BN, kpo)) return (int)cudaErrorNotSupported;
+    } else if (!make_map_bf16(&wm, W, N, K, BN)) {
         return (int)cudaErrorNotSupported;
     }
-    if (!make_map(&xm, X, M, K, 8 * NT)) return (int)cudaErrorNotSupported;
+    if (!make_map_bf16(&xm, X, M, K, 8 * NT)) return (int)cudaErrorNotSupported;
     int ops = ring_bytes(NT) / (kpo * STAGE_BYTES);
     if (ops > MAX_OPS) ops = MAX_OPS;
     size_t smem = (size_t)ring_bytes(NT) + (size_t)MAX_KBLOCKS * 8 * NT * BK * 2 + (2 * MAX_OPS + 1) * 8 + 1024;

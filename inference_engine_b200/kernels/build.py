@@ -74,7 +74,7 @@ def build_dir() -> Path:
 
 def _digest(sources: list[Path], defines: list[str]) -> str:
     h = hashlib.sha256()
-    for extra in sorted(CSRC.glob("*.cuh")):
+    for extra in sorted(list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))):
         h.update(extra.name.encode())
         h.update(extra.read_bytes())
     for src in sources:

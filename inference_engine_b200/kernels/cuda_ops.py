@@ -318,9 +318,20 @@ class CudaOps:
         total_pages = k_cache.shape[0]
         if q.dtype == torch.bfloat16 and hd in ATTENTION_HEAD_DIMS and groups <= 16:
             lib = self._attention_lib(hd)
-            small = [ql * groups <= 16 for ql in ctx.q_lens]
+            # which requests go to which kernel: the same for every layer of the step
+            plan = getattr(ctx, "_attention_plan", None)
+            if plan is None or plan["groups"] != groups:
+                small = [ql * groups <= 16 for ql in ctx.q_lens]
+                plan = {"groups": groups, "small": small, "any": any(small), "all": all(small)}
+                if not plan["all"]:
+                    rows = lib.ie_attention_prefill_rows()
+                    per_seq = [-(-ql // rows) for ql, s in zip(ctx.q_lens, small) if not s]
+                    plan["tiles"] = sum(per_seq)
+                    plan["tile_pairs"] = sum(-(-t // 2) for t in per_seq)
+                ctx._attention_plan = plan
+            small, any_small, all_small = plan["small"], plan["any"], plan["all"]
             stream = self._stream()
-            if any(small):
+            if any_small:
                 splits = self.decode_splits(ctx.num_seqs, nkv)
                 floats = lib.ie_attention_decode_scratch_floats(ctx.num_seqs, nkv, splits)
                 scratch = tickets = None
@@ -334,16 +345,15 @@ class CudaOps:
                     block_tables.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_lens.data_ptr(), out.data_ptr(),
                     self._ptr(scratch), self._ptr(tickets), ctx.num_seqs, nh, nkv, page_size,
                     total_pages, scale, window, splits, self._err_ptr, stream), "attention_decode")
-            if not all(small):
-                rows = lib.ie_attention_prefill_rows()
-                tiles = sum(-(-ql // rows) for ql, s in zip(ctx.q_lens, small) if not s)
+            if not all_small:
+                tiles = plan["tiles"]
                 if self.attn_tc5 and lib.ie_attention_prefill_tc5_ok(page_size, ctx.max_ctx_len):
                     # head size 64, pages of 8 tokens or more: the tcgen05 / TMEM / TMA kernel.
                     # While the blocks would fill the GPU less than about twice, a block takes two
                     # tiles of a request, a late (long) and an early (short) one.
                     paired = tiles * nh <= 4 * self.sm_count
                     if paired:
-                        tiles = sum(-(-(-(-ql // rows)) // 2) for ql, s in zip(ctx.q_lens, small) if not s)
+                        tiles = plan["tile_pairs"]
                     self._check(lib.ie_attention_prefill_tc5(
                         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
                         block_tables.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_lens.data_ptr(), out.data_ptr(),

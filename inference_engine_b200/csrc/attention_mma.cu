@@ -87,13 +87,24 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 template <int KT, int NTHREADS>
 struct TilePages {
     static constexpr int ITERS = (KT * C + NTHREADS - 1) / NTHREADS;
-    int page[ITERS];
+    // A warp that stages a tile by itself, whole rows per instruction (the decode kernel): lane l
+    // keeps the one block-table entry (key0 >> page_shift) + l, and the copies take theirs from
+    // the lane that has it.  A tile never spans more than KT <= 32 entries.
+    static constexpr bool BY_LANE = NTHREADS == 32 && 32 % C == 0 && KT <= 32;
+    int page[BY_LANE ? 1 : ITERS];
 };
 
 template <int KT, int NTHREADS>
 __device__ __forceinline__ void fetch_pages(TilePages<KT, NTHREADS>& pg, const int* __restrict__ table,
                                             int table_width, int key0, int lo, int hi, int page_shift,
                                             int tid) {
+    if constexpr (TilePages<KT, NTHREADS>::BY_LANE) {
+        int entry = (key0 >> page_shift) + tid;
+        int first = entry << page_shift, last = first + (1 << page_shift) - 1;
+        bool wanted = last >= max(key0, lo) && first <= min(key0 + KT - 1, hi) && entry < table_width;
+        pg.page[0] = wanted ? table[entry] : -1;
+        return;
+    }
 #pragma unroll
     for (int i = 0; i < TilePages<KT, NTHREADS>::ITERS; ++i) {
         int idx = i * NTHREADS + tid;
@@ -112,33 +123,37 @@ __device__ __forceinline__ int issue_kv(bf16* ktile, bf16* vtile, const TilePage
                                         const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                                         int key0, int lo, int hi, int kvh, int nkv, int page_shift,
                                         int total_pages, int tid, int* err) {
-    if constexpr (REPORT && NTHREADS == 32 && 32 % C == 0) {
+    if constexpr (REPORT && TilePages<KT, NTHREADS>::BY_LANE) {
         // A warp's own tile (the decode kernel): every instruction copies R whole rows, so the
         // shared-memory offsets are constants of the lane and the unrolled iteration, and the
-        // global offset needs one 64-bit product per page.  (The decode kernel is bound by
-        // the issue of these copies; the general form below costs twice the instructions.)
+        // global address is one 64-bit multiply-add per instruction.  Tiles that lie wholly
+        // inside [lo, hi] (all but a request's first and last) skip the range checks.  (The
+        // decode kernel is bound by the number of instructions it issues per tile.)
         constexpr int R = 32 / C;                 // rows per instruction
         constexpr int V = R >= 8 ? 1 : 8 / R;     // distinct (row & 7) patterns over iterations
         const int sub = tid / C, c = tid % C;
-        const int page_mask = (1 << page_shift) - 1;
+        const int page_mask = (1 << page_shift) - 1, entry0 = key0 >> page_shift;
         const unsigned ks = (unsigned)__cvta_generic_to_shared(ktile), vs = (unsigned)__cvta_generic_to_shared(vtile);
+        const unsigned page_bytes = (unsigned)(HD * 2) << page_shift;   // one head's rows of a page
+        const unsigned long long kb = (unsigned long long)k_cache, vb = (unsigned long long)v_cache;
         unsigned dst_lane[V];
 #pragma unroll
         for (int v = 0; v < V; ++v) dst_lane[v] = (unsigned)((sub * C + swz(sub + v * R, c)) * 16);
+        const bool inner = key0 >= lo && key0 + KT - 1 <= hi;  // the same for the whole warp
 #pragma unroll
         for (int i = 0; i < KT / R; ++i) {
             int kpos = key0 + sub + i * R;
-            int page = pg.page[i];
-            bool in_range = kpos >= lo && kpos <= hi;
+            int page = __shfl_sync(0xffffffffu, pg.page[0], (kpos >> page_shift) - entry0);
+            bool in_range = inner || (kpos >= lo && kpos <= hi);
             bool valid = in_range && (unsigned)page < (unsigned)total_pages;
             if (in_range && !valid) ie_report(err, page < 0 ? IE_ERR_TABLE : IE_ERR_PAGE, page, kpos);
-            size_t off = valid ? (((size_t)(page * nkv + kvh)) << page_shift) * HD +
-                                     (size_t)((kpos & page_mask) * HD + c * 8)
-                               : 0;
+            unsigned long long off = valid ? (unsigned long long)(unsigned)(page * nkv + kvh) * page_bytes +
+                                                 (unsigned)(((kpos & page_mask) * HD + c * 8) * 2)
+                                           : 0ull;
             unsigned dst = (unsigned)(i * R * C * 16) + dst_lane[((i * R) & 7) / R % V];
             int bytes = valid ? 16 : 0;  // 0: nothing is read, the 16 bytes are zero-filled
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(ks + dst), "l"(k_cache + off), "r"(bytes));
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(vs + dst), "l"(v_cache + off), "r"(bytes));
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(ks + dst), "l"(kb + off), "r"(bytes));
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(vs + dst), "l"(vb + off), "r"(bytes));
         }
         return 0x7fffffff;
     }
@@ -212,6 +227,7 @@ __device__ __forceinline__ void softmax_rows(RowState& st, float (&s)[KT / 8][4]
         }
     }
     float alpha[2], m_safe[2];
+    bool grew = false;
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         float t = tile_max[r];
@@ -220,13 +236,19 @@ __device__ __forceinline__ void softmax_rows(RowState& st, float (&s)[KT / 8][4]
         float m_new = fmaxf(st.m[r], t * scale_log2);  // the scale is positive: max commutes
         m_safe[r] = (m_new == -INFINITY) ? 0.f : m_new;
         alpha[r] = fast_exp2(st.m[r] - m_safe[r]);  // 0 when nothing was seen before
+        grew = grew || m_new > st.m[r];
         st.m[r] = m_new;
-        st.l[r] *= alpha[r];
     }
+    // the sum and the output so far shrink only when a row's maximum grew; on most tiles of a
+    // long context none of the warp's rows does
+    if (__any_sync(0xffffffffu, grew)) {
+        st.l[0] *= alpha[0];
+        st.l[1] *= alpha[1];
 #pragma unroll
-    for (int d = 0; d < DT; ++d) {
-        st.o[d][0] *= alpha[0]; st.o[d][1] *= alpha[0];
-        st.o[d][2] *= alpha[1]; st.o[d][3] *= alpha[1];
+        for (int d = 0; d < DT; ++d) {
+            st.o[d][0] *= alpha[0]; st.o[d][1] *= alpha[0];
+            st.o[d][2] *= alpha[1]; st.o[d][3] *= alpha[1];
+        }
     }
 #pragma unroll
     for (int n = 0; n < NT; ++n) {

@@ -5,14 +5,15 @@
 // dims) and a block takes 320 columns of tensor memory, so one block runs per SM instead of two.
 //
 // One block = 128 query tokens of one head (a tcgen05.mma of M = 128: TMEM lane = query row =
-// thread of the softmax warps).  Six warps in three roles, decoupled by mbarriers:
+// thread of the softmax warps).  Six (or seven) warps in three roles, decoupled by mbarriers:
 //   * warp 4, one thread: copies the pages of every 64-key tile of K and V with TMA
 //     (cp.async.bulk.tensor, one box per page, 128-byte swizzle) into a three-stage ring;
 //   * warp 5, one thread: issues S(t) = Q K(t)^T (four tcgen05.mma of k = 16, A = Q from tensor
 //     memory, B = K from shared memory) into one of two 64-column TMEM buffers, one tile ahead
 //     of the softmax, and O += P(t) V(t) (A = P from tensor memory, V as an MN-major B operand)
 //     as soon as the weights of tile t are written; tcgen05.commit signals the softmax warps
-//     and frees the ring stage;
+//     and frees the ring stage (head size 128: a seventh warp issues the second product, so
+//     that the two products' instructions go out side by side);
 //   * warps 0-3: every thread puts its row of Q into tensor memory once, then for every tile
 //     reads its row of S (tcgen05.ld 32x32b), masks (diagonal and window tiles only), keeps the
 //     running maximum and sum -- a row is private to a thread, no shuffles -- rounds the weights
@@ -42,7 +43,11 @@ constexpr int HALVES = HD / 64;           // 64-wide column halves of a K or V r
 constexpr int BM = 128;             // query rows per block
 constexpr int KT = 64;              // keys per tile
 constexpr int SOFTMAX_THREADS = 128;
-constexpr int THREADS = 192;                // + the copy warp and the tensor-core warp
+// Head size 128: a thread gets a tcgen05.mma out about every 117 clocks whatever its size, and a
+// tile's sixteen products would keep one thread busy longer than the softmax takes, so each of the
+// two products has an issuing warp of its own.
+constexpr bool SPLIT_ISSUE = HD == 128;
+constexpr int THREADS = SPLIT_ISSUE ? 224 : 192;  // + the copy warp and the tensor-core warp(s)
 constexpr int KV_STAGES = HD == 64 ? 3 : 4;   // head size 128: 132 KB of shared memory, one block per SM as its tensor memory asks
 constexpr int KV_BYTES = KT * HD * 2;       // K (and as much V) of a stage: HALVES tiles of 64 keys x 64 dims, 8 KB each
 constexpr int HALF_BYTES = KT * 128;
@@ -225,7 +230,7 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
                 const Part& pt = parts[pi];
                 for (int t = 0; t < pt.n_tiles; ++t, ++g) {
                     int stage = g % KV_STAGES;
-                    if (g >= KV_STAGES && !mbar_wait(&bars->kv_empty[stage], (g / KV_STAGES - 1) & 1)) { ok = false; break; }
+                    if (g >= KV_STAGES && !mbar_wait_compact(&bars->kv_empty[stage], (g / KV_STAGES - 1) & 1)) { ok = false; break; }
                     mbar_expect_tx(&bars->kv_full[stage], 2 * KV_BYTES);
                     int entry = ((pt.key_begin + t * KT) >> page_shift) - first_entry;
                     for (int p = 0; p < pages_per_tile; ++p) {
@@ -242,14 +247,15 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
             }
             if (!ok) bars->failed = 1;
         }
-    } else if (warp == 5) {
-        // ---- tensor core: one thread ----
+    } else if (!SPLIT_ISSUE && warp == 5) {
+        // ---- tensor core: one thread issues both products (head size 64: the exponentials bound
+        // the kernel, a second issuing warp only takes issue slots from the softmax warps) ----
         if (lane == 0) {
             unsigned idesc_qk = instr_desc(false), idesc_pv = instr_desc(true);
             bool ok = true;
             auto issue_s = [&](int g) {  // S = Q K^T of key tile g into S buffer g & 1
                 int stage = g % KV_STAGES;
-                if (!mbar_wait(&bars->kv_full[stage], (g / KV_STAGES) & 1)) return false;
+                if (!mbar_wait_compact(&bars->kv_full[stage], (g / KV_STAGES) & 1)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 unsigned ka = smem_u32(k_s + stage * KV_BYTES);
 #pragma unroll
@@ -264,16 +270,74 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
                 int n_tiles = parts[pi].n_tiles;
                 // the part's Q is in tensor memory (and the softmax warps are done with the
                 // accumulator of the part before)
-                ok = mbar_wait(&bars->q_full, pi & 1) && issue_s(g);
+                ok = mbar_wait_compact(&bars->q_full, pi & 1) && issue_s(g);
                 for (int t = 0; t < n_tiles && ok; ++t, ++g) {
                     if (t + 1 < n_tiles) {
                         // its S buffer held the weights of tile g - 1: that product must have read them
-                        if (g > 0 && !mbar_wait(&bars->o_done, (g - 1) & 1)) { ok = false; break; }
+                        if (g > 0 && !mbar_wait_compact(&bars->o_done, (g - 1) & 1)) { ok = false; break; }
                         ok = issue_s(g + 1);
                     }
-                    if (!ok || !mbar_wait(&bars->p_ready[g & 1], (g >> 1) & 1)) { ok = false; break; }
+                    if (!ok || !mbar_wait_compact(&bars->p_ready[g & 1], (g >> 1) & 1)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     int stage = g % KV_STAGES;
+                    unsigned va = smem_u32(v_s + stage * KV_BYTES);
+#pragma unroll
+                    for (int h = 0; h < HALVES; ++h)  // 64 output dims per product
+#pragma unroll
+                        for (int ks = 0; ks < KT / 16; ++ks)  // P: 8 columns of two keys each; V: 16 keys = 2048 bytes
+                            umma_ta(tmem_o + h * 64, tmem + (g & 1) * KT + ks * 8,
+                                    umma_desc_sw128(va + h * HALF_BYTES + ks * 2048), idesc_pv, (t > 0 || ks > 0) ? 1u : 0u);
+                    umma_commit(&bars->o_done);
+                    umma_commit(&bars->kv_empty[stage]);
+                }
+            }
+            if (!ok) bars->failed = 1;
+        }
+    } else if (SPLIT_ISSUE && warp == 5) {
+        // ---- tensor core, first product: one thread issues S = Q K^T of every key tile ----
+        // (a thread gets a tcgen05.mma out about every 117 clocks whatever its size, so the two
+        // products of a tile are issued by a thread each)
+        if (lane == 0) {
+            unsigned idesc_qk = instr_desc(false);
+            bool ok = true;
+            int g = 0;
+            for (int pi = 0; pi < nparts && ok; ++pi) {
+                // the part's Q is in tensor memory
+                ok = mbar_wait_compact(&bars->q_full, pi & 1);
+                for (int t = 0; t < parts[pi].n_tiles && ok; ++t, ++g) {
+                    // S buffer g & 1 held the weights of tile g - 2: that product must have read
+                    // them.  (Waited for right after S(g - 1) went out, so the barrier cannot be
+                    // more than one phase ahead.  For a part's first two tiles the wait for Q
+                    // covers it: the softmax warps had waited for all products of the part before,
+                    // and by now this barrier may be any number of phases ahead.)
+                    if (t >= 2 && !mbar_wait_compact(&bars->o_done, (g - 2) & 1)) { ok = false; break; }
+                    int stage = g % KV_STAGES;
+                    if (!mbar_wait_compact(&bars->kv_full[stage], (g / KV_STAGES) & 1)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    unsigned ka = smem_u32(k_s + stage * KV_BYTES);
+#pragma unroll
+                    for (int ks = 0; ks < HD / 16; ++ks)  // 32 bytes further along k per step, 4 steps to a half
+                        umma_ta(tmem + (g & 1) * KT, tmem_q + ks * 8,
+                                umma_desc_sw128(ka + (ks >> 2) * HALF_BYTES + (ks & 3) * 32), idesc_qk, ks > 0);
+                    umma_commit(&bars->s_done[g & 1]);
+                }
+            }
+            if (!ok) bars->failed = 1;
+        }
+    } else if (SPLIT_ISSUE && warp == 6) {
+        // ---- tensor core, second product: one thread issues O += P V of every key tile ----
+        if (lane == 0) {
+            unsigned idesc_pv = instr_desc(true);
+            bool ok = true;
+            int g = 0;
+            for (int pi = 0; pi < nparts && ok; ++pi) {
+                for (int t = 0; t < parts[pi].n_tiles; ++t, ++g) {
+                    int stage = g % KV_STAGES;
+                    // (the softmax warps are done with the accumulator of the part before: they
+                    // read it before they wrote this part's Q and its first weights)
+                    if (!mbar_wait_compact(&bars->kv_full[stage], (g / KV_STAGES) & 1) ||
+                        !mbar_wait_compact(&bars->p_ready[g & 1], (g >> 1) & 1)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     unsigned va = smem_u32(v_s + stage * KV_BYTES);
 #pragma unroll
                     for (int h = 0; h < HALVES; ++h)  // 64 output dims per product
@@ -321,7 +385,7 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
             }
             for (int t = 0; t < n_tiles; ++t, ++g) {
                 int key0 = pt.key_begin + t * KT;
-                if (!mbar_wait(&bars->s_done[g & 1], (g >> 1) & 1)) { ok = false; break; }
+                if (!mbar_wait_compact(&bars->s_done[g & 1], (g >> 1) & 1)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 float s[KT];
                 tmem_ld64(s, tmem + (g & 1) * KT + lane_addr);
@@ -367,7 +431,7 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
                 if (t > 0) {
                     // the previous tile's product has had this tile's softmax to finish; waiting for
                     // it here every tile also keeps this barrier's phase in step
-                    if (!mbar_wait(&bars->o_done, (g - 1) & 1)) { ok = false; break; }
+                    if (!mbar_wait_compact(&bars->o_done, (g - 1) & 1)) { ok = false; break; }
                     if (rescale) {
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
@@ -383,7 +447,7 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 mbar_arrive(&bars->p_ready[g & 1]);
             }
-            if (ok && !mbar_wait(&bars->o_done, (g - 1) & 1)) ok = false;
+            if (ok && !mbar_wait_compact(&bars->o_done, (g - 1) & 1)) ok = false;
             if (ok) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 float inv = l > 0.f ? 1.0f / l : 0.f;

@@ -398,31 +398,44 @@ __global__ void silu_mul_kernel(const InT* __restrict__ gate_up, int num_partial
     }
 }
 
-// bfloat16 in and out, one array, width a multiple of 8: eight values per thread, 16-byte
-// loads and stores (a prefill step moves a hundred megabytes through this kernel).
+// bfloat16 in and out, one array, width a multiple of 8: 16-byte loads and stores, two of each
+// per thread in flight (a prefill step moves a hundred megabytes through this kernel), the row
+// from the grid (no division), and the special-function unit's reciprocal and exponential: their
+// error, a few units in the last place of a 32-bit value, vanishes in the rounding to bfloat16.
+constexpr int SILU_VECS = 2;  // 8-value vectors per thread
 __global__ void __launch_bounds__(256)
-silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
-                       int inter, size_t total_vec) {
+silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, int inter) {
     ie_pdl_trigger();
     ie_pdl_wait();
-    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= total_vec) return;
     int per_row = inter / 8;
-    size_t row = idx / per_row;
-    int i = (int)(idx - row * per_row) * 8;
-    const __nv_bfloat16* g = gate_up + row * 2 * inter + i;
-    uint4 graw = *reinterpret_cast<const uint4*>(g);
-    uint4 uraw = *reinterpret_cast<const uint4*>(g + inter);
-    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&graw);
-    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uraw);
-    uint4 oraw;
-    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&oraw);
+    size_t row = blockIdx.y;
+    const __nv_bfloat16* g_row = gate_up + row * 2 * inter;
+    int v0 = blockIdx.x * (256 * SILU_VECS) + threadIdx.x;
+    uint4 graw[SILU_VECS], uraw[SILU_VECS];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        float2 gf = __bfloat1622float2(g2[k]), uf = __bfloat1622float2(u2[k]);
-        o2[k] = __floats2bfloat162_rn(gf.x / (1.0f + expf(-gf.x)) * uf.x, gf.y / (1.0f + expf(-gf.y)) * uf.y);
+    for (int k = 0; k < SILU_VECS; ++k) {
+        int v = v0 + k * 256;
+        if (v < per_row) {
+            graw[k] = *reinterpret_cast<const uint4*>(g_row + (size_t)v * 8);
+            uraw[k] = *reinterpret_cast<const uint4*>(g_row + inter + (size_t)v * 8);
+        }
     }
-    *reinterpret_cast<uint4*>(out + row * inter + i) = oraw;
+#pragma unroll
+    for (int k = 0; k < SILU_VECS; ++k) {
+        int v = v0 + k * 256;
+        if (v >= per_row) continue;
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&graw[k]);
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uraw[k]);
+        uint4 oraw;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&oraw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float2 gf = __bfloat1622float2(g2[j]), uf = __bfloat1622float2(u2[j]);
+            o2[j] = __floats2bfloat162_rn(__fdividef(gf.x, 1.0f + __expf(-gf.x)) * uf.x,
+                                          __fdividef(gf.y, 1.0f + __expf(-gf.y)) * uf.y);
+        }
+        *reinterpret_cast<uint4*>(out + row * inter + (size_t)v * 8) = oraw;
+    }
 }
 
 // `gate_up` has the output's dtype, or is 32-bit (in_dtype), possibly the sum of `num_partials`
@@ -437,10 +450,10 @@ IE_API int ie_silu_mul(const void* gate_up, int in_dtype, int num_partials, long
     size_t want = (total + threads - 1) / threads;
     int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
     size_t ps = (size_t)partial_stride;
-    if (dtype == IE_BF16 && in_dtype == IE_BF16 && num_partials == 1 && inter % 8 == 0) {
-        size_t total_vec = total / 8;
-        return ie_launch(silu_mul_bf16x8_kernel, dim3((unsigned)((total_vec + 255) / 256)), dim3(256), 0, s,
-                         (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total_vec);
+    if (dtype == IE_BF16 && in_dtype == IE_BF16 && num_partials == 1 && inter % 8 == 0 && num_rows <= 65535) {
+        int per_block = 256 * SILU_VECS;
+        return ie_launch(silu_mul_bf16x8_kernel, dim3((unsigned)((inter / 8 + per_block - 1) / per_block), (unsigned)num_rows),
+                         dim3(256), 0, s, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter);
     }
     if (dtype == IE_BF16 && in_dtype == IE_BF16)
         return ie_launch(silu_mul_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(blocks), dim3(threads), 0, s,

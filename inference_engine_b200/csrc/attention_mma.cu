@@ -103,15 +103,15 @@ __device__ __forceinline__ void fetch_pages(TilePages<KT, NTHREADS>& pg, const i
         int first = entry << page_shift, last = first + (1 << page_shift) - 1;
         bool wanted = last >= max(key0, lo) && first <= min(key0 + KT - 1, hi) && entry < table_width;
         pg.page[0] = wanted ? table[entry] : -1;
-        return;
-    }
+    } else {
 #pragma unroll
-    for (int i = 0; i < TilePages<KT, NTHREADS>::ITERS; ++i) {
-        int idx = i * NTHREADS + tid;
-        int kpos = key0 + idx / C;
-        int entry = kpos >> page_shift;
-        bool wanted = idx < KT * C && kpos >= lo && kpos <= hi && entry < table_width;
-        pg.page[i] = wanted ? table[entry] : -1;
+        for (int i = 0; i < TilePages<KT, NTHREADS>::ITERS; ++i) {
+            int idx = i * NTHREADS + tid;
+            int kpos = key0 + idx / C;
+            int entry = kpos >> page_shift;
+            bool wanted = idx < KT * C && kpos >= lo && kpos <= hi && entry < table_width;
+            pg.page[i] = wanted ? table[entry] : -1;
+        }
     }
 }
 
@@ -585,6 +585,446 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
 }
 
 // -------------------------------------------------------------------------------------------------
+// Decode for batches whose contexts differ: the same tile code, the work dealt by length.
+//
+// The kernel above gives every (request, head) pair the same number of blocks, whatever the
+// request's length: right when the contexts are alike, and it knows its tiles from its block
+// number alone.  With one long context among short ones the long one's blocks hold the step up.
+// Here a fixed one-dimensional grid (as many blocks as the device runs at once) deals the key
+// tiles of all requests by their number; every block works the assignment out from the lengths
+// (the step's inputs, there before the previous kernel ends), which costs one trip to memory
+// more than the kernel above.  A pair that lies in several blocks is merged by the block that
+// finishes last (ticket counter), in the order of the blocks.
+// Partials: part_o[slot * 16 + row][HD], part_ml[slot * 16 + row][2] = (maximum in log2 units,
+// sum); at most pairs + gridDim.x slots are used.
+// -------------------------------------------------------------------------------------------------
+constexpr int MAX_BALANCED_SEQS = 512;  // requests a balanced launch takes (their running sums sit in shared memory)
+
+// The end of a pair's tiles in a decode block (all its threads call this together): the warps'
+// partial results are merged through shared memory.  `whole`: the block held all tiles of the
+// pair and writes the output.  Otherwise it writes its partial result to `slot`, and the block
+// that finishes last of the pair's `parts` blocks merges their slots first_slot, first_slot + 1,
+// ... in that order.  The ticket counter goes back to zero for the next launch.
+template <int NWARPS>
+__device__ __forceinline__ void decode_merge_slots(RowState& st, unsigned char* smem_raw, int* is_last, int warp,
+                                                   int lane, int rows, int G, int q0, int kvh, int nh, bool whole,
+                                                   int slot, int first_slot, int parts, int* ticket,
+                                                   bf16* __restrict__ out, float* __restrict__ part_o,
+                                                   float* __restrict__ part_ml) {
+    constexpr int WARPS = NWARPS;
+    int tid = warp * 32 + lane;
+    finish_rows(st);
+    decode_barrier<NWARPS>();  // every warp is done with its tiles: the shared memory is reused below
+    // [warp][row] m, l and [warp][row][HD] o in shared memory
+    float* sm_ml = reinterpret_cast<float*>(smem_raw);            // [WARPS][16][2]
+    float* sm_o = sm_ml + WARPS * MAX_ROWS * 2;                   // [WARPS][16][HD]
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        int row = (lane >> 2) + r * 8;
+        if ((lane & 3) == 0) {
+            sm_ml[(warp * MAX_ROWS + row) * 2] = st.m[r];
+            sm_ml[(warp * MAX_ROWS + row) * 2 + 1] = st.l[r];
+        }
+#pragma unroll
+        for (int d = 0; d < DT; ++d) {
+            float* dst = sm_o + ((size_t)(warp * MAX_ROWS + row)) * HD + d * 8 + (lane & 3) * 2;
+            dst[0] = st.o[d][r * 2];
+            dst[1] = st.o[d][r * 2 + 1];
+        }
+    }
+    decode_barrier<NWARPS>();
+    for (int idx = tid; idx < rows * HD; idx += WARPS * 32) {
+        int row = idx / HD, d = idx - row * HD;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) m = fmaxf(m, sm_ml[(w * MAX_ROWS + row) * 2]);
+        float m_safe = (m == -INFINITY) ? 0.f : m;
+        float l = 0.f, o = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+            float f = exp2f(sm_ml[(w * MAX_ROWS + row) * 2] - m_safe);
+            l += sm_ml[(w * MAX_ROWS + row) * 2 + 1] * f;
+            o += sm_o[((size_t)(w * MAX_ROWS + row)) * HD + d] * f;
+        }
+        if (whole) {
+            int tok = row / G, g = row - tok * G;
+            out[((size_t)(q0 + tok) * nh + kvh * G + g) * HD + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+        } else {
+            size_t p = (size_t)slot * MAX_ROWS + row;
+            part_o[p * HD + d] = o;
+            if (d == 0) { part_ml[p * 2] = m; part_ml[p * 2 + 1] = l; }
+        }
+    }
+    if (whole) return;
+    __threadfence();
+    decode_barrier<NWARPS>();
+    if (tid == 0) {
+        int t = atomicAdd(ticket, 1);
+        *is_last = (t == parts - 1);
+        if (*is_last) *ticket = 0;
+    }
+    decode_barrier<NWARPS>();
+    if (!*is_last) return;
+    __threadfence();
+    size_t base = (size_t)first_slot * MAX_ROWS;
+    for (int idx = tid; idx < rows * HD; idx += WARPS * 32) {
+        int row = idx / HD, d = idx - row * HD;
+        // the blocks' partial results: loaded eight at a time, merged in the order of the blocks
+        float m = -INFINITY;
+        for (int s0 = 0; s0 < parts; s0 += 8) {
+            float t[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                t[j] = s0 + j < parts ? __ldcg(part_ml + (base + (size_t)(s0 + j) * MAX_ROWS + row) * 2) : -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) m = fmaxf(m, t[j]);
+        }
+        float m_safe = (m == -INFINITY) ? 0.f : m;
+        float l = 0.f, o = 0.f;
+        for (int s0 = 0; s0 < parts; s0 += 8) {
+            float tm[8], tl[8], to[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                bool in = s0 + j < parts;
+                size_t p = base + (size_t)(in ? s0 + j : 0) * MAX_ROWS + row;
+                tm[j] = in ? __ldcg(part_ml + p * 2) : -INFINITY;
+                tl[j] = in ? __ldcg(part_ml + p * 2 + 1) : 0.f;
+                to[j] = in ? __ldcg(part_o + p * HD + d) : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (s0 + j < parts) {
+                    float f = exp2f(tm[j] - m_safe);
+                    l += tl[j] * f;
+                    o += to[j] * f;
+                }
+            }
+        }
+        int tok = row / G, g = row - tok * G;
+        out[((size_t)(q0 + tok) * nh + kvh * G + g) * HD + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+    }
+}
+
+// Key tiles of a request for the decode kernel (0: the prefill kernel takes it) and its key range.
+struct DecodeSeq {
+    int q0, qlen, ctx, lo, hi, n_tiles;
+};
+__device__ __forceinline__ DecodeSeq decode_seq(const int* __restrict__ cu_q, const int* __restrict__ ctx_lens,
+                                                int seq, int G, int window) {
+    DecodeSeq d;
+    d.q0 = cu_q[seq];
+    d.qlen = cu_q[seq + 1] - d.q0;
+    d.ctx = ctx_lens[seq];
+    int first_qpos = d.ctx - d.qlen;
+    d.hi = d.ctx - 1;
+    d.lo = (window > 0 && first_qpos - window + 1 > 0) ? first_qpos - window + 1 : 0;
+    bool mine = d.qlen > 0 && d.qlen * G <= MAX_ROWS && d.hi >= d.lo;
+    d.n_tiles = mine ? (d.hi - d.lo) / KT_DECODE + 1 : 0;
+    return d;
+}
+
+// Pieces a pair of n tiles is cut into when an even share of all tiles is `share`: the nearest
+// whole number of shares, leaving every piece at least a tile per warp.
+__device__ __forceinline__ int decode_pieces(int n, int share, int warps) {
+    if (n <= 0) return 0;
+    int k = (n + share / 2) / share;
+    int most = n / warps;
+    if (k > most) k = most;
+    return k < 1 ? 1 : k;
+}
+
+template <int NWARPS>
+__global__ void __launch_bounds__(NWARPS * 32)
+attention_decode_balanced_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache,
+                        const bf16* __restrict__ v_cache, const int* __restrict__ tables,
+                        int table_width, const int* __restrict__ cu_q, const int* __restrict__ ctx_lens,
+                        bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+                        int* __restrict__ tickets, int num_seqs, int nh, int nkv, int page_shift,
+                        int total_pages, float scale_log2, int window, int* err) {
+    constexpr int KT = KT_DECODE, TILE_ELEMS = KT * HD, WARPS = NWARPS;
+    __shared__ int is_last;
+    // balanced launches: tiles (of one head) and pieces (of all heads) of the requests before each request
+    __shared__ int tiles_before[MAX_BALANCED_SEQS + 1];
+    __shared__ int pieces_before[MAX_BALANCED_SEQS + 1];
+    __shared__ int warp_sums[NWARPS];
+    __shared__ int largest_piece_s;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    bf16* smem = reinterpret_cast<bf16*>(smem_raw);
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int G = nh / nkv;
+    bf16* ring = smem + (size_t)warp * DSTAGES * 2 * TILE_ELEMS;
+    typedef TilePages<KT, 32> Pages;
+    ie_pdl_trigger();
+
+    // ---- how the tiles are dealt (lengths and tables were copied in before the step's first
+    // kernel: nothing here waits for the kernel before this one).  The tile list: all tiles of
+    // request 0's head 0, then its head 1, ..., then request 1's.  Two ways to deal it:
+    //   pieces: every (request, head) pair's tiles are cut into k equal pieces, k so that a piece
+    //     is about an even share of the list (never less than a tile per warp); pieces are
+    //     numbered in list order and block b takes pieces b, b + gridDim.x, ...  A block has one
+    //     pair to set up; the blocks' loads differ by as much as the pieces do;
+    //   ranges: the list is cut into gridDim.x equal ranges, one per block; a range may end one
+    //     pair and begin the next (two set-ups), the loads are equal.
+    // Every block takes the same decision from the same lengths: ranges when the pieces would
+    // leave the slowest block well behind an even share (ragged batches).
+    int num_items, share = 0;
+    bool by_range = false;
+    {
+        long long all_tiles;
+        int num_pieces, largest_piece;
+        if (num_seqs <= 32) {
+            // a small batch: every warp works the sums out by itself, a request to a lane, and
+            // no warp waits for another (the warps store the same values)
+            int n = lane < num_seqs ? decode_seq(cu_q, ctx_lens, lane, G, window).n_tiles : 0;
+            int total = n;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) total += __shfl_xor_sync(0xffffffffu, total, off);
+            all_tiles = (long long)total * nkv;
+            share = (int)((all_tiles + gridDim.x - 1) / gridDim.x);
+            if (share < WARPS) share = WARPS;
+            int k = decode_pieces(n, share, WARPS);
+            int incl_t = n, incl_p = k * nkv;
+            largest_piece = k > 0 ? (n + k - 1) / k : 0;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                int vt = __shfl_up_sync(0xffffffffu, incl_t, off), vp = __shfl_up_sync(0xffffffffu, incl_p, off);
+                if (lane >= off) { incl_t += vt; incl_p += vp; }
+                largest_piece = max(largest_piece, __shfl_xor_sync(0xffffffffu, largest_piece, off));
+            }
+            num_pieces = __shfl_sync(0xffffffffu, incl_p, 31);
+            if (lane < num_seqs) {
+                tiles_before[lane + 1] = incl_t;
+                pieces_before[lane + 1] = incl_p;
+            }
+            if (lane == 0) tiles_before[0] = pieces_before[0] = 0;
+            __syncwarp();
+        } else {
+            int mine = 0;
+            for (int s = threadIdx.x; s < num_seqs; s += WARPS * 32) {
+                int n = decode_seq(cu_q, ctx_lens, s, G, window).n_tiles;
+                tiles_before[s + 1] = n;
+                mine += n;
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, off);
+            if (lane == 0) warp_sums[warp] = mine;
+            __syncthreads();
+            int total = 0;  // tiles of one head over all requests
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) total += warp_sums[w];
+            all_tiles = (long long)total * nkv;
+            share = (int)((all_tiles + gridDim.x - 1) / gridDim.x);
+            if (share < WARPS) share = WARPS;
+            if (warp == 0) {  // running sums of tiles and of pieces: a lane sums its stretch, the warp scans the lanes' sums
+                int per = (num_seqs + 31) / 32, first = lane * per, sum_t = 0, sum_p = 0, largest = 0;
+                for (int i = 0; i < per; ++i)
+                    if (first + i < num_seqs) {
+                        int n = tiles_before[first + i + 1], k = decode_pieces(n, share, WARPS);
+                        sum_t += n;
+                        sum_p += k * nkv;
+                        if (k > 0) largest = max(largest, (n + k - 1) / k);
+                    }
+                int incl_t = sum_t, incl_p = sum_p;
+#pragma unroll
+                for (int off = 1; off < 32; off <<= 1) {
+                    int vt = __shfl_up_sync(0xffffffffu, incl_t, off), vp = __shfl_up_sync(0xffffffffu, incl_p, off);
+                    if (lane >= off) { incl_t += vt; incl_p += vp; }
+                    largest = max(largest, __shfl_xor_sync(0xffffffffu, largest, off));
+                }
+                int run_t = incl_t - sum_t, run_p = incl_p - sum_p;
+                for (int i = 0; i < per; ++i)
+                    if (first + i < num_seqs) {
+                        int n = tiles_before[first + i + 1];
+                        run_t += n;
+                        run_p += decode_pieces(n, share, WARPS) * nkv;
+                        tiles_before[first + i + 1] = run_t;
+                        pieces_before[first + i + 1] = run_p;
+                    }
+                if (lane == 0) {
+                    tiles_before[0] = 0;
+                    pieces_before[0] = 0;
+                    largest_piece_s = largest;
+                }
+            }
+            __syncthreads();
+            num_pieces = pieces_before[num_seqs];
+            largest_piece = largest_piece_s;
+        }
+        long long rounds = (num_pieces + (int)gridDim.x - 1) / (int)gridDim.x;
+        // a pair's set-up costs a block about as much as six tiles per warp
+        by_range = rounds * largest_piece > (long long)share + 6 * WARPS;
+        num_items = by_range ? (int)min(all_tiles, (long long)0x7fffffff) : num_pieces;
+    }
+
+    bool waited = false;
+    // items: tiles (ranges) or pieces; a block's first item, and how many it takes at a time
+    long long item = by_range ? (long long)blockIdx.x * share : blockIdx.x;
+    int left = by_range ? share : 1;   // ranges: tiles still to take from this block's range
+    int seq = -1, kvh = 0, tile0 = 0;  // ranges: where the next tile of the range lies
+    while (item < num_items && left > 0) {
+        int part = 0, parts = 1, tile_end, first_slot = 0, slot = 0;
+        DecodeSeq ds;
+        if (by_range) {
+            if (seq < 0) {
+                // the request that holds tile `item`: the last one whose first tile is at or before it
+                int lo_s = 0, hi_s = num_seqs - 1;
+                while (lo_s < hi_s) {
+                    int mid = (lo_s + hi_s + 1) >> 1;
+                    if ((long long)tiles_before[mid] * nkv <= item) lo_s = mid; else hi_s = mid - 1;
+                }
+                seq = lo_s;
+                int n = tiles_before[seq + 1] - tiles_before[seq];  // > 0: the tile lies inside it
+                int r = (int)(item - (long long)tiles_before[seq] * nkv);
+                kvh = r / n;
+                tile0 = r - kvh * n;
+            }
+            ds = decode_seq(cu_q, ctx_lens, seq, G, window);
+            if (ds.n_tiles == 0) {  // the prefill kernel's request: no tiles in the list
+                ++seq; kvh = 0; tile0 = 0;
+                if (seq >= num_seqs) break;
+                continue;
+            }
+            tile_end = min(ds.n_tiles, tile0 + left);
+            if (tile0 > 0 || tile_end < ds.n_tiles) {
+                // the pair lies in several blocks: one slot each, numbered pair + block (unique:
+                // later pairs lie in later blocks)
+                long long pair_begin = (long long)tiles_before[seq] * nkv + (long long)kvh * ds.n_tiles;
+                int first_block = (int)(pair_begin / share);
+                parts = (int)((pair_begin + ds.n_tiles - 1) / share) - first_block + 1;
+                first_slot = seq * nkv + kvh + first_block;
+                slot = seq * nkv + kvh + (int)blockIdx.x;
+            }
+        } else {
+            int piece = (int)item;
+            int lo_s = 0, hi_s = num_seqs - 1;
+            while (lo_s < hi_s) {
+                int mid = (lo_s + hi_s + 1) >> 1;
+                if (pieces_before[mid] <= piece) lo_s = mid; else hi_s = mid - 1;
+            }
+            seq = lo_s;
+            parts = (pieces_before[seq + 1] - pieces_before[seq]) / nkv;  // > 0: the piece lies inside it
+            int r = piece - pieces_before[seq];
+            kvh = r / parts;
+            part = r - kvh * parts;
+            ds = decode_seq(cu_q, ctx_lens, seq, G, window);
+            tile0 = (int)((long long)part * ds.n_tiles / parts);
+            tile_end = (int)((long long)(part + 1) * ds.n_tiles / parts);
+            first_slot = pieces_before[seq] + kvh * parts;  // the pair's pieces have consecutive numbers
+            slot = first_slot + part;
+        }
+        bool whole = parts == 1;
+        const int* table = tables + (size_t)seq * table_width;
+        int q0 = ds.q0, qlen = ds.qlen, lo = ds.lo, hi = ds.hi;
+        int rows = qlen * G, first_qpos = ds.ctx - qlen;
+        int n_tiles = tile_end;                   // tiles of this pair the block works on end here
+        int j0 = tile0 + warp, stride = WARPS;    // this warp's first tile, tiles between two of its tiles
+
+        // 1. block-table entries of the first tiles
+        Pages pg[DSTAGES];
+#pragma unroll
+        for (int s = 0; s < DSTAGES; ++s)
+            fetch_pages<KT, 32>(pg[s], table, table_width, lo + (j0 + s * stride) * KT, lo, hi, page_shift, lane);
+        // 2. the first tiles' keys and values.  Tiles that lie wholly before this step's tokens
+        //    were written by earlier steps: their copies start before the wait for the previous
+        //    kernel and overlap it.  A warp whose first tiles reach this step's tokens (short
+        //    contexts) starts its copies after the wait.
+        bool ahead = !waited;
+#pragma unroll
+        for (int s = 0; s < DSTAGES - 1; ++s) {
+            int j = j0 + s * stride;
+            ahead = ahead && (j >= n_tiles || lo + (j + 1) * KT <= first_qpos);
+        }
+        if (ahead) {
+#pragma unroll
+            for (int s = 0; s < DSTAGES - 1; ++s) {
+                int j = j0 + s * stride;
+                if (j < n_tiles) {
+                    bf16* st_k = ring + (size_t)s * 2 * TILE_ELEMS;
+                    issue_kv<KT, 32, true>(st_k, st_k + TILE_ELEMS, pg[s], k_cache, v_cache, lo + j * KT, lo, hi,
+                                           kvh, nkv, page_shift, total_pages, lane, err);
+                }
+                cp_async_commit();
+            }
+        }
+        if (!waited) {
+            ie_pdl_wait();
+            waited = true;
+        } else {
+            ahead = false;
+        }
+        if (!ahead) {
+#pragma unroll
+            for (int s = 0; s < DSTAGES - 1; ++s) {
+                int j = j0 + s * stride;
+                if (j < n_tiles) {
+                    bf16* st_k = ring + (size_t)s * 2 * TILE_ELEMS;
+                    issue_kv<KT, 32, true>(st_k, st_k + TILE_ELEMS, pg[s], k_cache, v_cache, lo + j * KT, lo, hi,
+                                           kvh, nkv, page_shift, total_pages, lane, err);
+                }
+                cp_async_commit();
+            }
+        }
+        // 3. the queries while those are in flight
+        int qpos[1][2], qlo[1][2];
+        unsigned qf[1][KS][4];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            int row = (lane >> 2) + r * 8;
+            bool exists = row < rows;
+            int tok = exists ? row / G : 0, g = exists ? row - tok * G : 0;
+            qpos[0][r] = exists ? first_qpos + tok : -1;
+            qlo[0][r] = (window > 0 && qpos[0][r] - window + 1 > 0) ? qpos[0][r] - window + 1 : 0;
+            const bf16* qrow = q + ((size_t)(q0 + tok) * nh + kvh * G + g) * HD;
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+                int d = ks * 16 + (lane & 3) * 2;
+                qf[0][ks][r] = exists ? *reinterpret_cast<const unsigned*>(qrow + d) : 0u;
+                qf[0][ks][r + 2] = exists ? *reinterpret_cast<const unsigned*>(qrow + d + 8) : 0u;
+            }
+        }
+        RowState sts[1];
+        sts[0].init();
+        RowState& st = sts[0];
+        // 4. the ring: the copies of tile i+2 use block-table entries fetched one tile earlier, and
+        //    the entries of tile i+3 are fetched now, so no lookup is waited for
+        Pages next = pg[DSTAGES - 1];
+        int i = 0;
+        for (int j = j0; j < n_tiles; j += stride, ++i) {
+            int pre = j + (DSTAGES - 1) * stride;
+            if (pre < n_tiles) {
+                bf16* st_k = ring + (size_t)((i + DSTAGES - 1) % DSTAGES) * 2 * TILE_ELEMS;
+                issue_kv<KT, 32, true>(st_k, st_k + TILE_ELEMS, next, k_cache, v_cache, lo + pre * KT, lo, hi,
+                                       kvh, nkv, page_shift, total_pages, lane, err);
+            }
+            cp_async_commit();
+            if (pre + stride < n_tiles)
+                fetch_pages<KT, 32>(next, table, table_width, lo + (pre + stride) * KT, lo, hi, page_shift, lane);
+            cp_async_wait<DSTAGES - 1>();
+            __syncwarp();
+            const bf16* cur = ring + (size_t)(i % DSTAGES) * 2 * TILE_ELEMS;
+            process_tile<KT, 1>(sts, qf, cur, cur + TILE_ELEMS, lo + j * KT, qpos, qlo, hi, scale_log2, lane);
+            __syncwarp();
+        }
+        cp_async_wait<0>();
+        // 5. merge the warps; write the output or this block's partial result
+        decode_merge_slots<NWARPS>(st, smem_raw, &is_last, warp, lane, rows, G, q0, kvh, nh, whole, slot,
+                                   first_slot, parts, tickets + seq * nkv + kvh, out, part_o, part_ml);
+        decode_barrier<NWARPS>();  // the merge read shared memory that the next pair's copies overwrite
+        if (by_range) {
+            int took = tile_end - tile0;
+            left -= took;
+            item += took;
+            tile0 = 0;
+            if (++kvh == nkv) { kvh = 0; ++seq; }
+            if (seq >= num_seqs) break;
+        } else {
+            item += gridDim.x;
+        }
+    }
+    if (!waited) ie_pdl_wait();
+}
+
+// -------------------------------------------------------------------------------------------------
 // Prefill: portions with more than 16 rows.  grid = (128-token tiles over all requests, heads);
 // four warps of 32 rows (two 16-row tiles that share every K and V fragment).
 // -------------------------------------------------------------------------------------------------
@@ -791,6 +1231,83 @@ IE_API int ie_attention_decode(const void* q, const void* k_cache, const void* v
     return launch_decode(q, k_cache, v_cache, tables, table_width, cu_q, ctx_lens, out, part_o, part_ml, tickets,
                          num_seqs, nh, nkv, page_shift, total_pages, scale, window, num_splits, err,
                          (cudaStream_t)stream);
+}
+
+namespace {
+// Blocks of a balanced launch: what the device runs at once (blocks of four warps, two to an SM,
+// when there are more pairs than SMs), no more than `max_blocks_per_pair` times the pairs.
+int balanced_sms() {
+    int sms = 148, dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+        sms = 148;
+    return sms;
+}
+long long balanced_blocks(long long pairs, int max_blocks_per_pair) {
+    int sms = balanced_sms();
+    long long slots = pairs > sms ? 2LL * sms : sms;
+    long long want = pairs * (max_blocks_per_pair < 1 ? 1 : max_blocks_per_pair);
+    return want < slots ? want : slots;
+}
+
+template <int NWARPS>
+int launch_balanced_as(const void* q, const void* k_cache, const void* v_cache, const int* tables, int table_width,
+                       const int* cu_q, const int* ctx_lens, void* out, float* part_o, float* part_ml, int* tickets,
+                       int num_seqs, int nh, int nkv, int page_shift, int total_pages, float scale, int window,
+                       int blocks, int* err, cudaStream_t s) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_balanced_kernel<NWARPS>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(NWARPS));
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    return ie_launch(attention_decode_balanced_kernel<NWARPS>, dim3(blocks), dim3(NWARPS * 32), decode_smem(NWARPS), s,
+                     (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, tables, table_width, cu_q, ctx_lens,
+                     (bf16*)out, part_o, part_ml, tickets, num_seqs, nh, nkv, page_shift, total_pages,
+                     scale * 1.4426950408889634f, window, err);
+}
+}  // namespace
+
+// Requests a balanced launch takes at most.
+IE_API int ie_attention_decode_balanced_max_seqs() { return MAX_BALANCED_SEQS; }
+
+// Floats of scratch `ie_attention_decode_balanced` needs: a partial result for every (pair, block)
+// that can occur.
+IE_API long long ie_attention_decode_balanced_scratch_floats(int num_seqs, int nkv, int max_blocks_per_pair) {
+    if (num_seqs <= 0 || nkv <= 0) return 0;
+    long long pairs = (long long)num_seqs * nkv;
+    return (pairs + balanced_blocks(pairs, max_blocks_per_pair)) * MAX_ROWS * (HD + 2);
+}
+
+// The decode attention of `ie_attention_decode` with the key tiles of all requests dealt evenly
+// over the blocks: for batches whose contexts differ in length (at most
+// ie_attention_decode_balanced_max_seqs requests).  `scratch`:
+// ie_attention_decode_balanced_scratch_floats floats (contents do not matter); `tickets`:
+// num_seqs * nkv ints that are zero before the first launch (every launch leaves them zero).
+IE_API int ie_attention_decode_balanced(const void* q, const void* k_cache, const void* v_cache,
+                                        const int* tables, int table_width, const int* cu_q,
+                                        const int* ctx_lens, void* out, float* scratch, int* tickets,
+                                        int num_seqs, int nh, int nkv, int page_size, int total_pages,
+                                        float scale, int window, int max_blocks_per_pair, int* err, void* stream) {
+    if (num_seqs <= 0) return 0;
+    if (nkv <= 0 || nh % nkv != 0 || (page_size & (page_size - 1)) != 0 || num_seqs > MAX_BALANCED_SEQS ||
+        scratch == nullptr || tickets == nullptr)
+        return (int)cudaErrorInvalidValue;
+    int page_shift = 0;
+    while ((1 << page_shift) < page_size) ++page_shift;
+    long long pairs = (long long)num_seqs * nkv;
+    long long blocks = balanced_blocks(pairs, max_blocks_per_pair);
+    float* part_o = scratch;
+    float* part_ml = scratch + (size_t)(pairs + blocks) * MAX_ROWS * HD;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (pairs > balanced_sms())
+        return launch_balanced_as<DWARPS_SHARED>(q, k_cache, v_cache, tables, table_width, cu_q, ctx_lens, out, part_o,
+                                                 part_ml, tickets, num_seqs, nh, nkv, page_shift, total_pages, scale,
+                                                 window, (int)blocks, err, s);
+    return launch_balanced_as<DWARPS>(q, k_cache, v_cache, tables, table_width, cu_q, ctx_lens, out, part_o, part_ml,
+                                      tickets, num_seqs, nh, nkv, page_shift, total_pages, scale, window, (int)blocks,
+                                      err, s);
 }
 
 // Requests with more than 16 rows.  `max_tiles` bounds the number of query tiles over all

@@ -62,3 +62,4 @@ class StepContext:
     max_q_len: int
     max_ctx_len: int
     padded: bool = False  # a fixed-size launch: sizes above are upper bounds
+    ragged: bool = False  # the requests' contexts differ much in length (a hint for the attention's launch)

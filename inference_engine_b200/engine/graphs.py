@@ -10,6 +10,8 @@ length.  Bucket sizes are the reference's (engine/runtime/cuda_graphs.py:20-108)
 
 from __future__ import annotations
 
+from .runner import contexts_are_ragged
+
 BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 
 
@@ -22,7 +24,9 @@ class DecodeGraphs:
         self.buckets = [b for b in BUCKETS if b <= max_num_seqs]
         if not self.buckets or self.buckets[-1] < max_num_seqs:
             self.buckets.append(max_num_seqs)
-        self._graphs: dict[int, tuple] = {}
+        # one capture per (bucket, whether the contexts' lengths differ much): the attention is
+        # launched differently for the two
+        self._graphs: dict[tuple, tuple] = {}
         self._version = None
         self.replays = 0
 
@@ -34,14 +38,16 @@ class DecodeGraphs:
 
     def kernels_per_replay(self, num_seqs: int) -> int:
         """How many of the engine's own kernels one replay for ``num_seqs`` sequences launches."""
-        entry = self._graphs.get(self.bucket_for(num_seqs))
+        bucket = self.bucket_for(num_seqs)
+        entry = self._graphs.get((bucket, False)) or self._graphs.get((bucket, True))
         return entry[2] if entry else 0
 
     def prepare(self, req_ids: list, positions: list[int]):
         """Pack the next decode step ahead of time (while the device still works on this one)
         if a captured launch sequence for its batch size exists; None otherwise."""
         bucket = self.bucket_for(len(req_ids))
-        if bucket is None or bucket not in self._graphs or self._version != self.runner.ws.version:
+        key = (bucket, contexts_are_ragged([p + 1 for p in positions]))
+        if bucket is None or key not in self._graphs or self._version != self.runner.ws.version:
             return None
         cache = self.runner.cache
         if any(len(cache.table(g, r)) > self.table_width for r in req_ids
@@ -50,16 +56,16 @@ class DecodeGraphs:
         handle = self.runner.prepare_decode(req_ids, positions, bucket, self.table_width)
         if self._version != self.runner.ws.version:
             return None
-        return (bucket, handle)
+        return (key, handle)
 
     def run_prepared(self, prepared, tokens, count: int | None = None):
         """Fill the sampled tokens (a list, or a device tensor of which the first ``count`` are
         taken) into a step packed by :meth:`prepare` and replay it."""
-        bucket, handle = prepared
-        if bucket not in self._graphs or self._version != self.runner.ws.version:
+        key, handle = prepared
+        if key not in self._graphs or self._version != self.runner.ws.version:
             return None
         self.runner.commit_prepared(handle, tokens)
-        graph, logits, _ = self._graphs[bucket]
+        graph, logits, _ = self._graphs[key]
         graph.replay()
         self.replays += 1
         return logits[: len(tokens) if count is None else count]
@@ -81,7 +87,8 @@ class DecodeGraphs:
         if self._version != runner.ws.version:  # a buffer moved: captured addresses are stale
             self._graphs.clear()
             self._version = runner.ws.version
-        captured = bucket in self._graphs
+        key = (bucket, contexts_are_ragged([e.start + 1 for e in entries]))
+        captured = key in self._graphs
         ctx, rows = runner.build_context(entries, pad_to_seqs=bucket, table_width=self.table_width,
                                          views=not captured)
         if self._version != runner.ws.version:  # the staging buffer itself had to grow
@@ -107,8 +114,8 @@ class DecodeGraphs:
             before = getattr(runner.ops, "launches", 0)
             with torch.cuda.graph(graph):
                 logits = runner.model.forward(ctx, rows)
-            self._graphs[bucket] = (graph, logits, getattr(runner.ops, "launches", 0) - before)
-        graph, logits, _ = self._graphs[bucket]
+            self._graphs[key] = (graph, logits, getattr(runner.ops, "launches", 0) - before)
+        graph, logits, _ = self._graphs[key]
         graph.replay()
         self.replays += 1
         return logits[: len(entries)]

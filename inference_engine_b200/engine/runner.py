@@ -26,6 +26,17 @@ def _align4(n: int) -> int:
     return (n + 3) & ~3
 
 
+def contexts_are_ragged(ctx_lens) -> bool:
+    """Whether a step's contexts differ so much in length that dealing attention work by request
+    would leave most of the GPU waiting for the longest one: the longest is well above the mean
+    and long enough to matter."""
+    n = len(ctx_lens)
+    if n < 2:
+        return False
+    longest = max(ctx_lens)
+    return longest >= 512 and longest * n > 1.5 * sum(ctx_lens)
+
+
 class ModelRunner:
     def __init__(self, model: Model, cache: CacheManager, storage: CacheStorage, ops,
                  device, max_tokens_per_step: int, max_seqs_per_step: int) -> None:
@@ -187,6 +198,7 @@ class ModelRunner:
             cu_q=dview(v_cu), ctx_lens=dview(v_ctx), groups=groups,
             q_starts=q_starts, q_lens=q_lens, start_positions=start_positions,
             max_q_len=max(q_lens), max_ctx_len=max(ctx_lens), padded=pad_to_seqs is not None,
+            ragged=contexts_are_ragged(ctx_lens[:real_b]),
         )
         return ctx, dview(v_rows)
 
@@ -308,6 +320,7 @@ class ModelRunner:
             cu_q=dview(v_cu), ctx_lens=dview(v_ctx), groups=groups,
             q_starts=list(range(b)), q_lens=[1] * b, start_positions=start_positions,
             max_q_len=1, max_ctx_len=int(positions.max()) + 1, padded=pad_to_seqs is not None,
+            ragged=contexts_are_ragged((positions + 1).tolist()),
         )
         return ctx, dview(v_rows)
 

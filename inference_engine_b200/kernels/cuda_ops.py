@@ -72,6 +72,11 @@ class CudaOps:
         self.attn_tc5 = os.environ.get("IE_B200_ATTN_TC5", "1") != "0"  # tcgen05 prefill attention
         # the decode kernel cuts contexts until about this many blocks run (one block per SM)
         self.decode_split_target = int(os.environ.get("IE_B200_DECODE_SPLIT_TARGET", 128))
+        # batches whose contexts differ much in length go to the decode kernel that deals key tiles
+        # by length ("auto": when the step's context says so; "1": always; "0": never)
+        self.decode_balanced = os.environ.get("IE_B200_DECODE_BALANCED", "auto")
+        self.decode_balanced_blocks_per_pair = 32
+        self.balanced_launches = 0
         self.few_row_gemm = os.environ.get("IE_B200_FEW_ROW_GEMM", "tma")
         # ... up to this many 128-feature tiles (measured on the 1B shape: up to 8 rows the kernel
         # streams 67 MB in 12.0 us where the vendor library takes 12.7, and the 525 MB of the
@@ -285,6 +290,9 @@ class CudaOps:
             lib.ie_attention_prefill_tc5_ok.argtypes = [I, I]
             lib.ie_attention_decode_scratch_floats.argtypes = [I, I, I]
             lib.ie_attention_decode_scratch_floats.restype = ctypes.c_longlong
+            lib.ie_attention_decode_balanced.argtypes = [P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, F, I, I, P, P]
+            lib.ie_attention_decode_balanced_scratch_floats.argtypes = [I, I, I]
+            lib.ie_attention_decode_balanced_scratch_floats.restype = ctypes.c_longlong
             self._attn_libs[hd] = lib
         return lib
 
@@ -331,7 +339,22 @@ class CudaOps:
                 ctx._attention_plan = plan
             small, any_small, all_small = plan["small"], plan["any"], plan["all"]
             stream = self._stream()
-            if any_small:
+            balanced = (self.decode_balanced == "1" or
+                        (self.decode_balanced == "auto" and getattr(ctx, "ragged", False)))
+            if any_small and balanced and ctx.num_seqs <= lib.ie_attention_decode_balanced_max_seqs():
+                per_pair = self.decode_balanced_blocks_per_pair
+                floats = lib.ie_attention_decode_balanced_scratch_floats(ctx.num_seqs, nkv, per_pair)
+                ws = getattr(ctx, "ws", None)
+                scratch = (ws.buffer("attn.partial", 1, floats, torch.float32) if ws is not None
+                           else torch.empty(floats, dtype=torch.float32, device=q.device))
+                tickets = self._decode_tickets(ctx.num_seqs * nkv)
+                self._check(lib.ie_attention_decode_balanced(
+                    q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
+                    block_tables.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_lens.data_ptr(), out.data_ptr(),
+                    scratch.data_ptr(), tickets.data_ptr(), ctx.num_seqs, nh, nkv, page_size,
+                    total_pages, scale, window, per_pair, self._err_ptr, stream), "attention_decode_balanced")
+                self.balanced_launches += 1
+            elif any_small:
                 splits = self.decode_splits(ctx.num_seqs, nkv)
                 floats = lib.ie_attention_decode_scratch_floats(ctx.num_seqs, nkv, splits)
                 scratch = tickets = None

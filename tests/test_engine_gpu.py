@@ -194,3 +194,31 @@ def test_smoke_entry():
     import __graft_entry__
 
     __graft_entry__.smoke()
+
+
+@pytest.mark.gpu
+def test_a_long_request_among_short_ones_decodes_the_same_with_either_attention_launch(monkeypatch):
+    """Contexts that differ much in length switch the decode attention to the kernel that deals
+    key tiles by length (captured separately); the tokens are those of the plain launch."""
+    from inference_engine_b200 import SamplingParams
+    from inference_engine_b200.engine.llm_engine import LLMEngine
+
+    g = torch.Generator().manual_seed(5)
+    vocab = TINY_A["vocab_size"]
+    prompts = {"long": torch.randint(0, vocab, (900,), generator=g).tolist()}
+    for i in range(5):
+        prompts[f"short{i}"] = torch.randint(0, vocab, (7 + 3 * i,), generator=g).tolist()
+    params = SamplingParams(temperature=0, max_tokens=12)
+    results = {}
+    for mode in ("auto", "0"):
+        cfg = dict(TINY_A, max_position_embeddings=2048)
+        eng = LLMEngine.from_random(cfg, seed=3, dtype="bfloat16", device="cuda", max_model_len=1024,
+                                    num_blocks=160, block_size=8, max_num_seqs=8, enable_cuda_graphs=True)
+        monkeypatch.setattr(eng.ops, "decode_balanced", mode)
+        before = eng.ops.balanced_launches
+        results[mode] = eng.generate(prompts, params)
+        assert (eng.ops.balanced_launches > before) == (mode == "auto")
+        assert any(key[1] for key in eng.graphs._graphs), "no step with ragged contexts was captured"
+        eng.ops.check_errors()
+    same = sum(results["auto"][r] == results["0"][r] for r in prompts)
+    assert same >= len(prompts) - 1, results  # (a near-tie may flip one greedy choice between summation orders)

@@ -365,7 +365,7 @@ def test_paged_attention_decode_only_and_prefill_only(ops, nh, nkv, hd, ps, wind
 
 
 def test_decode_attention_with_many_splits_is_the_same_as_one(ops):
-    """A single request fills the GPU by cutting its context into many splits; the merged
+    """A single request fills the GPU: its context is spread over many blocks; the merged
     result equals the unsplit one up to rounding."""
     nh, nkv, hd, ps = 8, 2, 64, 16
     q, k, v, tables, ctx = _attention_case(nh, nkv, hd, ps, [1], [3000], torch.bfloat16, seed=4)
@@ -375,6 +375,37 @@ def test_decode_attention_with_many_splits_is_the_same_as_one(ops):
     want = torch.empty_like(q)
     RefOps().paged_attention(q, k, v, tables, ctx, nh, nkv, hd, ps, hd ** -0.5, 0, want)
     torch.testing.assert_close(got.float(), want.float(), atol=1e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps", [(32, 8, 64, 16), (8, 2, 128, 16), (6, 3, 80, 8), (4, 4, 32, 4)])
+@pytest.mark.parametrize("window", [0, 300])
+@pytest.mark.parametrize("blocks_per_pair", [1, 2, 3, 32])
+def test_decode_attention_deals_ragged_contexts_evenly(ops, nh, nkv, hd, ps, window, blocks_per_pair, monkeypatch):
+    """The decode kernel that deals key tiles by length: contexts from one key to thousands in
+    one step, portions of one to four tokens, a request in the middle that the prefill kernel
+    takes.  However many blocks the tiles are dealt to (as many as there are requests and heads;
+    twice or three times as many; all the device runs), every request gets its own result.  One
+    far key per request stands out, so a block that took the wrong tiles, or a partial result
+    merged into the wrong request, shows."""
+    ctx_lens = [1, 5000, 31, 32, 33, 700, 64, 2, 1500, 96, 4097, 12, 257, 640, 9, 3000]
+    q_lens = [1, 1, 2, 1, 1, 1, 64, 1, 1, 3, 1, 1, 1, 1, 4, 1]
+    group = nh // nkv
+    q_lens = [ql if ql == 64 or ql * group <= 16 else 1 for ql in q_lens]
+    # a key every query of the portion sees: far back, or in the middle of the window
+    spike = [max(0, c - ql - window // 2) if window else (c - ql) // 3 for c, ql in zip(ctx_lens, q_lens)]
+    monkeypatch.setattr(ops, "decode_balanced", "1")
+    monkeypatch.setattr(ops, "decode_balanced_blocks_per_pair", blocks_per_pair)
+    q, k, v, tables, ctx = _attention_case(nh, nkv, hd, ps, q_lens, ctx_lens, torch.bfloat16, seed=11, spike=spike)
+    got = torch.empty_like(q)
+    want = torch.empty_like(q)
+    ops.paged_attention(q, k, v, tables, ctx, nh, nkv, hd, ps, hd ** -0.5, window, got)
+    RefOps().paged_attention(q, k, v, tables, ctx, nh, nkv, hd, ps, hd ** -0.5, window, want)
+    torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+    ops.check_errors()
+    # the launch left its ticket counters at zero: a second one on the same data gives the same
+    again = torch.empty_like(q)
+    ops.paged_attention(q, k, v, tables, ctx, nh, nkv, hd, ps, hd ** -0.5, window, again)
+    assert torch.equal(again, got)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -10,8 +10,6 @@ length.  Bucket sizes are the reference's (engine/runtime/cuda_graphs.py:20-108)
 
 from __future__ import annotations
 
-from .runner import contexts_are_ragged
-
 BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 
 
@@ -46,7 +44,7 @@ class DecodeGraphs:
         """Pack the next decode step ahead of time (while the device still works on this one)
         if a captured launch sequence for its batch size exists; None otherwise."""
         bucket = self.bucket_for(len(req_ids))
-        key = (bucket, contexts_are_ragged([p + 1 for p in positions]))
+        key = (bucket, self.runner.contexts_are_ragged([p + 1 for p in positions]))
         if bucket is None or key not in self._graphs or self._version != self.runner.ws.version:
             return None
         cache = self.runner.cache
@@ -87,7 +85,7 @@ class DecodeGraphs:
         if self._version != runner.ws.version:  # a buffer moved: captured addresses are stale
             self._graphs.clear()
             self._version = runner.ws.version
-        key = (bucket, contexts_are_ragged([e.start + 1 for e in entries]))
+        key = (bucket, self.runner.contexts_are_ragged([e.start + 1 for e in entries]))
         captured = key in self._graphs
         ctx, rows = runner.build_context(entries, pad_to_seqs=bucket, table_width=self.table_width,
                                          views=not captured)

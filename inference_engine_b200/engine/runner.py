@@ -26,17 +26,6 @@ def _align4(n: int) -> int:
     return (n + 3) & ~3
 
 
-def contexts_are_ragged(ctx_lens) -> bool:
-    """Whether a step's contexts differ so much in length that dealing attention work by request
-    would leave most of the GPU waiting for the longest one: the longest is well above the mean
-    and long enough to matter."""
-    n = len(ctx_lens)
-    if n < 2:
-        return False
-    longest = max(ctx_lens)
-    return longest >= 512 and longest * n > 1.5 * sum(ctx_lens)
-
-
 class ModelRunner:
     def __init__(self, model: Model, cache: CacheManager, storage: CacheStorage, ops,
                  device, max_tokens_per_step: int, max_seqs_per_step: int) -> None:
@@ -51,6 +40,16 @@ class ModelRunner:
         self._staging_dev = None
         self.last_h2d_bytes = 0
         self._ensure_staging(self._staging_ints(self.max_tokens, self.max_seqs, self.max_seqs, 8))
+
+    def contexts_are_ragged(self, ctx_lens) -> bool:
+        """A hint for the attention's launch: whether these requests' contexts differ so much in
+        length that work dealt request by request would leave most of the GPU waiting for the
+        longest one.  The kernels' side decides (it knows how many requests the device takes at
+        once); without such kernels the answer is no."""
+        decide = getattr(self.ops, "decode_by_length", None)
+        if decide is None or not self.cache.paged_groups or len(ctx_lens) < 2:
+            return False
+        return bool(decide(ctx_lens, self.cache.paged_groups[0].num_kv_heads))
 
     # --- staging ----------------------------------------------------------------------------
 
@@ -198,7 +197,7 @@ class ModelRunner:
             cu_q=dview(v_cu), ctx_lens=dview(v_ctx), groups=groups,
             q_starts=q_starts, q_lens=q_lens, start_positions=start_positions,
             max_q_len=max(q_lens), max_ctx_len=max(ctx_lens), padded=pad_to_seqs is not None,
-            ragged=contexts_are_ragged(ctx_lens[:real_b]),
+            ragged=self.contexts_are_ragged(ctx_lens[:real_b]),
         )
         return ctx, dview(v_rows)
 
@@ -320,7 +319,7 @@ class ModelRunner:
             cu_q=dview(v_cu), ctx_lens=dview(v_ctx), groups=groups,
             q_starts=list(range(b)), q_lens=[1] * b, start_positions=start_positions,
             max_q_len=1, max_ctx_len=int(positions.max()) + 1, padded=pad_to_seqs is not None,
-            ragged=contexts_are_ragged((positions + 1).tolist()),
+            ragged=self.contexts_are_ragged((positions + 1).tolist()),
         )
         return ctx, dview(v_rows)
 

@@ -310,6 +310,22 @@ class CudaOps:
         blocks = max(num_seqs * nkv, 1)
         return max(1, min(self.decode_split_target // blocks, 32))
 
+    def decode_by_length(self, ctx_lens, nkv: int) -> bool:
+        """Whether a decode step over contexts of these lengths should use the kernel that deals
+        key tiles by length.  In tokens one block walks: dealt by request the step lasts as long
+        as the longest context over its splits (or the whole work over the blocks the device
+        runs at once, if that is more); dealt by length, the work over those blocks, plus the
+        set-up that kernel pays (measured: about 600 tokens' worth, and 15 % for second pairs in
+        a block)."""
+        if self.decode_balanced in ("0", "1"):
+            return self.decode_balanced == "1"
+        pairs = len(ctx_lens) * nkv
+        work = sum(ctx_lens) * nkv
+        longest = max(ctx_lens)
+        slots = self.sm_count if pairs <= self.sm_count else 2 * self.sm_count
+        by_request = max(longest / self.decode_splits(len(ctx_lens), nkv), work / slots)
+        return by_request > 1.15 * work / slots + 600
+
     def paged_attention(self, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, page_size,
                         scale, window, out) -> None:
         """Attention of every token of the step over its request's cached keys and values.
@@ -339,8 +355,7 @@ class CudaOps:
                 ctx._attention_plan = plan
             small, any_small, all_small = plan["small"], plan["any"], plan["all"]
             stream = self._stream()
-            balanced = (self.decode_balanced == "1" or
-                        (self.decode_balanced == "auto" and getattr(ctx, "ragged", False)))
+            balanced = self.decode_balanced == "1" or (self.decode_balanced == "auto" and getattr(ctx, "ragged", False))
             if any_small and balanced and ctx.num_seqs <= lib.ie_attention_decode_balanced_max_seqs():
                 per_pair = self.decode_balanced_blocks_per_pair
                 floats = lib.ie_attention_decode_balanced_scratch_floats(ctx.num_seqs, nkv, per_pair)

@@ -198,8 +198,8 @@ def test_smoke_entry():
 
 @pytest.mark.gpu
 def test_a_long_request_among_short_ones_decodes_the_same_with_either_attention_launch(monkeypatch):
-    """Contexts that differ much in length switch the decode attention to the kernel that deals
-    key tiles by length (captured separately); the tokens are those of the plain launch."""
+    """The decode attention that deals key tiles by length (for contexts that differ much;
+    captured separately) gives the tokens of the launch that deals them by request."""
     from inference_engine_b200 import SamplingParams
     from inference_engine_b200.engine.llm_engine import LLMEngine
 
@@ -210,15 +210,21 @@ def test_a_long_request_among_short_ones_decodes_the_same_with_either_attention_
         prompts[f"short{i}"] = torch.randint(0, vocab, (7 + 3 * i,), generator=g).tolist()
     params = SamplingParams(temperature=0, max_tokens=12)
     results = {}
-    for mode in ("auto", "0"):
+    for mode in ("1", "0"):
         cfg = dict(TINY_A, max_position_embeddings=2048)
         eng = LLMEngine.from_random(cfg, seed=3, dtype="bfloat16", device="cuda", max_model_len=1024,
                                     num_blocks=160, block_size=8, max_num_seqs=8, enable_cuda_graphs=True)
         monkeypatch.setattr(eng.ops, "decode_balanced", mode)
         before = eng.ops.balanced_launches
         results[mode] = eng.generate(prompts, params)
-        assert (eng.ops.balanced_launches > before) == (mode == "auto")
-        assert any(key[1] for key in eng.graphs._graphs), "no step with ragged contexts was captured"
+        assert (eng.ops.balanced_launches > before) == (mode == "1")
+        assert all(key[1] == (mode == "1") for key in eng.graphs._graphs) and eng.graphs._graphs
         eng.ops.check_errors()
-    same = sum(results["auto"][r] == results["0"][r] for r in prompts)
+    same = sum(results["1"][r] == results["0"][r] for r in prompts)
     assert same >= len(prompts) - 1, results  # (a near-tie may flip one greedy choice between summation orders)
+    # left to itself the engine deals by length only where that pays
+    monkeypatch.setattr(eng.ops, "decode_balanced", "auto")
+    assert eng.ops.decode_by_length([32768] + [256] * 31, 8)
+    assert eng.ops.decode_by_length([8000] + [500] * 7, 8)
+    assert not eng.ops.decode_by_length([1024] * 8, 8)
+    assert not eng.ops.decode_by_length([2304] * 32, 8)

@@ -127,14 +127,64 @@ struct __align__(8) Barriers {
     unsigned long long q_full, kv_full[KV_STAGES], kv_empty[KV_STAGES], s_done[2], p_ready[2], o_done;
     unsigned tmem_base;
     int failed;
+    int is_last;
 };
 
+// The last block of a tile and head merges the shares of the tile's keys that `ksplit` blocks
+// left in scratch, in their order: one thread per query row.  Kept out of line: inlined, its
+// registers slowed the kernel's main path down.
+__device__ __noinline__ void merge_key_shares(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                              size_t first, int ksplit, bf16* __restrict__ orow) {
+    __threadfence();
+    float m_all = -INFINITY;
+    for (int z = 0; z < ksplit; ++z) m_all = fmaxf(m_all, __ldcg(part_ml + (first + (size_t)z * BM) * 2));
+    float m_safe = (m_all == -INFINITY) ? 0.f : m_all;
+    float l_all = 0.f;
+    for (int z = 0; z < ksplit; ++z) {
+        size_t p = first + (size_t)z * BM;
+        l_all += __ldcg(part_ml + p * 2 + 1) * exp2f(__ldcg(part_ml + p * 2) - m_safe);
+    }
+    float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
+#pragma unroll 1
+    for (int half = 0; half < HD / 32; ++half) {
+        float acc[32];
+#pragma unroll
+        for (int d = 0; d < 32; ++d) acc[d] = 0.f;
+        for (int z = 0; z < ksplit; ++z) {
+            size_t p = first + (size_t)z * BM;
+            float f = exp2f(__ldcg(part_ml + p * 2) - m_safe);
+            const float4* src = reinterpret_cast<const float4*>(part_o + p * HD + half * 32);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                float4 v = __ldcg(src + c);
+                acc[4 * c] += v.x * f; acc[4 * c + 1] += v.y * f;
+                acc[4 * c + 2] += v.z * f; acc[4 * c + 3] += v.w * f;
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            unsigned w[4];
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+                __nv_bfloat162 pk = __floats2bfloat162_rn(acc[c * 8 + 2 * h] * inv, acc[c * 8 + 2 * h + 1] * inv);
+                w[h] = *reinterpret_cast<unsigned*>(&pk);
+            }
+            *reinterpret_cast<uint4*>(orow + half * 32 + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    }
+}
+
+// SPLIT: the keys of a tile are shared among gridDim.z blocks (an instance of its own: the code
+// for it cost the plain kernel 4 % on long prompts).
+template <bool SPLIT>
 __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM)
 attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__ CUtensorMap k_map,
                              const __grid_constant__ CUtensorMap v_map, const int* __restrict__ tables,
                              int table_width, const int* __restrict__ cu_q, const int* __restrict__ ctx_lens,
                              bf16* __restrict__ out, int num_seqs, int nh, int nkv, int page_shift,
-                             int total_pages, float scale_log2, int window, int paired, int* err) {
+                             int total_pages, float scale_log2, int window, int paired, int ksplit,
+                             float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ tickets,
+                             int* err) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     unsigned char* k_s = smem;                                  // stages x 8 KB
@@ -178,6 +228,12 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
         int lo = (window > 0 && p.qpos_lo - window + 1 > 0) ? p.qpos_lo - window + 1 : 0;
         p.key_begin = (lo / KT) * KT;
         p.n_tiles = (p.qpos_hi - p.key_begin) / KT + 1;
+        if (SPLIT) {  // this block's share of the tile's keys (it may be empty)
+            int first = (int)((long long)blockIdx.z * p.n_tiles / ksplit);
+            int end = (int)((long long)(blockIdx.z + 1) * p.n_tiles / ksplit);
+            p.key_begin += first * KT;
+            p.n_tiles = end - first;
+        }
         return p;
     };
     Part parts[2];
@@ -270,7 +326,7 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
                 int n_tiles = parts[pi].n_tiles;
                 // the part's Q is in tensor memory (and the softmax warps are done with the
                 // accumulator of the part before)
-                ok = mbar_wait_compact(&bars->q_full, pi & 1) && issue_s(g);
+                ok = mbar_wait_compact(&bars->q_full, pi & 1) && (n_tiles == 0 || issue_s(g));
                 for (int t = 0; t < n_tiles && ok; ++t, ++g) {
                     if (t + 1 < n_tiles) {
                         // its S buffer held the weights of tile g - 1: that product must have read them
@@ -447,28 +503,63 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 mbar_arrive(&bars->p_ready[g & 1]);
             }
-            if (ok && !mbar_wait_compact(&bars->o_done, (g - 1) & 1)) ok = false;
-            if (ok) {
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                float inv = l > 0.f ? 1.0f / l : 0.f;
-                bf16* orow = out + ((size_t)(q0 + pt.t0 + row) * nh + head) * HD;
+            if (ok && n_tiles > 0 && !mbar_wait_compact(&bars->o_done, (g - 1) & 1)) ok = false;
+            bf16* orow = out + ((size_t)(q0 + pt.t0 + row) * nh + head) * HD;
+            if (!SPLIT) {
+                if (ok) {
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    float inv = l > 0.f ? 1.0f / l : 0.f;
 #pragma unroll
-                for (int half = 0; half < HD / 32; ++half) {
-                    float acc[32];
-                    tmem_ld32(acc, tmem_o + half * 32 + lane_addr);
-                    if (exists) {
+                    for (int half = 0; half < HD / 32; ++half) {
+                        float acc[32];
+                        tmem_ld32(acc, tmem_o + half * 32 + lane_addr);
+                        if (exists) {
 #pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            unsigned w[4];
+                            for (int c = 0; c < 4; ++c) {
+                                unsigned w[4];
 #pragma unroll
-                            for (int h = 0; h < 4; ++h) {
-                                __nv_bfloat162 pk = __floats2bfloat162_rn(acc[c * 8 + 2 * h] * inv, acc[c * 8 + 2 * h + 1] * inv);
-                                w[h] = *reinterpret_cast<unsigned*>(&pk);
+                                for (int h = 0; h < 4; ++h) {
+                                    __nv_bfloat162 pk = __floats2bfloat162_rn(acc[c * 8 + 2 * h] * inv, acc[c * 8 + 2 * h + 1] * inv);
+                                    w[h] = *reinterpret_cast<unsigned*>(&pk);
+                                }
+                                *reinterpret_cast<uint4*>(orow + half * 32 + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
                             }
-                            *reinterpret_cast<uint4*>(orow + half * 32 + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
                         }
                     }
                 }
+            } else {
+                // The tile's keys are shared among ksplit blocks: this one's row of the accumulator
+                // (relative to its maximum m), m and the sum go to scratch; the block that finishes
+                // last for this tile and head (ticket counter) merges the shares in their order.
+                // All softmax threads pass the two barriers, whatever happened before.
+                size_t pair = (size_t)blockIdx.x * nh + head;
+                size_t at = (pair * ksplit + blockIdx.z) * BM + row;
+                bool filled = ok && n_tiles > 0;  // (no keys for this share: an empty part)
+                part_ml[at * 2] = filled ? m : -INFINITY;
+                part_ml[at * 2 + 1] = filled ? l : 0.f;
+                if (filled) asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int half = 0; half < HD / 32; ++half) {
+                    float acc[32];
+                    if (filled) {
+                        tmem_ld32(acc, tmem_o + half * 32 + lane_addr);
+                    } else {
+#pragma unroll
+                        for (int d = 0; d < 32; ++d) acc[d] = 0.f;
+                    }
+                    float4* dst = reinterpret_cast<float4*>(part_o + at * HD + half * 32);
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) dst[c] = make_float4(acc[4 * c], acc[4 * c + 1], acc[4 * c + 2], acc[4 * c + 3]);
+                }
+                __threadfence();
+                named_barrier(2, SOFTMAX_THREADS);
+                if (tid == 0) {
+                    int ticket = atomicAdd(&tickets[pair], 1);
+                    bars->is_last = ticket == ksplit - 1;
+                    if (bars->is_last) tickets[pair] = 0;  // zero again for the next launch
+                }
+                named_barrier(2, SOFTMAX_THREADS);
+                if (bars->is_last && exists) merge_key_shares(part_o, part_ml, pair * ksplit * BM + row, ksplit, orow);
             }
         }
         if (!ok) bars->failed = 1;
@@ -491,13 +582,24 @@ IE_API int ie_attention_prefill_tc5_ok(int page_size, int max_ctx) {
     return (max_ctx + KT) / page_size <= MAX_TABLE ? 1 : 0;
 }
 
+// Floats of scratch for `ksplit` > 1: a partial result per (work item, head, share of the keys).
+IE_API long long ie_attention_prefill_tc5_scratch_floats(int max_items, int nh, int ksplit) {
+    if (ksplit <= 1) return 0;
+    return (long long)max_items * nh * ksplit * BM * (HD + 2);
+}
+
+// `ksplit` > 1 (not with `paired`): the keys of every 128-token tile are shared among that many
+// blocks, for steps with few tiles and long contexts; needs `scratch`
+// (ie_attention_prefill_tc5_scratch_floats floats) and `tickets` (max_items * nh ints, zero before
+// the first launch; a launch leaves them zero).
 IE_API int ie_attention_prefill_tc5(const void* q, const void* k_cache, const void* v_cache, const int* tables,
                                     int table_width, const int* cu_q, const int* ctx_lens, void* out,
                                     int num_tokens, int num_seqs, int max_items, int paired, int nh, int nkv,
-                                    int page_size, int total_pages, float scale, int window, int* err,
-                                    void* stream) {
+                                    int page_size, int total_pages, float scale, int window, int ksplit,
+                                    float* scratch, int* tickets, int* err, void* stream) {
     if (num_seqs <= 0 || max_items <= 0) return 0;
-    if (nkv <= 0 || nh % nkv != 0 || (page_size & (page_size - 1)) != 0 || page_size < 8 || page_size > KT)
+    if (nkv <= 0 || nh % nkv != 0 || (page_size & (page_size - 1)) != 0 || page_size < 8 || page_size > KT ||
+        ksplit < 1 || ksplit > 64 || (ksplit > 1 && (paired || scratch == nullptr || tickets == nullptr)))
         return (int)cudaErrorInvalidValue;
     int page_shift = 0;
     while ((1 << page_shift) < page_size) ++page_shift;
@@ -508,22 +610,34 @@ IE_API int ie_attention_prefill_tc5(const void* q, const void* k_cache, const vo
         return (int)cudaErrorNotSupported;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc5_kernel,
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc5_kernel<false>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(attention_prefill_tc5_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    return ie_launch(attention_prefill_tc5_kernel, dim3(max_items, nh), dim3(THREADS), SMEM_BYTES,
+    float* part_o = scratch;
+    float* part_ml = scratch ? scratch + (size_t)max_items * nh * ksplit * BM * HD : nullptr;
+    float scale_log2 = scale * 1.4426950408889634f;
+    if (ksplit > 1)
+        return ie_launch(attention_prefill_tc5_kernel<true>, dim3(max_items, nh, ksplit), dim3(THREADS), SMEM_BYTES,
+                         (cudaStream_t)stream, (const bf16*)q, km, vm, tables, table_width, cu_q, ctx_lens, (bf16*)out,
+                         num_seqs, nh, nkv, page_shift, total_pages, scale_log2, window, paired, ksplit, part_o, part_ml,
+                         tickets, err);
+    return ie_launch(attention_prefill_tc5_kernel<false>, dim3(max_items, nh), dim3(THREADS), SMEM_BYTES,
                      (cudaStream_t)stream, (const bf16*)q, km, vm, tables, table_width, cu_q, ctx_lens, (bf16*)out, num_seqs,
-                     nh, nkv, page_shift, total_pages, scale * 1.4426950408889634f, window, paired, err);
+                     nh, nkv, page_shift, total_pages, scale_log2, window, paired, ksplit, part_o, part_ml, tickets, err);
 }
 
 #else  // other head sizes: the mma.sync kernels of attention_mma.cu serve them
 
 IE_API int ie_attention_prefill_tc5_ok(int, int) { return 0; }
+IE_API long long ie_attention_prefill_tc5_scratch_floats(int, int, int) { return 0; }
 IE_API int ie_attention_prefill_tc5(const void*, const void*, const void*, const int*, int, const int*,
-                                    const int*, void*, int, int, int, int, int, int, int, int, float, int, int*,
-                                    void*) {
+                                    const int*, void*, int, int, int, int, int, int, int, int, float, int, int,
+                                    float*, int*, int*, void*) {
     return (int)cudaErrorNotSupported;
 }
 

@@ -70,6 +70,7 @@ class CudaOps:
         # which kernel takes few-row bfloat16 products: "tma" (TMA-fed ring), "cp" (cp.async
         # rings per warp), "auto" (cp for few output features, the vendor library otherwise)
         self.attn_tc5 = os.environ.get("IE_B200_ATTN_TC5", "1") != "0"  # tcgen05 prefill attention
+        self.prefill_key_splits = os.environ.get("IE_B200_PREFILL_KEY_SPLITS", "1") != "0"
         # the decode kernel cuts contexts until about this many blocks run (one block per SM)
         self.decode_split_target = int(os.environ.get("IE_B200_DECODE_SPLIT_TARGET", 128))
         # batches whose contexts differ much in length go to the decode kernel that deals key tiles
@@ -286,7 +287,9 @@ class CudaOps:
             P, I, F = c_void_p, c_int, c_float
             lib.ie_attention_decode.argtypes = [P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, F, I, I, P, P]
             lib.ie_attention_prefill.argtypes = [P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P, P]
-            lib.ie_attention_prefill_tc5.argtypes = [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P]
+            lib.ie_attention_prefill_tc5.argtypes = [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P, P, P]
+            lib.ie_attention_prefill_tc5_scratch_floats.argtypes = [I, I, I]
+            lib.ie_attention_prefill_tc5_scratch_floats.restype = ctypes.c_longlong
             lib.ie_attention_prefill_tc5_ok.argtypes = [I, I]
             lib.ie_attention_decode_scratch_floats.argtypes = [I, I, I]
             lib.ie_attention_decode_scratch_floats.restype = ctypes.c_longlong
@@ -325,6 +328,21 @@ class CudaOps:
         slots = self.sm_count if pairs <= self.sm_count else 2 * self.sm_count
         by_request = max(longest / self.decode_splits(len(ctx_lens), nkv), work / slots)
         return by_request > 1.15 * work / slots + 600
+
+    def prefill_key_split(self, blocks: int, hd: int, max_ctx_len: int) -> int:
+        """Among how many blocks the tcgen05 prefill kernel shares the keys of a query tile: the
+        count that needs the fewest rounds of blocks over the device per share of the keys, if
+        that saves a quarter of the time and leaves every block four key tiles of the longest
+        context; 1 when the tiles fill the device anyway."""
+        slots = self.sm_count * (2 if hd == 64 else 1)
+        if blocks <= 0 or blocks >= slots:
+            return 1
+        key_tiles = max(max_ctx_len // 64, 1)
+        # rounds of blocks over the device, each block 1 / ks of a tile's keys plus a set-up worth two key tiles
+        cost = lambda ks: -(-blocks * ks // slots) * (1.0 / ks + 2.0 / key_tiles)
+        limit = max(1, min(16, max_ctx_len // 256))
+        best = min(range(1, limit + 1), key=lambda ks: (cost(ks), ks))
+        return best if cost(best) <= 0.75 * cost(1) else 1
 
     def paged_attention(self, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, page_size,
                         scale, window, out) -> None:
@@ -389,14 +407,26 @@ class CudaOps:
                     # head size 64, pages of 8 tokens or more: the tcgen05 / TMEM / TMA kernel.
                     # While the blocks would fill the GPU less than about twice, a block takes two
                     # tiles of a request, a late (long) and an early (short) one.
-                    paired = tiles * nh <= 4 * self.sm_count
+                    # With so few tiles that even then half the GPU would idle (a short portion
+                    # of a long prompt), the keys of every tile are shared among several blocks
+                    # instead, each with at least four key tiles of the longest context.
+                    ksplit = self.prefill_key_split(tiles * nh, hd, ctx.max_ctx_len) if self.prefill_key_splits else 1
+                    paired = ksplit == 1 and tiles * nh <= 4 * self.sm_count
                     if paired:
                         tiles = plan["tile_pairs"]
+                    scratch = tickets = None
+                    if ksplit > 1:
+                        floats = lib.ie_attention_prefill_tc5_scratch_floats(tiles, nh, ksplit)
+                        ws = getattr(ctx, "ws", None)
+                        scratch = (ws.buffer("attn.prefill_partial", 1, floats, torch.float32) if ws is not None
+                                   else torch.empty(floats, dtype=torch.float32, device=q.device))
+                        tickets = self._decode_tickets(max(tiles * nh, ctx.num_seqs * nkv))
                     self._check(lib.ie_attention_prefill_tc5(
                         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
                         block_tables.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_lens.data_ptr(), out.data_ptr(),
                         ctx.num_tokens, ctx.num_seqs, tiles, 1 if paired else 0, nh, nkv, page_size, total_pages,
-                        scale, window, self._err_ptr, stream), "attention_prefill_tc5")
+                        scale, window, ksplit, self._ptr(scratch), self._ptr(tickets), self._err_ptr, stream),
+                        "attention_prefill_tc5")
                     return
                 self._check(lib.ie_attention_prefill(
                     q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),

@@ -408,6 +408,32 @@ def test_decode_attention_deals_ragged_contexts_evenly(ops, nh, nkv, hd, ps, win
     assert torch.equal(again, got)
 
 
+@pytest.mark.parametrize("nh,nkv,hd,ps", [(32, 8, 64, 16), (8, 2, 128, 16), (4, 1, 64, 8)])
+@pytest.mark.parametrize("window", [0, 1000])
+@pytest.mark.parametrize("q_lens,ctx_lens", [([200], [3000]), ([130, 1, 260], [2600, 900, 260]), ([17], [1100])])
+def test_prefill_attention_shares_the_keys_of_few_tiles_among_blocks(ops, nh, nkv, hd, ps, window, q_lens, ctx_lens):
+    """A short portion at the end of a long prompt: too few query tiles to fill the GPU, so the
+    keys of every tile are shared among several blocks and merged (head sizes 64 and 128).  One
+    far key per request stands out; the result is the same with and without the sharing."""
+    spike = [min(c - q, max(0, c - q - window // 2) if window else (c - q) // 3) for c, q in zip(ctx_lens, q_lens)]
+    q, k, v, tables, ctx = _attention_case(nh, nkv, hd, ps, q_lens, ctx_lens, torch.bfloat16, seed=21, spike=spike)
+    want = torch.empty_like(q)
+    RefOps().paged_attention(q, k, v, tables, ctx, nh, nkv, hd, ps, hd ** -0.5, window, want)
+    outs = []
+    for share in (True, False):
+        ops.prefill_key_splits = share
+        try:
+            got = torch.zeros_like(q)
+            ops.paged_attention(q, k, v, tables, ctx, nh, nkv, hd, ps, hd ** -0.5, window, got)
+            ctx._attention_plan = None
+        finally:
+            ops.prefill_key_splits = True
+        torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+        outs.append(got)
+    torch.testing.assert_close(outs[0].float(), outs[1].float(), atol=1e-2, rtol=1e-2)
+    ops.check_errors()
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkv,hd,ps", [(32, 8, 64, 16), (3, 1, 32, 8), (8, 2, 128, 16)])
 def test_paged_attention_finds_one_far_key(ops, dtype, nh, nkv, hd, ps):

@@ -90,11 +90,15 @@ class CudaOps:
         # shape at 64 rows: the down projection (K = 8192) 11.0 us against the library's 13.0,
         # but QKV, output and gate-up (K = 2048) 7.3 / 6.3 / 16.3 against 5.7 / 5.5 / 13.5: every
         # block copies all tokens' activations through its SM's copy engine beside the weights,
-        # which the library's kernels share within a cluster.  So only long inner dimensions.
+        # which the library's kernels share within a cluster.  So only long inner dimensions, and
+        # only where its blocks (feature tiles x cuts along k) fit the SMs in one round: at the 3B
+        # shape the down projection (3072 x 8192) 13.5 against 14.2 us, at the 8B shape (4096 x
+        # 14336: 224 blocks) 33.6 against 25.4, and its K = 4096 products 13 to 45 % behind.
         self.batch_gemm = os.environ.get("IE_B200_BATCH_GEMM", "1") != "0"
         self.batch_gemm_rows = int(os.environ.get("IE_B200_BATCH_GEMM_ROWS", 64))
         self.batch_gemm_max_tiles = int(os.environ.get("IE_B200_BATCH_GEMM_MAX_TILES", 256))
-        self.batch_gemm_min_k = int(os.environ.get("IE_B200_BATCH_GEMM_MIN_K", 4096))
+        self.batch_gemm_min_k = int(os.environ.get("IE_B200_BATCH_GEMM_MIN_K", 8192))
+        self.batch_gemm_one_round = True  # only where the kernel's blocks fit the SMs in one round
         self._device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self._raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
         self.launches = 0  # launches of this library's kernels (library matrix products not counted)
@@ -235,7 +239,9 @@ class CudaOps:
         # kernel with the operands' roles swapped, cut along k like the few-row kernel.
         if (self.batch_gemm and self.SKINNY_ROWS < m <= self.batch_gemm_rows and x.is_contiguous()
                 and w.is_contiguous() and self._gemm_tc5_ok(m, n, k)
-                and -(-n // 128) <= self.batch_gemm_max_tiles and k >= self.batch_gemm_min_k):
+                and -(-n // 128) <= self.batch_gemm_max_tiles and k >= self.batch_gemm_min_k
+                and (not self.batch_gemm_one_round or (
+                    allow_split and out is None and -(-n // 128) * self.tma_split(n, k)[1] <= self.sm_count))):
             per, splits = self.tma_split(n, k) if allow_split and out is None else (k // 64, 1)
             if splits > 1:
                 out = ws.buffer(tag, splits * m, n, torch.float32).view(splits, m, n)

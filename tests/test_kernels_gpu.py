@@ -215,8 +215,9 @@ def test_tcgen05_gemm_for_a_batch_of_decode_tokens(ops, m, n, k):
     w = (torch.randn(n, k, device="cuda", generator=g) * 0.05).bfloat16()
     want = x.double() @ w.double().t()
     ws = Workspace("cuda")
-    saved = ops.batch_gemm, ops.batch_gemm_rows, ops.batch_gemm_max_tiles, ops.batch_gemm_min_k
+    saved = ops.batch_gemm, ops.batch_gemm_rows, ops.batch_gemm_max_tiles, ops.batch_gemm_min_k, ops.batch_gemm_one_round
     ops.batch_gemm, ops.batch_gemm_rows, ops.batch_gemm_max_tiles, ops.batch_gemm_min_k = True, 256, 1 << 20, 0
+    ops.batch_gemm_one_round = False
     launches = ops.launches
     try:
         for _ in range(2):
@@ -233,7 +234,8 @@ def test_tcgen05_gemm_for_a_batch_of_decode_tokens(ops, m, n, k):
         assert ops.launches - launches == 6  # every product ran this kernel, none the vendor library
         ops.check_errors()
     finally:
-        ops.batch_gemm, ops.batch_gemm_rows, ops.batch_gemm_max_tiles, ops.batch_gemm_min_k = saved
+        (ops.batch_gemm, ops.batch_gemm_rows, ops.batch_gemm_max_tiles, ops.batch_gemm_min_k,
+         ops.batch_gemm_one_round) = saved
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

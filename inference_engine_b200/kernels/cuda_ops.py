@@ -85,6 +85,7 @@ class CudaOps:
         # wide matrices, so only those that must be cut along k to fill the GPU go to it)
         self.tma_max_tiles = int(os.environ.get("IE_B200_TMA_MAX_TILES", 256))
         self.tma_max_tiles_wide = min(self.tma_max_tiles, self.sm_count // 2)  # 9 to 16 rows
+        self.tma_max_blocks = int(os.environ.get("IE_B200_TMA_MAX_BLOCKS", 3 * self.sm_count // 2))
         # Products of 17 to `batch_gemm_rows` rows with a long inner dimension: the tcgen05
         # weight-streaming kernel (IE_B200_BATCH_GEMM=0: the vendor library).  Measured on the 1B
         # shape at 64 rows: the down projection (K = 8192) 11.0 us against the library's 13.0,
@@ -227,7 +228,9 @@ class CudaOps:
         if (few_rows and self.few_row_gemm == "tma" and not self.force_skinny
                 and -(-n // 128) <= (self.tma_max_tiles if m <= 8 else self.tma_max_tiles_wide)):
             kbps, splits = self.tma_split(n, k) if allow_split and out is None else (-(-k // 64), 1)
-            if kbps <= 32:
+            # (more than one and a half rounds of blocks over the SMs: the library's kernels are
+            # ahead there, 41.8 against 45.7 us on the 8B shape's gate-up matrix)
+            if kbps <= 32 and -(-n // 128) * splits <= self.tma_max_blocks:
                 if splits > 1:
                     out = ws.buffer(tag, splits * m, n, torch.float32).view(splits, m, n)
                 elif out is None:

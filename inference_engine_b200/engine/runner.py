@@ -197,7 +197,8 @@ class ModelRunner:
             cu_q=dview(v_cu), ctx_lens=dview(v_ctx), groups=groups,
             q_starts=q_starts, q_lens=q_lens, start_positions=start_positions,
             max_q_len=max(q_lens), max_ctx_len=max(ctx_lens), padded=pad_to_seqs is not None,
-            ragged=self.contexts_are_ragged(ctx_lens[:real_b]),
+            # (of the requests that bring one token: the others are not the decode kernel's)
+            ragged=self.contexts_are_ragged([c for c, ql in zip(ctx_lens[:real_b], q_lens) if ql == 1]),
         )
         return ctx, dview(v_rows)
 

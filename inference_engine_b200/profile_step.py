@@ -1,5 +1,5 @@
-"""A steady-state driver for profilers: a few decode steps or one prefill of a random-weight
-Llama shape, launched eagerly (no captured launch sequence) so that every kernel shows up by
+"""A steady-state driver for profilers: a few decode steps, one prefill, or a step with a prompt's last
+portion beside decoding requests (``--mode mixed``), of a random-weight Llama shape, launched eagerly (no captured launch sequence) so that every kernel shows up by
 name.  The reference has bench/profile_step.py in this role.
 
     python -m inference_engine_b200.profile_step --mode decode --batch 8 --context 1024 --layers 4
@@ -17,10 +17,12 @@ import json
 
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--mode", choices=["decode", "prefill"], default="decode")
+    ap.add_argument("--mode", choices=["decode", "prefill", "mixed"], default="decode",
+                    help="mixed: the last --tokens tokens of a --prompt-token prompt beside batch - 1 decoding requests")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=1024, help="tokens cached per request (decode)")
-    ap.add_argument("--tokens", type=int, default=2048, help="prompt tokens (prefill)")
+    ap.add_argument("--tokens", type=int, default=2048, help="prompt tokens (prefill), tokens of the portion (mixed)")
+    ap.add_argument("--prompt-tokens", type=int, default=4096, help="length of the prompt whose last portion runs (mixed)")
     ap.add_argument("--layers", type=int, default=16)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=2)
@@ -48,7 +50,8 @@ def main() -> int:
         }
     cfg["num_hidden_layers"] = args.layers
     block = 16
-    per_req = (args.context if args.mode == "decode" else args.tokens) + args.steps + args.warmup + 16
+    per_req = {"decode": args.context, "prefill": args.tokens,
+               "mixed": max(args.context, args.prompt_tokens)}[args.mode] + args.steps + args.warmup + 16
     engine = LLMEngine.from_random(
         cfg, seed=0, dtype=args.dtype, device="cuda", max_model_len=max(per_req, 64),
         num_blocks=args.batch * (-(-per_req // block) + 1), block_size=block,
@@ -69,6 +72,31 @@ def main() -> int:
             torch.cuda.synchronize()
             times.append(s.elapsed_time(e))
             cache.free(r)
+    elif args.mode == "mixed":
+        chunk = 2048
+        cache.add_request("prompt")
+        cache.grow("prompt", 0, args.prompt_tokens)
+        done = args.prompt_tokens - args.tokens
+        for start in range(0, done, chunk):
+            n = min(chunk, done - start)
+            runner.step([StepEntry("prompt", torch.randint(0, vocab, (n,), generator=g).tolist(), start, [])])
+        ids = list(range(args.batch - 1))
+        for rid in ids:
+            cache.add_request(rid)
+            cache.grow(rid, 0, args.context + 1)
+            for start in range(0, args.context, chunk):
+                n = min(chunk, args.context - start)
+                runner.step([StepEntry(rid, torch.randint(0, vocab, (n,), generator=g).tolist(), start, [])])
+        portion = torch.randint(0, vocab, (args.tokens,), generator=g).tolist()
+        entries = [StepEntry("prompt", portion, done, [args.tokens - 1])]
+        entries += [StepEntry(rid, [int(torch.randint(0, vocab, (1,), generator=g))], args.context, [0]) for rid in ids]
+        for k in range(args.warmup + args.steps):  # the same step again and again: it writes the same cache slots
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            runner.step(entries)
+            e.record()
+            torch.cuda.synchronize()
+            times.append(s.elapsed_time(e))
     else:
         ids = list(range(args.batch))
         for rid in ids:

@@ -250,7 +250,7 @@ class LLMEngine:
             "step": self.steps_total,
             "ms": round((time.perf_counter() - started) * 1000, 3),
             "seqs": len(seqs),
-            "prefill_tokens": sum(counts) - decode_tokens,
+            "prefill_tokens": max(sum(counts) - decode_tokens, 0),  # (a step launched ahead was counted when it was launched)
             "decode_tokens": decode_tokens,
             "graph": used_graph,
             "preempted": self.scheduler.num_preemptions - preempted_before,

@@ -65,6 +65,7 @@ class CudaOps:
         self._argmax_scratch = None
         self.force_skinny = False  # tests run every few-row product through the streaming kernel
         self._tickets = None
+        self._retired_tickets = []
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.skinny_max_blocks = int(os.environ.get("IE_B200_SKINNY_MAX_BLOCKS", self.sm_count))
         # which kernel takes few-row bfloat16 products: "tma" (TMA-fed ring), "cp" (cp.async
@@ -311,7 +312,9 @@ class CudaOps:
     def _decode_tickets(self, count: int):
         """Zeroed counters for the decode kernel's split merge; every launch leaves them zero."""
         if self._tickets is None or self._tickets.numel() < count:
-            self._tickets = self.torch.zeros(max(count, 4096), dtype=self.torch.int32, device=self.device)
+            if self._tickets is not None:
+                self._retired_tickets.append(self._tickets)  # captured launches may still point at it
+            self._tickets = self.torch.zeros(max(count, 16384), dtype=self.torch.int32, device=self.device)
         return self._tickets
 
     def decode_splits(self, num_seqs: int, nkv: int) -> int:

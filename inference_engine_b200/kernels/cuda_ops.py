@@ -367,10 +367,8 @@ class CudaOps:
             raise KernelError(f"head_dim {hd} is not supported: it must be a multiple of 8, at most 256")
         if nkv < 1 or nh % nkv:
             raise KernelError(f"{nh} query heads cannot share {nkv} key/value heads")
-        torch = self.torch
         groups = nh // nkv
-        total_pages = k_cache.shape[0]
-        if q.dtype == torch.bfloat16 and hd in ATTENTION_HEAD_DIMS and groups <= 16:
+        if q.dtype == self.torch.bfloat16 and hd in ATTENTION_HEAD_DIMS and groups <= 16:
             lib = self._attention_lib(hd)
             # which requests go to which kernel: the same for every layer of the step
             plan = getattr(ctx, "_attention_plan", None)
@@ -383,71 +381,83 @@ class CudaOps:
                     plan["tiles"] = sum(per_seq)
                     plan["tile_pairs"] = sum(-(-t // 2) for t in per_seq)
                 ctx._attention_plan = plan
-            small, any_small, all_small = plan["small"], plan["any"], plan["all"]
-            stream = self._stream()
-            balanced = self.decode_balanced == "1" or (self.decode_balanced == "auto" and getattr(ctx, "ragged", False))
-            if any_small and balanced and ctx.num_seqs <= lib.ie_attention_decode_balanced_max_seqs():
-                per_pair = self.decode_balanced_blocks_per_pair
-                floats = lib.ie_attention_decode_balanced_scratch_floats(ctx.num_seqs, nkv, per_pair)
-                ws = getattr(ctx, "ws", None)
-                scratch = (ws.buffer("attn.partial", 1, floats, torch.float32) if ws is not None
-                           else torch.empty(floats, dtype=torch.float32, device=q.device))
-                tickets = self._decode_tickets(ctx.num_seqs * nkv)
-                self._check(lib.ie_attention_decode_balanced(
-                    q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
-                    block_tables.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_lens.data_ptr(), out.data_ptr(),
-                    scratch.data_ptr(), tickets.data_ptr(), ctx.num_seqs, nh, nkv, page_size,
-                    total_pages, scale, window, per_pair, self._err_ptr, stream), "attention_decode_balanced")
-                self.balanced_launches += 1
-            elif any_small:
-                splits = self.decode_splits(ctx.num_seqs, nkv)
-                floats = lib.ie_attention_decode_scratch_floats(ctx.num_seqs, nkv, splits)
-                scratch = tickets = None
-                if floats:
-                    ws = getattr(ctx, "ws", None)
-                    scratch = (ws.buffer("attn.partial", 1, floats, torch.float32) if ws is not None
-                               else torch.empty(floats, dtype=torch.float32, device=q.device))
-                    tickets = self._decode_tickets(ctx.num_seqs * nkv)
-                self._check(lib.ie_attention_decode(
-                    q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
-                    block_tables.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_lens.data_ptr(), out.data_ptr(),
-                    self._ptr(scratch), self._ptr(tickets), ctx.num_seqs, nh, nkv, page_size,
-                    total_pages, scale, window, splits, self._err_ptr, stream), "attention_decode")
-            if not all_small:
-                tiles = plan["tiles"]
-                if self.attn_tc5 and lib.ie_attention_prefill_tc5_ok(page_size, ctx.max_ctx_len):
-                    # head size 64, pages of 8 tokens or more: the tcgen05 / TMEM / TMA kernel.
-                    # While the blocks would fill the GPU less than about twice, a block takes two
-                    # tiles of a request, a late (long) and an early (short) one.
-                    # With so few tiles that even then half the GPU would idle (a short portion
-                    # of a long prompt), the keys of every tile are shared among several blocks
-                    # instead, each with at least four key tiles of the longest context.
-                    ksplit = self.prefill_key_split(tiles * nh, hd, ctx.max_ctx_len) if self.prefill_key_splits else 1
-                    paired = ksplit == 1 and tiles * nh <= 4 * self.sm_count
-                    if paired:
-                        tiles = plan["tile_pairs"]
-                    scratch = tickets = None
-                    if ksplit > 1:
-                        floats = lib.ie_attention_prefill_tc5_scratch_floats(tiles, nh, ksplit)
-                        ws = getattr(ctx, "ws", None)
-                        scratch = (ws.buffer("attn.prefill_partial", 1, floats, torch.float32) if ws is not None
-                                   else torch.empty(floats, dtype=torch.float32, device=q.device))
-                        tickets = self._decode_tickets(max(tiles * nh, ctx.num_seqs * nkv))
-                    self._check(lib.ie_attention_prefill_tc5(
-                        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
-                        block_tables.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_lens.data_ptr(), out.data_ptr(),
-                        ctx.num_tokens, ctx.num_seqs, tiles, 1 if paired else 0, nh, nkv, page_size, total_pages,
-                        scale, window, ksplit, self._ptr(scratch), self._ptr(tickets), self._err_ptr, stream),
-                        "attention_prefill_tc5")
-                    return
-                self._check(lib.ie_attention_prefill(
-                    q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
-                    block_tables.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_lens.data_ptr(), out.data_ptr(),
-                    ctx.num_seqs, tiles, nh, nkv, page_size, total_pages, scale, window,
-                    self._err_ptr, stream), "attention_prefill")
+            args = (q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, page_size, scale, window, out)
+            if plan["any"]:
+                self._decode_attention(lib, *args)
+            if not plan["all"]:
+                self._prefill_attention(lib, plan, *args)
             return
         self.paged_attention_general(q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, page_size,
                                      scale, window, out)
+
+    def _scratch(self, ctx, name: str, floats: int, device):
+        ws = getattr(ctx, "ws", None)
+        if ws is not None:
+            return ws.buffer(name, 1, floats, self.torch.float32)
+        return self.torch.empty(floats, dtype=self.torch.float32, device=device)
+
+    def _decode_attention(self, lib, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, page_size, scale,
+                          window, out) -> None:
+        """The requests with few rows (the kernels skip the others): key tiles dealt by length
+        when the step's context says its lengths differ much, else by request."""
+        total_pages, stream = k_cache.shape[0], self._stream()
+        by_length = self.decode_balanced == "1" or (self.decode_balanced == "auto" and getattr(ctx, "ragged", False))
+        if by_length and ctx.num_seqs <= lib.ie_attention_decode_balanced_max_seqs():
+            per_pair = self.decode_balanced_blocks_per_pair
+            floats = lib.ie_attention_decode_balanced_scratch_floats(ctx.num_seqs, nkv, per_pair)
+            scratch = self._scratch(ctx, "attn.partial", floats, q.device)
+            tickets = self._decode_tickets(ctx.num_seqs * nkv)
+            self._check(lib.ie_attention_decode_balanced(
+                q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
+                block_tables.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_lens.data_ptr(), out.data_ptr(),
+                scratch.data_ptr(), tickets.data_ptr(), ctx.num_seqs, nh, nkv, page_size,
+                total_pages, scale, window, per_pair, self._err_ptr, stream), "attention_decode_balanced")
+            self.balanced_launches += 1
+            return
+        splits = self.decode_splits(ctx.num_seqs, nkv)
+        floats = lib.ie_attention_decode_scratch_floats(ctx.num_seqs, nkv, splits)
+        scratch = tickets = None
+        if floats:
+            scratch = self._scratch(ctx, "attn.partial", floats, q.device)
+            tickets = self._decode_tickets(ctx.num_seqs * nkv)
+        self._check(lib.ie_attention_decode(
+            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
+            block_tables.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_lens.data_ptr(), out.data_ptr(),
+            self._ptr(scratch), self._ptr(tickets), ctx.num_seqs, nh, nkv, page_size,
+            total_pages, scale, window, splits, self._err_ptr, stream), "attention_decode")
+
+    def _prefill_attention(self, lib, plan, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, page_size,
+                           scale, window, out) -> None:
+        """The requests with more than 16 rows, in query tiles of `ie_attention_prefill_rows` tokens."""
+        total_pages, stream = k_cache.shape[0], self._stream()
+        tiles = plan["tiles"]
+        if self.attn_tc5 and lib.ie_attention_prefill_tc5_ok(page_size, ctx.max_ctx_len):
+            # Head sizes 64 and 128, pages of 8 tokens or more: the tcgen05 / TMEM / TMA kernel.
+            # While the blocks would fill the GPU less than about twice, a block takes two tiles
+            # of a request, a late (long) and an early (short) one.  With so few tiles that even
+            # then much of the GPU would idle (a short portion of a long prompt), the keys of
+            # every tile are shared among several blocks instead.
+            ksplit = self.prefill_key_split(tiles * nh, hd, ctx.max_ctx_len) if self.prefill_key_splits else 1
+            paired = ksplit == 1 and tiles * nh <= 4 * self.sm_count
+            if paired:
+                tiles = plan["tile_pairs"]
+            scratch = tickets = None
+            if ksplit > 1:
+                floats = lib.ie_attention_prefill_tc5_scratch_floats(tiles, nh, ksplit)
+                scratch = self._scratch(ctx, "attn.prefill_partial", floats, q.device)
+                tickets = self._decode_tickets(max(tiles * nh, ctx.num_seqs * nkv))
+            self._check(lib.ie_attention_prefill_tc5(
+                q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
+                block_tables.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_lens.data_ptr(), out.data_ptr(),
+                ctx.num_tokens, ctx.num_seqs, tiles, 1 if paired else 0, nh, nkv, page_size, total_pages,
+                scale, window, ksplit, self._ptr(scratch), self._ptr(tickets), self._err_ptr, stream),
+                "attention_prefill_tc5")
+            return
+        self._check(lib.ie_attention_prefill(
+            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
+            block_tables.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_lens.data_ptr(), out.data_ptr(),
+            ctx.num_seqs, tiles, nh, nkv, page_size, total_pages, scale, window,
+            self._err_ptr, stream), "attention_prefill")
 
     def paged_attention_general(self, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd,
                                 page_size, scale, window, out) -> None:

@@ -100,7 +100,8 @@ class CudaOps:
         self.batch_gemm_rows = int(os.environ.get("IE_B200_BATCH_GEMM_ROWS", 64))
         self.batch_gemm_max_tiles = int(os.environ.get("IE_B200_BATCH_GEMM_MAX_TILES", 256))
         self.batch_gemm_min_k = int(os.environ.get("IE_B200_BATCH_GEMM_MIN_K", 8192))
-        self.batch_gemm_one_round = True  # only where the kernel's blocks fit the SMs in one round
+        # only where the kernel's blocks fit the SMs in one round
+        self.batch_gemm_one_round = os.environ.get("IE_B200_BATCH_GEMM_ONE_ROUND", "1") != "0"
         self._device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self._raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
         self.launches = 0  # launches of this library's kernels (library matrix products not counted)

@@ -1,17 +1,21 @@
 // Paged attention in bfloat16 on the tensor cores, one build per head size (-DIE_HD=64).
 //
-// Two kernels share the tile code below:
+// Three kernels share the tile code below:
 //   * decode: requests that bring few tokens (tokens x group size <= 16 rows: one decoded
 //     token, or a portion of two or three) -- one block per (request, key/value head, split of
 //     the context).  The group's query heads are rows of one 16-row matrix, so every key and
 //     value is read once for the whole group; the context is split over blocks and over the
-//     four warps of a block (flash-decoding), and a small second kernel merges the splits in
-//     a fixed order.
-//   * prefill: longer portions -- one block per (64 query tokens, query head), four warps of
-//     16 rows each, walking the keys from the start of the window to the last query position
-//     (bottom-right causal mask for portions that start mid-sequence).
+//     warps of a block (flash-decoding), and the block that finishes last merges the splits in
+//     a fixed order;
+//   * decode with the work dealt by length: the same for steps whose contexts differ much --
+//     a fixed grid, every block works out from the lengths which key tiles are its own;
+//   * prefill: longer portions -- one block per (128 query tokens, query head; 64 tokens above
+//     head size 64), four warps of 32 or 16 rows each, walking the keys from the start of the window to the
+//     last query position (bottom-right causal mask for portions that start mid-sequence).  Head
+//     sizes 64 and 128 with pages of 8 tokens or more go to the tcgen05 kernel of
+//     attention_tc5.cu instead.
 // Keys and values come through the block table row by row (a row is a head's head_dim values
-// of one token, contiguous), are staged in shared memory with cp.async (double buffered,
+// of one token, contiguous), are staged in shared memory with cp.async (rings of three tiles,
 // zero-filled outside the valid range) and read with ldmatrix; products are
 // mma.sync.m16n8k16 with 32-bit accumulators.  Scores, the running maximum and sum are
 // 32-bit; the weights are rounded to bfloat16 before they multiply the values, as in the

@@ -1,0 +1,58 @@
+"""The host-side choices among kernel launches (no GPU needed: they are arithmetic on lengths).
+
+`CudaOps.decode_by_length` picks between the two decode attention launches from the step's context
+lengths, `CudaOps.prefill_key_split` among how many blocks the prefill attention shares a query
+tile's keys, `CudaOps.decode_splits` into how many parts the by-request decode attention cuts a
+context.  The numbers they were set from are in profiles/attention_decode_b8.md and
+profiles/mixed_step_512_launches.md.
+"""
+
+from __future__ import annotations
+
+import types
+
+from inference_engine_b200.kernels.cuda_ops import CudaOps
+
+
+def _ops(sm_count=148, balanced="auto", split_target=128):
+    ops = types.SimpleNamespace(sm_count=sm_count, decode_balanced=balanced, decode_split_target=split_target)
+    ops.decode_splits = lambda num_seqs, nkv: CudaOps.decode_splits(ops, num_seqs, nkv)
+    return ops
+
+
+def test_contexts_are_cut_only_for_small_batches():
+    ops = _ops()
+    assert CudaOps.decode_splits(ops, 1, 8) == 16
+    assert CudaOps.decode_splits(ops, 8, 8) == 2
+    assert CudaOps.decode_splits(ops, 16, 8) == 1
+    assert CudaOps.decode_splits(ops, 64, 8) == 1
+    assert CudaOps.decode_splits(ops, 1, 1) == 32  # never more than 32 parts
+
+
+def test_work_is_dealt_by_length_only_where_that_pays():
+    ops = _ops()
+    by_length = lambda lens, nkv=8: CudaOps.decode_by_length(ops, lens, nkv)
+    assert by_length([32768] + [256] * 31)          # one long context among short ones
+    assert by_length([8000] + [500] * 7)
+    assert by_length([4352, 128] * 16)              # half long, half short, more pairs than SMs
+    assert not by_length([1024] * 8)                # equal lengths: the by-request launch is a trip to memory shorter
+    assert not by_length([2304] * 32)
+    assert not by_length([100, 2000, 700, 1500, 300, 900, 1200, 400])  # small differences do not pay for the set-up
+    assert not by_length([64 + 31 * i for i in range(64)])  # 512 pairs: the hardware's dispatch evens them out
+    # the switch overrides the estimate
+    assert CudaOps.decode_by_length(_ops(balanced="1"), [1024] * 8, 8)
+    assert not CudaOps.decode_by_length(_ops(balanced="0"), [32768] + [256] * 31, 8)
+
+
+def test_keys_of_a_query_tile_are_shared_when_tiles_are_few_and_contexts_long():
+    ops = _ops()
+    split = lambda blocks, hd, ctx: CudaOps.prefill_key_split(ops, blocks, hd, ctx)
+    assert split(128, 64, 4096) == 2      # 4 tiles x 32 heads on 296 block slots
+    assert split(96, 128, 4096) == 3      # head size 128: one block per SM, 148 slots
+    assert split(512, 64, 4096) == 1      # the tiles fill the device
+    assert split(200, 64, 4000) == 1      # two thirds full: sharing would not save a quarter
+    assert split(128, 64, 200) == 1       # too short a context to share
+    for blocks in (1, 8, 32, 64, 128):
+        for ctx in (256, 1024, 8192, 131072):
+            ks = split(blocks, 64, ctx)
+            assert 1 <= ks <= 16 and ks <= max(1, ctx // 256)

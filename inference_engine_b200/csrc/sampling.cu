@@ -26,12 +26,14 @@ __device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
     return c;
 }
 
-__device__ __forceinline__ float uniform_for(unsigned long long seed, unsigned long long draw, unsigned i) {
-    uint4 r = philox4x32_10(make_uint4(i >> 2, (unsigned)draw, (unsigned)(draw >> 32), 0u),
-                            make_uint2((unsigned)seed, (unsigned)(seed >> 32)));
-    unsigned x = (i & 3) == 0 ? r.x : (i & 3) == 1 ? r.y : (i & 3) == 2 ? r.z : r.w;
-    // 23 random bits plus a half: every value is exact in 32-bit and strictly inside (0, 1)
-    return ((float)(x >> 9) + 0.5f) * (1.0f / 8388608.0f);
+// Token i of a row takes word i % 4 of the generator's call i / 4 (counter: call, draw; key: seed).
+__device__ __forceinline__ uint4 random_words(unsigned long long seed, unsigned long long draw, unsigned call) {
+    return philox4x32_10(make_uint4(call, (unsigned)draw, (unsigned)(draw >> 32), 0u),
+                         make_uint2((unsigned)seed, (unsigned)(seed >> 32)));
+}
+// 23 random bits plus a half: every value is exact in 32-bit and strictly inside (0, 1)
+__device__ __forceinline__ float uniform_of(unsigned word) {
+    return ((float)(word >> 9) + 0.5f) * (1.0f / 8388608.0f);
 }
 
 struct Best { float v; int i; };
@@ -92,13 +94,28 @@ __device__ unsigned radix_threshold(const float* row, int vocab, float inv_temp,
         __syncthreads();
         unsigned shift = level * 8;
         unsigned mask_hi = level == 3 ? 0u : (0xffffffffu << (shift + 8));
+        // Neighbouring logits mostly fall into the same bucket (at the top level nearly all of a
+        // row share two or three): a thread adds up its run of equal buckets in a register and
+        // touches shared memory only when the bucket changes.  (One atomic per token made this
+        // loop twenty times slower: a hundred thousand adds to the same few words.)
+        int run_bucket = -1;
+        float run_sum = 0.f;
         for (int i = threadIdx.x; i < vocab; i += THREADS) {
             float z = scaled_logit(row, i, inv_temp, penalty, seen_bits);
             if (z < keep_min) continue;
             unsigned key = float_key(z);
             if ((key & mask_hi) != (prefix & mask_hi)) continue;
-            atomicAdd(&hist[(key >> shift) & 255u], mode == 0 ? 1.f : expf(z - zmax));
+            int bucket = (int)((key >> shift) & 255u);
+            float w = mode == 0 ? 1.f : expf(z - zmax);
+            if (bucket == run_bucket) {
+                run_sum += w;
+            } else {
+                if (run_bucket >= 0) atomicAdd(&hist[run_bucket], run_sum);
+                run_bucket = bucket;
+                run_sum = w;
+            }
         }
+        if (run_bucket >= 0) atomicAdd(&hist[run_bucket], run_sum);
         __syncthreads();
         // thread 0 walks the buckets from the top
         if (threadIdx.x == 0) {
@@ -179,11 +196,24 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
         unsigned long long seed = (unsigned long long)seeds[r];
         unsigned long long draw = (unsigned long long)draws[r];
         Best g{-INFINITY, 0x7fffffff};
-        for (int i = threadIdx.x; i < vocab; i += THREADS) {
-            float z = scaled_logit(row, i, inv_temp, pen, seen);
-            if (z < keep_min) continue;
-            float u = uniform_for(seed, draw, (unsigned)i);
-            g = better(g, Best{z - logf(-logf(u)), i});
+        // four tokens to a thread and turn: they share one call of the generator (token i takes
+        // word i % 4 of call i / 4), which is most of this loop's arithmetic
+        for (int i4 = threadIdx.x * 4; i4 < vocab; i4 += THREADS * 4) {
+            float z[4];
+            bool kept = false;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                z[j] = i4 + j < vocab ? scaled_logit(row, i4 + j, inv_temp, pen, seen) : -INFINITY;
+                kept = kept || (z[j] >= keep_min && z[j] > -INFINITY);
+            }
+            if (!kept) continue;
+            uint4 rnd = random_words(seed, draw, (unsigned)i4 >> 2);
+            unsigned words[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (i4 + j >= vocab || z[j] < keep_min) continue;
+                g = better(g, Best{z[j] - logf(-logf(uniform_of(words[j]))), i4 + j});
+            }
         }
         g = block_best(g, best_scratch);
         choice = g.i;

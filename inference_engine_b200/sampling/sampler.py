@@ -25,6 +25,7 @@ class Sampler:
         self._host = [None, None]     # pinned copies of the tokens
         self._events = [None, None]
         self._turn = 0
+        self._param_dev, self._param_cap, self._param_key, self._param_draws, self._param_turn = None, 0, None, [], 0
 
     def _out(self, rows: int):
         i = self._turn = 1 - self._turn
@@ -55,21 +56,8 @@ class Sampler:
         if all(p.greedy and p.repetition_penalty == 1.0 for p in params):
             self.ops.sample(logits, out, logprob=logprob)
         else:
-            dev = self.device
-            f32 = lambda vals: torch.tensor(vals, dtype=torch.float32, device=dev)  # noqa: E731
-            kwargs = dict(
-                temperature=f32([p.temperature for p in params]),
-                seeds=torch.tensor([s & 0x7FFFFFFFFFFFFFFF for s in seeds], dtype=torch.int64, device=dev),
-                draws=torch.tensor(list(draws), dtype=torch.int64, device=dev),
-            )
-            if any(p.top_k > 0 for p in params):
-                kwargs["top_k"] = torch.tensor([p.top_k for p in params], dtype=torch.int32, device=dev)
-            if any(p.top_p < 1.0 for p in params):
-                kwargs["top_p"] = f32([p.top_p for p in params])
-            if any(p.min_p > 0.0 for p in params):
-                kwargs["min_p"] = f32([p.min_p for p in params])
+            kwargs = self._row_parameters(params, seeds, draws)
             if any(p.repetition_penalty != 1.0 for p in params):
-                kwargs["penalty"] = f32([p.repetition_penalty for p in params])
                 kwargs["seen_bits"] = self._seen_bits(params, histories)
             self.ops.sample(logits, out, logprob=logprob, **kwargs)
         # the tokens start on their way to the host right behind the kernel
@@ -78,6 +66,67 @@ class Sampler:
         if self._events[turn] is not None:
             self._events[turn].record()
         return out, logprob, host, self._events[turn]
+
+    # The rows' parameters live in one device buffer.  They reach it as one copy from pinned
+    # memory (a copy from pageable memory would make the host wait for the stream, and with it
+    # for the step that is still running); while the same requests decode on, nothing but the
+    # draw counters changes, and those are advanced on the device.
+    RING = 4
+
+    def _row_parameters(self, params, seeds, draws) -> dict:
+        import numpy as np
+
+        torch = self.torch
+        rows = len(params)
+        settings = tuple((p.temperature, p.top_k, p.top_p, p.min_p, p.repetition_penalty) for p in params)
+        key = (settings, tuple(seeds))
+        cap = self._param_cap
+        if rows > cap or self._param_dev is None:
+            cap = self._param_cap = max(64, 2 * rows)
+            pinned = torch.device(self.device).type == "cuda"
+            self._param_dev = torch.zeros(9 * cap, dtype=torch.int32, device=self.device)
+            self._param_host = [torch.zeros(9 * cap, dtype=torch.int32, pin_memory=pinned) for _ in range(self.RING)]
+            self._param_events = [torch.cuda.Event() if pinned else None for _ in range(self.RING)]
+            self._param_used = [False] * self.RING
+            self._param_key = None
+        dev = self._param_dev
+        section = lambda i, width=1: dev[i * cap: (i + width) * cap]  # noqa: E731
+        views = {
+            "temperature": section(0).view(torch.float32)[:rows], "top_k": section(1)[:rows],
+            "top_p": section(2).view(torch.float32)[:rows], "min_p": section(3).view(torch.float32)[:rows],
+            "penalty": section(4).view(torch.float32)[:rows],
+            "seeds": section(5, 2).view(torch.int64)[:rows], "draws": section(7, 2).view(torch.int64)[:rows],
+        }
+        if key == self._param_key and list(draws) == [d + 1 for d in self._param_draws]:
+            views["draws"].add_(1)  # the same requests, one token further
+        else:
+            turn = self._param_turn = (self._param_turn + 1) % self.RING
+            if self._param_used[turn] and self._param_events[turn] is not None:
+                self._param_events[turn].synchronize()  # the copy that last read this buffer has run
+            host = self._param_host[turn].numpy()
+            host[0 * cap: 0 * cap + rows] = np.asarray([s[0] for s in settings], dtype=np.float32).view(np.int32)
+            host[1 * cap: 1 * cap + rows] = np.asarray([s[1] for s in settings], dtype=np.int32)
+            host[2 * cap: 2 * cap + rows] = np.asarray([s[2] for s in settings], dtype=np.float32).view(np.int32)
+            host[3 * cap: 3 * cap + rows] = np.asarray([s[3] for s in settings], dtype=np.float32).view(np.int32)
+            host[4 * cap: 4 * cap + rows] = np.asarray([s[4] for s in settings], dtype=np.float32).view(np.int32)
+            host[5 * cap: 5 * cap + 2 * rows] = np.asarray([s & 0x7FFFFFFFFFFFFFFF for s in seeds], dtype=np.int64).view(np.int32)
+            host[7 * cap: 7 * cap + 2 * rows] = np.asarray(list(draws), dtype=np.int64).view(np.int32)
+            dev.copy_(self._param_host[turn], non_blocking=True)
+            if self._param_events[turn] is not None:
+                self._param_events[turn].record()
+                self._param_used[turn] = True
+            self._param_key = key
+        self._param_draws = list(draws)
+        kwargs = {"temperature": views["temperature"], "seeds": views["seeds"], "draws": views["draws"]}
+        if any(s[1] > 0 for s in settings):
+            kwargs["top_k"] = views["top_k"]
+        if any(s[2] < 1.0 for s in settings):
+            kwargs["top_p"] = views["top_p"]
+        if any(s[3] > 0.0 for s in settings):
+            kwargs["min_p"] = views["min_p"]
+        if any(s[4] != 1.0 for s in settings):
+            kwargs["penalty"] = views["penalty"]
+        return kwargs
 
     def collect(self, pending):
         out, logprob, host, event = pending

@@ -81,6 +81,40 @@ __device__ __forceinline__ float scaled_logit(const float* row, int i, float inv
     return z * inv_temp;
 }
 
+// Calls f(z, i) for the penalised, temperature-scaled logit of every token i of the row that is
+// this thread's.  A block walks a row of a hundred thousand logits alone, so what counts is how
+// many loads a thread has in flight: 16-byte loads, two per turn, when the row allows them (width
+// a multiple of 4), single ones otherwise.
+template <typename F>
+__device__ __forceinline__ void for_each_scaled(const float* row, int vocab, float inv_temp, float penalty,
+                                                const unsigned* seen_bits, F&& f) {
+    auto scaled = [&](float z, int i) {
+        if (seen_bits && (seen_bits[i >> 5] >> (i & 31) & 1u)) z = z > 0.f ? z / penalty : z * penalty;
+        return z * inv_temp;
+    };
+    if ((vocab & 3) == 0 && (reinterpret_cast<size_t>(row) & 15) == 0) {
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        int n4 = vocab >> 2;
+        for (int j = threadIdx.x; j < n4; j += 2 * THREADS) {
+            int j2 = j + THREADS;
+            float4 a = row4[j];
+            float4 b = j2 < n4 ? row4[j2] : make_float4(0.f, 0.f, 0.f, 0.f);
+            f(scaled(a.x, 4 * j), 4 * j);
+            f(scaled(a.y, 4 * j + 1), 4 * j + 1);
+            f(scaled(a.z, 4 * j + 2), 4 * j + 2);
+            f(scaled(a.w, 4 * j + 3), 4 * j + 3);
+            if (j2 < n4) {
+                f(scaled(b.x, 4 * j2), 4 * j2);
+                f(scaled(b.y, 4 * j2 + 1), 4 * j2 + 1);
+                f(scaled(b.z, 4 * j2 + 2), 4 * j2 + 2);
+                f(scaled(b.w, 4 * j2 + 3), 4 * j2 + 3);
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < vocab; i += THREADS) f(scaled(row[i], i), i);
+    }
+}
+
 // The largest threshold t (as a key) such that stat({z >= t}) >= target, found by a radix
 // descent over the 32 key bits, 8 bits a level.  mode 0: stat = count (top-k);
 // mode 1: stat = sum of exp(z - zmax) (top-p, target = top_p * total mass).
@@ -100,11 +134,10 @@ __device__ unsigned radix_threshold(const float* row, int vocab, float inv_temp,
         // loop twenty times slower: a hundred thousand adds to the same few words.)
         int run_bucket = -1;
         float run_sum = 0.f;
-        for (int i = threadIdx.x; i < vocab; i += THREADS) {
-            float z = scaled_logit(row, i, inv_temp, penalty, seen_bits);
-            if (z < keep_min) continue;
+        for_each_scaled(row, vocab, inv_temp, penalty, seen_bits, [&](float z, int) {
+            if (z < keep_min) return;
             unsigned key = float_key(z);
-            if ((key & mask_hi) != (prefix & mask_hi)) continue;
+            if ((key & mask_hi) != (prefix & mask_hi)) return;
             int bucket = (int)((key >> shift) & 255u);
             float w = mode == 0 ? 1.f : expf(z - zmax);
             if (bucket == run_bucket) {
@@ -114,7 +147,7 @@ __device__ unsigned radix_threshold(const float* row, int vocab, float inv_temp,
                 run_bucket = bucket;
                 run_sum = w;
             }
-        }
+        });
         if (run_bucket >= 0) atomicAdd(&hist[run_bucket], run_sum);
         __syncthreads();
         // thread 0 walks the buckets from the top
@@ -157,10 +190,7 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
 
     // Pass 1: the maximum of the scaled logits (it is the greedy answer too).
     Best b{-INFINITY, 0x7fffffff};
-    for (int i = threadIdx.x; i < vocab; i += THREADS) {
-        float z = scaled_logit(row, i, inv_temp, pen, seen);
-        b = better(b, Best{z, i});
-    }
+    for_each_scaled(row, vocab, inv_temp, pen, seen, [&](float z, int i) { b = better(b, Best{z, i}); });
     b = block_best(b, best_scratch);
     float zmax = b.v;
     int choice = b.i;
@@ -177,10 +207,9 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
         }
         if (p < 1.f) {
             float mass = 0.f;
-            for (int i = threadIdx.x; i < vocab; i += THREADS) {
-                float z = scaled_logit(row, i, inv_temp, pen, seen);
+            for_each_scaled(row, vocab, inv_temp, pen, seen, [&](float z, int) {
                 if (z >= keep_min) mass += expf(z - zmax);
-            }
+            });
             mass = block_sum(mass, sum_scratch);
             // Keep the smallest set of top tokens whose mass reaches top_p
             // (engine/runtime/sampler.py:59-68, with its 1e-6 slack).
@@ -222,10 +251,10 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
         // log-probability of the chosen token under the model's own distribution, before
         // temperature and cut-offs (engine/runtime/engine.py:283-298).
         Best raw{-INFINITY, 0};
-        for (int i = threadIdx.x; i < vocab; i += THREADS) raw = better(raw, Best{row[i], i});
+        for_each_scaled(row, vocab, 1.f, 1.f, nullptr, [&](float z, int i) { raw = better(raw, Best{z, i}); });
         raw = block_best(raw, best_scratch);
         float s = 0.f;
-        for (int i = threadIdx.x; i < vocab; i += THREADS) s += expf(row[i] - raw.v);
+        for_each_scaled(row, vocab, 1.f, 1.f, nullptr, [&](float z, int) { s += expf(z - raw.v); });
         s = block_sum(s, sum_scratch);
         if (threadIdx.x == 0) out_logprob[r] = row[choice] - raw.v - logf(s);
     }

@@ -13,7 +13,7 @@
 #include <math.h>
 
 namespace {
-constexpr int THREADS = 512;
+constexpr int THREADS = 1024;
 
 __device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
 #pragma unroll
@@ -120,11 +120,14 @@ __device__ __forceinline__ void for_each_scaled(const float* row, int vocab, flo
 // mode 1: stat = sum of exp(z - zmax) (top-p, target = top_p * total mass).
 __device__ unsigned radix_threshold(const float* row, int vocab, float inv_temp, float penalty,
                                     const unsigned* seen_bits, float keep_min, int mode, float target,
-                                    float zmax, float* hist /*[256]*/, float* scratch) {
+                                    float zmax, float* hist /*[THREADS / 32][256]*/, float* scratch) {
     unsigned prefix = 0;
     float above = 0.f;  // stat of everything strictly above the current bucket range
     for (int level = 3; level >= 0; --level) {
-        for (int b = threadIdx.x; b < 256; b += THREADS) hist[b] = 0.f;
+        // a histogram per warp: the tokens of a row crowd into a few dozen buckets, and with one
+        // histogram for the block its adds queued up behind each other (200 us a level)
+        for (int b = threadIdx.x; b < (THREADS / 32) * 256; b += THREADS) hist[b] = 0.f;
+        float* mine = hist + (threadIdx.x >> 5) * 256;
         __syncthreads();
         unsigned shift = level * 8;
         unsigned mask_hi = level == 3 ? 0u : (0xffffffffu << (shift + 8));
@@ -143,12 +146,18 @@ __device__ unsigned radix_threshold(const float* row, int vocab, float inv_temp,
             if (bucket == run_bucket) {
                 run_sum += w;
             } else {
-                if (run_bucket >= 0) atomicAdd(&hist[run_bucket], run_sum);
+                if (run_bucket >= 0) atomicAdd(&mine[run_bucket], run_sum);
                 run_bucket = bucket;
                 run_sum = w;
             }
         });
-        if (run_bucket >= 0) atomicAdd(&hist[run_bucket], run_sum);
+        if (run_bucket >= 0) atomicAdd(&mine[run_bucket], run_sum);
+        __syncthreads();
+        if (threadIdx.x < 256) {  // the warps' histograms summed (in warp order) into the first
+            float total = 0.f;
+            for (int w = 0; w < THREADS / 32; ++w) total += hist[w * 256 + threadIdx.x];
+            hist[threadIdx.x] = total;
+        }
         __syncthreads();
         // thread 0 walks the buckets from the top
         if (threadIdx.x == 0) {
@@ -178,7 +187,7 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
               int* __restrict__ out_tokens, float* __restrict__ out_logprob) {
     __shared__ Best best_scratch[THREADS / 32];
     __shared__ float sum_scratch[THREADS / 32];
-    __shared__ float hist[256];
+    __shared__ float hist[(THREADS / 32) * 256];
     __shared__ float small[2];
     int r = blockIdx.x;
     const float* row = logits + (size_t)r * vocab;

@@ -214,7 +214,8 @@ class LLMEngine:
                 needs_history = any(p.repetition_penalty != 1.0 for p in params)
                 pending = self.sampler.launch(
                     logits, params, [s.seed for s in sampled], [len(s.output_ids) for s in sampled],
-                    [s.all_ids for s in sampled] if needs_history else None)
+                    [s.all_ids for s in sampled] if needs_history else None,
+                    history_keys=[s.seq_id for s in sampled] if needs_history else None)
             if used_graph and len(sampled) == len(seqs):
                 # while the device is busy: start the next step on the tokens it is sampling,
                 # or at least pack that step's index data

@@ -26,6 +26,8 @@ class Sampler:
         self._events = [None, None]
         self._turn = 0
         self._param_dev, self._param_cap, self._param_key, self._param_draws, self._param_turn = None, 0, None, [], 0
+        self._bits_host, self._bits_dev, self._bits_turn = None, None, 0
+        self._masks: dict = {}  # request key -> (ids of its history already in the mask, the mask)
 
     def _out(self, rows: int):
         i = self._turn = 1 - self._turn
@@ -39,15 +41,17 @@ class Sampler:
         return i, self._tokens[i][:rows]
 
     def sample(self, logits, params: Seq[Any], seeds: Seq[int], draws: Seq[int],
-               histories: Seq[Seq[int]] | None = None):
+               histories: Seq[Seq[int]] | None = None, history_keys: Seq[Any] | None = None):
         """``logits``: 32-bit ``[R, vocab]``.  ``params[r]``: the row's SamplingParams,
         ``seeds[r]``/``draws[r]``: its request's seed and the number of tokens it has already
         produced; ``histories[r]``: the ids the repetition penalty looks at.
         Returns ``(tokens, logprobs)``: a list of ints and a list of floats or None."""
-        return self.collect(self.launch(logits, params, seeds, draws, histories))
+        return self.collect(self.launch(logits, params, seeds, draws, histories, history_keys))
 
-    def launch(self, logits, params, seeds, draws, histories=None):
-        """Start the sampling kernel; :meth:`collect` waits for it and fetches the tokens."""
+    def launch(self, logits, params, seeds, draws, histories=None, history_keys=None):
+        """Start the sampling kernel; :meth:`collect` waits for it and fetches the tokens.
+        ``history_keys[r]`` (optional): something that names row r's request from step to step,
+        so that its history's bit mask is extended by the new ids instead of built again."""
         torch = self.torch
         rows = logits.shape[0]
         turn, out = self._out(rows)
@@ -58,7 +62,7 @@ class Sampler:
         else:
             kwargs = self._row_parameters(params, seeds, draws)
             if any(p.repetition_penalty != 1.0 for p in params):
-                kwargs["seen_bits"] = self._seen_bits(params, histories)
+                kwargs["seen_bits"] = self._seen_bits(params, histories, history_keys)
             self.ops.sample(logits, out, logprob=logprob, **kwargs)
         # the tokens start on their way to the host right behind the kernel
         host = self._host[turn][:rows]
@@ -135,18 +139,48 @@ class Sampler:
         tokens = host.tolist()
         return tokens, (logprob.tolist() if logprob is not None else None)
 
-    def _seen_bits(self, params, histories):
-        """One bit per vocabulary entry and row: set where the id occurs in the row's history."""
+    def _seen_bits(self, params, histories, keys=None):
+        """One bit per vocabulary entry and row: set where the id occurs in the row's history.
+        A history only grows (and its request's key stays), so a row's mask from the last step
+        is extended by the ids that are new; the masks go to the device as one copy from pinned
+        memory."""
         import numpy as np
 
-        words = (self.vocab_size + 31) // 32
-        bits = np.zeros((len(params), words), dtype=np.uint32)
+        torch = self.torch
+        rows, words = len(params), (self.vocab_size + 31) // 32
+        if self._bits_host is None or self._bits_host[0].shape[0] < rows:
+            cap = max(8, 2 * rows)
+            pinned = torch.device(self.device).type == "cuda"
+            self._bits_host = [torch.zeros(cap, words, dtype=torch.int32, pin_memory=pinned) for _ in range(self.RING)]
+            self._bits_events = [torch.cuda.Event() if pinned else None for _ in range(self.RING)]
+            self._bits_used = [False] * self.RING
+            self._bits_dev = torch.zeros(cap, words, dtype=torch.int32, device=self.device)
+        turn = self._bits_turn = (self._bits_turn + 1) % self.RING
+        if self._bits_used[turn] and self._bits_events[turn] is not None:
+            self._bits_events[turn].synchronize()
+        host = self._bits_host[turn].numpy().view(np.uint32)
+        if len(self._masks) > 4096:  # requests long gone
+            self._masks.clear()
         for r, (p, hist) in enumerate(zip(params, histories or [])):
             if p.repetition_penalty == 1.0 or not hist:
+                host[r] = 0
                 continue
-            ids = np.unique(np.asarray(hist, dtype=np.int64))
-            np.bitwise_or.at(bits[r], ids >> 5, (np.uint32(1) << (ids & 31).astype(np.uint32)))
-        return self.torch.from_numpy(bits.view(np.int32)).to(self.device)
+            key = keys[r] if keys is not None else None
+            known, mask = self._masks.get(key, (0, None)) if key is not None else (0, None)
+            if mask is None or known > len(hist):
+                known, mask = 0, np.zeros(words, dtype=np.uint32)
+            ids = np.asarray(hist[known:], dtype=np.int64)
+            if ids.size:
+                np.bitwise_or.at(mask, ids >> 5, (np.uint32(1) << (ids & 31).astype(np.uint32)))
+            if key is not None:
+                self._masks[key] = (len(hist), mask)
+            host[r] = mask
+        dev = self._bits_dev[:rows]
+        dev.copy_(self._bits_host[turn][:rows], non_blocking=True)
+        if self._bits_events[turn] is not None:
+            self._bits_events[turn].record()
+            self._bits_used[turn] = True
+        return dev
 
     def top_logprobs(self, logits_row, k: int) -> list[tuple[int, float]]:
         """The ``k`` most likely alternatives of one row with their log-probabilities

@@ -56,3 +56,40 @@ def test_keys_of_a_query_tile_are_shared_when_tiles_are_few_and_contexts_long():
         for ctx in (256, 1024, 8192, 131072):
             ks = split(blocks, 64, ctx)
             assert 1 <= ks <= 16 and ks <= max(1, ctx // 256)
+
+
+def test_the_history_masks_of_the_repetition_penalty_grow_with_the_histories():
+    """The sampler keeps every request's bit mask from step to step (by the request's key) and adds
+    only the ids that are new; the result is the mask built from the whole history."""
+    import numpy as np
+    import torch
+
+    from inference_engine_b200.sampling.params import SamplingParams
+    from inference_engine_b200.sampling.sampler import Sampler
+
+    vocab = 1000
+    sampler = Sampler(ops=None, device="cpu", vocab_size=vocab)
+    rng = np.random.default_rng(0)
+    params = [SamplingParams(temperature=0.7, repetition_penalty=1.2), SamplingParams(temperature=0.7),
+              SamplingParams(temperature=0.7, repetition_penalty=1.1)]
+    histories = [list(rng.integers(0, vocab, 40)), list(rng.integers(0, vocab, 5)), list(rng.integers(0, vocab, 300))]
+
+    def expected(hists):
+        bits = np.zeros((len(hists), (vocab + 31) // 32), dtype=np.uint32)
+        for r, (p, h) in enumerate(zip(params, hists)):
+            if p.repetition_penalty != 1.0:
+                for t in h:
+                    bits[r, t >> 5] |= np.uint32(1) << np.uint32(t & 31)
+        return bits
+
+    for step in range(6):
+        got = sampler._seen_bits(params, histories, keys=["a", "b", "c"]).numpy().view(np.uint32)
+        assert (got == expected(histories)).all()
+        histories = [h + [int(rng.integers(0, vocab))] for h in histories]
+    # another request under a known key (a shorter history): its mask starts again
+    histories[0] = [3, 4]
+    got = sampler._seen_bits(params, histories, keys=["a", "b", "c"]).numpy().view(np.uint32)
+    assert (got == expected(histories)).all()
+    # without keys every mask is built from the whole history
+    got = sampler._seen_bits(params, histories).numpy().view(np.uint32)
+    assert (got == expected(histories)).all()

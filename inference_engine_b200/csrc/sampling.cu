@@ -197,18 +197,24 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
     bool greedy = !(temp > 0.f);
     float inv_temp = greedy ? 1.f : 1.f / temp;
 
-    // Pass 1: the maximum of the scaled logits (it is the greedy answer too).
-    Best b{-INFINITY, 0x7fffffff};
-    for_each_scaled(row, vocab, inv_temp, pen, seen, [&](float z, int i) { b = better(b, Best{z, i}); });
-    b = block_best(b, best_scratch);
-    float zmax = b.v;
-    int choice = b.i;
+    int k = (!greedy && top_k) ? top_k[r] : 0;
+    float p = (!greedy && top_p) ? top_p[r] : 1.f;
+    float mp = (!greedy && min_p) ? min_p[r] : 0.f;
+
+    // Pass 1: the maximum of the scaled logits: the greedy answer, and what the cut-offs are
+    // taken against.  A row that is drawn from all tokens needs neither.
+    float zmax = 0.f;
+    int choice = 0;
+    if (greedy || (k > 0 && k < vocab) || p < 1.f || mp > 0.f) {
+        Best b{-INFINITY, 0x7fffffff};
+        for_each_scaled(row, vocab, inv_temp, pen, seen, [&](float z, int i) { b = better(b, Best{z, i}); });
+        b = block_best(b, best_scratch);
+        zmax = b.v;
+        choice = b.i;
+    }
     float keep_min = -INFINITY;  // tokens with a scaled logit below this are cut off
 
     if (!greedy) {
-        int k = top_k ? top_k[r] : 0;
-        float p = top_p ? top_p[r] : 1.f;
-        float mp = min_p ? min_p[r] : 0.f;
         if (k > 0 && k < vocab) {
             unsigned key = radix_threshold(row, vocab, inv_temp, pen, seen, keep_min, 0, (float)k,
                                            zmax, hist, small);

@@ -5,7 +5,7 @@
     tokens = engine.generate({"a": [1, 2, 3]}, SamplingParams(temperature=0, max_tokens=16))
 """
 
-from .config import EngineConfig, LlamaConfig, load_config, register_architecture
+from .config import EngineConfig, load_config, register_architecture
 from .sampling.params import SamplingParams
 
 __version__ = "0.1.0"
@@ -28,5 +28,5 @@ def __getattr__(name: str):
     raise AttributeError(name)
 
 
-__all__ = ["EngineConfig", "LLMEngine", "LlamaConfig", "SamplingParams", "generate",
+__all__ = ["EngineConfig", "LLMEngine", "SamplingParams", "generate",
            "load_config", "load_model", "random_model", "register_architecture"]

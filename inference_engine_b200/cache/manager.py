@@ -133,6 +133,26 @@ class CacheManager:
             needed.append(n)
         return needed
 
+    def missing_pages(self, req_id, num_computed: int, num_tokens: int) -> list[int] | None:
+        """``pages_needed``, but None when no group needs a page: the usual case of a decoding
+        request with room in its last page costs a few comparisons."""
+        tables = self._requests[req_id].tables
+        if not self._has_window:
+            last_page = -(-num_tokens // self.page_size)
+            if all(len(t) >= last_page for t in tables):
+                return None
+        need = self.pages_needed(req_id, num_computed, num_tokens)
+        return need if any(need) else None
+
+    def pages_for_new_request(self, num_tokens: int) -> list[int]:
+        """Pages per group that a request not yet registered needs for its first
+        ``num_tokens`` positions."""
+        return [-(-num_tokens // self.page_size)] * len(self.paged_groups)
+
+    def pages_held(self, req_id) -> list[int]:
+        """Pages per group the request holds now (what it gives back when it is freed)."""
+        return [sum(1 for page in t if page >= 0) for t in self._requests[req_id].tables]
+
     def can_grow(self, req_id, num_computed: int, num_tokens: int) -> bool:
         need = self.pages_needed(req_id, num_computed, num_tokens)
         return all(n <= pool.num_free for n, pool in zip(need, self.pools))
@@ -182,7 +202,9 @@ class CacheManager:
         ``num_computed - window + 1`` in windowed groups.  Returns how many were freed."""
         if not self._has_window:
             return 0
-        req = self._requests[req_id]
+        req = self._requests.get(req_id)
+        if req is None:  # it ended meanwhile (a step launched before its last token was seen)
+            return 0
         freed = 0
         for g, table in enumerate(req.tables):
             first = min(self._first_needed_page(g, num_computed), len(table))

@@ -29,6 +29,30 @@ class PagedStorage:
         return self.num_pages
 
 
+HEADROOM_BYTES = 512 * 2**20  # left free beside the cache for activations and libraries' workspaces
+
+
+def pages_that_fit(paged_groups, page_size: int, dtype_bytes: int, device, utilization: float) -> int:
+    """How many pages per cache group the device has room for.  The engine may fill the
+    fraction ``utilization`` of the device; what is taken already (weights, other processes)
+    counts against that, and ``HEADROOM_BYTES`` stay free.  Every group gets the same number
+    of pages, so a page costs the sum over the groups (the reference sizes its one pool the
+    same way, engine/runtime/engine.py:130-140)."""
+    import torch
+
+    if not str(device).startswith("cuda"):
+        raise ValueError("pass num_blocks explicitly when not running on CUDA")
+    free_now, capacity = torch.cuda.mem_get_info(device)
+    taken = capacity - free_now
+    room = utilization * capacity - taken - HEADROOM_BYTES
+    page_bytes = sum(g.bytes_per_page(page_size, dtype_bytes) for g in paged_groups)
+    pages = int(room // page_bytes) if page_bytes else 1
+    if pages < 1:
+        raise RuntimeError(f"no GPU memory left for the KV cache ({free_now / 2**30:.1f} GiB free of "
+                           f"{capacity / 2**30:.1f}, gpu_memory_utilization {utilization})")
+    return pages
+
+
 class CacheStorage:
     def __init__(self, manager: CacheManager, dtype, device) -> None:
         import torch

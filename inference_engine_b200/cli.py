@@ -20,25 +20,39 @@ GIB = 2**30
 
 
 def cmd_info(args: argparse.Namespace) -> int:
-    """Model shape and whether it fits a GPU of --gpu-mem GiB.  Needs no torch."""
-    from .config import estimate_param_count, get_architecture, load_config, max_kv_tokens
+    """Model shape and whether it fits a GPU of --gpu-mem GiB.  What is printed comes from the
+    architecture's registry entry; an architecture that registered no footprint is built
+    (without weights) and counted."""
+    from .config import build_model_spec, get_architecture, load_config
 
     cfg = load_config(args.model)
     arch = get_architecture(cfg.architecture)
     for line in (arch.describe(cfg) if arch.describe else [f"architecture        {cfg.architecture}"]):
         print(line)
-    params = estimate_param_count(cfg)
+    if arch.footprint is not None:
+        footprint = arch.footprint(cfg)
+    else:
+        from .engine.model import Model
+
+        footprint = Model(build_model_spec(cfg), "bfloat16", max_positions=1).footprint()
+        print(f"parameters          {footprint.parameters / 1e9:.3f} B")
+        print(f"cache per token     {footprint.cache_bytes_per_token(2) / 1024:.1f} KiB (bf16)")
+    if footprint.state_values_per_request:
+        print(f"state per request   {footprint.state_values_per_request * 4 / 1024:.1f} KiB (fp32)")
     print(f"\nOn a {args.gpu_mem:g} GiB GPU (1 GiB reserved for activations and CUDA context):")
     for label, bytes_per_param in (("bf16", 2.0), ("fp32", 4.0)):
-        tokens = max_kv_tokens(cfg, args.gpu_mem, bytes_per_param)
+        tokens = footprint.cache_tokens_that_fit(args.gpu_mem, bytes_per_param,
+                                                 cache_dtype_bytes=int(bytes_per_param))
         verdict = f"{tokens:>11,} KV tokens fit" if tokens else "        does not fit"
-        print(f"  {label}  weights {params * bytes_per_param / GIB:6.1f} GiB  ->{verdict}")
+        print(f"  {label}  weights {footprint.parameters * bytes_per_param / GIB:6.1f} GiB  ->{verdict}")
     return 0
 
 
-def _engine_kwargs(args: argparse.Namespace) -> dict:
-    return dict(
-        num_blocks=args.num_blocks, block_size=args.block_size, max_num_seqs=args.max_num_seqs,
+def _engine_config(args: argparse.Namespace):
+    from .config import EngineConfig
+
+    return EngineConfig(
+        dtype=args.dtype, num_blocks=args.num_blocks, block_size=args.block_size, max_num_seqs=args.max_num_seqs,
         max_num_batched_tokens=args.max_num_batched_tokens,
         gpu_memory_utilization=args.gpu_memory_utilization,
         enable_chunked_prefill=not args.no_chunked_prefill,
@@ -54,8 +68,8 @@ def cmd_generate(args: argparse.Namespace) -> int:
     tokenizer = None
     if args.random_config:
         with open(args.random_config, encoding="utf-8") as f:
-            engine = LLMEngine.from_random(json.load(f), args.seed or 0, args.dtype, args.device,
-                                           **_engine_kwargs(args))
+            engine = LLMEngine.from_random(json.load(f), args.seed or 0, device=args.device,
+                                           config=_engine_config(args))
     else:
         if args.model is None:
             raise SystemExit("engine generate: --model or --random-config is required")
@@ -63,8 +77,12 @@ def cmd_generate(args: argparse.Namespace) -> int:
             from transformers import AutoTokenizer  # tokenizer only; the model code is ours
 
             tokenizer = AutoTokenizer.from_pretrained(args.model)
-        engine = LLMEngine.from_model_dir(args.model, args.dtype, args.device, tokenizer=tokenizer,
-                                          **_engine_kwargs(args))
+        engine = LLMEngine.from_model_dir(args.model, device=args.device, tokenizer=tokenizer,
+                                          config=_engine_config(args))
+    print(f"[engine] {engine.dtype}, max_model_len {engine.max_model_len}, "
+          f"{engine.cache.pools[0].num_pages if engine.cache.pools else 0} cache pages of "
+          f"{engine.cache.page_size} tokens, captured decode steps {'on' if engine.graphs else 'off'}",
+          file=sys.stderr)
     if args.prompt is not None and tokenizer is not None:
         messages = [{"role": "user", "content": args.prompt}]
         if getattr(tokenizer, "chat_template", None):
@@ -100,15 +118,11 @@ def cmd_generate(args: argparse.Namespace) -> int:
 
 
 def cmd_replay(args: argparse.Namespace) -> int:
-    """The trace replay program (same as ``bin/trace_run``)."""
-    import os
-    import runpy
+    """The trace replay program (what ``bin/trace_run`` runs)."""
+    from .engine.replay import main as replay_main
 
-    script = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bin", "trace_run")
-    sys.argv = [script, "--model", args.model, "--dtype", args.dtype, "--out", args.out,
-                "--max-tokens", str(args.max_tokens), "--block-size", str(args.block_size)]
-    runpy.run_path(script, run_name="__main__")
-    return 0
+    return replay_main(["--model", args.model, "--dtype", args.dtype, "--out", args.out,
+                        "--max-tokens", str(args.max_tokens), "--block-size", str(args.block_size)])
 
 
 def build_parser() -> argparse.ArgumentParser:

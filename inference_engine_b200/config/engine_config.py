@@ -16,7 +16,7 @@ class EngineConfig:
     gpu_memory_utilization: float = 0.9
     enable_chunked_prefill: bool = True
     max_model_len: int | None = None
-    enable_cuda_graphs: bool = True
+    enable_cuda_graphs: bool | None = None  # None: where they can be captured (a GPU, no state slots)
     debug_checks: bool = False
 
     def __post_init__(self) -> None:
@@ -32,3 +32,5 @@ class EngineConfig:
             raise ValueError("max_num_batched_tokens must be >= max_num_seqs (one per decode)")
         if not 0.0 < self.gpu_memory_utilization <= 1.0:
             raise ValueError("gpu_memory_utilization must be in (0, 1]")
+        if self.max_model_len is not None and self.max_model_len < 1:
+            raise ValueError("max_model_len must be >= 1")

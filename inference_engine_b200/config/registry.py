@@ -13,7 +13,7 @@ from dataclasses import dataclass
 from pathlib import Path
 from typing import Any, Callable
 
-from .model_config import ConfigError, architecture_name, read_config_dict
+from .model_config import ConfigError, Footprint, architecture_name, read_config_dict
 from .spec import ModelSpec
 
 
@@ -22,8 +22,8 @@ class Architecture:
     name: str
     config_class: type  # has ``from_dict(raw) -> config``
     build_spec: Callable[[Any], ModelSpec]
-    # random_init(config) -> {"default_std": float, ...}; how seeded random weights are drawn
-    describe: Callable[[Any], list[str]] | None = None
+    describe: Callable[[Any], list[str]] | None = None  # the lines `engine info` prints about the shape
+    footprint: Callable[[Any], Footprint] | None = None  # parameters and cache per token, without building the model
 
 
 _ARCHITECTURES: dict[str, Architecture] = {}
@@ -34,11 +34,12 @@ def register_architecture(
     config_class: type,
     build_spec: Callable[[Any], ModelSpec],
     describe: Callable[[Any], list[str]] | None = None,
+    footprint: Callable[[Any], Footprint] | None = None,
     replace: bool = False,
 ) -> None:
     if name in _ARCHITECTURES and not replace:
         raise ValueError(f"architecture {name!r} is already registered")
-    _ARCHITECTURES[name] = Architecture(name, config_class, build_spec, describe)
+    _ARCHITECTURES[name] = Architecture(name, config_class, build_spec, describe, footprint)
 
 
 def _load_builtin() -> None:

@@ -1176,13 +1176,9 @@ int launch_decode_as(const void* q, const void* k_cache, const void* v_cache, co
                      const int* cu_q, const int* ctx_lens, void* out, float* part_o, float* part_ml, int* tickets,
                      int num_seqs, int nh, int nkv, int page_shift, int total_pages, float scale, int window,
                      int num_splits, int* err, cudaStream_t s) {
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<NWARPS>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(NWARPS));
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static IePerDevice configured;
+    cudaError_t e = ie_allow_smem(configured, attention_decode_kernel<NWARPS>, decode_smem(NWARPS));
+    if (e != cudaSuccess) return (int)e;
     dim3 grid(num_seqs, nkv, num_splits);
     return ie_launch(attention_decode_kernel<NWARPS>, grid, dim3(NWARPS * 32), decode_smem(NWARPS), s,
                      (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, tables, table_width, cu_q,
@@ -1197,13 +1193,7 @@ int launch_decode(const void* q, const void* k_cache, const void* v_cache, const
                   const int* cu_q, const int* ctx_lens, void* out, float* part_o, float* part_ml, int* tickets,
                   int num_seqs, int nh, int nkv, int page_shift, int total_pages, float scale, int window,
                   int num_splits, int* err, cudaStream_t s) {
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-            sms = 148;
-    }
+    int sms = ie_sm_count();
     long long blocks = (long long)num_seqs * nkv * num_splits;
     if (blocks > sms)
         return launch_decode_as<DWARPS_SHARED>(q, k_cache, v_cache, tables, table_width, cu_q, ctx_lens, out, part_o,
@@ -1240,13 +1230,7 @@ IE_API int ie_attention_decode(const void* q, const void* k_cache, const void* v
 namespace {
 // Blocks of a balanced launch: what the device runs at once (blocks of four warps, two to an SM,
 // when there are more pairs than SMs), no more than `max_blocks_per_pair` times the pairs.
-int balanced_sms() {
-    int sms = 148, dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess ||
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-        sms = 148;
-    return sms;
-}
+int balanced_sms() { return ie_sm_count(); }
 long long balanced_blocks(long long pairs, int max_blocks_per_pair) {
     int sms = balanced_sms();
     long long slots = pairs > sms ? 2LL * sms : sms;
@@ -1259,13 +1243,9 @@ int launch_balanced_as(const void* q, const void* k_cache, const void* v_cache, 
                        const int* cu_q, const int* ctx_lens, void* out, float* part_o, float* part_ml, int* tickets,
                        int num_seqs, int nh, int nkv, int page_shift, int total_pages, float scale, int window,
                        int blocks, int* err, cudaStream_t s) {
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_balanced_kernel<NWARPS>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(NWARPS));
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static IePerDevice configured;
+    cudaError_t e = ie_allow_smem(configured, attention_decode_balanced_kernel<NWARPS>, decode_smem(NWARPS));
+    if (e != cudaSuccess) return (int)e;
     return ie_launch(attention_decode_balanced_kernel<NWARPS>, dim3(blocks), dim3(NWARPS * 32), decode_smem(NWARPS), s,
                      (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, tables, table_width, cu_q, ctx_lens,
                      (bf16*)out, part_o, part_ml, tickets, num_seqs, nh, nkv, page_shift, total_pages,
@@ -1325,13 +1305,9 @@ IE_API int ie_attention_prefill(const void* q, const void* k_cache, const void* 
     if (nkv <= 0 || nh % nkv != 0 || (page_size & (page_size - 1)) != 0) return (int)cudaErrorInvalidValue;
     int page_shift = 0;
     while ((1 << page_shift) < page_size) ++page_shift;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PREFILL_SMEM);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static IePerDevice configured;
+    cudaError_t e = ie_allow_smem(configured, attention_prefill_kernel, PREFILL_SMEM);
+    if (e != cudaSuccess) return (int)e;
     dim3 grid(max_tiles, nh);
     return ie_launch(attention_prefill_kernel, grid, dim3(WARPS * 32), PREFILL_SMEM, (cudaStream_t)stream,
                      (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, tables, table_width, cu_q,

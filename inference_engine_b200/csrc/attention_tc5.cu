@@ -608,16 +608,10 @@ IE_API int ie_attention_prefill_tc5(const void* q, const void* k_cache, const vo
     if (!make_map_bf16(&km, k_cache, kv_rows, HD, page_size) ||
         !make_map_bf16(&vm, v_cache, kv_rows, HD, page_size))
         return (int)cudaErrorNotSupported;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc5_kernel<false>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(attention_prefill_tc5_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)SMEM_BYTES);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static IePerDevice configured_whole, configured_shared;
+    cudaError_t e = ie_allow_smem(configured_whole, attention_prefill_tc5_kernel<false>, SMEM_BYTES);
+    if (e == cudaSuccess) e = ie_allow_smem(configured_shared, attention_prefill_tc5_kernel<true>, SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)max_items * nh * ksplit * BM * HD : nullptr;
     float scale_log2 = scale * 1.4426950408889634f;

@@ -66,6 +66,36 @@ inline int& ie_pdl_enabled() {
     return enabled;
 }
 
+// What is set on a kernel function (its dynamic shared memory limit) or asked of a device (its SM
+// count) holds for the device that was current at the time, so "done already" is kept per device.
+constexpr int IE_MAX_DEVICES = 64;
+struct IePerDevice {
+    bool done[IE_MAX_DEVICES] = {};
+};
+
+template <typename Kernel>
+inline cudaError_t ie_allow_smem(IePerDevice& state, Kernel kernel, size_t bytes) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    bool known = dev >= 0 && dev < IE_MAX_DEVICES;
+    if (known && state.done[dev]) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e == cudaSuccess && known) state.done[dev] = true;
+    return e;
+}
+
+// SMs of the current device (148 if the runtime cannot say).
+inline int ie_sm_count() {
+    static int sms[IE_MAX_DEVICES] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= IE_MAX_DEVICES) return 148;
+    if (sms[dev] == 0 &&
+        (cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms[dev] <= 0))
+        sms[dev] = 148;
+    return sms[dev];
+}
+
 template <typename... KArgs, typename... Args>
 inline int ie_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                      Args... args) {

@@ -213,8 +213,10 @@ IE_API int ie_rmsnorm(float* h, const float* delta, int num_partials, long long 
 //          = x[d] cos[d - rd/2] + x[d - rd/2] sin[d - rd/2]   for rd/2 <= d < rd
 //          = x[d]                                        for d >= rd  (and all of v)
 // ---------------------------------------------------------------------------------------------
+// `qkv` may be the sum of `num_partials` arrays, added in order (see the vector kernel below).
 template <typename T>
-__global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const int* __restrict__ positions,
+__global__ void rope_kv_write_kernel(const float* __restrict__ qkv, int num_partials, size_t partial_stride,
+                                     const int* __restrict__ positions,
                                      const float* __restrict__ table, int rotary_dim, int table_rows,
                                      T* __restrict__ q_out, T* __restrict__ k_cache,
                                      T* __restrict__ v_cache, const int* __restrict__ slot_mapping,
@@ -240,12 +242,17 @@ __global__ void rope_kv_write_kernel(const float* __restrict__ qkv, const int* _
         write_kv = false;
     }
     int limit = write_kv ? heads * hd : nh * hd;
+    auto value = [&](int e) {
+        float sum = x[e];
+        for (int p = 1; p < num_partials; ++p) sum += x[(size_t)p * partial_stride + e];
+        return sum;
+    };
     for (int e = threadIdx.x; e < limit; e += blockDim.x) {
         int head = e / hd, d = e - head * hd;
-        float v = x[e];
+        float v = value(e);
         if (rotate && head < nh + nkv && d < rotary_dim) {
-            if (d < half) v = v * cs[d] - x[e + half] * cs[half + d];
-            else          v = v * cs[d - half] + x[e - half] * cs[d];
+            if (d < half) v = v * cs[d] - value(e + half) * cs[half + d];
+            else          v = v * cs[d - half] + value(e - half) * cs[d];
         }
         if (head < nh) {
             ie_store(q_out + (size_t)n * nh * hd + e, v);
@@ -350,9 +357,9 @@ static int launch_rope(const float* qkv, int num_partials, size_t partial_stride
                          positions, rotates ? table : (const float*)nullptr, table_rows, q_out, k_cache, v_cache,
                          slot_mapping, nh, nkv, hd, page_size, total_pages, err);
     } else {
-        if (num_partials != 1) return (int)cudaErrorInvalidValue;
         int threads = (nh + 2 * nkv) * hd >= 1024 ? 256 : 128;
-        return ie_launch(rope_kv_write_kernel<T>, dim3(num_tokens), dim3(threads), 0, s, qkv, positions, table,
+        return ie_launch(rope_kv_write_kernel<T>, dim3(num_tokens), dim3(threads), 0, s, qkv, num_partials,
+                         partial_stride, positions, table,
                          rotary_dim, table_rows, q_out, k_cache, v_cache, slot_mapping, nh, nkv, hd, page_size,
                          total_pages, err);
     }

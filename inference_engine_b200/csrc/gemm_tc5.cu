@@ -173,13 +173,9 @@ int launch(const void* X, const void* W, OutT* out, const Tc5Plan& p, int splits
     CUtensorMap wm, xm;
     if (!make_map_bf16_3d(&wm, W, p.N, p.K, BN, p.kpo) || !make_map_bf16_3d(&xm, X, p.M, p.K, p.m_pad, p.kpo))
         return (int)cudaErrorNotSupported;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc5_kernel<OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)SMEM_BYTES);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static IePerDevice configured;
+    cudaError_t e = ie_allow_smem(configured, gemm_tc5_kernel<OutT>, SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
     dim3 grid((p.N + BN - 1) / BN, splits);
     return ie_launch(gemm_tc5_kernel<OutT>, grid, dim3(THREADS), SMEM_BYTES, s, wm, xm, out, p, err);
 }

@@ -199,13 +199,9 @@ int launch(const void* X, const void* W, OutT* out, int M, int N, int K, int kbl
     int ops = ring_bytes(NT) / (kpo * STAGE_BYTES);
     if (ops > MAX_OPS) ops = MAX_OPS;
     size_t smem = (size_t)ring_bytes(NT) + (size_t)MAX_KBLOCKS * 8 * NT * BK * 2 + (2 * MAX_OPS + 1) * 8 + 1024;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tma_kernel<NT, OutT>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static IePerDevice configured;
+    cudaError_t e = ie_allow_smem(configured, gemm_tma_kernel<NT, OutT>, smem);
+    if (e != cudaSuccess) return (int)e;
     dim3 grid((N + BN - 1) / BN, splits);
     return ie_launch(gemm_tma_kernel<NT, OutT>, grid, dim3(THREADS), smem, s, wm, xm, out, M, N, K,
                      kblocks_per_split, ops, kpo, w3d, err);

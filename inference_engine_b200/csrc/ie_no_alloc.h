@@ -15,7 +15,10 @@
 // are still the caller's.  It calls no cudaMalloc, cudaFree or allocating library routine.
 //
 // Limits and rules.
-//   * The scratch array holds IE_STATIC_DECODE_SCRATCH_FLOATS floats (4 MiB).  A call needs
+//   * The scratch array holds IE_STATIC_DECODE_SCRATCH_FLOATS floats (4 MiB).  The attention
+//     library is built once per head size (libie_b200_attn_hd<N>), and each of them carries an
+//     array of its own: a process holds 4 MiB per loaded head-size library on every GPU it
+//     uses, not 4 MiB in all.  A call needs
 //     num_seqs * nkv * num_splits * 16 * (head_dim + 2) floats when num_splits > 1 and none
 //     when num_splits == 1.  A call that needs more is refused with
 //     IE_STATIC_SCRATCH_TOO_SMALL and a message that says how much was asked for; nothing is
@@ -32,6 +35,16 @@
 //     need no clearing: a call writes every partial it later reads.  Because they are shared,
 //     two calls whose kernels can overlap on the GPU (different streams, no dependency) race
 //     on it; run such calls on one stream or order them with events.
+//   * What must be complete before the call.  The kernel is launched so that it may start
+//     while the kernel before it on the stream is still finishing (programmatic stream
+//     serialization), and it reads `cu_q`, `ctx_lens`, `tables` and the cached keys and values
+//     of earlier positions before it waits for that kernel; only `q` and the newest position's
+//     keys and values are read after the wait.  So if the kernel directly before this call on
+//     the stream writes lengths, tables or older cache entries, either that kernel must not
+//     signal its dependents early (kernels that never call griddepcontrol.launch_dependents,
+//     and copies, do not), or switch the early start off for this library with ie_set_pdl(0).
+//   * Kernel set-up (shared-memory limit, SM count) is kept per device, like the array's
+//     address: the entry point may be used on several GPUs of one process.
 //   * `msg`, if not null, receives a zero-terminated explanation when the return value is
 //     not 0 (at most msg_len bytes).
 #pragma once

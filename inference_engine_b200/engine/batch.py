@@ -34,6 +34,7 @@ class PagedGroupView:
     block_tables: Any  # int32 [B, table_width]; -1 where a window has passed
     table_width: int
     slot_mapping: Any  # int32 [N]: flat slot (page * page_size + offset) of each new token
+    ragged: bool = False  # the contexts this group's mixers see differ much in length (a launch hint)
 
 
 @dataclass
@@ -62,4 +63,4 @@ class StepContext:
     max_q_len: int
     max_ctx_len: int
     padded: bool = False  # a fixed-size launch: sizes above are upper bounds
-    ragged: bool = False  # the requests' contexts differ much in length (a hint for the attention's launch)
+    ragged: tuple = ()  # per paged group: its ``ragged`` hint (part of what a captured launch is keyed by)

@@ -6,6 +6,12 @@ captured once and replayed: the step's index data is copied into the same stagin
 padded up to the bucket with rows that read and write the cache's scratch page, and every
 kernel takes lengths and tables from device memory, so one capture serves every context
 length.  Bucket sizes are the reference's (engine/runtime/cuda_graphs.py:20-108).
+
+The block tables' row stride is fixed in a capture.  A stride for the longest context the
+engine allows (8,192 entries of 16 tokens at Llama 3.2's 131,072 positions) would make every
+step copy megabytes of table to the device for contexts of a few hundred tokens, so the
+stride is part of what a capture is keyed by: the smallest of 64, 128, 256, ... entries
+(up to the engine's limit) that holds the step's longest context.
 """
 
 from __future__ import annotations
@@ -22,8 +28,8 @@ class DecodeGraphs:
         self.buckets = [b for b in BUCKETS if b <= max_num_seqs]
         if not self.buckets or self.buckets[-1] < max_num_seqs:
             self.buckets.append(max_num_seqs)
-        # one capture per (bucket, whether the contexts' lengths differ much): the attention is
-        # launched differently for the two
+        # one capture per (bucket, whether the contexts' lengths differ much: the attention is
+        # launched differently for the two, block-table row stride)
         self._graphs: dict[tuple, tuple] = {}
         self._version = None
         self.replays = 0
@@ -34,24 +40,35 @@ class DecodeGraphs:
                 return b
         return None
 
+    MIN_WIDTH = 64
+
+    def width_for(self, last_position: int) -> int:
+        """The block-table row stride for a step whose longest request reaches ``last_position``."""
+        pages = last_position // self.runner.page_size + 1
+        width = self.MIN_WIDTH
+        while width < pages:
+            width *= 2
+        return max(min(width, self.table_width), pages)
+
     def kernels_per_replay(self, num_seqs: int) -> int:
         """How many of the engine's own kernels one replay for ``num_seqs`` sequences launches."""
         bucket = self.bucket_for(num_seqs)
-        entry = self._graphs.get((bucket, False)) or self._graphs.get((bucket, True))
-        return entry[2] if entry else 0
+        for (size, *_), entry in self._graphs.items():
+            if size == bucket:
+                return entry[2]
+        return 0
 
     def prepare(self, req_ids: list, positions: list[int]):
         """Pack the next decode step ahead of time (while the device still works on this one)
         if a captured launch sequence for its batch size exists; None otherwise."""
         bucket = self.bucket_for(len(req_ids))
-        key = (bucket, self.runner.contexts_are_ragged([p + 1 for p in positions]))
+        width = self.width_for(max(positions))
+        key = (bucket, self.runner.contexts_are_ragged([p + 1 for p in positions]), width)
         if bucket is None or key not in self._graphs or self._version != self.runner.ws.version:
             return None
-        cache = self.runner.cache
-        if any(len(cache.table(g, r)) > self.table_width for r in req_ids
-               for g in range(len(cache.paged_groups))):
+        if width > self.table_width:
             return None
-        handle = self.runner.prepare_decode(req_ids, positions, bucket, self.table_width)
+        handle = self.runner.prepare_decode(req_ids, positions, bucket, width)
         if self._version != self.runner.ws.version:
             return None
         return (key, handle)
@@ -73,9 +90,7 @@ class DecodeGraphs:
             return False
         if self.bucket_for(len(entries)) is None:
             return False
-        cache = self.runner.cache
-        return all(len(cache.table(g, e.req_id)) <= self.table_width
-                   for e in entries for g in range(len(cache.paged_groups)))
+        return self.width_for(max(e.start for e in entries)) <= self.table_width
 
     def run(self, entries):
         """Returns the ``[len(entries), vocab]`` logits of a decode-only step (every entry
@@ -85,15 +100,16 @@ class DecodeGraphs:
         if self._version != runner.ws.version:  # a buffer moved: captured addresses are stale
             self._graphs.clear()
             self._version = runner.ws.version
-        key = (bucket, self.runner.contexts_are_ragged([e.start + 1 for e in entries]))
+        width = self.width_for(max(e.start for e in entries))
+        key = (bucket, self.runner.contexts_are_ragged([e.start + 1 for e in entries]), width)
         captured = key in self._graphs
-        ctx, rows = runner.build_context(entries, pad_to_seqs=bucket, table_width=self.table_width,
+        ctx, rows = runner.build_context(entries, pad_to_seqs=bucket, table_width=width,
                                          views=not captured)
         if self._version != runner.ws.version:  # the staging buffer itself had to grow
             self._graphs.clear()
             self._version = runner.ws.version
             captured = False
-            ctx, rows = runner.build_context(entries, pad_to_seqs=bucket, table_width=self.table_width)
+            ctx, rows = runner.build_context(entries, pad_to_seqs=bucket, table_width=width)
         if not captured:
             # Run once outside a capture (buffers get allocated, libraries initialised) ...
             stream = torch.cuda.Stream()
@@ -105,8 +121,7 @@ class DecodeGraphs:
             if self._version != runner.ws.version:
                 self._graphs.clear()
                 self._version = runner.ws.version
-                ctx, rows = runner.build_context(entries, pad_to_seqs=bucket,
-                                                 table_width=self.table_width)
+                ctx, rows = runner.build_context(entries, pad_to_seqs=bucket, table_width=width)
             # ... then record the same launches.
             graph = torch.cuda.CUDAGraph()
             before = getattr(runner.ops, "launches", 0)

@@ -14,6 +14,7 @@ and only used for text deltas and stop strings.  Not thread-safe.
 
 from __future__ import annotations
 
+import dataclasses
 import itertools
 import os
 import random
@@ -22,7 +23,8 @@ from collections import deque
 from typing import Any
 
 from ..cache.manager import CacheManager
-from ..cache.storage import CacheStorage
+from ..cache.storage import CacheStorage, pages_that_fit
+from ..config.engine_config import EngineConfig
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
 from .batch import StepEntry
@@ -30,17 +32,27 @@ from .graphs import DecodeGraphs
 from .model import Model
 from .output import OutputProcessor, RequestOutput
 from .runner import ModelRunner
-from .scheduler import Scheduler, Sequence
+from .request import Sequence
+from .scheduler import Scheduler
 
 
 class LLMEngine:
-    def __init__(self, model: Model, tokenizer: Any = None, stop_token_ids: tuple[int, ...] = (), *,
-                 num_blocks: int | None = None, block_size: int = 16, max_num_seqs: int = 64,
-                 max_num_batched_tokens: int = 4096, gpu_memory_utilization: float = 0.9,
-                 enable_chunked_prefill: bool = True, enable_cuda_graphs: bool | None = None,
-                 max_model_len: int | None = None, debug_checks: bool = False, ops=None) -> None:
+    def __init__(self, model: Model, tokenizer: Any = None, stop_token_ids: tuple[int, ...] = (),
+                 config: EngineConfig | None = None, *, ops=None, **settings) -> None:
+        """``config``: the engine's settings; or give them by name (``num_blocks``,
+        ``block_size``, ``max_num_seqs``, ``max_num_batched_tokens``, ``gpu_memory_utilization``,
+        ``enable_chunked_prefill``, ``enable_cuda_graphs``, ``max_model_len``,
+        ``debug_checks``: the reference's argument names, engine/runtime/engine.py:47-66) and
+        they are checked as an :class:`EngineConfig`."""
         import torch
 
+        if config is None:
+            config = EngineConfig(dtype=model.env.dtype, **settings)
+        elif settings:
+            config = dataclasses.replace(config, **settings)
+        if config.dtype != model.env.dtype:
+            raise ValueError(f"the model was built for {model.env.dtype}, the engine configuration says {config.dtype}")
+        self.config = config
         self.model, self.tokenizer = model, tokenizer
         self.stop_token_ids = tuple(stop_token_ids)
         self.device = model.env.device
@@ -50,27 +62,29 @@ class LLMEngine:
 
             ops = get_ops(self.device)
         self.ops = ops
-        elt = 2 if self.dtype == "bfloat16" else 4
+        block_size, max_num_seqs = config.block_size, config.max_num_seqs
+        num_blocks = config.num_blocks
         if num_blocks is None:
-            num_blocks = self._blocks_that_fit(block_size, gpu_memory_utilization, elt)
-        self.max_model_len = min(max_model_len or model.spec.max_position_embeddings,
+            num_blocks = pages_that_fit(model.paged_groups, block_size, 2 if self.dtype == "bfloat16" else 4,
+                                        self.device, config.gpu_memory_utilization)
+        self.max_model_len = min(config.max_model_len or model.spec.max_position_embeddings,
                                  num_blocks * block_size if model.paged_groups else 2**62,
                                  model.env.max_positions)
+        table_width = -(-self.max_model_len // block_size)
         self.cache = CacheManager(model.paged_groups, model.state_groups, num_blocks, block_size,
-                                  max_num_seqs, max_pages_per_request=-(-self.max_model_len // block_size))
+                                  max_num_seqs, max_pages_per_request=table_width)
         self.storage = CacheStorage(self.cache, model.env.torch_dtype, self.device)
         self.runner = ModelRunner(model, self.cache, self.storage, ops, self.device,
-                                  max_num_batched_tokens, max_num_seqs)
-        self.scheduler = Scheduler(self.cache, max_num_seqs, max_num_batched_tokens,
-                                   enable_chunked_prefill)
+                                  config.max_num_batched_tokens, max_num_seqs)
+        self.scheduler = Scheduler(self.cache, max_num_seqs, config.max_num_batched_tokens,
+                                   config.enable_chunked_prefill)
         self.sampler = Sampler(ops, self.device, model.spec.vocab_size)
-        on_cuda = str(self.device).startswith("cuda") and torch.cuda.is_available()
-        if enable_cuda_graphs is None:
-            enable_cuda_graphs = on_cuda and not model.state_groups
-        self.graphs = None
-        if enable_cuda_graphs:
-            self.graphs = DecodeGraphs(self.runner, max_num_seqs, -(-self.max_model_len // block_size))
-        self.debug_checks = debug_checks
+        use_graphs = config.enable_cuda_graphs
+        if use_graphs is None:  # where they can be captured: on a GPU, no per-request state slots
+            use_graphs = (str(self.device).startswith("cuda") and torch.cuda.is_available()
+                          and not model.state_groups)
+        self.graphs = DecodeGraphs(self.runner, max_num_seqs, table_width) if use_graphs else None
+        self.debug_checks = config.debug_checks
         self._seq_ids = itertools.count()
         self._requests: dict[str, Sequence] = {}
         self._rng = random.Random()
@@ -85,63 +99,87 @@ class LLMEngine:
     # --- construction helpers ---------------------------------------------------------------
 
     @classmethod
-    def from_model_dir(cls, model_dir, dtype: str = "bfloat16", device="cuda",
-                       max_model_len: int | None = None, **kwargs) -> "LLMEngine":
+    def from_model_dir(cls, model_dir, dtype: str | None = None, device="cuda",
+                       config: EngineConfig | None = None, **settings) -> "LLMEngine":
         """Load ``config.json`` and the safetensors weights of ``model_dir`` and build the
         engine; stop ids come from the folder (config and generation config)."""
         from ..config.model_config import load_stop_token_ids
         from .loading import load_model
 
-        model, cfg = load_model(model_dir, dtype, device, max_positions=max_model_len)
-        kwargs.setdefault("stop_token_ids", load_stop_token_ids(model_dir))
-        return cls(model, max_model_len=max_model_len, **kwargs)
+        tokenizer = settings.pop("tokenizer", None)
+        stop_ids = settings.pop("stop_token_ids", None)
+        config = cls._settings(config, dtype, settings)
+        model, _ = load_model(model_dir, config.dtype, device, max_positions=config.max_model_len)
+        if stop_ids is None:
+            stop_ids = load_stop_token_ids(model_dir)
+        return cls(model, tokenizer, stop_ids, config, ops=settings.pop("ops", None))
 
     @classmethod
-    def from_random(cls, config: dict, seed: int = 0, dtype: str = "bfloat16", device="cuda",
-                    max_model_len: int | None = None, **kwargs) -> "LLMEngine":
+    def from_random(cls, model_config: dict, seed: int = 0, dtype: str | None = None, device="cuda",
+                    config: EngineConfig | None = None, **settings) -> "LLMEngine":
+        """An engine around a model of the given ``config.json`` dictionary with seeded random
+        weights."""
         from .loading import random_model
 
-        model, cfg = random_model(config, seed, dtype, device, max_positions=max_model_len)
-        return cls(model, max_model_len=max_model_len, **kwargs)
+        tokenizer = settings.pop("tokenizer", None)
+        stop_ids = settings.pop("stop_token_ids", ())
+        ops = settings.pop("ops", None)
+        config = cls._settings(config, dtype, settings)
+        model, _ = random_model(model_config, seed, config.dtype, device, max_positions=config.max_model_len)
+        return cls(model, tokenizer, stop_ids, config, ops=ops)
 
-    def _blocks_that_fit(self, block_size: int, utilization: float, elt: int) -> int:
-        """(free - (1 - utilization) * total - 512 MiB) // bytes per page over all groups
-        (engine/runtime/engine.py:130-140)."""
-        import torch
-
-        if not str(self.device).startswith("cuda"):
-            raise ValueError("pass num_blocks explicitly when not running on CUDA")
-        free, total = torch.cuda.mem_get_info(self.device)
-        budget = free - (1 - utilization) * total - 512 * 2**20
-        per_page = sum(g.bytes_per_page(block_size, elt) for g in self.model.paged_groups) or 1
-        blocks = int(budget // per_page)
-        if blocks < 1:
-            raise RuntimeError("no GPU memory left for the KV cache")
-        return blocks
+    @staticmethod
+    def _settings(config: EngineConfig | None, dtype: str | None, settings: dict) -> EngineConfig:
+        names = {f.name for f in dataclasses.fields(EngineConfig)}
+        given = {k: settings.pop(k) for k in list(settings) if k in names}
+        if dtype is not None:
+            given["dtype"] = dtype
+        unknown = set(settings) - {"ops"}
+        if unknown:
+            raise TypeError(f"unknown engine settings: {sorted(unknown)}")
+        return dataclasses.replace(config, **given) if config is not None else EngineConfig(**given)
 
     # --- requests ---------------------------------------------------------------------------
 
     def add_request(self, request_id: str, prompt_ids: list[int], params: SamplingParams) -> None:
-        if request_id in self._requests:
-            raise ValueError(f"duplicate request id {request_id!r}")
-        if not prompt_ids:
-            raise ValueError("prompt must have at least one token")
-        if len(prompt_ids) + params.max_tokens > self.max_model_len:
-            raise ValueError(f"prompt + max_tokens = {len(prompt_ids) + params.max_tokens} tokens "
-                             f"exceeds max_model_len ({self.max_model_len})")
-        vocab = self.model.spec.vocab_size
-        if any(not 0 <= t < vocab for t in prompt_ids):
-            raise ValueError(f"prompt holds a token id outside the vocabulary (0..{vocab - 1})")
+        """Queue a request.  Refused with a ValueError: an id that is still live, an empty
+        prompt, ids outside the vocabulary, and a request that could outgrow ``max_model_len``
+        or the cache even alone (the reference's checks, engine/runtime/engine.py:144-159)."""
+        problem = self._why_not(request_id, prompt_ids, params)
+        if problem:
+            raise ValueError(problem)
         seq = Sequence(next(self._seq_ids), request_id, list(prompt_ids), params)
-        seq.seed = params.seed if params.seed is not None else self._rng.getrandbits(62)
+        seq.seed = self._rng.getrandbits(62) if params.seed is None else params.seed
         seq.processor = OutputProcessor(self.tokenizer, params, self.stop_token_ids)
-        self.scheduler.add(seq)  # raises if it can never fit
+        self.scheduler.add(seq)  # (refuses what the cache could never hold)
         self._requests[request_id] = seq
+
+    def _why_not(self, request_id: str, prompt_ids: list[int], params: SamplingParams) -> str | None:
+        vocab = self.model.spec.vocab_size
+        longest = len(prompt_ids) + params.max_tokens
+        if request_id in self._requests:
+            return f"duplicate request id {request_id!r}"
+        if len(prompt_ids) == 0:
+            return "prompt must have at least one token"
+        if longest > self.max_model_len:
+            return f"prompt + max_tokens = {longest} tokens exceeds max_model_len ({self.max_model_len})"
+        if min(prompt_ids) < 0 or max(prompt_ids) >= vocab:
+            return f"prompt holds a token id outside the vocabulary (0..{vocab - 1})"
+        return None
 
     def abort(self, request_id: str) -> bool:
         """Stop a request and give its pages back now.  False if it was already done."""
         self._requests.pop(request_id, None)
-        return self.scheduler.abort(request_id) is not None
+        found = self.scheduler.abort(request_id) is not None
+        if self._ahead is not None and not self._anyone_left(self._ahead[0]):
+            self._ahead = None  # the step that is running ahead has nobody to deliver to
+        return found
+
+    def _alive(self, seq: Sequence) -> bool:
+        return self._requests.get(seq.request_id) is seq
+
+    def _anyone_left(self, seqs: list[Sequence]) -> bool:
+        return any(self._alive(s) for s in seqs)
 
     def has_unfinished(self) -> bool:
         return self.scheduler.has_unfinished()
@@ -182,16 +220,10 @@ class LLMEngine:
             decode_tokens = 0
             for seq, n in zip(seqs, counts):
                 start = seq.num_computed
-                n_prompt = len(seq.prompt_ids)
-                if n == 1 and start >= n_prompt:
-                    tokens = [seq.output_ids[start - n_prompt]]
-                    decode_tokens += 1
-                elif start + n <= n_prompt:
-                    tokens = seq.prompt_ids[start:start + n]
-                else:
-                    tokens = (seq.prompt_ids + seq.output_ids)[start:start + n]
+                tokens = seq.ids_from(start, n)
+                decode_tokens += n == 1 and start >= len(seq.prompt_ids)
                 if not seq.output_ids and start == 0:
-                    self.prompt_tokens_total += n_prompt
+                    self.prompt_tokens_total += len(seq.prompt_ids)
                 last = start + n == seq.length
                 entries.append(StepEntry(seq.seq_id, tokens, start, [n - 1] if last else []))
                 if last:
@@ -204,8 +236,9 @@ class LLMEngine:
                 logits = self.runner.step(entries)
 
         for seq, n in zip(seqs, counts):
-            seq.num_computed += n
-            self.cache.release_behind_window(seq.seq_id, seq.num_computed)
+            if n and self._alive(seq):  # (one that ended while this step ran ahead holds nothing)
+                seq.num_computed += n
+                self.cache.release_behind_window(seq.seq_id, seq.num_computed)
 
         outputs: list[RequestOutput] = []
         if sampled:
@@ -224,7 +257,7 @@ class LLMEngine:
                     self._prepared = self._prepare_next(seqs)
             tokens, logprobs = self.sampler.collect(pending)
             for row, (seq, token) in enumerate(zip(sampled, tokens)):
-                if self._requests.get(seq.request_id) is not seq:
+                if not self._alive(seq):
                     continue  # it ended or was aborted after this step had been launched ahead
                 seq.output_ids.append(token)
                 text, finished, reason = seq.processor.process(token)
@@ -238,8 +271,7 @@ class LLMEngine:
                     self.scheduler.finish(seq, reason)
                     self._requests.pop(seq.request_id, None)
                 outputs.append(out)
-            if self._ahead is not None and not any(
-                    self._requests.get(s.request_id) is s for s in self._ahead[0]):
+            if self._ahead is not None and not self._anyone_left(self._ahead[0]):
                 self._ahead = None  # nobody is left to take that step's tokens
         if self.debug_checks:
             self.cache.check_invariants()
@@ -265,16 +297,15 @@ class LLMEngine:
     # decides as usual.
 
     def _prepare_next(self, seqs: list[Sequence]):
-        if self.graphs is None or self.scheduler.waiting or self.scheduler.running != seqs:
+        if self.graphs is None:
             return None
-        positions = []
-        for seq in seqs:
-            pos = seq.num_computed  # where the token sampled now will go
-            if len(seq.output_ids) + 1 >= seq.params.max_tokens:
-                return None  # it ends with this token
-            if not self.cache.try_grow(seq.seq_id, pos, pos + 1):
-                return None  # pages ran out: the scheduler has to preempt
-            positions.append(pos)
+        # the scheduler's own answer to "what would the next step be": these requests, one
+        # token each, or something else (someone waits, ends at its limit, pages run out)
+        plan = self.scheduler.plan_steady_decode(seqs)
+        if plan is None:
+            return None
+        self.scheduler.commit(plan)  # takes the pages the sampled tokens will need
+        positions = [s.num_computed for s in seqs]  # where the tokens sampled now will go
         handle = self.graphs.prepare([s.seq_id for s in seqs], positions)
         return (list(seqs), handle) if handle is not None else None
 
@@ -309,40 +340,41 @@ class LLMEngine:
                 and all(s.num_computed == s.length - 1 for s in seqs))
 
     def generate(self, prompts: dict[str, list[int]], params: SamplingParams) -> dict[str, list[int]]:
-        """Run requests to completion; returns the generated token ids per request."""
+        """Run ``prompts`` (request id -> token ids) to their end with the same ``params``;
+        returns the produced ids per request."""
+        produced: dict[str, list[int]] = {}
         for request_id, prompt in prompts.items():
             self.add_request(request_id, prompt, params)
-        tokens: dict[str, list[int]] = {rid: [] for rid in prompts}
+            produced[request_id] = []
         while self.has_unfinished():
             for out in self.step():
-                tokens[out.request_id].append(out.token_id)
-        return tokens
+                produced[out.request_id].append(out.token_id)
+        return produced
 
     def snapshot(self) -> dict:
-        """Counters and queue state as plain data (engine/runtime/engine.py:300-375)."""
+        """The engine's state as plain data, for a status page or a log: settings, totals since
+        start, who runs and who waits, and the latest step records (what the reference's
+        ``snapshot`` reports, engine/runtime/engine.py:300-375)."""
         sched = self.scheduler
-
-        def describe(seq: Sequence) -> dict:
-            return {"id": seq.seq_id, "request": seq.request_id, "prompt": len(seq.prompt_ids),
-                    "output": len(seq.output_ids), "computed": seq.num_computed,
-                    "max_tokens": seq.params.max_tokens, "preemptions": seq.num_preemptions}
-
-        return {
-            "uptime_s": round(time.time() - self.started_at, 1),
-            "config": {"dtype": self.dtype, "block_size": self.cache.page_size,
-                       "num_blocks": [p.num_pages for p in self.cache.pools],
-                       "capacity_tokens": sched.capacity_tokens, "max_model_len": self.max_model_len,
-                       "max_num_seqs": sched.max_num_seqs,
-                       "max_num_batched_tokens": sched.max_num_batched_tokens,
-                       "cuda_graphs": self.graphs is not None,
-                       "chunked_prefill": sched.enable_chunked_prefill},
-            "running": [describe(s) for s in sched.running],
-            "waiting": [describe(s) for s in list(sched.waiting)[:32]],
-            "num_waiting": len(sched.waiting),
-            "totals": {"steps": self.steps_total, "generated_tokens": self.generated_total,
-                       "finished_requests": self.finished_total,
-                       "prompt_tokens": self.prompt_tokens_total,
-                       "preemptions": sched.num_preemptions,
-                       "free_blocks": self.cache.num_free_pages},
-            "steps": list(self.step_log)[-120:],
+        fields = (("id", lambda s: s.seq_id), ("request", lambda s: s.request_id),
+                  ("prompt", lambda s: len(s.prompt_ids)), ("output", lambda s: len(s.output_ids)),
+                  ("computed", lambda s: s.num_computed), ("max_tokens", lambda s: s.params.max_tokens),
+                  ("preemptions", lambda s: s.num_preemptions))
+        rows = lambda seqs: [{name: get(s) for name, get in fields} for s in seqs]  # noqa: E731
+        settings = {
+            "dtype": self.dtype, "block_size": self.cache.page_size,
+            "num_blocks": [pool.num_pages for pool in self.cache.pools],
+            "capacity_tokens": sched.capacity_tokens, "max_model_len": self.max_model_len,
+            "max_num_seqs": sched.max_num_seqs,
+            "max_num_batched_tokens": sched.max_num_batched_tokens,
+            "cuda_graphs": self.graphs is not None, "chunked_prefill": sched.enable_chunked_prefill,
         }
+        totals = {
+            "steps": self.steps_total, "generated_tokens": self.generated_total,
+            "finished_requests": self.finished_total, "prompt_tokens": self.prompt_tokens_total,
+            "preemptions": sched.num_preemptions, "free_blocks": self.cache.num_free_pages,
+        }
+        return {"uptime_s": round(time.time() - self.started_at, 1), "config": settings,
+                "totals": totals, "running": rows(sched.running),
+                "waiting": rows(itertools.islice(sched.waiting, 32)), "num_waiting": len(sched.waiting),
+                "steps": list(self.step_log)[-120:]}

@@ -7,6 +7,7 @@ the mixers and sorted into cache groups.
 
 from __future__ import annotations
 
+import math
 from typing import Any
 
 from ..cache.manager import PagedGroupSpec, StateGroupSpec
@@ -102,6 +103,16 @@ class Model:
             b if b is None or b.group >= 0 else CacheBinding(n_paged + (-1 - b.group), b.slot, b.writes)
             for b in self.bindings
         ]
+
+    def footprint(self):
+        """Parameters (every declared tensor once) and cache per token and per request, counted
+        from the parts themselves: what an architecture's own ``footprint`` callable would say."""
+        from ..config.model_config import Footprint
+
+        parameters = sum(math.prod(d.shape) for d in self.declared_weights().values())
+        per_token = sum(2 * g.num_layers * g.num_kv_heads * g.head_dim for g in self.paged_groups)
+        per_request = sum(g.num_layers * math.prod(g.shape) for g in self.state_groups)
+        return Footprint(parameters, per_token, per_request)
 
     # --- forward ----------------------------------------------------------------------------
 

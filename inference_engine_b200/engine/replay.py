@@ -16,10 +16,8 @@ from __future__ import annotations
 from pathlib import Path
 from typing import Any
 
-from ..config.registry import build_model_spec, load_config
-from ..weights.loader import load_weights
 from .batch import StepEntry
-from .model import Model
+from .loading import load_model
 from .runner import make_runner
 
 LIVE_REQUESTS = 8  # state slots; a trace keeps at most four requests alive
@@ -33,14 +31,12 @@ class ReplaySession:
 
             ops = get_ops(device)
         self.ops, self.device, self.page_size = ops, device, page_size
-        cfg = load_config(model_dir)
-        spec = build_model_spec(cfg)
         # The pool holds `max_tokens` tokens, each request's count rounded up to a multiple
         # of 64 by the caller; pages are smaller than 64, so this many pages always suffice.
         num_pages = max(-(-int(max_tokens) // page_size), 1)
         capacity = num_pages * page_size
-        self.model = Model(spec, dtype, max_positions=capacity, device=device)
-        self.model.load(load_weights(model_dir, self.model.declared_weights(), device))
+        self.model, _ = load_model(model_dir, dtype, device, max_positions=capacity)
+        spec = self.model.spec
         self.runner = make_runner(self.model, ops, device, page_size, num_pages,
                                   max_requests=LIVE_REQUESTS, max_tokens_per_step=64)
         self.cache = self.runner.cache
@@ -74,3 +70,47 @@ class ReplaySession:
                 self.cache.free(rid)
                 del self.fed[rid]
         return logits
+
+
+def main(argv: list[str] | None = None) -> int:
+    """The replay program: ``bin/trace_run`` and ``engine replay`` both end up here.
+
+        trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N
+
+    Steps are read from standard input, one JSON object a line.  For a step in which something
+    is wanted, ``DIR/<step>.f32`` receives the logits at the wanted places, in the order of the
+    entries and of ``want``, as little-endian 32-bit floats ``[wanted, vocab]``.  After every
+    step a line ``done <step>`` is printed and flushed.
+    """
+    import argparse
+    import json
+    import os
+    import sys
+
+    ap = argparse.ArgumentParser(prog="trace_run", description=main.__doc__,
+                                 formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
+    ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
+    ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
+    ap.add_argument("--max-tokens", type=int, required=True,
+                    help="most tokens live requests hold at any time (sizes the cache pool)")
+    ap.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
+    args = ap.parse_args(argv)
+
+    print("[trace_run] loading the model; kernels are compiled at the first call ...",
+          file=sys.stderr, flush=True)
+    session = ReplaySession(args.model, args.dtype, args.max_tokens, device="cuda",
+                            page_size=args.block_size)
+    os.makedirs(args.out, exist_ok=True)
+    print("[trace_run] ready", file=sys.stderr, flush=True)
+    for line in sys.stdin:
+        line = line.strip()
+        if not line:
+            continue
+        step = json.loads(line)
+        logits = session.run_step(step)
+        if logits is not None:
+            with open(os.path.join(args.out, f"{step['step']}.f32"), "wb") as f:
+                f.write(logits.contiguous().numpy().astype("<f4", copy=False).tobytes())
+        print(f"done {step['step']}", flush=True)
+    return 0

@@ -41,15 +41,21 @@ class ModelRunner:
         self.last_h2d_bytes = 0
         self._ensure_staging(self._staging_ints(self.max_tokens, self.max_seqs, self.max_seqs, 8))
 
-    def contexts_are_ragged(self, ctx_lens) -> bool:
-        """A hint for the attention's launch: whether these requests' contexts differ so much in
-        length that work dealt request by request would leave most of the GPU waiting for the
-        longest one.  The kernels' side decides (it knows how many requests the device takes at
-        once); without such kernels the answer is no."""
+    def contexts_are_ragged(self, ctx_lens) -> tuple[bool, ...]:
+        """A hint for the attention's launch, one answer per paged cache group: whether these
+        requests' contexts (what a group's window leaves of them) differ so much in length that
+        work dealt request by request would leave most of the GPU waiting for the longest one.
+        The kernels' side decides (it knows how many requests the device takes at once and the
+        group's number of key/value heads); without such kernels the answer is no."""
         decide = getattr(self.ops, "decode_by_length", None)
-        if decide is None or not self.cache.paged_groups or len(ctx_lens) < 2:
-            return False
-        return bool(decide(ctx_lens, self.cache.paged_groups[0].num_kv_heads))
+        groups = self.cache.paged_groups
+        if decide is None or len(ctx_lens) < 2:
+            return (False,) * len(groups)
+        answers = []
+        for g in groups:
+            seen = ctx_lens if g.window is None else [min(c, g.window) for c in ctx_lens]
+            answers.append(bool(decide(seen, g.num_kv_heads)))
+        return tuple(answers)
 
     # --- staging ----------------------------------------------------------------------------
 
@@ -184,10 +190,12 @@ class ModelRunner:
             t = dev[view[0]: view[0] + view[1]]
             return t if shape is None else t.view(*shape)
 
+        # (of the requests that bring one token: the others are not the decode kernel's)
+        ragged = self.contexts_are_ragged([c for c, ql in zip(ctx_lens[:real_b], q_lens) if ql == 1])
         groups: list[Any] = []
         for g, st in enumerate(self.storage.paged):
             groups.append(PagedGroupView(st.k, st.v, ps, st.window, dview(v_tables[g], (b, width)),
-                                         width, dview(v_slots[g])))
+                                         width, dview(v_slots[g]), ragged[g]))
         state_dev = dview(v_state)
         for st in self.storage.state:
             groups.append(StateGroupView(st, state_dev, state_slots))
@@ -197,8 +205,7 @@ class ModelRunner:
             cu_q=dview(v_cu), ctx_lens=dview(v_ctx), groups=groups,
             q_starts=q_starts, q_lens=q_lens, start_positions=start_positions,
             max_q_len=max(q_lens), max_ctx_len=max(ctx_lens), padded=pad_to_seqs is not None,
-            # (of the requests that bring one token: the others are not the decode kernel's)
-            ragged=self.contexts_are_ragged([c for c, ql in zip(ctx_lens[:real_b], q_lens) if ql == 1]),
+            ragged=ragged,
         )
         return ctx, dview(v_rows)
 
@@ -305,10 +312,11 @@ class ModelRunner:
             t = dev[view[0]: view[0] + view[1]]
             return t if shape is None else t.view(*shape)
 
+        ragged = self.contexts_are_ragged((positions + 1).tolist())
         groups: list[Any] = []
         for g, st in enumerate(self.storage.paged):
             groups.append(PagedGroupView(st.k, st.v, ps, st.window, dview(v_tables[g], (b, width)),
-                                         width, dview(v_slots[g])))
+                                         width, dview(v_slots[g]), ragged[g]))
         state_dev = dview(v_state)
         all_slots = state_slots + [cache.max_requests] * pad
         for st in self.storage.state:
@@ -320,7 +328,7 @@ class ModelRunner:
             cu_q=dview(v_cu), ctx_lens=dview(v_ctx), groups=groups,
             q_starts=list(range(b)), q_lens=[1] * b, start_positions=start_positions,
             max_q_len=1, max_ctx_len=int(positions.max()) + 1, padded=pad_to_seqs is not None,
-            ragged=self.contexts_are_ragged((positions + 1).tolist()),
+            ragged=ragged,
         )
         return ctx, dview(v_rows)
 

@@ -26,7 +26,7 @@ NVCC_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC", "--expt-r
 
 # Sources of the always-needed library.  Kernels specialised on a model's sizes are listed
 # in SPECIALISED and built by `build_specialised` with -D flags.
-CORE_SOURCES = ["elementwise.cu", "gemm_f32.cu", "gemm_skinny.cu", "gemm_tma.cu", "gemm_tc5.cu", "attention_generic.cu", "sampling.cu"]
+CORE_SOURCES = ["elementwise.cu", "gemm_f32.cu", "gemm_tma.cu", "gemm_tc5.cu", "attention_generic.cu", "sampling.cu"]
 
 
 class BuildError(RuntimeError):

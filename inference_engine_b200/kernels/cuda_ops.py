@@ -63,13 +63,9 @@ class CudaOps:
         self._err_ptr = self.err.data_ptr()
         self._attn_libs: dict[int, object] = {}
         self._argmax_scratch = None
-        self.force_skinny = False  # tests run every few-row product through the streaming kernel
         self._tickets = None
         self._retired_tickets = []
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
-        self.skinny_max_blocks = int(os.environ.get("IE_B200_SKINNY_MAX_BLOCKS", self.sm_count))
-        # which kernel takes few-row bfloat16 products: "tma" (TMA-fed ring), "cp" (cp.async
-        # rings per warp), "auto" (cp for few output features, the vendor library otherwise)
         self.attn_tc5 = os.environ.get("IE_B200_ATTN_TC5", "1") != "0"  # tcgen05 prefill attention
         self.prefill_key_splits = os.environ.get("IE_B200_PREFILL_KEY_SPLITS", "1") != "0"
         # the decode kernel cuts contexts until about this many blocks run (one block per SM)
@@ -79,6 +75,8 @@ class CudaOps:
         self.decode_balanced = os.environ.get("IE_B200_DECODE_BALANCED", "auto")
         self.decode_balanced_blocks_per_pair = 32
         self.balanced_launches = 0
+        # which kernel takes few-row bfloat16 products: "tma" (the TMA-fed weight-streaming kernel)
+        # or "lib" (the vendor library, for comparisons)
         self.few_row_gemm = os.environ.get("IE_B200_FEW_ROW_GEMM", "tma")
         # ... up to this many 128-feature tiles (measured on the 1B shape: up to 8 rows the kernel
         # streams 67 MB in 12.0 us where the vendor library takes 12.7, and the 525 MB of the
@@ -105,6 +103,7 @@ class CudaOps:
         self._device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self._raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
         self.launches = 0  # launches of this library's kernels (library matrix products not counted)
+        self.launch_counts: dict[str, int] = {}  # the same, per kernel
 
     def _declare(self) -> None:
         P, I, F, L = c_void_p, c_int, c_float, ctypes.c_longlong
@@ -115,7 +114,6 @@ class CudaOps:
             "ie_silu_mul": [P, I, I, L, P, I, I, I, P],
             "ie_argmax": [P, I, I, I, P, P, P],
             "ie_gemm_f32": [P, P, P, I, I, I, P],
-            "ie_gemm_skinny_bf16": [P, P, P, I, I, I, I, I, I, P],
             "ie_gemm_tma_bf16": [P, P, P, I, I, I, I, I, I, P, P],
             "ie_gemm_tc5_bf16": [P, P, P, I, I, I, I, I, I, P, P],
             "ie_gemm_tc5_ok": [I, I, I],
@@ -138,6 +136,7 @@ class CudaOps:
 
     def _check(self, code: int, what: str) -> None:
         self.launches += 1
+        self.launch_counts[what] = self.launch_counts.get(what, 0) + 1
         if code != 0:
             raise KernelError(f"{what}: CUDA error {code} at launch")
 
@@ -147,11 +146,17 @@ class CudaOps:
 
     def check_errors(self) -> None:
         """Read the device error word (this waits for the stream) and raise if a kernel saw
-        an index out of range."""
-        code, value, where = self.err[:3].tolist()
+        an index out of range or gave up a wait."""
+        self.raise_reported(self.err.tolist())
+
+    def raise_reported(self, words) -> None:
+        """``words``: a copy of the error word (code, value, where, spare).  A non-zero code
+        clears the word on the device (the first report wins, so the next fault must find it
+        empty) and raises."""
+        code, value, where = words[:3]
         if code:
             self.err.zero_()
-            raise KernelError(f"kernel index check failed: {_ERRORS.get(code, code)} "
+            raise KernelError(f"kernel check failed: {_ERRORS.get(code, code)} "
                               f"(value {value}, at row/token {where})")
 
     # --- kernels ----------------------------------------------------------------------------
@@ -176,16 +181,7 @@ class CudaOps:
                                   out.data_ptr(), _dtype_code(out), self._ptr(rows), n,
                                   h.shape[1], self._stream()), "rmsnorm")
 
-    SKINNY_ROWS = 16  # up to this many rows a bfloat16 product runs the weight-streaming kernel
-
-    def skinny_split(self, n_out: int, k: int) -> tuple[int, int]:
-        """(slice of the inner dimension per split, number of splits) for a few-row product:
-        enough warps to fill the GPU, slices of whole 256-wide stages."""
-        fblocks = -(-n_out // 16)
-        want = max(1, (self.sm_count * 8) // fblocks)
-        per = max(256, (k // want) // 128 * 128)
-        per = min(per, -(-k // 16) * 16)
-        return per, -(-k // per)
+    FEW_ROWS = 16  # up to this many rows a bfloat16 product runs the weight-streaming kernel
 
     def tma_split(self, n_out: int, k: int) -> tuple[int, int]:
         """(64-wide k blocks per split, splits) for the TMA-fed few-row product: one block of
@@ -226,8 +222,8 @@ class CudaOps:
             return out
         # The weight-streaming kernel pays where the library leaves SMs idle: few output
         # features (fewer 16-feature blocks than SMs) and a long inner dimension to split.
-        few_rows = 0 < m <= self.SKINNY_ROWS and k % 8 == 0 and x.is_contiguous() and w.is_contiguous()
-        if (few_rows and self.few_row_gemm == "tma" and not self.force_skinny
+        few_rows = 0 < m <= self.FEW_ROWS and k % 8 == 0 and x.is_contiguous() and w.is_contiguous()
+        if (few_rows and self.few_row_gemm == "tma"
                 and -(-n // 128) <= (self.tma_max_tiles if m <= 8 else self.tma_max_tiles_wide)):
             kbps, splits = self.tma_split(n, k) if allow_split and out is None else (-(-k // 64), 1)
             # (more than one and a half rounds of blocks over the SMs: the library's kernels are
@@ -242,7 +238,7 @@ class CudaOps:
                 return out
         # A batch of decode tokens (17 to 256 rows): still a stream of weights; the tcgen05
         # kernel with the operands' roles swapped, cut along k like the few-row kernel.
-        if (self.batch_gemm and self.SKINNY_ROWS < m <= self.batch_gemm_rows and x.is_contiguous()
+        if (self.batch_gemm and self.FEW_ROWS < m <= self.batch_gemm_rows and x.is_contiguous()
                 and w.is_contiguous() and self._gemm_tc5_ok(m, n, k)
                 and -(-n // 128) <= self.batch_gemm_max_tiles and k >= self.batch_gemm_min_k
                 and (not self.batch_gemm_one_round or (
@@ -254,17 +250,6 @@ class CudaOps:
                 out = ws.buffer(tag, m, n, out_dtype)
             self._check(self._gemm_tc5_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), _dtype_code(out),
                                             m, n, k, per, splits, self._err_ptr, self._stream()), "gemm_tc5")
-            return out
-        skinny = (0 < m <= self.SKINNY_ROWS and k % 8 == 0 and x.is_contiguous() and w.is_contiguous()
-                  and (self.force_skinny or (allow_split and out is None and -(-n // 16) <= self.skinny_max_blocks)))
-        if skinny:
-            per, splits = self.skinny_split(n, k) if allow_split and out is None else (-(-k // 16) * 16, 1)
-            if splits > 1:
-                out = ws.buffer(tag, splits * m, n, torch.float32).view(splits, m, n)
-            elif out is None:
-                out = ws.buffer(tag, m, n, out_dtype)
-            self._check(self._gemm_skinny_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), _dtype_code(out),
-                                               m, n, k, per, splits, self._stream()), "gemm_skinny")
             return out
         if out is None:
             out = ws.buffer(tag, m, n, out_dtype)
@@ -358,7 +343,7 @@ class CudaOps:
         return best if cost(best) <= 0.75 * cost(1) else 1
 
     def paged_attention(self, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, page_size,
-                        scale, window, out) -> None:
+                        scale, window, out, ragged: bool | None = None) -> None:
         """Attention of every token of the step over its request's cached keys and values.
         bfloat16 with a head size the tensor-core kernels take and at most 16 query heads per
         key/value head: requests with few rows go to the split decode kernel, longer portions
@@ -372,19 +357,26 @@ class CudaOps:
         if q.dtype == self.torch.bfloat16 and hd in ATTENTION_HEAD_DIMS and groups <= 16:
             lib = self._attention_lib(hd)
             # which requests go to which kernel: the same for every layer of the step
-            plan = getattr(ctx, "_attention_plan", None)
-            if plan is None or plan["groups"] != groups:
+            # (kept on the step's context, one per (heads per key/value head, head size): mixers
+            # of different shapes in one model each get their own)
+            plans = getattr(ctx, "_attention_plans", None)
+            if plans is None:
+                plans = ctx._attention_plans = {}
+            plan = plans.get((groups, hd))
+            if plan is None:
                 small = [ql * groups <= 16 for ql in ctx.q_lens]
-                plan = {"groups": groups, "small": small, "any": any(small), "all": all(small)}
+                plan = {"small": small, "any": any(small), "all": all(small)}
                 if not plan["all"]:
                     rows = lib.ie_attention_prefill_rows()
                     per_seq = [-(-ql // rows) for ql, s in zip(ctx.q_lens, small) if not s]
                     plan["tiles"] = sum(per_seq)
                     plan["tile_pairs"] = sum(-(-t // 2) for t in per_seq)
-                ctx._attention_plan = plan
+                plans[(groups, hd)] = plan
             args = (q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, page_size, scale, window, out)
             if plan["any"]:
-                self._decode_attention(lib, *args)
+                if ragged is None:
+                    ragged = any(getattr(ctx, "ragged", ()) or ())
+                self._decode_attention(lib, ragged, *args)
             if not plan["all"]:
                 self._prefill_attention(lib, plan, *args)
             return
@@ -397,12 +389,12 @@ class CudaOps:
             return ws.buffer(name, 1, floats, self.torch.float32)
         return self.torch.empty(floats, dtype=self.torch.float32, device=device)
 
-    def _decode_attention(self, lib, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, page_size, scale,
+    def _decode_attention(self, lib, ragged, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, page_size, scale,
                           window, out) -> None:
         """The requests with few rows (the kernels skip the others): key tiles dealt by length
         when the step's context says its lengths differ much, else by request."""
         total_pages, stream = k_cache.shape[0], self._stream()
-        by_length = self.decode_balanced == "1" or (self.decode_balanced == "auto" and getattr(ctx, "ragged", False))
+        by_length = self.decode_balanced == "1" or (self.decode_balanced == "auto" and bool(ragged))
         if by_length and ctx.num_seqs <= lib.ie_attention_decode_balanced_max_seqs():
             per_pair = self.decode_balanced_blocks_per_pair
             floats = lib.ie_attention_decode_balanced_scratch_floats(ctx.num_seqs, nkv, per_pair)

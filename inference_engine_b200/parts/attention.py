@@ -75,7 +75,7 @@ class PagedAttention(Mixer):
         ctx.ops.paged_attention(
             q, group.k[binding.slot], group.v[binding.slot], group.block_tables, ctx,
             self.num_heads, self.num_kv_heads, self.head_dim, group.page_size,
-            self.scale, self.window or 0, out,
+            self.scale, self.window or 0, out, ragged=group.ragged,
         )
         return ctx.ops.linear(out, self.w_o, ws=ctx.ws, tag="mixer.delta", out_dtype=torch.float32,
                               allow_split=True)

@@ -23,6 +23,7 @@ class Sampler:
         # this step's tokens on the device, and its sampling before it has fetched these.
         self._tokens = [torch.empty(0, dtype=torch.int32, device=device) for _ in range(2)]
         self._host = [None, None]     # pinned copies of the tokens
+        self._err_host = [None, None]  # pinned copies of the kernels' error word, fetched with the tokens
         self._events = [None, None]
         self._turn = 0
         self._param_dev, self._param_cap, self._param_key, self._param_draws, self._param_turn = None, 0, None, [], 0
@@ -37,6 +38,7 @@ class Sampler:
             self._tokens[i] = torch.empty(n, dtype=torch.int32, device=self.device)
             pinned = torch.device(self.device).type == "cuda"
             self._host[i] = torch.empty(n, dtype=torch.int32, pin_memory=pinned)
+            self._err_host[i] = torch.zeros(4, dtype=torch.int32, pin_memory=pinned)
             self._events[i] = torch.cuda.Event() if pinned else None
         return i, self._tokens[i][:rows]
 
@@ -67,9 +69,16 @@ class Sampler:
         # the tokens start on their way to the host right behind the kernel
         host = self._host[turn][:rows]
         host.copy_(out, non_blocking=True)
+        # ... and with them the word in which the step's kernels report an index out of range or
+        # a wait that ran out (16 bytes; no extra wait: it is read when the tokens are)
+        err_word = getattr(self.ops, "err", None)
+        err_host = None
+        if err_word is not None:
+            err_host = self._err_host[turn]
+            err_host.copy_(err_word, non_blocking=True)
         if self._events[turn] is not None:
             self._events[turn].record()
-        return out, logprob, host, self._events[turn]
+        return out, logprob, host, self._events[turn], err_host
 
     # The rows' parameters live in one device buffer.  They reach it as one copy from pinned
     # memory (a copy from pageable memory would make the host wait for the stream, and with it
@@ -133,9 +142,11 @@ class Sampler:
         return kwargs
 
     def collect(self, pending):
-        out, logprob, host, event = pending
+        out, logprob, host, event, err_host = pending
         if event is not None:
             event.synchronize()  # the step's one wait for the device: until its tokens have arrived
+        if err_host is not None and int(err_host[0]):
+            self.ops.raise_reported(err_host.tolist())  # these tokens cannot be trusted
         tokens = host.tolist()
         return tokens, (logprob.tolist() if logprob is not None else None)
 

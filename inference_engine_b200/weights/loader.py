@@ -36,16 +36,18 @@ class WeightError(RuntimeError):
 
 
 def find_safetensors_files(model_dir: str | Path) -> list[Path]:
-    model_dir = Path(model_dir)
-    index = model_dir / "model.safetensors.index.json"
-    if index.exists():
-        with open(index, encoding="utf-8") as f:
-            names = sorted(set(json.load(f)["weight_map"].values()))
-        return [model_dir / n for n in names]
-    single = model_dir / "model.safetensors"
-    if single.exists():
-        return [single]
-    raise FileNotFoundError(f"no safetensors weights in {model_dir}")
+    """The checkpoint's files: the shards that ``model.safetensors.index.json`` maps tensors to
+    (each once, by name), else the single ``model.safetensors``
+    (engine/model/loader.py:18-29)."""
+    folder = Path(model_dir)
+    index_file = folder / "model.safetensors.index.json"
+    if not index_file.exists():
+        whole = folder / "model.safetensors"
+        if whole.exists():
+            return [whole]
+        raise FileNotFoundError(f"no safetensors weights in {folder}")
+    shard_of = json.loads(index_file.read_text(encoding="utf-8"))["weight_map"]
+    return [folder / shard for shard in sorted(set(shard_of.values()))]
 
 
 def check_names_and_shapes(found: dict[str, tuple[int, ...]], expected: dict[str, Any],

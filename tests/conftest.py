@@ -23,3 +23,14 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_terminal_summary(terminalreporter):
+    """The largest logit differences the comparisons with the plain implementation saw."""
+    from tests import helpers
+
+    for dtype, seen in sorted(helpers.ACHIEVED.items()):
+        bounds = helpers.TOL[dtype]
+        terminalreporter.write_line(
+            f"logits vs plain implementation, {dtype}: " + ", ".join(
+                f"{k} {v:.3g}" for k, v in sorted(seen.items())) + f"  (bounds: {bounds})")

@@ -117,16 +117,19 @@ def decoder_layer(cfg: dict, weights: dict, i: int, x: torch.Tensor, cos, sin) -
                       rms_norm(h, weights[f"{p}.post_attention_layernorm.weight"], eps))
 
 
-def logits_for(cfg: dict, weights: dict, token_ids) -> torch.Tensor:
+def logits_for(cfg: dict, weights: dict, token_ids, rows=None) -> torch.Tensor:
     """engine/model/llama.py:60-68 -- embed, the layers in order, final norm, head; the head
     is the embedding table when ``tie_word_embeddings`` is set (engine/model/loader.py:91-92).
-    token_ids: one whole sequence -> [T, vocab] 32-bit logits for every position."""
+    token_ids: one whole sequence -> [T, vocab] 32-bit logits for every position (or for the
+    positions listed in ``rows`` only: the head of a large vocabulary is the slow part)."""
     ids = torch.as_tensor(token_ids, dtype=torch.long)
     positions = torch.arange(ids.shape[0])
     cos, sin = rope_angles(rope_inv_freq(cfg), positions)
     x = embed(weights, ids)
     for i in range(cfg["num_hidden_layers"]):
         x = decoder_layer(cfg, weights, i, x, cos, sin)
+    if rows is not None:
+        x = x[torch.as_tensor(rows, dtype=torch.long)]
     x = rms_norm(x, weights["model.norm.weight"], float(cfg.get("rms_norm_eps", 1e-5)))
     head = "model.embed_tokens.weight" if cfg.get("tie_word_embeddings", False) else "lm_head.weight"
     return x @ weights[head].float().t()

@@ -63,7 +63,7 @@ class RefOps:
             v_cache[page, :, offset] = v.to(v_cache.dtype)
 
     def paged_attention(self, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, page_size,
-                        scale, window, out):
+                        scale, window, out, ragged=None):
         groups = nh // nkv
         tables = block_tables.long().cpu()
         positions = ctx.positions.cpu().tolist()

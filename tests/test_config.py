@@ -6,10 +6,10 @@ import json
 
 import pytest
 
+from inference_engine_b200.architectures.llama import LlamaConfig
 from inference_engine_b200.config import (
-    ConfigError, LlamaConfig, build_model_spec, config_from_dict, estimate_param_count,
-    kv_bytes_per_token, load_config, load_stop_token_ids, max_kv_tokens, register_architecture,
-    supported_architectures,
+    ConfigError, build_model_spec, config_from_dict, get_architecture, load_config,
+    load_stop_token_ids, register_architecture, supported_architectures,
 )
 from inference_engine_b200.config.spec import ModelSpec, PartSpec, ScheduleEntry
 from tests.tiny_configs import TINY_A, TINY_B, TINY_C
@@ -54,14 +54,30 @@ def test_defaults_as_the_reference():
 
 @pytest.mark.parametrize("raw,expected", [(LLAMA_1B, 1_235_814_400), (LLAMA_8B, 8_030_261_248)])
 def test_param_count_matches_published_models(raw, expected):
-    assert estimate_param_count(config_from_dict(raw)) == expected
+    assert _footprint(raw).parameters == expected
+
+
+def _footprint(raw):
+    cfg = config_from_dict(raw)
+    return get_architecture(cfg.architecture).footprint(cfg)
 
 
 def test_memory_estimates():
-    assert kv_bytes_per_token(config_from_dict(LLAMA_1B)) == 32 * 1024
-    assert kv_bytes_per_token(config_from_dict(LLAMA_8B)) == 128 * 1024
-    assert max_kv_tokens(config_from_dict(LLAMA_8B), gpu_mem_gib=8) == 0
-    assert max_kv_tokens(config_from_dict(LLAMA_8B), gpu_mem_gib=180) > 1_000_000
+    assert _footprint(LLAMA_1B).cache_bytes_per_token(2) == 32 * 1024
+    assert _footprint(LLAMA_8B).cache_bytes_per_token(2) == 128 * 1024
+    assert _footprint(LLAMA_8B).cache_tokens_that_fit(gpu_mem_gib=8) == 0
+    assert _footprint(LLAMA_8B).cache_tokens_that_fit(gpu_mem_gib=180) > 1_000_000
+
+
+def test_the_footprint_an_architecture_reports_is_that_of_the_built_model():
+    """Counted from the parts' declared tensors and the cache groups (what `engine info` falls
+    back to for an architecture that reports none)."""
+    from inference_engine_b200.engine.model import Model
+
+    for raw in (TINY_A, TINY_B, TINY_C):
+        cfg = config_from_dict(raw)
+        built = Model(build_model_spec(cfg), "bfloat16", max_positions=8).footprint()
+        assert built == _footprint(raw)
 
 
 def test_errors_name_what_is_wrong():

@@ -7,6 +7,8 @@ from __future__ import annotations
 import random
 
 import pytest
+from hypothesis import HealthCheck, given, settings
+from hypothesis import strategies as st
 
 from tests import helpers as H
 from tests import plain_llama
@@ -25,6 +27,19 @@ def _engine(cfg, weights, **kw):
 
 @pytest.mark.parametrize("seed", range(6))
 def test_random_workloads_equal_plain_greedy(seed):
+    _random_workload(seed)
+
+
+@settings(max_examples=12, deadline=None, derandomize=True,
+          suppress_health_check=[HealthCheck.too_slow])
+@given(st.integers(min_value=6, max_value=2**31))
+def test_random_workloads_drawn_by_hypothesis(seed):
+    """The same property over seeds that Hypothesis draws (and shrinks, if one fails): sizes,
+    pages, budgets, arrivals and an abort are all derived from the seed."""
+    _random_workload(seed)
+
+
+def _random_workload(seed):
     from inference_engine_b200 import SamplingParams
 
     rng = random.Random(seed)

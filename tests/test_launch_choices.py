@@ -3,8 +3,7 @@
 `CudaOps.decode_by_length` picks between the two decode attention launches from the step's context
 lengths, `CudaOps.prefill_key_split` among how many blocks the prefill attention shares a query
 tile's keys, `CudaOps.decode_splits` into how many parts the by-request decode attention cuts a
-context.  The numbers they were set from are in profiles/attention_decode_b8.md and
-profiles/mixed_step_512_launches.md.
+context.
 """
 
 from __future__ import annotations

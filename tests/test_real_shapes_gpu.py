@@ -1,0 +1,189 @@
+"""The layer sizes that are benchmarked, checked as a model.
+
+The tiny configurations never reach the kernels that serve real sizes: the tcgen05 prefill
+attention (head sizes 64 and 128), the TMA-fed few-row products with their inner dimension
+cut into partial sums, the tcgen05 product for batches of decode tokens, the vendor library's
+products at hundreds of rows, the decode attention's context splits at head size 64, captured
+decode steps with padded rows.  Here two configurations with real layer sizes and few layers
+run the same four ways of cutting the work, in true 32-bit and in bfloat16, against the plain
+implementation (the reference checks its 1B path end to end: bench/batch_invariance.py:1-19,
+tests/test_engine.py:53-68):
+
+* "1B shape, 2 of 16 layers": hidden 2048, 32 query and 8 key/value heads of 64, feed-forward
+  8192, vocabulary 128256, llama3 scaling with factor 32, tied head, 16-token pages;
+* "8B shape, 1 of 32 layers, vocabulary shrunk to 32003": hidden 4096, 32 and 8 heads of 128,
+  feed-forward 14336, factor 8, untied head (the full vocabulary would make the plain
+  implementation on the CPU the slowest part of the suite).
+
+Logits are asked for at a subset of positions (the last 40 of every request, the first ones,
+the edges of pages and of 64- and 128-token tiles, every 61st): every position of 2,000 tokens
+at 128,256 logits would be a gigabyte per run.
+"""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from tests import helpers as H
+from tests import plain_llama
+
+pytestmark = pytest.mark.gpu
+
+SHAPE_1B_2L = {
+    "architectures": ["LlamaForCausalLM"],
+    "num_hidden_layers": 2, "hidden_size": 2048, "num_attention_heads": 32,
+    "num_key_value_heads": 8, "head_dim": 64, "intermediate_size": 8192, "vocab_size": 128256,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 131072,
+}
+
+SHAPE_8B_1L = {
+    "architectures": ["LlamaForCausalLM"],
+    "num_hidden_layers": 1, "hidden_size": 4096, "num_attention_heads": 32,
+    "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 14336, "vocab_size": 32003,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": 131072,
+}
+
+SHAPES = {"1B-shape-2-of-16-layers": SHAPE_1B_2L,
+          "8B-shape-1-of-32-layers-vocab-32003": SHAPE_8B_1L}
+LENGTHS = {"1B-shape-2-of-16-layers": [1150, 333, 420, 305, 200, 262],
+           "8B-shape-1-of-32-layers-vocab-32003": [1130, 310, 345, 280, 150]}
+PAGE = 16
+# portions that reach every launch: one or two tokens (the decode kernels), 19 to 64 (the
+# tcgen05 product of a batch of tokens), hundreds (tensor-core prefill attention over several
+# query tiles, the vendor library's products)
+PORTIONS = (130, 2, 257, 19, 3, 512, 64, 33, 5, 17, 100)
+
+
+def _weights(cfg, seed):
+    # N(0, 0.02) as the benchmark's; queries and keys twice as large, so that a few keys among
+    # hundreds carry a position's attention and a lost or misplaced one shows
+    return H.make_weights(cfg, seed=seed, sharp=2.0, std=0.02)
+
+
+def _wanted(n: int) -> set[int]:
+    marks = {0, 1, 2, 15, 16, 17, 63, 64, 65, 127, 128, 129, 255, 256, 257, 511, 512, 1023, 1024, 1025}
+    return {p for p in marks | set(range(0, n, 61)) | set(range(n - 40, n)) if 0 <= p < n}
+
+
+@pytest.fixture(scope="module", params=list(SHAPES))
+def case(request, tmp_path_factory):
+    name = request.param
+    cfg = SHAPES[name]
+    weights = _weights(cfg, seed=len(name))
+    folder = H.write_model_dir(tmp_path_factory.mktemp("real_shape"), cfg, weights)
+    requests = {f"r{i}": H.random_tokens(cfg, n, 1000 + 7 * i) for i, n in enumerate(LENGTHS[name])}
+    wanted = {rid: _wanted(len(toks)) for rid, toks in requests.items()}
+    want = {rid: plain_llama.logits_for(cfg, weights, toks, rows=sorted(wanted[rid]))
+            for rid, toks in requests.items()}
+    del weights
+    return name, cfg, folder, requests, wanted, want
+
+
+def _run(case, dtype, steps, max_tokens):
+    from inference_engine_b200.engine.replay import ReplaySession
+
+    name, cfg, folder, requests, wanted, want = case
+    session = ReplaySession(folder, dtype, max_tokens, device="cuda", page_size=PAGE)
+    before = dict(session.ops.launch_counts)
+    got = H.collect(session, H.restrict_wants(steps, wanted))
+    for rid in requests:
+        H.assert_close(got[rid], want[rid], dtype, f"{name} {dtype} request {rid}")
+    assert session.cache.num_free_pages == [p.num_pages for p in session.cache.pools]
+    launches = {k: n - before.get(k, 0) for k, n in session.ops.launch_counts.items()}
+    del session
+    torch.cuda.empty_cache()
+    return got, launches
+
+
+def _cuttings(case):
+    name, cfg, folder, requests, wanted, want = case
+    total = sum(H.round64(len(t)) for t in requests.values())
+    longest = max(H.round64(len(t)) for t in requests.values())
+    mixed, peak = H.trace_mixed(requests, seed=4, max_portion=300, tail=14)
+    assert peak < total and max(len(s["entries"]) for s in mixed) >= 3
+    return {
+        "whole": (H.trace_whole(requests), longest),
+        "last 32 one by one": (H.trace_decode_tail(requests, 32), longest),
+        "portions": (H.trace_portions(requests, sizes=PORTIONS), longest),
+        "mixed": (mixed, peak),
+    }
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("cut", ["whole", "last 32 one by one", "portions", "mixed"])
+def test_real_shape_logits(case, cut, dtype):
+    steps, max_tokens = _cuttings(case)[cut]
+    _run(case, dtype, steps, max_tokens)
+
+
+def test_real_shape_float32_is_the_same_however_it_is_cut(case):
+    cuts = _cuttings(case)
+    whole, _ = _run(case, "float32", *cuts["whole"])
+    for cut in ("last 32 one by one", "portions", "mixed"):
+        other, _ = _run(case, "float32", *cuts[cut])
+        for rid in whole:
+            assert torch.equal(whole[rid], other[rid]), f"{cut}: request {rid} depends on the cutting"
+
+
+def test_real_shape_bfloat16_runs_the_kernels_it_is_meant_to(case):
+    """The portions above reach the tensor-core prefill attention, the split few-row products,
+    the tcgen05 product for batches of tokens and the decode attention (counted by the kernel
+    set's launch counters, so that a changed routing cannot quietly leave one untested)."""
+    name, cfg, *_ = case
+    cuts = _cuttings(case)
+    _, launches = _run(case, "bfloat16", *cuts["portions"])
+    kernels = ["attention_prefill_tc5", "attention_decode", "gemm_tma"]
+    if cfg["hidden_size"] == 2048:
+        kernels.append("gemm_tc5")  # (at the 8B shape its blocks would not fit the SMs in one round)
+    for kernel in kernels:
+        assert launches.get(kernel, 0) > 0, f"{kernel} never ran: {launches}"
+    _, launches = _run(case, "bfloat16", *cuts["last 32 one by one"])
+    assert launches.get("attention_decode", 0) >= 32 * cfg["num_hidden_layers"]
+
+
+# --- the engine at the benchmarked shape -------------------------------------------------------
+
+
+@pytest.mark.parametrize("num_requests", [9, 40])
+def test_engine_at_1b_shape_with_padded_captured_steps(num_requests):
+    """Greedy generation with `max_num_seqs=64`: 9 and 40 requests decode in captured steps of
+    16 and 48 rows (padded), launched ahead of the host or not: the same tokens, and each is
+    the plain implementation's choice given the same prefix (or within a small gap of it)."""
+    from inference_engine_b200 import SamplingParams
+    from inference_engine_b200.engine.llm_engine import LLMEngine
+    from inference_engine_b200.engine.loading import model_from_tensors
+
+    cfg = SHAPE_1B_2L
+    weights = _weights(cfg, seed=5)
+    prompts = {f"p{i}": H.random_tokens(cfg, 9 + (5 * i) % 41, 300 + i) for i in range(num_requests)}
+    params = SamplingParams(temperature=0, max_tokens=6)
+    outs = []
+    for ahead in (True, False):
+        model, _ = model_from_tensors(cfg, weights, "bfloat16", "cuda", 256)
+        engine = LLMEngine(model, None, (), num_blocks=64 * 8, block_size=PAGE, max_num_seqs=64,
+                           max_num_batched_tokens=512, max_model_len=128, enable_cuda_graphs=True,
+                           debug_checks=True)
+        engine.launch_ahead = ahead
+        outs.append(engine.generate(prompts, params))
+        bucket = engine.graphs.bucket_for(num_requests)
+        assert bucket > num_requests  # padded rows
+        assert any(key[:2] == (bucket, (False,)) for key in engine.graphs._graphs) and engine.graphs.replays >= 4
+        assert engine.cache.num_free_pages == [64 * 8]
+        del engine, model
+        torch.cuda.empty_cache()
+    assert outs[0] == outs[1]
+    for rid, prompt in prompts.items():
+        ids = list(prompt)
+        for i, token in enumerate(outs[0][rid]):
+            logits = plain_llama.logits_for(cfg, weights, ids, rows=[len(ids) - 1])[0]
+            best = int(logits.argmax())
+            gap = float(logits[best] - logits[token])
+            assert token == best or gap < 0.1, f"{rid} token {i}: engine {token}, plain {best} (gap {gap:.4f})"
+            ids.append(token)

@@ -5,8 +5,11 @@ of the library instead of asking the caller for scratch.
 
 The test calls the exported C symbol directly, twice in a row with different inputs (the
 second call finds the array as the first left it), and compares with the regular entry point
-`ie_attention_decode`, which gets scratch from the caller.  It also checks that a call whose
-partials would not fit the built-in array is refused with a message and launches nothing.
+`ie_attention_decode`, which gets scratch from the caller, and with the plain PyTorch attention
+of `tests/ref_ops.py`, which shares no code with either.  The device's free memory as the
+driver reports it (not torch's allocator, which an allocation inside the C function would
+bypass) must be the same before and after the calls.  It also checks that a call whose partials
+would not fit the built-in array is refused with a message and launches nothing.
 This file sorts last on purpose, so a run that stops at the first failure has already run
 every other test.
 """
@@ -36,6 +39,22 @@ def _library():
     lib.ie_attention_decode_scratch_floats.restype = ctypes.c_longlong
     lib.ie_attention_decode_static_capacity_floats.restype = ctypes.c_longlong
     return lib
+
+
+def _plain_attention(q, k, v, tables, ctx_lens):
+    """What the entry point computes, by the plain PyTorch stand-in of the attention kernels."""
+    import types
+
+    from tests.ref_ops import RefOps
+
+    b = len(ctx_lens)
+    ctx = types.SimpleNamespace(
+        num_tokens=b, num_seqs=b,
+        positions=torch.tensor([c - 1 for c in ctx_lens], dtype=torch.int32, device="cuda"),
+        seq_of_token=torch.arange(b, dtype=torch.int32, device="cuda"))
+    out = torch.empty_like(q)
+    RefOps().paged_attention(q, k, v, tables, ctx, NH, NKV, HD, PAGE, HD ** -0.5, 0, out)
+    return out
 
 
 def _case(ctx_lens, seed):
@@ -78,18 +97,24 @@ def test_static_scratch_entry_point_matches_the_regular_one_twice_in_a_row():
         assert rc == 0
         torch.cuda.synchronize()
         assert not tickets.any()  # the launch left its counters at zero
+        plain = _plain_attention(q, k, v, tables, ctx_lens)
         got = torch.zeros_like(q)
+        torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
+        free_before, _ = torch.cuda.mem_get_info()
         rc = lib.ie_attention_decode_static(q.data_ptr(), k.data_ptr(), v.data_ptr(), tables.data_ptr(),
                                             tables.shape[1], cu_q.data_ptr(), ctx.data_ptr(), got.data_ptr(),
                                             b, NH, NKV, PAGE, k.shape[0], HD ** -0.5, 0, splits,
                                             err.data_ptr(), stream, msg, len(msg))
         assert rc == 0, msg.value.decode()
         torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        assert free_after == free_before, "the device's free memory changed across the call"
         assert torch.cuda.memory_allocated() == before
         assert err.tolist()[0] == 0
         assert bool(got.float().abs().sum() > 0)
         torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+        torch.testing.assert_close(got.float(), plain.float(), atol=2e-2, rtol=2e-2)
 
 
 def test_static_scratch_entry_point_refuses_what_does_not_fit():

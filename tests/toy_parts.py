@@ -118,6 +118,7 @@ def register_toys() -> None:
     register_part("feed_forward", "toy_routed", ToyRoutedFeedForward, replace=True)
     register_part("position", "toy_learned", ToyLearnedPositions, replace=True)
     register_architecture("ToyHybridForTests", ToyConfig, toy_spec, replace=True)
+    register_architecture("ToyTwoAttentionsForTests", TwoAttentionsConfig, two_attentions_spec, replace=True)
 
 
 # --- the toy architecture -----------------------------------------------------------------------
@@ -260,3 +261,103 @@ def plain_toy_logits(weights: dict, ids: list[int]) -> torch.Tensor:
     x = state_layer(x)
     x = attn_layer(x, "l0", None, reuse="l0")
     return P.rms_norm(x, w["norm"], c["eps"]) @ w["head"].t()
+
+
+# --- a second toy: two attention groups of different head size, one of them windowed ------------
+# (no state of its own, so decode steps can be captured and launched ahead)
+
+
+@dataclasses.dataclass(frozen=True)
+class TwoAttentionsConfig:
+    architecture: str
+    vocab_size: int
+    hidden_size: int
+    intermediate_size: int
+    wide: tuple  # (query heads, key/value heads, head size) of the layer that sees everything
+    narrow: tuple  # the same for the layer that sees a window
+    window: int
+    eps: float
+    max_position_embeddings: int
+
+    @classmethod
+    def from_dict(cls, raw):
+        values = {f.name: raw[f.name] for f in dataclasses.fields(cls)[1:]}
+        values["wide"], values["narrow"] = tuple(values["wide"]), tuple(values["narrow"])
+        return cls(raw["architectures"][0], **values)
+
+
+TWO_ATTENTIONS_CONFIG = {
+    "architectures": ["ToyTwoAttentionsForTests"], "vocab_size": 113, "hidden_size": 48,
+    "intermediate_size": 56, "wide": [6, 2, 16], "narrow": [2, 1, 32], "window": 11, "eps": 1e-5,
+    "max_position_embeddings": 256,
+}
+
+
+def two_attentions_spec(cfg: TwoAttentionsConfig) -> ModelSpec:
+    def layer(p, shape, position, window):
+        nh, nkv, hd = shape
+        return LayerSpec(
+            prefix=p, block=PartSpec("prenorm_residual"),
+            mixer=PartSpec("paged_attention", {
+                "q_proj": f"{p}.q", "k_proj": f"{p}.k", "v_proj": f"{p}.v", "o_proj": f"{p}.o",
+                "num_heads": nh, "num_kv_heads": nkv, "head_dim": hd, "position": position, "window": window}),
+            feed_forward=PartSpec("swiglu", {"gate_proj": f"{p}.gate", "up_proj": f"{p}.up",
+                                             "down_proj": f"{p}.down",
+                                             "intermediate_size": cfg.intermediate_size}),
+            norms={"pre_mixer": PartSpec("rms", {"weight": f"{p}.n1", "eps": cfg.eps}),
+                   "pre_feed_forward": PartSpec("rms", {"weight": f"{p}.n2", "eps": cfg.eps})})
+
+    return ModelSpec(
+        architecture=cfg.architecture, vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size,
+        max_position_embeddings=cfg.max_position_embeddings,
+        embedding=PartSpec("token", {"weight": "embed", "vocab_size": cfg.vocab_size}),
+        positions={"rotary_wide": PartSpec("rotary", {"rotary_dim": cfg.wide[2], "theta": 10000.0}),
+                   "rotary_narrow": PartSpec("rotary", {"rotary_dim": cfg.narrow[2], "theta": 3000.0})},
+        layers=(layer("a", cfg.wide, "rotary_wide", None), layer("b", cfg.narrow, "rotary_narrow", cfg.window)),
+        schedule=(ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0)),  # the wide layer runs twice
+        final_norm=PartSpec("rms", {"weight": "norm", "eps": cfg.eps}),
+        head=PartSpec("linear", {"weight": None, "vocab_size": cfg.vocab_size}))
+
+
+def two_attentions_weights(seed: int = 0) -> dict:
+    from inference_engine_b200.config import build_model_spec, config_from_dict
+    from inference_engine_b200.engine.model import declared_weights
+
+    register_toys()
+    decl = declared_weights(build_model_spec(config_from_dict(TWO_ATTENTIONS_CONFIG)))
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, d in decl.items():
+        t = torch.randn(d.shape, generator=g) * 0.08
+        if name.endswith((".n1", ".n2")) or name == "norm":
+            t = t + 1.0
+        if name.endswith((".q", ".k")):
+            t = t * 3.0
+        out[name] = t.to(torch.bfloat16)
+    return out
+
+
+def plain_two_attentions_logits(weights: dict, ids: list[int]) -> torch.Tensor:
+    c = TWO_ATTENTIONS_CONFIG
+    w = {k: v.float() for k, v in weights.items()}
+    t = len(ids)
+    x = w["embed"][torch.tensor(ids)]
+
+    def layer(x, p, shape, theta, window):
+        nh, nkv, hd = shape
+        inv = 1.0 / (theta ** (torch.arange(0, hd, 2).float() / hd))
+        cos, sin = P.rope_angles(inv, torch.arange(t))
+        z = P.rms_norm(x, w[f"{p}.n1"], c["eps"])
+        q = P.apply_rope((z @ w[f"{p}.q"].t()).view(t, nh, hd).transpose(0, 1), cos, sin)
+        k = P.apply_rope((z @ w[f"{p}.k"].t()).view(t, nkv, hd).transpose(0, 1), cos, sin)
+        v = (z @ w[f"{p}.v"].t()).view(t, nkv, hd).transpose(0, 1)
+        h = x + P.attention(q, k, v, window).transpose(0, 1).reshape(t, nh * hd) @ w[f"{p}.o"].t()
+        z = P.rms_norm(h, w[f"{p}.n2"], c["eps"])
+        act = z @ w[f"{p}.gate"].t()
+        act = act / (1 + torch.exp(-act)) * (z @ w[f"{p}.up"].t())
+        return h + act @ w[f"{p}.down"].t()
+
+    x = layer(x, "a", c["wide"], 10000.0, None)
+    x = layer(x, "b", c["narrow"], 3000.0, c["window"])
+    x = layer(x, "a", c["wide"], 10000.0, None)
+    return P.rms_norm(x, w["norm"], c["eps"]) @ w["embed"].t()

@@ -15,7 +15,12 @@ request and step over 16-token cache pages.  A "step" is one decode step.
                wall clock with a device synchronisation on both sides;
 ``prefill``    one 2,048-token prompt through the step function;
 ``roofline``   bytes the decode step has to read (every weight once, the live cache) / time;
-``points``     decode tokens per second at batch 1 and 64.
+``points``     decode tokens per second at batch 1 and 64, each with its fraction of the HBM
+               roofline (``decode_b1_frac``, ``decode_b64_frac``);
+``kernels``    where the time goes: CUDA-event time of every kind of kernel inside an eagerly
+               launched decode step (batch 8, and the attention at batch 64) and inside the
+               2,048-token prefill, per launch, with the bytes or flops it has to move and the
+               fraction of the measured peak that makes.
 
 ``--impl reference`` runs the unmodified reference engine (installed under baseline/_ref) on
 the same shape and batch through its own ``load_model`` / ``LLMEngine`` and prints the same
@@ -50,6 +55,7 @@ LLAMA_1B = {
     "bos_token_id": 128000, "eos_token_id": [128001, 128008, 128009], "torch_dtype": "bfloat16",
 }
 PROMPT_LEN, PREFILL_LEN, BLOCK_SIZE, MAX_CONTEXT = 1024, 2048, 16, 8192
+METRIC = "decode tokens/s, Llama 3.2 1B shape, batch 8"  # both arms print the same string
 
 
 def measured_peaks() -> tuple[dict, str]:
@@ -143,9 +149,10 @@ def prefill_flops(cfg: dict, tokens: int) -> float:
 # --- our engine ---------------------------------------------------------------------------------
 
 
-def decode_device_timed(engine, batch: int, steps: int, warmup: int, seed: int):
+def decode_device_timed(engine, batch: int, steps: int, warmup: int, seed: int, breakdown: bool = False):
     """Prefill `batch` prompts, then time `steps` decode steps of the step function on the
-    device.  Returns (tokens/s, ms per step, mean context, launches of our kernels)."""
+    device.  Returns (tokens/s, ms per step, mean context, launches of our kernels, and with
+    `breakdown` the device time per kind of kernel of an eagerly launched step)."""
     import torch
 
     from inference_engine_b200.engine.batch import StepEntry
@@ -188,10 +195,23 @@ def decode_device_timed(engine, batch: int, steps: int, warmup: int, seed: int):
     if engine.graphs is not None:
         launches += steps * engine.graphs.kernels_per_replay(batch)
     engine.ops.check_errors()
+    kinds = None
+    if breakdown:  # a few more steps, launched eagerly with events around every kernel
+        runs = []
+        for k in range(3):
+            for rid in ids:
+                cache.grow(rid, pos, pos + 1)
+            entries = [StepEntry(rid, [feed[k][i]], pos, [0]) for i, rid in enumerate(ids)]
+            with engine.ops.timed() as timer:
+                runner.step(entries)
+            runs.append(timer.summary())
+            pos += 1
+        kinds = {name: {"launches": runs[-1][name]["launches"],
+                        "ms": statistics.median(r[name]["ms"] for r in runs)} for name in runs[-1]}
     for rid in ids:
         cache.free(rid)
     mean_ctx = (first_ctx + pos) / 2
-    return batch * steps / (ms / 1e3), ms / steps, mean_ctx, launches
+    return batch * steps / (ms / 1e3), ms / steps, mean_ctx, launches, kinds
 
 
 def decode_end_to_end(engine, batch: int, steps: int, warmup: int, seed: int):
@@ -219,7 +239,7 @@ def decode_end_to_end(engine, batch: int, steps: int, warmup: int, seed: int):
     h2d = engine.runner.last_h2d_bytes
     for i in range(batch):
         engine.abort(f"e2e-{seed}-{i}")
-    return tokens / elapsed, h2d, batch * 4
+    return tokens / elapsed, h2d, batch * 4 + 16  # the tokens and the kernels' 16-byte error word
 
 
 def prefill_timed(engine, repeats: int = 5):
@@ -244,7 +264,53 @@ def prefill_timed(engine, repeats: int = 5):
         if r >= 2:
             times.append(s.elapsed_time(e))
         cache.free(rid)
-    return statistics.median(times)
+    # once more with events around every kernel
+    prompt = torch.randint(0, vocab, (PREFILL_LEN,), generator=g).tolist()
+    cache.add_request("prefill-kinds")
+    cache.grow("prefill-kinds", 0, PREFILL_LEN)
+    with engine.ops.timed() as timer:
+        runner.step([StepEntry("prefill-kinds", prompt, 0, [PREFILL_LEN - 1])])
+    kinds = timer.summary()
+    cache.free("prefill-kinds")
+    return statistics.median(times), kinds
+
+
+KINDS = {"linear:attn.qkv": "K3_qkv", "attention.decode": "K5_decode_attention",
+         "attention.prefill": "K6_prefill_attention", "linear:mixer.delta": "K7_out_proj",
+         "linear:ffn.gate_up": "K8_gate_up", "linear:ffn.delta": "K10_down", "linear:head": "K11_head",
+         "norm": "K2_norm", "rotary+cache": "K4_rotary_cache", "activation": "K9_silu_mul",
+         "embedding": "K1_embedding"}
+
+
+def kernel_rows(cfg: dict, kinds: dict, peaks: dict, tokens: int, batch: int, ctx: float, decode: bool) -> dict:
+    """Per kind of kernel: microseconds per launch and what that is of the measured peak: of the
+    copy bandwidth for the bytes a decode launch has to read (its weights once; for the attention
+    the batch's cached keys and values of one layer), of the burst bf16 rate for the flops of a
+    prefill launch.  Kinds without such a figure (norms, rotary, activation) give the time only."""
+    h, i, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    q = cfg["num_attention_heads"] * cfg["head_dim"]
+    kv = cfg["num_key_value_heads"] * cfg["head_dim"]
+    weights = {"K3_qkv": h * (q + 2 * kv), "K7_out_proj": q * h, "K8_gate_up": 2 * h * i,
+               "K10_down": i * h, "K11_head": v * h}
+    rows = {}
+    for kind, row in kinds.items():
+        name = KINDS.get(kind, kind)
+        us = row["ms"] / row["launches"] * 1e3
+        out = {"us": round(us, 2), "launches": row["launches"]}
+        if decode and name in weights:
+            gbs = 2 * weights[name] / (us * 1e-6) / 1e9
+            out.update(gbs=round(gbs, 1), frac=round(gbs / peaks["hbm_gbs"], 3))
+        elif decode and name == "K5_decode_attention":
+            gbs = batch * ctx * 2 * kv * 2 / (us * 1e-6) / 1e9
+            out.update(gbs=round(gbs, 1), frac=round(gbs / peaks["hbm_gbs"], 3))
+        elif not decode and name in weights and name != "K11_head":
+            tflops = 2.0 * tokens * weights[name] / (us * 1e-6) / 1e12
+            out.update(tflops=round(tflops, 1), frac=round(tflops / peaks["bf16_tflops"], 3))
+        elif not decode and name == "K6_prefill_attention":
+            tflops = 2.0 * tokens * tokens * q / (us * 1e-6) / 1e12  # causal: half of 4 T^2 nh hd
+            out.update(tflops=round(tflops, 1), frac=round(tflops / peaks["bf16_tflops"], 3))
+        rows[name] = out
+    return rows
 
 
 def run_ours(args) -> dict:
@@ -264,19 +330,31 @@ def run_ours(args) -> dict:
         max_num_batched_tokens=4 * PROMPT_LEN, enable_cuda_graphs=True)
     sampler = ClockSampler()
     sampler.start()
-    tps, ms_step, mean_ctx, launches = decode_device_timed(engine, args.batch, args.steps, args.warmup, 1)
+    tps, ms_step, mean_ctx, launches, kinds8 = decode_device_timed(engine, args.batch, args.steps, args.warmup, 1,
+                                                                   breakdown=True)
     e2e_tps, h2d, d2h = decode_end_to_end(engine, args.batch, args.steps, args.warmup, 2)
-    prefill_ms = prefill_timed(engine)
+    prefill_ms, kinds_prefill = prefill_timed(engine)
     small = max(args.steps // 2, 16)
-    b1, _, _, _ = decode_device_timed(engine, 1, small, args.warmup, 3)
-    b64, ms64, ctx64, _ = decode_device_timed(engine, 64, small, args.warmup, 4)
+    b1, ms1, ctx1, _, _ = decode_device_timed(engine, 1, small, args.warmup, 3)
+    b64, ms64, ctx64, _, kinds64 = decode_device_timed(engine, 64, small, args.warmup, 4, breakdown=True)
     clocks = sampler.stop()
 
-    step_bytes = weight_bytes_read_per_step(cfg) + args.batch * mean_ctx * kv_bytes_per_token(cfg)
-    achieved = step_bytes / (ms_step / 1e3) / 1e9
+    def hbm_rate(batch, ctx, ms):
+        return (weight_bytes_read_per_step(cfg) + batch * ctx * kv_bytes_per_token(cfg)) / (ms / 1e3) / 1e9
+
+    achieved = hbm_rate(args.batch, mean_ctx, ms_step)
     flops = prefill_flops(cfg, PREFILL_LEN)
+    kernels = {
+        f"decode_b{args.batch}": kernel_rows(cfg, kinds8, peaks, args.batch, args.batch, mean_ctx, True),
+        "decode_b64": {k: v for k, v in kernel_rows(cfg, kinds64, peaks, 64, 64, ctx64, True).items()
+                       if k == "K5_decode_attention"},
+        f"prefill_{PREFILL_LEN}": kernel_rows(cfg, kinds_prefill, peaks, PREFILL_LEN, 1, PREFILL_LEN, False),
+        "how": "CUDA events around every kernel of one eagerly launched step (median of 3 for decode), "
+               "per launch; decode: bytes / time of the measured copy rate, prefill: flops / time of the "
+               "measured burst bf16 rate",
+    }
     return {
-        "metric": "decode tokens/s, Llama 3.2 1B shape, batch 8 (prefill and batch 1/64 alongside)",
+        "metric": METRIC,
         "value": round(tps, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms_step, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
@@ -290,6 +368,7 @@ def run_ours(args) -> dict:
             "global_batch": args.batch, "seq_len": PROMPT_LEN, "max_context": MAX_CONTEXT,
             "prefill_tokens": PREFILL_LEN, "block_size": BLOCK_SIZE, "parallelism": "single-gpu",
             "l2": "inputs larger than L2 (2.47 GB of weights per step)", "peaks": peaks_kind,
+            "max_model_len": engine.max_model_len,
         },
         "e2e": {"value": round(e2e_tps, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h},
@@ -298,7 +377,10 @@ def run_ours(args) -> dict:
                     "frac": round(flops / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4)},
-        "points": {"decode_b1": round(b1, 1), "decode_b64": round(b64, 1)},
+        "points": {"decode_b1": round(b1, 1), "decode_b64": round(b64, 1),
+                   "decode_b1_frac": round(hbm_rate(1, ctx1, ms1) / peaks["hbm_gbs"], 4),
+                   "decode_b64_frac": round(hbm_rate(64, ctx64, ms64) / peaks["hbm_gbs"], 4)},
+        "kernels": kernels,
         "gpu_launches": int(launches),
         "clocks": clocks,
     }
@@ -338,14 +420,14 @@ def run_reference(args) -> dict:
         prompts = torch.randint(0, LLAMA_1B["vocab_size"], (args.batch, PROMPT_LEN), generator=g).tolist()
         params = RefParams(temperature=0.0, max_tokens=args.warmup + args.steps + 8)
 
-        def attempt(tag: str, **mode):
+        def attempt(tag: str, batch: int, **mode):
             engine = RefEngine(model, _StubTokenizer(), (), num_blocks=blocks, block_size=BLOCK_SIZE,
-                               max_num_seqs=max(args.batch, 8), max_num_batched_tokens=4 * PROMPT_LEN,
+                               max_num_seqs=max(batch, 8), max_num_batched_tokens=4 * PROMPT_LEN,
                                enable_prefix_caching=False, max_model_len=MAX_CONTEXT, **mode)
-            for i, p in enumerate(prompts):
+            for i, p in enumerate(prompts[:batch]):
                 engine.add_request(f"ref-{tag}-{i}", p, params)
             produced = 0
-            while produced < args.batch * args.warmup:
+            while produced < batch * args.warmup:
                 produced += len(engine.step())
             torch.cuda.synchronize()
             t0 = time.perf_counter()
@@ -353,22 +435,48 @@ def run_reference(args) -> dict:
             for _ in range(args.steps):
                 tokens += len(engine.step())
             torch.cuda.synchronize()
-            return tokens, time.perf_counter() - t0
+            elapsed = time.perf_counter() - t0
+            used_graph = bool(engine.step_log and engine.step_log[-1].get("graph"))
+            for i in range(batch):
+                engine.abort(f"ref-{tag}-{i}")
+            return tokens, elapsed, used_graph
+
+        def copies(batch: int, graph: bool) -> tuple[int, int]:
+            """Bytes its step copies to the device and back, counted from the tensors it builds
+            (a captured decode step: engine/runtime/cuda_graphs.py:87-108; an eager one:
+            engine/runtime/paged_cache.py:98-123 and engine/runtime/engine.py:225-229); the
+            tokens come back as one 64-bit integer per row (engine.py:229)."""
+            ctx = PROMPT_LEN + args.warmup + args.steps // 2
+            if graph:  # ids, positions, slots (64-bit), lengths and block tables (32-bit), padded to the bucket
+                bucket = next(n for n in (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256) if n >= batch)
+                return bucket * (3 * 8 + 4) + bucket * -(-ctx // BLOCK_SIZE) * 4, batch * 8
+            # every cached position's slot per request, the new slots, starts, lengths (twice), ids, positions: 64-bit
+            return 8 * (batch * ctx + batch + (batch + 1) + 2 * batch + 2 * batch), batch * 8
 
         sampler = ClockSampler()
         sampler.start()
         mode = "default (Triton decode kernel, CUDA graphs)"
         try:
-            tokens, elapsed = attempt("default")
+            tokens, elapsed, used_graph = attempt("default", args.batch)
         except Exception as first:  # its fast path needs a newer torch than this image has
             mode = (f"eager (use_triton=False, its bench_decode.py 'eager' mode); the default mode "
                     f"raised {type(first).__name__}: {str(first)[:120]}")
             torch.cuda.synchronize()
-            tokens, elapsed = attempt("eager", use_triton=False)
+            tokens, elapsed, used_graph = attempt("eager", args.batch, use_triton=False)
+        # One request alone never meets the call that fails above (it is made for several prompts
+        # in one step), so batch 1 also runs in the reference's default, fastest mode.
+        points = {}
+        try:
+            t1, e1, g1 = attempt("b1", 1)
+            points = {"decode_b1": round(t1 / e1, 1),
+                      "decode_b1_mode": "default (Triton decode kernel%s)" % (", CUDA graphs" if g1 else "")}
+        except Exception as exc:
+            points = {"decode_b1": None, "decode_b1_mode": f"default mode raised {type(exc).__name__}: {str(exc)[:100]}"}
         clocks = sampler.stop()
         tps = tokens / elapsed
+        h2d, d2h = copies(args.batch, used_graph)
         return {
-            "metric": "decode tokens/s, Llama 3.2 1B shape, batch 8", "value": round(tps, 1),
+            "metric": METRIC, "value": round(tps, 1),
             "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(elapsed / args.steps * 1e3, 4), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "impl": "reference",
@@ -377,7 +485,9 @@ def run_reference(args) -> dict:
                        "seq_len": PROMPT_LEN, "block_size": BLOCK_SIZE, "parallelism": "single-gpu",
                        "mode": mode,
                        "timing": "wall clock around LLMEngine.step(), synchronised on both sides"},
-            "e2e": {"value": round(tps, 1), "unit": "tokens/s"},
+            "e2e": {"value": round(tps, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h},
+            "points": points,
             "clocks": clocks,
         }
     except Exception as exc:  # the reference is other people's code on hardware it never saw

@@ -18,6 +18,7 @@ class EngineConfig:
     max_model_len: int | None = None
     enable_cuda_graphs: bool | None = None  # None: where they can be captured (a GPU, no state slots)
     debug_checks: bool = False
+    profile_kernels: bool = False  # time every eagerly launched step per kind of kernel (into step_log)
 
     def __post_init__(self) -> None:
         if self.dtype not in ("bfloat16", "float32"):

@@ -365,6 +365,9 @@ static int launch_rope(const float* qkv, int num_partials, size_t partial_stride
     }
 }
 
+// 1: kernels are launched with the programmatic-serialization attribute (the default); 0: plain launches.
+IE_API void ie_set_pdl(int enabled) { ie_pdl_enabled() = enabled ? 1 : 0; }
+
 IE_API int ie_rope_kv_write(const float* qkv, int num_partials, long long partial_stride,
                             const int* positions, const float* table, int rotary_dim, int table_rows,
                             void* q_out, void* k_cache, void* v_cache, int dtype,

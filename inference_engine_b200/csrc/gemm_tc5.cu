@@ -39,6 +39,16 @@ struct Tc5Plan {
     int tmem_cols;          // power of two >= max(32, m_pad)
 };
 
+#ifdef IE_TEST_STARVE
+// Self-test build only (kernels/build.py: build_selftest).  While this flag is set, every block
+// leaves out the last copy of X although it has told the slot's mbarrier to expect its bytes:
+// the tensor-core thread's wait for that slot must run out, the block must record
+// IE_ERR_TIMEOUT, give its tensor memory back and return.  Nothing is in flight when it does:
+// every copy that was asked for is tracked by a barrier that completed long before the wait
+// gives up.  The library that serves generation is built without this code.
+static __device__ int g_starve_last_x;
+#endif
+
 struct __align__(8) Tc5Shared {
     unsigned long long full[MAX_OPS], empty[MAX_OPS], acc_done;
     unsigned tmem_base;
@@ -92,6 +102,9 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
                 tma_load_3d(ring + (size_t)s * op_bytes, &w_map, 0, n0, kb0 + o * p.kpo, &sh->full[s]);
             };
             auto copy_x = [&](int o) {
+#ifdef IE_TEST_STARVE
+                if (g_starve_last_x && o == nops - 1) return;
+#endif
                 int s = o % p.ops;
                 tma_load_3d(ring + (size_t)s * op_bytes + p.kpo * W_TILE_BYTES, &x_map, 0, 0, kb0 + o * p.kpo,
                             &sh->full[s]);
@@ -180,6 +193,12 @@ int launch(const void* X, const void* W, OutT* out, const Tc5Plan& p, int splits
     return ie_launch(gemm_tc5_kernel<OutT>, grid, dim3(THREADS), SMEM_BYTES, s, wm, xm, out, p, err);
 }
 }  // namespace
+
+#ifdef IE_TEST_STARVE
+IE_API int ie_test_starve_tc5(int on) {
+    return (int)cudaMemcpyToSymbol(g_starve_last_x, &on, sizeof(int));
+}
+#endif
 
 // 1 if the product of these sizes can run here: 16 < M <= 256, K a multiple of 64.
 IE_API int ie_gemm_tc5_ok(int M, int N, int K) {

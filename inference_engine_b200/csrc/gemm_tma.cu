@@ -40,6 +40,14 @@ constexpr int MAX_KPO = 4;                // k blocks per copy
 // Shared memory for tiles: what the 227 KB of an SM leave beside X (8 NT rows x 2048 k)
 __host__ __device__ constexpr int ring_bytes(int nt) { return nt == 1 ? 192 * 1024 : 160 * 1024; }
 
+#ifdef IE_TEST_STARVE
+// Self-test build only (kernels/build.py: build_selftest).  While this flag is set, every block
+// leaves out the last box of X although the barrier was told to expect all of them: the
+// consumers' wait for X must run out, the block must record IE_ERR_TIMEOUT and return.  The
+// copies of W that were asked for meanwhile are few and complete long before the wait gives up.
+static __device__ int g_starve_last_x;
+#endif
+
 // Shared memory: [ring: ops x kpo x 16 KB][X: kblocks x (8 NT rows x 128 B)][barriers], 1024-byte aligned.
 // NT: 8-token column tiles (1: M <= 8, 2: M <= 16).  `kpo` k blocks per copy (3-D map) or 1 (2-D map).
 template <int NT, typename OutT>
@@ -97,8 +105,12 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
             ie_pdl_wait();  // X is the previous kernel's output
             if (nkb > 0) {
                 mbar_expect_tx(x_full, nkb * XBOX_BYTES);
-                for (int kb = 0; kb < nkb; ++kb)
+                for (int kb = 0; kb < nkb; ++kb) {
+#ifdef IE_TEST_STARVE
+                    if (g_starve_last_x && kb == nkb - 1) break;
+#endif
                     tma_load_2d(xs + (size_t)kb * XBOX_BYTES, &x_map, (kb0 + kb) * BK, 0, x_full);
+                }
             }
             for (; issued < nops; ++issued) {
                 int round = issued / ops;  // this slot's round-th reuse: wait for its release
@@ -207,6 +219,12 @@ int launch(const void* X, const void* W, OutT* out, int M, int N, int K, int kbl
                      kblocks_per_split, ops, kpo, w3d, err);
 }
 }  // namespace
+
+#ifdef IE_TEST_STARVE
+IE_API int ie_test_starve_tma(int on) {
+    return (int)cudaMemcpyToSymbol(g_starve_last_x, &on, sizeof(int));
+}
+#endif
 
 // 1 if the driver offers tensor-map encoding (it always does on the GPUs this library targets).
 IE_API int ie_gemm_tma_available() { return encode_fn() != nullptr ? 1 : 0; }

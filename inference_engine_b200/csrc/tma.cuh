@@ -11,7 +11,12 @@ typedef __nv_bfloat16 bf16;
 // Polls of an mbarrier before a wait gives up.  A poll that fails comes back after about two
 // microseconds (the hardware suspends the thread meanwhile), so this is some tenths of a second:
 // far longer than any kernel a waiting block may sit behind, short enough to notice.
-constexpr int SPIN_LIMIT = 200000;
+// (IE_SPIN_LIMIT: the self-test build sets a few dozen polls, so that a wait which is made to
+// run out on purpose does so in a fraction of a millisecond.)
+#ifndef IE_SPIN_LIMIT
+#define IE_SPIN_LIMIT 200000
+#endif
+constexpr int SPIN_LIMIT = IE_SPIN_LIMIT;
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {

@@ -193,7 +193,7 @@ class LLMEngine:
     def step(self) -> list[RequestOutput]:
         started = time.perf_counter()
         preempted_before = self.scheduler.num_preemptions
-        logits = None
+        logits = kernel_times = None
         ahead, self._ahead = self._ahead, None
         prepared, self._prepared = self._prepared, None
         if ahead is not None:
@@ -232,6 +232,10 @@ class LLMEngine:
             if self.graphs is not None and len(sampled) == len(entries) and self.graphs.can_run(entries):
                 logits = self.graphs.run(entries)
                 used_graph = True
+            elif self.config.profile_kernels and hasattr(self.ops, "timed"):
+                with self.ops.timed() as timer:
+                    logits = self.runner.step(entries)
+                kernel_times = {k: round(v["ms"], 4) for k, v in timer.summary().items()}
             else:
                 logits = self.runner.step(entries)
 
@@ -288,6 +292,8 @@ class LLMEngine:
             "graph": used_graph,
             "preempted": self.scheduler.num_preemptions - preempted_before,
         })
+        if kernel_times is not None:  # device ms per kind of kernel (EngineConfig.profile_kernels)
+            self.step_log[-1]["kernels_ms"] = kernel_times
         return outputs
 
     # While the device runs a decode step the host already knows what the next one looks like

@@ -129,6 +129,16 @@ def build_core() -> Path:
     return build_library("ie_b200_core", CORE_SOURCES)
 
 
+def build_selftest() -> Path:
+    """The TMA-fed matrix products once more, as the tests' self-test library: waits give up
+    after 256 polls instead of 200,000, and a switch (``ie_test_starve_tma/tc5``) makes a block
+    expect a copy that is never asked for, so that a wait runs out, in a fraction of a
+    millisecond, and the way out of it (report, give tensor memory back, return) can be
+    tested.  Generation never loads this library."""
+    return build_library("ie_b200_selftest", ["gemm_tma.cu", "gemm_tc5.cu"],
+                         ["-DIE_SPIN_LIMIT=256", "-DIE_TEST_STARVE=1"])
+
+
 ATTENTION_HEAD_DIMS = tuple(range(16, 129, 16))  # head sizes the tensor-core attention takes
 
 
@@ -144,7 +154,7 @@ def build_attention(head_dim: int) -> Path:
 def build_all(prune: bool = True) -> list[Path]:
     """Every library the package can load (the build check compiles them all).  With `prune`,
     libraries of this package in the build folder that belong to older sources are removed."""
-    libs = [build_core()]
+    libs = [build_core(), build_selftest()]
     with ThreadPoolExecutor(max_workers=os.cpu_count() or 2) as pool:
         libs += list(pool.map(build_attention, ATTENTION_HEAD_DIMS))
     if prune:

@@ -11,6 +11,7 @@ the embedding gather and sampling are the kernels under ``csrc/``.
 
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import os
 from ctypes import c_float, c_int, c_void_p
@@ -28,6 +29,62 @@ _ERRORS = {
 
 class KernelError(RuntimeError):
     pass
+
+
+class KernelTimer:
+    """Device time per kind of kernel, from CUDA events recorded around every launch made while
+    the timer is active (``with ops.timed() as timer``).  The events sit between the kernels,
+    so a kernel's start-up no longer overlaps its predecessor: the sum is a little more than
+    the step takes untimed; the shares are what it is for."""
+
+    def __init__(self, torch) -> None:
+        self.torch = torch
+        self.spans: list[tuple[str, object, object]] = []
+
+    def begin(self, name: str):
+        start = self.torch.cuda.Event(enable_timing=True)
+        start.record()
+        return name, start
+
+    def end(self, span) -> None:
+        stop = self.torch.cuda.Event(enable_timing=True)
+        stop.record()
+        self.spans.append((span[0], span[1], stop))
+
+    def summary(self) -> dict[str, dict]:
+        """kind -> {"launches": n, "ms": total device time}; waits for the device."""
+        self.torch.cuda.synchronize()
+        out: dict[str, dict] = {}
+        for name, start, stop in self.spans:
+            row = out.setdefault(name, {"launches": 0, "ms": 0.0})
+            row["launches"] += 1
+            row["ms"] += start.elapsed_time(stop)
+        return out
+
+
+def _kind(name):
+    """Marks a kernel method with the kind its launches are counted under by a KernelTimer and
+    shown under in a profiler's timeline (NVTX ranges, with IE_B200_NVTX=1).  ``name`` is a
+    string or a function of the call's keyword arguments."""
+    def decorate(method):
+        def call(self, *args, **kwargs):
+            timer, nvtx = self._timer, self.nvtx
+            if timer is None and not nvtx:
+                return method(self, *args, **kwargs)
+            label = name if isinstance(name, str) else name(kwargs)
+            if nvtx:
+                self.torch.cuda.nvtx.range_push(label)
+            span = timer.begin(label) if timer is not None else None
+            try:
+                return method(self, *args, **kwargs)
+            finally:
+                if span is not None:
+                    timer.end(span)
+                if nvtx:
+                    self.torch.cuda.nvtx.range_pop()
+        call.__name__, call.__doc__ = method.__name__, method.__doc__
+        return call
+    return decorate
 
 
 def _dtype_code(t) -> int:
@@ -102,6 +159,8 @@ class CudaOps:
         self.batch_gemm_one_round = os.environ.get("IE_B200_BATCH_GEMM_ONE_ROUND", "1") != "0"
         self._device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self._raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+        self._timer: KernelTimer | None = None
+        self.nvtx = os.environ.get("IE_B200_NVTX", "0") == "1"  # an NVTX range around every kernel call
         self.launches = 0  # launches of this library's kernels (library matrix products not counted)
         self.launch_counts: dict[str, int] = {}  # the same, per kernel
 
@@ -159,8 +218,21 @@ class CudaOps:
             raise KernelError(f"kernel check failed: {_ERRORS.get(code, code)} "
                               f"(value {value}, at row/token {where})")
 
+    @contextlib.contextmanager
+    def timed(self):
+        """``with ops.timed() as timer: ...; timer.summary()``: CUDA-event time per kind of kernel
+        for everything launched inside the block (eager launches only: a replayed capture is one
+        launch)."""
+        timer = KernelTimer(self.torch)
+        self._timer = timer
+        try:
+            yield timer
+        finally:
+            self._timer = None
+
     # --- kernels ----------------------------------------------------------------------------
 
+    @_kind("embedding")
     def embedding(self, table, ids, out) -> None:
         self._check(self._embedding(table.data_ptr(), _dtype_code(table), ids.data_ptr(),
                                     out.data_ptr(), ids.shape[0], table.shape[1], table.shape[0],
@@ -174,6 +246,7 @@ class CudaOps:
             return 1, 0
         return t.shape[0], t.stride(0)
 
+    @_kind("norm")
     def rmsnorm(self, h, delta, weight, eps, out, rows=None) -> None:
         n = h.shape[0] if rows is None else rows.shape[0]
         parts, stride = self._partials(delta)
@@ -202,6 +275,7 @@ class CudaOps:
                 break
         return per, -(-total // per)
 
+    @_kind(lambda kwargs: "linear:" + kwargs.get("tag", "linear"))
     def linear(self, x, w, out=None, *, ws=None, tag="linear", out_dtype=None, allow_split=False):
         """``x[M, K] @ w[N, K]^T``.  With ``out`` given the product is written there; otherwise a
         buffer named ``tag`` is taken from ``ws``.  With ``allow_split`` the result may come back
@@ -261,6 +335,7 @@ class CudaOps:
             torch.mm(x, w.t(), out_dtype=out.dtype, out=out)
         return out
 
+    @_kind("rotary+cache")
     def rope_kv_write(self, qkv, positions, table, rotary_dim, q_out, k_cache, v_cache,
                       slot_mapping, nh, nkv, hd, page_size) -> None:
         if table is not None and table.shape[2] * 2 != rotary_dim:
@@ -389,6 +464,7 @@ class CudaOps:
             return ws.buffer(name, 1, floats, self.torch.float32)
         return self.torch.empty(floats, dtype=self.torch.float32, device=device)
 
+    @_kind("attention.decode")
     def _decode_attention(self, lib, ragged, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, page_size, scale,
                           window, out) -> None:
         """The requests with few rows (the kernels skip the others): key tiles dealt by length
@@ -419,6 +495,7 @@ class CudaOps:
             self._ptr(scratch), self._ptr(tickets), ctx.num_seqs, nh, nkv, page_size,
             total_pages, scale, window, splits, self._err_ptr, stream), "attention_decode")
 
+    @_kind("attention.prefill")
     def _prefill_attention(self, lib, plan, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, page_size,
                            scale, window, out) -> None:
         """The requests with more than 16 rows, in query tiles of `ie_attention_prefill_rows` tokens."""
@@ -452,6 +529,7 @@ class CudaOps:
             ctx.num_seqs, tiles, nh, nkv, page_size, total_pages, scale, window,
             self._err_ptr, stream), "attention_prefill")
 
+    @_kind("attention.general")
     def paged_attention_general(self, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd,
                                 page_size, scale, window, out) -> None:
         self._check(self._paged_attention_generic(
@@ -460,6 +538,7 @@ class CudaOps:
             ctx.positions.data_ptr(), out.data_ptr(), ctx.num_tokens, nh, nkv, hd, page_size,
             k_cache.shape[0], scale, window, self._err_ptr, self._stream()), "paged_attention")
 
+    @_kind("activation")
     def silu_mul(self, gate_up, out) -> None:
         parts, stride = self._partials(gate_up)
         self._check(self._silu_mul(gate_up.data_ptr(), _dtype_code(gate_up), parts, stride,
@@ -477,6 +556,7 @@ class CudaOps:
                                  self._argmax_scratch.data_ptr(), out.data_ptr(), self._stream()), "argmax")
         self.launches += 1
 
+    @_kind("sampling")
     def sample(self, logits, out, temperature=None, top_k=None, top_p=None, min_p=None,
                penalty=None, seen_bits=None, seeds=None, draws=None, logprob=None) -> None:
         """One token per row of 32-bit ``logits``; the per-row tensors are optional (absent:

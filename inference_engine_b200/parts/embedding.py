@@ -67,4 +67,4 @@ class LinearHead(Part):
         import torch
 
         logits = ctx.ws.buffer("logits", x.shape[0], self.vocab_size, torch.float32, rows_cap=None)
-        return ctx.ops.linear(x, self.weight, logits)
+        return ctx.ops.linear(x, self.weight, logits, tag="head")

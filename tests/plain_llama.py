@@ -13,24 +13,43 @@ import math
 
 import torch
 
+# The precision everything is computed in.  32-bit is what the engine is compared with;
+# `in_float64()` switches to 64-bit for the duration of a block, to measure how far 32-bit
+# arithmetic itself is from the exact result at a given size.
+PRECISION = torch.float32
+
+
+class in_float64:
+    def __enter__(self):
+        global PRECISION
+        self.saved, PRECISION = PRECISION, torch.float64
+
+    def __exit__(self, *exc):
+        global PRECISION
+        PRECISION = self.saved
+
+
+def _f(t: torch.Tensor) -> torch.Tensor:
+    return t.to(PRECISION)
+
 
 def embed(weights: dict, token_ids: torch.Tensor) -> torch.Tensor:
     """engine/model/llama.py:25,61 -- rows of the table, no scaling."""
-    return weights["model.embed_tokens.weight"].float()[token_ids]
+    return _f(weights["model.embed_tokens.weight"])[token_ids]
 
 
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     """engine/model/layers.py:41-43 -- x * rsqrt(mean(x^2) + eps), then times weight."""
-    x = x.float()
+    x = _f(x)
     normed = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
-    return weight.float() * normed
+    return _f(weight) * normed
 
 
 def rope_inv_freq(cfg: dict) -> torch.Tensor:
     """engine/model/layers.py:55-73 -- theta^(-2j/d), then the llama3 band scaling."""
     hd = cfg.get("head_dim") or cfg["hidden_size"] // cfg["num_attention_heads"]
     theta = float(cfg.get("rope_theta", 10000.0))
-    inv_freq = 1.0 / (theta ** (torch.arange(0, hd, 2, dtype=torch.int64).float() / hd))
+    inv_freq = 1.0 / (theta ** (_f(torch.arange(0, hd, 2, dtype=torch.int64)) / hd))
     s = cfg.get("rope_scaling")
     if not s:
         return inv_freq
@@ -50,7 +69,7 @@ def rope_inv_freq(cfg: dict) -> torch.Tensor:
 
 def rope_angles(inv_freq: torch.Tensor, positions: torch.Tensor):
     """engine/model/layers.py:75-79 -- cos and sin of position * inv_freq, halves repeated."""
-    freqs = positions[:, None].float() * inv_freq.float()[None, :]
+    freqs = _f(positions[:, None]) * _f(inv_freq)[None, :]
     emb = torch.cat((freqs, freqs), dim=-1)
     return emb.cos(), emb.sin()
 
@@ -91,20 +110,20 @@ def attention_block(cfg: dict, weights: dict, prefix: str, x: torch.Tensor, cos,
     nh = cfg["num_attention_heads"]
     nkv = cfg.get("num_key_value_heads") or nh
     hd = cfg.get("head_dim") or cfg["hidden_size"] // nh
-    q = (x @ weights[f"{prefix}.q_proj.weight"].float().t()).view(t, nh, hd).transpose(0, 1)
-    k = (x @ weights[f"{prefix}.k_proj.weight"].float().t()).view(t, nkv, hd).transpose(0, 1)
-    v = (x @ weights[f"{prefix}.v_proj.weight"].float().t()).view(t, nkv, hd).transpose(0, 1)
+    q = (x @ _f(weights[f"{prefix}.q_proj.weight"]).t()).view(t, nh, hd).transpose(0, 1)
+    k = (x @ _f(weights[f"{prefix}.k_proj.weight"]).t()).view(t, nkv, hd).transpose(0, 1)
+    v = (x @ _f(weights[f"{prefix}.v_proj.weight"]).t()).view(t, nkv, hd).transpose(0, 1)
     q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
     out = attention(q, k, v).transpose(0, 1).reshape(t, nh * hd)
-    return out @ weights[f"{prefix}.o_proj.weight"].float().t()
+    return out @ _f(weights[f"{prefix}.o_proj.weight"]).t()
 
 
 def swiglu(weights: dict, prefix: str, x: torch.Tensor) -> torch.Tensor:
     """engine/model/layers.py:277-281 -- down(silu(gate(x)) * up(x)), silu(g) = g / (1 + e^-g)."""
-    gate = x @ weights[f"{prefix}.gate_proj.weight"].float().t()
-    up = x @ weights[f"{prefix}.up_proj.weight"].float().t()
+    gate = x @ _f(weights[f"{prefix}.gate_proj.weight"]).t()
+    up = x @ _f(weights[f"{prefix}.up_proj.weight"]).t()
     act = gate / (1 + torch.exp(-gate)) * up
-    return act @ weights[f"{prefix}.down_proj.weight"].float().t()
+    return act @ _f(weights[f"{prefix}.down_proj.weight"]).t()
 
 
 def decoder_layer(cfg: dict, weights: dict, i: int, x: torch.Tensor, cos, sin) -> torch.Tensor:
@@ -132,7 +151,7 @@ def logits_for(cfg: dict, weights: dict, token_ids, rows=None) -> torch.Tensor:
         x = x[torch.as_tensor(rows, dtype=torch.long)]
     x = rms_norm(x, weights["model.norm.weight"], float(cfg.get("rms_norm_eps", 1e-5)))
     head = "model.embed_tokens.weight" if cfg.get("tie_word_embeddings", False) else "lm_head.weight"
-    return x @ weights[head].float().t()
+    return x @ _f(weights[head]).t()
 
 
 def greedy_generate(cfg: dict, weights: dict, prompt: list[int], max_tokens: int,

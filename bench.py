@@ -55,6 +55,7 @@ LLAMA_1B = {
     "bos_token_id": 128000, "eos_token_id": [128001, 128008, 128009], "torch_dtype": "bfloat16",
 }
 PROMPT_LEN, PREFILL_LEN, BLOCK_SIZE, MAX_CONTEXT = 1024, 2048, 16, 8192
+LEAD_MS = 2.0  # the device is kept busy this long before launches that are timed without the host's share
 METRIC = "decode tokens/s, Llama 3.2 1B shape, batch 8"  # both arms print the same string
 
 
@@ -196,18 +197,11 @@ def decode_device_timed(engine, batch: int, steps: int, warmup: int, seed: int, 
         launches += steps * engine.graphs.kernels_per_replay(batch)
     engine.ops.check_errors()
     kinds = None
-    if breakdown:  # a few more steps, launched eagerly with events around every kernel
-        runs = []
-        for k in range(3):
-            for rid in ids:
-                cache.grow(rid, pos, pos + 1)
-            entries = [StepEntry(rid, [feed[k][i]], pos, [0]) for i, rid in enumerate(ids)]
-            with engine.ops.timed() as timer:
-                runner.step(entries)
-            runs.append(timer.summary())
-            pos += 1
-        kinds = {name: {"launches": runs[-1][name]["launches"],
-                        "ms": statistics.median(r[name]["ms"] for r in runs)} for name in runs[-1]}
+    if breakdown:  # one more step, launched eagerly, and its kernels again kind by kind
+        for rid in ids:
+            cache.grow(rid, pos, pos + 1)
+        kinds = time_kinds(engine, [StepEntry(rid, [feed[0][i]], pos, [0]) for i, rid in enumerate(ids)])
+        pos += 1
     for rid in ids:
         cache.free(rid)
     mean_ctx = (first_ctx + pos) / 2
@@ -264,15 +258,47 @@ def prefill_timed(engine, repeats: int = 5):
         if r >= 2:
             times.append(s.elapsed_time(e))
         cache.free(rid)
-    # once more with events around every kernel
+    # once more, and its kernels again kind by kind
     prompt = torch.randint(0, vocab, (PREFILL_LEN,), generator=g).tolist()
     cache.add_request("prefill-kinds")
     cache.grow("prefill-kinds", 0, PREFILL_LEN)
-    with engine.ops.timed() as timer:
-        runner.step([StepEntry("prefill-kinds", prompt, 0, [PREFILL_LEN - 1])])
-    kinds = timer.summary()
+    kinds = time_kinds(engine, [StepEntry("prefill-kinds", prompt, 0, [PREFILL_LEN - 1])])
     cache.free("prefill-kinds")
     return statistics.median(times), kinds
+
+
+def time_kinds(engine, entries, passes: int = 5) -> dict:
+    """Run `entries` as one eagerly launched step while the kernel set records its calls, then
+    launch every kind of kernel again by itself: all of the step's launches of that kind (one per
+    layer, each on its own layer's weights and cache) back to back between two CUDA events,
+    queued behind a busy device so that the host's launch time is not in it, the L2 flushed
+    before every pass.  Returns kind -> {"launches", "ms"} (median of `passes`)."""
+    import torch
+
+    ops = engine.ops
+    with ops.recording() as calls:
+        engine.runner.step(entries)
+    torch.cuda.synchronize()
+    by_kind: dict[str, list] = {}
+    for kind, call in calls:
+        by_kind.setdefault(kind, []).append(call)
+    flush = torch.empty(256 * 2**20, dtype=torch.uint8, device=engine.device)
+    out = {}
+    for kind, launches in by_kind.items():
+        times = []
+        for _ in range(passes + 1):
+            flush.zero_()
+            ops.busy_wait(LEAD_MS)
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for call in launches:
+                call()
+            stop.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(stop))
+        out[kind] = {"launches": len(launches), "ms": statistics.median(times[1:])}
+    ops.check_errors()
+    return out
 
 
 KINDS = {"linear:attn.qkv": "K3_qkv", "attention.decode": "K5_decode_attention",
@@ -349,8 +375,9 @@ def run_ours(args) -> dict:
         "decode_b64": {k: v for k, v in kernel_rows(cfg, kinds64, peaks, 64, 64, ctx64, True).items()
                        if k == "K5_decode_attention"},
         f"prefill_{PREFILL_LEN}": kernel_rows(cfg, kinds_prefill, peaks, PREFILL_LEN, 1, PREFILL_LEN, False),
-        "how": "CUDA events around every kernel of one eagerly launched step (median of 3 for decode), "
-               "per launch; decode: bytes / time of the measured copy rate, prefill: flops / time of the "
+        "how": "every kind of kernel by itself: a step's launches of that kind (one per layer, on that "
+               "layer's weights and cache) back to back between two CUDA events, queued behind a busy "
+               "device, L2 flushed before, median of 5, per launch; decode: bytes / time of the measured copy rate, prefill: flops / time of the "
                "measured burst bf16 rate",
     }
     return {
@@ -464,12 +491,13 @@ def run_reference(args) -> dict:
             torch.cuda.synchronize()
             tokens, elapsed, used_graph = attempt("eager", args.batch, use_triton=False)
         # One request alone never meets the call that fails above (it is made for several prompts
-        # in one step), so batch 1 also runs in the reference's default, fastest mode.
+        # in one step, and for its captured mixed steps), so batch 1 also runs with the reference's
+        # fastest decode path: its Triton kernel inside captured decode steps.
         points = {}
         try:
-            t1, e1, g1 = attempt("b1", 1)
+            t1, e1, g1 = attempt("b1", 1, enable_mixed_graphs=False)
             points = {"decode_b1": round(t1 / e1, 1),
-                      "decode_b1_mode": "default (Triton decode kernel%s)" % (", CUDA graphs" if g1 else "")}
+                      "decode_b1_mode": "Triton decode kernel%s, enable_mixed_graphs=False" % (", CUDA graphs" if g1 else "")}
         except Exception as exc:
             points = {"decode_b1": None, "decode_b1_mode": f"default mode raised {type(exc).__name__}: {str(exc)[:100]}"}
         clocks = sampler.stop()

@@ -233,7 +233,8 @@ class LLMEngine:
                 logits = self.graphs.run(entries)
                 used_graph = True
             elif self.config.profile_kernels and hasattr(self.ops, "timed"):
-                with self.ops.timed() as timer:
+                # (the lead: about what the host needs to launch a layer's ten or so kernels, per layer)
+                with self.ops.timed(lead_ms=0.2 * len(self.model.spec.schedule)) as timer:
                     logits = self.runner.step(entries)
                 kernel_times = {k: round(v["ms"], 4) for k, v in timer.summary().items()}
             else:

@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import contextlib
 import ctypes
+import functools
 import os
 from ctypes import c_float, c_int, c_void_p
 
@@ -68,10 +69,12 @@ def _kind(name):
     string or a function of the call's keyword arguments."""
     def decorate(method):
         def call(self, *args, **kwargs):
-            timer, nvtx = self._timer, self.nvtx
-            if timer is None and not nvtx:
+            timer, nvtx, recorder = self._timer, self.nvtx, self._recorder
+            if timer is None and not nvtx and recorder is None:
                 return method(self, *args, **kwargs)
             label = name if isinstance(name, str) else name(kwargs)
+            if recorder is not None:
+                recorder.append((label, functools.partial(method, self, *args, **kwargs)))
             if nvtx:
                 self.torch.cuda.nvtx.range_push(label)
             span = timer.begin(label) if timer is not None else None
@@ -160,6 +163,7 @@ class CudaOps:
         self._device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self._raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
         self._timer: KernelTimer | None = None
+        self._recorder: list | None = None
         self.nvtx = os.environ.get("IE_B200_NVTX", "0") == "1"  # an NVTX range around every kernel call
         self.launches = 0  # launches of this library's kernels (library matrix products not counted)
         self.launch_counts: dict[str, int] = {}  # the same, per kernel
@@ -219,16 +223,39 @@ class CudaOps:
                               f"(value {value}, at row/token {where})")
 
     @contextlib.contextmanager
-    def timed(self):
+    def timed(self, lead_ms: float = 0.0):
         """``with ops.timed() as timer: ...; timer.summary()``: CUDA-event time per kind of kernel
         for everything launched inside the block (eager launches only: a replayed capture is one
-        launch)."""
+        launch).  The host launches small kernels more slowly than the device runs them, and an
+        event pair around a kernel that has not been launched yet measures the host; with
+        ``lead_ms`` the device is first kept busy that long, so that the block's launches queue
+        up behind it and the events see device time only."""
         timer = KernelTimer(self.torch)
+        if lead_ms > 0:
+            self.busy_wait(lead_ms)
         self._timer = timer
         try:
             yield timer
         finally:
             self._timer = None
+
+    @contextlib.contextmanager
+    def recording(self):
+        """``with ops.recording() as calls``: every kernel call made inside the block is also kept
+        as ``(kind, callable)``; calling the callable launches the same kernel on the same
+        tensors again (for timing one kind of kernel by itself, back to back over a step's
+        layers)."""
+        calls: list = []
+        self._recorder = calls
+        try:
+            yield calls
+        finally:
+            self._recorder = None
+
+    def busy_wait(self, ms: float) -> None:
+        """Keep the device busy for about ``ms``, so that what the host launches next queues up."""
+        khz = self.torch.cuda.get_device_properties(self.device).clock_rate
+        self.torch.cuda._sleep(int(ms * khz))
 
     # --- kernels ----------------------------------------------------------------------------
 

@@ -389,9 +389,14 @@ IE_API int ie_rope_kv_write(const float* qkv, int num_partials, long long partia
 // SiLU-and-multiply: out[n, i] = silu(gu[n, i]) * gu[n, I + i], silu(g) = g / (1 + exp(-g))
 // (engine/model/layers.py:277-281; engine/kernels/fused.py:82-90 evaluates it in 32-bit too)
 // ---------------------------------------------------------------------------------------------
+// Where gate i and up i sit in a row of `gate_up`: the gates in the first half and the ups in the
+// second (il == 0), or alternating in blocks of `il` values (il gates, their il ups, the next
+// il gates, ...), the layout in which a matrix-product kernel finds a gate and its up in one tile.
+__device__ __forceinline__ int gate_column(int i, int il) { return il ? (i / il) * 2 * il + i % il : i; }
+
 template <typename T, typename InT>
 __global__ void silu_mul_kernel(const InT* __restrict__ gate_up, int num_partials, size_t partial_stride,
-                                T* __restrict__ out, int inter, size_t total) {
+                                T* __restrict__ out, int inter, size_t total, int il) {
     ie_pdl_trigger();
     ie_pdl_wait();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -399,10 +404,11 @@ __global__ void silu_mul_kernel(const InT* __restrict__ gate_up, int num_partial
     for (; idx < total; idx += stride) {
         size_t row = idx / inter;
         int i = (int)(idx - row * inter);
+        int gc = gate_column(i, il), uc = gc + (il ? il : inter);
         float g = 0.f, u = 0.f;
         for (int p = 0; p < num_partials; ++p) {
-            g += ie_load(gate_up + p * partial_stride + row * 2 * inter + i);
-            u += ie_load(gate_up + p * partial_stride + row * 2 * inter + inter + i);
+            g += ie_load(gate_up + p * partial_stride + row * 2 * inter + gc);
+            u += ie_load(gate_up + p * partial_stride + row * 2 * inter + uc);
         }
         ie_store(out + idx, g / (1.0f + expf(-g)) * u);
     }
@@ -414,7 +420,7 @@ __global__ void silu_mul_kernel(const InT* __restrict__ gate_up, int num_partial
 // error, a few units in the last place of a 32-bit value, vanishes in the rounding to bfloat16.
 constexpr int SILU_VECS = 2;  // 8-value vectors per thread
 __global__ void __launch_bounds__(256)
-silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, int inter) {
+silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, int inter, int il) {
     ie_pdl_trigger();
     ie_pdl_wait();
     int per_row = inter / 8;
@@ -425,9 +431,10 @@ silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16*
 #pragma unroll
     for (int k = 0; k < SILU_VECS; ++k) {
         int v = v0 + k * 256;
-        if (v < per_row) {
-            graw[k] = *reinterpret_cast<const uint4*>(g_row + (size_t)v * 8);
-            uraw[k] = *reinterpret_cast<const uint4*>(g_row + inter + (size_t)v * 8);
+        if (v < per_row) {  // (il is a multiple of 8: a vector never straddles a block)
+            int gc = gate_column(v * 8, il);
+            graw[k] = *reinterpret_cast<const uint4*>(g_row + gc);
+            uraw[k] = *reinterpret_cast<const uint4*>(g_row + gc + (il ? il : inter));
         }
     }
 #pragma unroll
@@ -449,12 +456,16 @@ silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16*
 }
 
 // `gate_up` has the output's dtype, or is 32-bit (in_dtype), possibly the sum of `num_partials`
-// arrays `partial_stride` elements apart.
+// arrays `partial_stride` elements apart.  `interleave`: 0, or the size of the blocks in which
+// gates and ups alternate (a multiple of 8 that divides `inter`).
 IE_API int ie_silu_mul(const void* gate_up, int in_dtype, int num_partials, long long partial_stride,
-                       void* out, int dtype, int num_rows, int inter, void* stream) {
+                       void* out, int dtype, int num_rows, int inter, int interleave, void* stream) {
     size_t total = (size_t)num_rows * inter;
     if (total == 0) return 0;
     if (num_partials < 1 || (in_dtype != dtype && in_dtype != IE_F32)) return (int)cudaErrorInvalidValue;
+    if (interleave < 0 || (interleave > 0 && (interleave % 8 != 0 || inter % interleave != 0)))
+        return (int)cudaErrorInvalidValue;
+    int il = interleave;
     cudaStream_t s = (cudaStream_t)stream;
     int threads = 256;
     size_t want = (total + threads - 1) / threads;
@@ -463,14 +474,14 @@ IE_API int ie_silu_mul(const void* gate_up, int in_dtype, int num_partials, long
     if (dtype == IE_BF16 && in_dtype == IE_BF16 && num_partials == 1 && inter % 8 == 0 && num_rows <= 65535) {
         int per_block = 256 * SILU_VECS;
         return ie_launch(silu_mul_bf16x8_kernel, dim3((unsigned)((inter / 8 + per_block - 1) / per_block), (unsigned)num_rows),
-                         dim3(256), 0, s, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter);
+                         dim3(256), 0, s, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, il);
     }
     if (dtype == IE_BF16 && in_dtype == IE_BF16)
         return ie_launch(silu_mul_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(blocks), dim3(threads), 0, s,
-                         (const __nv_bfloat16*)gate_up, num_partials, ps, (__nv_bfloat16*)out, inter, total);
+                         (const __nv_bfloat16*)gate_up, num_partials, ps, (__nv_bfloat16*)out, inter, total, il);
     if (dtype == IE_BF16)
         return ie_launch(silu_mul_kernel<__nv_bfloat16, float>, dim3(blocks), dim3(threads), 0, s,
-                         (const float*)gate_up, num_partials, ps, (__nv_bfloat16*)out, inter, total);
+                         (const float*)gate_up, num_partials, ps, (__nv_bfloat16*)out, inter, total, il);
     return ie_launch(silu_mul_kernel<float, float>, dim3(blocks), dim3(threads), 0, s, (const float*)gate_up,
-                     num_partials, ps, (float*)out, inter, total);
+                     num_partials, ps, (float*)out, inter, total, il);
 }

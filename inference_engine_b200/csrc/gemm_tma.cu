@@ -50,7 +50,12 @@ static __device__ int g_starve_last_x;
 
 // Shared memory: [ring: ops x kpo x 16 KB][X: kblocks x (8 NT rows x 128 B)][barriers], 1024-byte aligned.
 // NT: 8-token column tiles (1: M <= 8, 2: M <= 16).  `kpo` k blocks per copy (3-D map) or 1 (2-D map).
-template <int NT, typename OutT>
+// GATED: W holds gates and ups alternating in blocks of 16 rows (rows 32 b .. 32 b + 15 the gates
+// 16 b .. 16 b + 15, the next 16 rows their ups), so a consumer warp's two 16-row tiles are 16
+// gates and their ups, and a thread holds a gate and its up for the same token.  The kernel then
+// writes out[m][i] = silu(gate_i) * up_i, silu(g) = g / (1 + exp(-g)) (engine/model/layers.py:277-281),
+// N / 2 values per token, instead of the product itself; the inner dimension is not cut (one split).
+template <int NT, typename OutT, bool GATED = false>
 __global__ void __launch_bounds__(THREADS)
 gemm_tma_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
                 OutT* __restrict__ out, int M, int N, int K, int kblocks_per_split, int ops, int kpo, int w3d,
@@ -177,6 +182,20 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
         if (!ok && lane == 0) failed = 1;
         // acc[mt][n][0,1]: feature f + lane/4, tokens n*8 + (lane%4)*2 + {0,1}; [2,3]: feature + 8
         OutT* dst = out + (size_t)split * M * N;
+        if constexpr (GATED) {
+            int inter = N / 2;
+#pragma unroll
+            for (int n = 0; n < NT; ++n)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    int gate_row = n0 + warp * 32 + (lane >> 2) + ((j >> 1) << 3);  // its up: 16 rows on
+                    int i = (n0 >> 1) + warp * 16 + (lane >> 2) + ((j >> 1) << 3);
+                    int m = n * 8 + (lane & 3) * 2 + (j & 1);
+                    float g = acc[0][n][j], u = acc[1][n][j];
+                    if (gate_row + 16 < N && m < M)
+                        ie_store(out + (size_t)m * inter + i, __fdividef(g, 1.0f + __expf(-g)) * u);
+                }
+        } else
 #pragma unroll
         for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
@@ -192,7 +211,7 @@ gemm_tma_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant
     if (threadIdx.x == 0 && failed) ie_report(err, IE_ERR_TIMEOUT, blockIdx.x, blockIdx.y);
 }
 
-template <int NT, typename OutT>
+template <int NT, typename OutT, bool GATED = false>
 int launch(const void* X, const void* W, OutT* out, int M, int N, int K, int kblocks_per_split, int splits,
            int* err, cudaStream_t s) {
     // k blocks per copy: as many as divide the block's slice (a copy must not reach into the
@@ -212,10 +231,10 @@ int launch(const void* X, const void* W, OutT* out, int M, int N, int K, int kbl
     if (ops > MAX_OPS) ops = MAX_OPS;
     size_t smem = (size_t)ring_bytes(NT) + (size_t)MAX_KBLOCKS * 8 * NT * BK * 2 + (2 * MAX_OPS + 1) * 8 + 1024;
     static IePerDevice configured;
-    cudaError_t e = ie_allow_smem(configured, gemm_tma_kernel<NT, OutT>, smem);
+    cudaError_t e = ie_allow_smem(configured, gemm_tma_kernel<NT, OutT, GATED>, smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid((N + BN - 1) / BN, splits);
-    return ie_launch(gemm_tma_kernel<NT, OutT>, grid, dim3(THREADS), smem, s, wm, xm, out, M, N, K,
+    return ie_launch(gemm_tma_kernel<NT, OutT, GATED>, grid, dim3(THREADS), smem, s, wm, xm, out, M, N, K,
                      kblocks_per_split, ops, kpo, w3d, err);
 }
 }  // namespace
@@ -246,4 +265,19 @@ IE_API int ie_gemm_tma_bf16(const void* X, const void* W, void* out, int out_dty
                       : launch<2, float>(X, W, (float*)out, M, N, K, kblocks_per_split, splits, err, s);
     return M <= 8 ? launch<1, bf16>(X, W, (bf16*)out, M, N, K, kblocks_per_split, splits, err, s)
                   : launch<2, bf16>(X, W, (bf16*)out, M, N, K, kblocks_per_split, splits, err, s);
+}
+
+// The gated feed-forward's first half in one kernel: W [N, K] holds gates and ups alternating in
+// blocks of 16 rows (see the kernel), `out` [M, N / 2] receives silu(gate) * up in bfloat16.  The
+// inner dimension is not cut: K at most 2048, a multiple of 8; N a multiple of 32; M <= 16.
+IE_API int ie_gemm_tma_gated_bf16(const void* X, const void* W, void* out, int M, int N, int K, int* err,
+                                  void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    int total_kblocks = (K + BK - 1) / BK;
+    if (M > 16 || K % 8 != 0 || N % 32 != 0 || total_kblocks > MAX_KBLOCKS || ((uintptr_t)X & 15) != 0 ||
+        ((uintptr_t)W & 15) != 0)
+        return (int)cudaErrorInvalidValue;
+    cudaStream_t s = (cudaStream_t)stream;
+    return M <= 8 ? launch<1, bf16, true>(X, W, (bf16*)out, M, N, K, total_kblocks, 1, err, s)
+                  : launch<2, bf16, true>(X, W, (bf16*)out, M, N, K, total_kblocks, 1, err, s);
 }

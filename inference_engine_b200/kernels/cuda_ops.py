@@ -154,6 +154,8 @@ class CudaOps:
         # only where its blocks (feature tiles x cuts along k) fit the SMs in one round: at the 3B
         # shape the down projection (3072 x 8192) 13.5 against 14.2 us, at the 8B shape (4096 x
         # 14336: 224 blocks) 33.6 against 25.4, and its K = 4096 products 13 to 45 % behind.
+        # the gated feed-forward's first product with the activation in its kernel (IE_B200_GATED_GEMM=0: off)
+        self.gated_gemm = os.environ.get("IE_B200_GATED_GEMM", "1") != "0"
         self.batch_gemm = os.environ.get("IE_B200_BATCH_GEMM", "1") != "0"
         self.batch_gemm_rows = int(os.environ.get("IE_B200_BATCH_GEMM_ROWS", 64))
         self.batch_gemm_max_tiles = int(os.environ.get("IE_B200_BATCH_GEMM_MAX_TILES", 256))
@@ -174,7 +176,8 @@ class CudaOps:
             "ie_embedding": [P, I, P, P, I, I, I, P, P],
             "ie_rmsnorm": [P, P, I, L, P, F, P, I, P, I, I, P],
             "ie_rope_kv_write": [P, I, L, P, P, I, I, P, P, P, I, P, I, I, I, I, I, I, P, P],
-            "ie_silu_mul": [P, I, I, L, P, I, I, I, P],
+            "ie_silu_mul": [P, I, I, L, P, I, I, I, I, P],
+            "ie_gemm_tma_gated_bf16": [P, P, P, I, I, I, P, P],
             "ie_argmax": [P, I, I, I, P, P, P],
             "ie_gemm_f32": [P, P, P, I, I, I, P],
             "ie_gemm_tma_bf16": [P, P, P, I, I, I, I, I, I, P, P],
@@ -566,11 +569,42 @@ class CudaOps:
             k_cache.shape[0], scale, window, self._err_ptr, self._stream()), "paged_attention")
 
     @_kind("activation")
-    def silu_mul(self, gate_up, out) -> None:
+    def silu_mul(self, gate_up, out, interleave: int = 0) -> None:
+        """``out[n, i] = silu(gate_i) * up_i`` from rows that hold the gates and then the ups
+        (``interleave`` 0) or gates and ups alternating in blocks of ``interleave`` values."""
         parts, stride = self._partials(gate_up)
         self._check(self._silu_mul(gate_up.data_ptr(), _dtype_code(gate_up), parts, stride,
                                    out.data_ptr(), _dtype_code(out), out.shape[0], out.shape[1],
-                                   self._stream()), "silu_mul")
+                                   interleave, self._stream()), "silu_mul")
+
+    GATE_BLOCK = 16  # rows of gates, then of ups, alternate in blocks of this many in a fused matrix
+
+    def gated_linear(self, x, w_gate_up, interleave: int, *, ws, tag="ffn", out_dtype=None):
+        """``silu(x @ gate^T) * (x @ up^T)`` with gate and up stacked in ``w_gate_up`` (halves, or
+        alternating in blocks of ``interleave`` rows).  A step of few rows whose matrix is laid
+        out in blocks of ``GATE_BLOCK`` runs one kernel that streams the weights and applies the
+        activation to the sums it holds; everything else is the product followed by
+        :meth:`silu_mul`."""
+        torch = self.torch
+        m, k = x.shape
+        n = w_gate_up.shape[0]
+        act = ws.buffer(tag + ".act", m, n // 2, out_dtype or x.dtype)
+        tiles = -(-n // 128)
+        if (self.gated_gemm and interleave == self.GATE_BLOCK and x.dtype == torch.bfloat16
+                and act.dtype == torch.bfloat16 and 0 < m <= self.FEW_ROWS and self.few_row_gemm == "tma"
+                and k % 8 == 0 and k <= 2048 and n % 32 == 0 and x.is_contiguous() and w_gate_up.is_contiguous()
+                and tiles <= (self.tma_max_tiles if m <= 8 else self.tma_max_tiles_wide)
+                and tiles <= self.tma_max_blocks):
+            self._gated(x, w_gate_up, act)
+            return act
+        gate_up = self.linear(x, w_gate_up, ws=ws, tag=tag + ".gate_up", out_dtype=act.dtype, allow_split=True)
+        self.silu_mul(gate_up, act, interleave)
+        return act
+
+    @_kind("linear:ffn.gate_up")
+    def _gated(self, x, w, act) -> None:
+        self._check(self._gemm_tma_gated_bf16(x.data_ptr(), w.data_ptr(), act.data_ptr(), x.shape[0], w.shape[0],
+                                              x.shape[1], self._err_ptr, self._stream()), "gemm_tma_gated")
 
     def argmax(self, logits, out) -> None:
         """Greedy token of every row (lowest index on ties)."""

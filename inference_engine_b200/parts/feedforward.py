@@ -1,6 +1,9 @@
 """Dense gated feed-forward: ``down(silu(gate(x)) * up(x))`` (engine/model/layers.py:277-281),
 ``silu(g) = g / (1 + exp(-g))`` evaluated in 32-bit.  Gate and up run as one matrix product
-over the row-concatenated weights."""
+over the stacked weights.  Their rows alternate in blocks of 16 (16 gate rows, the 16 up rows
+with the same indices, the next 16 gate rows, ...) when the width allows: every dot product is
+unchanged, and a kernel that owns a tile of rows then holds each gate beside its up and can
+apply the activation itself (``ops.gated_linear``)."""
 
 from __future__ import annotations
 
@@ -15,6 +18,9 @@ class SwiGLU(FeedForward):
         self.names = {"gate": gate_proj, "up": up_proj, "down": down_proj}
         self.hidden_size, self.intermediate_size, self.dtype = hidden_size, intermediate_size, dtype
         self.w_gate_up = self.w_down = None
+        self.interleave = 0
+
+    ROW_BLOCK = 16  # gate and up rows alternate in blocks of this many
 
     @classmethod
     def from_spec(cls, params: dict, env: BuildEnv, **_):
@@ -34,18 +40,19 @@ class SwiGLU(FeedForward):
     def bind(self, tensors, env: BuildEnv) -> None:
         import torch
 
-        self.w_gate_up = torch.cat(
-            [tensors[self.names["gate"]].to(self.dtype), tensors[self.names["up"]].to(self.dtype)]
-        ).contiguous()
+        gate, up = tensors[self.names["gate"]].to(self.dtype), tensors[self.names["up"]].to(self.dtype)
+        i, h, b = self.intermediate_size, self.hidden_size, self.ROW_BLOCK
+        if i % b == 0:
+            self.interleave = b
+            self.w_gate_up = torch.stack([gate.view(i // b, b, h), up.view(i // b, b, h)], dim=1).reshape(2 * i, h).contiguous()
+        else:
+            self.interleave = 0
+            self.w_gate_up = torch.cat([gate, up]).contiguous()
         self.w_down = tensors[self.names["down"]].to(self.dtype).contiguous()
 
     def forward(self, x, ctx):
         import torch
 
-        n, i = x.shape[0], self.intermediate_size
-        gate_up = ctx.ops.linear(x, self.w_gate_up, ws=ctx.ws, tag="ffn.gate_up", out_dtype=self.dtype,
-                                 allow_split=True)
-        act = ctx.ws.buffer("ffn.act", n, i, self.dtype)
-        ctx.ops.silu_mul(gate_up, act)
+        act = ctx.ops.gated_linear(x, self.w_gate_up, self.interleave, ws=ctx.ws, tag="ffn", out_dtype=self.dtype)
         return ctx.ops.linear(act, self.w_down, ws=ctx.ws, tag="ffn.delta", out_dtype=torch.float32,
                               allow_split=True)

@@ -83,12 +83,22 @@ class RefOps:
             probs = scores.softmax(-1)
             out[t] = torch.einsum("hk,khd->hd", probs, v).reshape(nh * hd).to(out.dtype)
 
-    def silu_mul(self, gate_up, out):
+    def silu_mul(self, gate_up, out, interleave=0):
         if gate_up.dim() == 3:
             gate_up = gate_up.float().sum(0)
         i = out.shape[1]
-        g, u = gate_up[:, :i].float(), gate_up[:, i:].float()
+        if interleave:  # gates and ups alternate in blocks of `interleave` values
+            blocks = gate_up.float().view(gate_up.shape[0], i // interleave, 2, interleave)
+            g, u = blocks[:, :, 0].reshape(-1, i), blocks[:, :, 1].reshape(-1, i)
+        else:
+            g, u = gate_up[:, :i].float(), gate_up[:, i:].float()
         out.copy_((g / (1 + torch.exp(-g)) * u).to(out.dtype))
+
+    def gated_linear(self, x, w_gate_up, interleave, *, ws, tag="ffn", out_dtype=None):
+        gate_up = self.linear(x, w_gate_up, ws=ws, tag=tag + ".gate_up", out_dtype=out_dtype or x.dtype)
+        act = ws.buffer(tag + ".act", x.shape[0], w_gate_up.shape[0] // 2, out_dtype or x.dtype)
+        self.silu_mul(gate_up, act, interleave)
+        return act
 
     def argmax(self, logits, out):
         out.copy_(logits.argmax(-1).to(out.dtype))

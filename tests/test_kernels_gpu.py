@@ -256,6 +256,46 @@ def test_silu_mul(ops, dtype, n, inter):
     ops.silu_mul(gu, got)
     RefOps().silu_mul(gu, want)
     torch.testing.assert_close(got.float(), want.float(), **_tol(dtype))
+    # gates and ups alternating in blocks of 8 or 16 values: the same numbers from other places
+    plain = want.clone()
+    for block in (8, 16):
+        if inter % block:
+            continue
+        mixed = torch.stack([gu[:, :inter].view(n, inter // block, block), gu[:, inter:].view(n, inter // block, block)],
+                            dim=2).reshape(n, 2 * inter).contiguous()
+        ops.silu_mul(mixed, got, block)
+        RefOps().silu_mul(mixed, want, block)
+        torch.testing.assert_close(got.float(), want.float(), **_tol(dtype))
+        assert torch.equal(want, plain)
+
+
+@pytest.mark.parametrize("m", [1, 5, 8, 9, 16])
+@pytest.mark.parametrize("inter,k", [(8192, 2048), (176, 96), (320, 64), (1008, 1032), (11008, 2048)])
+def test_gated_product_applies_the_activation_in_the_kernel(ops, m, inter, k):
+    """A few rows through the gated feed-forward's first half: the TMA-fed kernel on a matrix whose
+    gate and up rows alternate in blocks of 16 gives silu(x gate^T) * (x up^T), also where the
+    last tile of 128 rows is not full; other layouts and sizes take the two-kernel way."""
+    from inference_engine_b200.engine.workspace import Workspace
+
+    g = torch.Generator(device="cuda").manual_seed(inter + k + m)
+    x = torch.randn(m, k, device="cuda", generator=g).bfloat16()
+    gate = (torch.randn(inter, k, device="cuda", generator=g) * 0.05).bfloat16()
+    up = (torch.randn(inter, k, device="cuda", generator=g) * 0.05).bfloat16()
+    a, b = x.double() @ gate.double().t(), x.double() @ up.double().t()
+    want = a / (1 + torch.exp(-a)) * b
+    ws = Workspace("cuda")
+    block = ops.GATE_BLOCK
+    stacked = torch.stack([gate.view(inter // block, block, k), up.view(inter // block, block, k)], dim=1)
+    stacked = stacked.reshape(2 * inter, k).contiguous()
+    before = ops.launch_counts.get("gemm_tma_gated", 0)
+    got = ops.gated_linear(x, stacked, block, ws=ws, tag="t", out_dtype=torch.bfloat16)
+    fused = ops.launch_counts.get("gemm_tma_gated", 0) - before
+    assert fused == (1 if (m <= 8 or -(-2 * inter // 128) <= ops.tma_max_tiles_wide) else 0)
+    torch.testing.assert_close(got.double(), want, atol=0.01 * k ** 0.5 * 0.05 * 3, rtol=2e-2)
+    halves = ops.gated_linear(x, torch.cat([gate, up]).contiguous(), 0, ws=ws, tag="u", out_dtype=torch.bfloat16)
+    assert ops.launch_counts.get("gemm_tma_gated", 0) - before == fused  # the plain layout: two kernels
+    torch.testing.assert_close(halves.double(), want, atol=0.01 * k ** 0.5 * 0.05 * 3, rtol=2e-2)
+    ops.check_errors()
 
 
 def _attention_case(nh, nkv, hd, ps, q_lens, ctx_lens, dtype, seed=0, spike=None):

@@ -361,7 +361,18 @@ __device__ __forceinline__ void decode_barrier() { asm volatile("bar.sync 1, %0;
 // key/value head) merges all splits, always in the order 0, 1, 2, ...  The ticket counter goes
 // back to zero for the next launch.  Barrier 1 is used, so that other warps of the block need
 // not take part.
-template <int NWARPS>
+// PAIR: the two splits of a (request, key/value head) pair are a thread-block cluster of two.  Both
+// leave their results in the shared memory of the first (the second through the cluster's window),
+// and after a cluster barrier the first merges them, split 0 then split 1, and writes the output:
+// no partial results through memory, no ticket.  `stage` is the first's [2][16][HD + 2] floats
+// beyond the tile rings (the rings may still be in use there while the second already writes).
+__device__ __forceinline__ void pair_store(float* stage, float v) {
+    unsigned local = (unsigned)__cvta_generic_to_shared(stage), remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(remote) : "r"(local));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+
+template <int NWARPS, bool PAIR = false>
 __device__ __forceinline__ void decode_merge_store(RowState& st, unsigned char* smem_raw, int* is_last, int warp,
                                                    int lane, int rows, int G, int q0, int seq, int kvh, int split,
                                                    int num_splits, int nh, int nkv, bf16* __restrict__ out,
@@ -374,6 +385,8 @@ __device__ __forceinline__ void decode_merge_store(RowState& st, unsigned char* 
     // [warp][row] m, l and [warp][row][HD] o in shared memory
     float* sm_ml = reinterpret_cast<float*>(smem_raw);            // [WARPS][16][2]
     float* sm_o = sm_ml + WARPS * MAX_ROWS * 2;                   // [WARPS][16][HD]
+    float* pair_stage = reinterpret_cast<float*>(smem_raw + (size_t)WARPS * DSTAGES * 2 * KT_DECODE * HD * sizeof(bf16));
+    (void)pair_stage;
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         int row = (lane >> 2) + r * 8;
@@ -405,6 +418,10 @@ __device__ __forceinline__ void decode_merge_store(RowState& st, unsigned char* 
         if (num_splits == 1) {
             int tok = row / G, g = row - tok * G;
             out[((size_t)(q0 + tok) * nh + kvh * G + g) * HD + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+        } else if (PAIR) {
+            float* slot = pair_stage + ((size_t)split * MAX_ROWS + row) * (HD + 2);
+            pair_store(slot + d, o);
+            if (d == 0) { pair_store(slot + HD, m); pair_store(slot + HD + 1, l); }
         } else {
             size_t p = (((size_t)seq * nkv + kvh) * num_splits + split) * MAX_ROWS + row;
             part_o[p * HD + d] = o;
@@ -412,6 +429,26 @@ __device__ __forceinline__ void decode_merge_store(RowState& st, unsigned char* 
         }
     }
     if (num_splits == 1) return;
+    if (PAIR) {
+        asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+        if (split != 0) return;  // its results are in the first block's shared memory
+        asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+        for (int idx = tid; idx < rows * HD; idx += WARPS * 32) {
+            int row = idx / HD, d = idx - row * HD;
+            const float* s0 = pair_stage + (size_t)row * (HD + 2);
+            const float* s1 = pair_stage + ((size_t)MAX_ROWS + row) * (HD + 2);
+            float m0 = s0[HD], m1 = s1[HD];
+            float m = fmaxf(m0, m1);
+            float m_safe = (m == -INFINITY) ? 0.f : m;
+            float f0 = exp2f(m0 - m_safe), f1 = exp2f(m1 - m_safe);
+            float l = 0.f, o = 0.f;
+            l += s0[HD + 1] * f0; o += s0[d] * f0;
+            l += s1[HD + 1] * f1; o += s1[d] * f1;
+            int tok = row / G, g = row - tok * G;
+            out[((size_t)(q0 + tok) * nh + kvh * G + g) * HD + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+        }
+        return;
+    }
     __threadfence();
     decode_barrier<NWARPS>();
     if (tid == 0) {
@@ -462,7 +499,7 @@ __device__ __forceinline__ void decode_merge_store(RowState& st, unsigned char* 
 }
 
 
-template <int NWARPS>
+template <int NWARPS, bool PAIR = false>
 __global__ void __launch_bounds__(NWARPS * 32)
 attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache,
                         const bf16* __restrict__ v_cache, const int* __restrict__ tables,
@@ -584,8 +621,8 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
         __syncwarp();
     }
     cp_async_wait<0>();
-    decode_merge_store<NWARPS>(st, smem_raw, &is_last, warp, lane, rows, G, q0, seq, kvh, split, num_splits, nh, nkv, out,
-                       part_o, part_ml, tickets);
+    decode_merge_store<NWARPS, PAIR>(st, smem_raw, &is_last, warp, lane, rows, G, q0, seq, kvh, split, num_splits, nh,
+                                     nkv, out, part_o, part_ml, tickets);
 }
 
 // -------------------------------------------------------------------------------------------------
@@ -1158,7 +1195,15 @@ constexpr size_t decode_smem(int warps) {
 constexpr size_t PREFILL_SMEM = (size_t)3 * 2 * KT_PREFILL * HD * sizeof(bf16);
 }  // namespace
 
+constexpr size_t PAIR_STAGE_BYTES = (size_t)2 * MAX_ROWS * (HD + 2) * sizeof(float);
+// 1 (default): two splits merge as a cluster of two blocks through shared memory; 0: through memory.
+inline int& decode_pair_enabled() {
+    static int enabled = 1;
+    return enabled;
+}
+
 IE_API int ie_attention_head_dim() { return HD; }
+IE_API void ie_set_decode_pair(int enabled) { decode_pair_enabled() = enabled ? 1 : 0; }
 // Query tokens one block of the prefill kernel takes (callers count tiles with it).
 IE_API int ie_attention_prefill_rows() { return BM; }
 IE_API void ie_set_pdl(int enabled) { ie_pdl_enabled() = enabled ? 1 : 0; }
@@ -1176,10 +1221,21 @@ int launch_decode_as(const void* q, const void* k_cache, const void* v_cache, co
                      const int* cu_q, const int* ctx_lens, void* out, float* part_o, float* part_ml, int* tickets,
                      int num_seqs, int nh, int nkv, int page_shift, int total_pages, float scale, int window,
                      int num_splits, int* err, cudaStream_t s) {
+    dim3 grid(num_seqs, nkv, num_splits);
+    if (num_splits == 2 && decode_pair_enabled()) {
+        // two splits: the pair is a cluster that merges through shared memory
+        static IePerDevice configured_pair;
+        size_t smem = decode_smem(NWARPS) + PAIR_STAGE_BYTES;
+        cudaError_t e = ie_allow_smem(configured_pair, attention_decode_kernel<NWARPS, true>, smem);
+        if (e != cudaSuccess) return (int)e;
+        return ie_launch_cluster(attention_decode_kernel<NWARPS, true>, grid, dim3(NWARPS * 32), smem, s, dim3(1, 1, 2),
+                                 (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, tables, table_width, cu_q,
+                                 ctx_lens, (bf16*)out, part_o, part_ml, tickets, nh, nkv, page_shift, total_pages,
+                                 scale * 1.4426950408889634f, window, num_splits, err);
+    }
     static IePerDevice configured;
     cudaError_t e = ie_allow_smem(configured, attention_decode_kernel<NWARPS>, decode_smem(NWARPS));
     if (e != cudaSuccess) return (int)e;
-    dim3 grid(num_seqs, nkv, num_splits);
     return ie_launch(attention_decode_kernel<NWARPS>, grid, dim3(NWARPS * 32), decode_smem(NWARPS), s,
                      (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, tables, table_width, cu_q,
                      ctx_lens, (bf16*)out, part_o, part_ml, tickets, nh, nkv, page_shift, total_pages,

@@ -66,6 +66,28 @@ inline int& ie_pdl_enabled() {
     return enabled;
 }
 
+// The same launch as a grid of thread-block clusters of (cx, cy, cz) blocks: the blocks of a cluster
+// run at the same time and can write into each other's shared memory.
+template <typename... KArgs, typename... Args>
+inline int ie_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             dim3 cluster, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster.x;
+    attr[0].val.clusterDim.y = cluster.y;
+    attr[0].val.clusterDim.z = cluster.z;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ie_pdl_enabled() ? 2 : 1;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // What is set on a kernel function (its dynamic shared memory limit) or asked of a device (its SM
 // count) holds for the device that was current at the time, so "done already" is kept per device.
 constexpr int IE_MAX_DEVICES = 64;

@@ -385,6 +385,7 @@ class CudaOps:
         if lib is None:
             lib = ctypes.CDLL(str(build_attention(hd)))
             lib.ie_set_pdl(1 if self.pdl else 0)
+            lib.ie_set_decode_pair(0 if os.environ.get("IE_B200_DECODE_PAIR", "1") == "0" else 1)
             P, I, F = c_void_p, c_int, c_float
             lib.ie_attention_decode.argtypes = [P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, F, I, I, P, P]
             lib.ie_attention_prefill.argtypes = [P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P, P]

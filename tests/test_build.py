@@ -19,7 +19,7 @@ def test_every_declared_entry_point_is_exported():
     CudaOps._declare(fake)  # looks every core entry point up by name
     assert hasattr(core, "ie_set_pdl")
     attention = ctypes.CDLL(str(build_attention(64)))
-    for name in ("ie_set_pdl", "ie_attention_decode", "ie_attention_decode_balanced", "ie_attention_prefill",
+    for name in ("ie_set_pdl", "ie_set_decode_pair", "ie_attention_decode", "ie_attention_decode_balanced", "ie_attention_prefill",
                  "ie_attention_prefill_tc5", "ie_attention_prefill_tc5_ok", "ie_attention_prefill_rows",
                  "ie_attention_decode_scratch_floats", "ie_attention_decode_balanced_scratch_floats",
                  "ie_attention_decode_balanced_max_seqs", "ie_attention_prefill_tc5_scratch_floats",

@@ -427,6 +427,38 @@ def test_decode_attention_deals_ragged_contexts_evenly(ops, nh, nkv, hd, ps, win
     assert torch.equal(again, got)
 
 
+@pytest.mark.parametrize("nh,nkv,hd,ps,seqs", [(32, 8, 64, 16, 8), (8, 2, 128, 16, 30), (6, 3, 32, 8, 17), (16, 8, 64, 16, 7)])
+@pytest.mark.parametrize("window", [0, 300])
+def test_two_splits_of_a_context_merge_through_shared_memory(ops, nh, nkv, hd, ps, seqs, window):
+    """Batches for which the decode attention cuts every context in two run the two blocks of a
+    (request, head) pair as a thread-block cluster that merges through the first block's shared
+    memory.  The result is that of the merge through memory (same sums in the same order: equal
+    bit for bit) and the plain attention's; a far key per request stands out; contexts from one
+    key (the second block has nothing) to thousands, portions of one to four tokens."""
+    assert ops.decode_splits(seqs, nkv) == 2
+    ctx_lens = ([1, 17, 1024, 333, 2048, 64, 700, 31, 4097, 2, 96, 5000] * 3)[:seqs]
+    group = nh // nkv
+    q_lens = [(1 + i % 4) if (1 + i % 4) * group <= 16 else 1 for i in range(seqs)]
+    q_lens = [min(ql, c) for ql, c in zip(q_lens, ctx_lens)]
+    spike = [max(0, c - ql - window // 2) if window else (c - ql) // 3 for c, ql in zip(ctx_lens, q_lens)]
+    q, k, v, tables, ctx = _attention_case(nh, nkv, hd, ps, q_lens, ctx_lens, torch.bfloat16, seed=5, spike=spike)
+    want = torch.empty_like(q)
+    RefOps().paged_attention(q, k, v, tables, ctx, nh, nkv, hd, ps, hd ** -0.5, window, want)
+    lib = ops._attention_lib(hd)
+    outs = []
+    try:
+        for pair in (1, 0, 1):
+            lib.ie_set_decode_pair(pair)
+            got = torch.zeros_like(q)
+            ops.paged_attention(q, k, v, tables, ctx, nh, nkv, hd, ps, hd ** -0.5, window, got)
+            torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+            outs.append(got)
+    finally:
+        lib.ie_set_decode_pair(1)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    ops.check_errors()
+
+
 @pytest.mark.parametrize("nh,nkv,hd,ps", [(32, 8, 64, 16), (8, 2, 128, 16), (4, 1, 64, 8)])
 @pytest.mark.parametrize("window", [0, 1000])
 @pytest.mark.parametrize("q_lens,ctx_lens", [([200], [3000]), ([130, 1, 260], [2600, 900, 260]), ([17], [1100])])

@@ -361,11 +361,12 @@ __device__ __forceinline__ void decode_barrier() { asm volatile("bar.sync 1, %0;
 // key/value head) merges all splits, always in the order 0, 1, 2, ...  The ticket counter goes
 // back to zero for the next launch.  Barrier 1 is used, so that other warps of the block need
 // not take part.
-// PAIR: the two splits of a (request, key/value head) pair are a thread-block cluster of two.  Both
-// leave their results in the shared memory of the first (the second through the cluster's window),
-// and after a cluster barrier the first merges them, split 0 then split 1, and writes the output:
-// no partial results through memory, no ticket.  `stage` is the first's [2][16][HD + 2] floats
-// beyond the tile rings (the rings may still be in use there while the second already writes).
+// PAIR: the splits of a (request, key/value head) pair (2, 4 or 8 of them) are one thread-block
+// cluster.  All leave their results in the shared memory of the first (the others through the
+// cluster's window), and after a cluster barrier the first merges them in the order 0, 1, 2, ...
+// and writes the output: no partial results through memory, no ticket.  `stage` is the first's
+// [splits][16][HD + 2] floats beyond the tile rings (the rings may still be in use there while
+// another block already writes).
 __device__ __forceinline__ void pair_store(float* stage, float v) {
     unsigned local = (unsigned)__cvta_generic_to_shared(stage), remote;
     asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(remote) : "r"(local));
@@ -435,15 +436,17 @@ __device__ __forceinline__ void decode_merge_store(RowState& st, unsigned char* 
         asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
         for (int idx = tid; idx < rows * HD; idx += WARPS * 32) {
             int row = idx / HD, d = idx - row * HD;
-            const float* s0 = pair_stage + (size_t)row * (HD + 2);
-            const float* s1 = pair_stage + ((size_t)MAX_ROWS + row) * (HD + 2);
-            float m0 = s0[HD], m1 = s1[HD];
-            float m = fmaxf(m0, m1);
+            const float* slot = pair_stage + (size_t)row * (HD + 2);
+            const size_t next = (size_t)MAX_ROWS * (HD + 2);
+            float m = -INFINITY;
+            for (int z = 0; z < num_splits; ++z) m = fmaxf(m, slot[z * next + HD]);
             float m_safe = (m == -INFINITY) ? 0.f : m;
-            float f0 = exp2f(m0 - m_safe), f1 = exp2f(m1 - m_safe);
             float l = 0.f, o = 0.f;
-            l += s0[HD + 1] * f0; o += s0[d] * f0;
-            l += s1[HD + 1] * f1; o += s1[d] * f1;
+            for (int z = 0; z < num_splits; ++z) {
+                float f = exp2f(slot[z * next + HD] - m_safe);
+                l += slot[z * next + HD + 1] * f;
+                o += slot[z * next + d] * f;
+            }
             int tok = row / G, g = row - tok * G;
             out[((size_t)(q0 + tok) * nh + kvh * G + g) * HD + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
         }
@@ -1195,15 +1198,17 @@ constexpr size_t decode_smem(int warps) {
 constexpr size_t PREFILL_SMEM = (size_t)3 * 2 * KT_PREFILL * HD * sizeof(bf16);
 }  // namespace
 
-constexpr size_t PAIR_STAGE_BYTES = (size_t)2 * MAX_ROWS * (HD + 2) * sizeof(float);
-// 1 (default): two splits merge as a cluster of two blocks through shared memory; 0: through memory.
+constexpr size_t PAIR_SLOT_BYTES = (size_t)MAX_ROWS * (HD + 2) * sizeof(float);
+constexpr size_t MAX_DYNAMIC_SMEM = 227 * 1024;
+// The largest number of splits (2, 4, 8) that merge as one cluster of blocks through shared
+// memory; 0: every merge goes through memory.
 inline int& decode_pair_enabled() {
-    static int enabled = 1;
+    static int enabled = 8;
     return enabled;
 }
 
 IE_API int ie_attention_head_dim() { return HD; }
-IE_API void ie_set_decode_pair(int enabled) { decode_pair_enabled() = enabled ? 1 : 0; }
+IE_API void ie_set_decode_pair(int max_splits) { decode_pair_enabled() = max_splits; }
 // Query tokens one block of the prefill kernel takes (callers count tiles with it).
 IE_API int ie_attention_prefill_rows() { return BM; }
 IE_API void ie_set_pdl(int enabled) { ie_pdl_enabled() = enabled ? 1 : 0; }
@@ -1222,13 +1227,18 @@ int launch_decode_as(const void* q, const void* k_cache, const void* v_cache, co
                      int num_seqs, int nh, int nkv, int page_shift, int total_pages, float scale, int window,
                      int num_splits, int* err, cudaStream_t s) {
     dim3 grid(num_seqs, nkv, num_splits);
-    if (num_splits == 2 && decode_pair_enabled()) {
-        // two splits: the pair is a cluster that merges through shared memory
+    size_t pair_smem = decode_smem(NWARPS) + (size_t)num_splits * PAIR_SLOT_BYTES;
+    if ((num_splits == 2 || num_splits == 4 || num_splits == 8) && num_splits <= decode_pair_enabled() &&
+        pair_smem <= MAX_DYNAMIC_SMEM) {
+        // the splits are a cluster that merges through shared memory
         static IePerDevice configured_pair;
-        size_t smem = decode_smem(NWARPS) + PAIR_STAGE_BYTES;
+        size_t smem = decode_smem(NWARPS) + (size_t)8 * PAIR_SLOT_BYTES;  // (what the function is set up for)
+        if (smem > MAX_DYNAMIC_SMEM) smem = MAX_DYNAMIC_SMEM;
         cudaError_t e = ie_allow_smem(configured_pair, attention_decode_kernel<NWARPS, true>, smem);
         if (e != cudaSuccess) return (int)e;
-        return ie_launch_cluster(attention_decode_kernel<NWARPS, true>, grid, dim3(NWARPS * 32), smem, s, dim3(1, 1, 2),
+        smem = pair_smem;
+        return ie_launch_cluster(attention_decode_kernel<NWARPS, true>, grid, dim3(NWARPS * 32), smem, s,
+                                 dim3(1, 1, (unsigned)num_splits),
                                  (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, tables, table_width, cu_q,
                                  ctx_lens, (bf16*)out, part_o, part_ml, tickets, nh, nkv, page_shift, total_pages,
                                  scale * 1.4426950408889634f, window, num_splits, err);

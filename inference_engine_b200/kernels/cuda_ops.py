@@ -130,6 +130,10 @@ class CudaOps:
         self.prefill_key_splits = os.environ.get("IE_B200_PREFILL_KEY_SPLITS", "1") != "0"
         # the decode kernel cuts contexts until about this many blocks run (one block per SM)
         self.decode_split_target = int(os.environ.get("IE_B200_DECODE_SPLIT_TARGET", 128))
+        # up to this many parts of a context merge inside a thread-block cluster (2, 4, 8; 0: never),
+        # for steps whose block tables hold at most `decode_cluster_tokens` tokens per request
+        self.decode_cluster_max = int(os.environ.get("IE_B200_DECODE_PAIR", 8))
+        self.decode_cluster_tokens = int(os.environ.get("IE_B200_DECODE_CLUSTER_TOKENS", 4096))
         # batches whose contexts differ much in length go to the decode kernel that deals key tiles
         # by length ("auto": when the step's context says so; "1": always; "0": never)
         self.decode_balanced = os.environ.get("IE_B200_DECODE_BALANCED", "auto")
@@ -385,7 +389,7 @@ class CudaOps:
         if lib is None:
             lib = ctypes.CDLL(str(build_attention(hd)))
             lib.ie_set_pdl(1 if self.pdl else 0)
-            lib.ie_set_decode_pair(0 if os.environ.get("IE_B200_DECODE_PAIR", "1") == "0" else 1)
+            lib.ie_set_decode_pair(self.decode_cluster_max)
             P, I, F = c_void_p, c_int, c_float
             lib.ie_attention_decode.argtypes = [P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, F, I, I, P, P]
             lib.ie_attention_prefill.argtypes = [P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P, P]
@@ -409,13 +413,20 @@ class CudaOps:
             self._tickets = self.torch.zeros(max(count, 16384), dtype=self.torch.int32, device=self.device)
         return self._tickets
 
-    def decode_splits(self, num_seqs: int, nkv: int) -> int:
+    def decode_splits(self, num_seqs: int, nkv: int, table_tokens: int = 0) -> int:
         """Into how many parts the decode kernel cuts each context.  One block per (request,
         key/value head) streams at an SM's full rate, so contexts are only cut when there are
-        few such blocks (small batches); the number depends on the batch alone, never on the
-        contexts' lengths, so that a captured launch stays valid."""
+        few such blocks (small batches).  2, 4 or 8 parts run as one thread-block cluster and
+        merge through shared memory, which is worth more than the last few blocks: the count is
+        rounded down to one of those, except for long contexts at the smallest batches
+        (``table_tokens``: what the step's block tables can hold), where 16 or 32 parts that
+        merge through memory stream faster.  The number depends on the batch and the tables'
+        width alone, never on the contexts' lengths, so that a captured launch stays valid."""
         blocks = max(num_seqs * nkv, 1)
-        return max(1, min(self.decode_split_target // blocks, 32))
+        parts = max(1, min(self.decode_split_target // blocks, 32))
+        if self.decode_cluster_max < 2 or parts < 2 or (parts > 8 and table_tokens > self.decode_cluster_tokens):
+            return parts
+        return min(8 if parts >= 8 else 4 if parts >= 4 else 2, self.decode_cluster_max)
 
     def decode_by_length(self, ctx_lens, nkv: int) -> bool:
         """Whether a decode step over contexts of these lengths should use the kernel that deals
@@ -514,7 +525,7 @@ class CudaOps:
                 total_pages, scale, window, per_pair, self._err_ptr, stream), "attention_decode_balanced")
             self.balanced_launches += 1
             return
-        splits = self.decode_splits(ctx.num_seqs, nkv)
+        splits = self.decode_splits(ctx.num_seqs, nkv, block_tables.shape[1] * page_size)
         floats = lib.ie_attention_decode_scratch_floats(ctx.num_seqs, nkv, splits)
         scratch = tickets = None
         if floats:

@@ -388,7 +388,7 @@ def test_decode_attention_with_many_splits_is_the_same_as_one(ops):
     result equals the unsplit one up to rounding."""
     nh, nkv, hd, ps = 8, 2, 64, 16
     q, k, v, tables, ctx = _attention_case(nh, nkv, hd, ps, [1], [3000], torch.bfloat16, seed=4)
-    assert ops.decode_splits(1, nkv) >= 8
+    assert ops.decode_splits(1, nkv, tables.shape[1] * ps) >= 8
     got = torch.empty_like(q)
     ops.paged_attention(q, k, v, tables, ctx, nh, nkv, hd, ps, hd ** -0.5, 0, got)
     want = torch.empty_like(q)
@@ -427,16 +427,19 @@ def test_decode_attention_deals_ragged_contexts_evenly(ops, nh, nkv, hd, ps, win
     assert torch.equal(again, got)
 
 
-@pytest.mark.parametrize("nh,nkv,hd,ps,seqs", [(32, 8, 64, 16, 8), (8, 2, 128, 16, 30), (6, 3, 32, 8, 17), (16, 8, 64, 16, 7)])
+@pytest.mark.parametrize("nh,nkv,hd,ps,seqs,parts", [
+    (32, 8, 64, 16, 8, 2), (8, 2, 128, 16, 30, 2), (6, 3, 32, 8, 17, 2), (16, 8, 64, 16, 7, 2),
+    (32, 8, 64, 16, 4, 4), (32, 8, 64, 16, 1, 8), (8, 2, 128, 16, 9, 4), (8, 2, 128, 16, 2, 8), (5, 5, 48, 4, 3, 8)])
 @pytest.mark.parametrize("window", [0, 300])
-def test_two_splits_of_a_context_merge_through_shared_memory(ops, nh, nkv, hd, ps, seqs, window):
-    """Batches for which the decode attention cuts every context in two run the two blocks of a
+def test_splits_of_a_context_merge_through_shared_memory(ops, nh, nkv, hd, ps, seqs, parts, window):
+    """Batches for which the decode attention cuts every context in 2, 4 or 8 run the blocks of a
     (request, head) pair as a thread-block cluster that merges through the first block's shared
-    memory.  The result is that of the merge through memory (same sums in the same order: equal
-    bit for bit) and the plain attention's; a far key per request stands out; contexts from one
-    key (the second block has nothing) to thousands, portions of one to four tokens."""
-    assert ops.decode_splits(seqs, nkv) == 2
-    ctx_lens = ([1, 17, 1024, 333, 2048, 64, 700, 31, 4097, 2, 96, 5000] * 3)[:seqs]
+    memory (head size 128 with 8 parts has no room for that and merges through memory).  The
+    result is that of the merge through memory (same sums in the same order: equal bit for bit)
+    and the plain attention's; a far key per request stands out; contexts from one key (the later
+    blocks have nothing) to thousands, portions of one to four tokens."""
+    ctx_lens = ([1, 17, 1024, 333, 2048, 64, 700, 31, 3000, 2, 96, 1500] * 3)[:seqs]
+    assert ops.decode_splits(seqs, nkv, -(-max(ctx_lens) // ps) * ps) == parts
     group = nh // nkv
     q_lens = [(1 + i % 4) if (1 + i % 4) * group <= 16 else 1 for i in range(seqs)]
     q_lens = [min(ql, c) for ql, c in zip(q_lens, ctx_lens)]
@@ -447,14 +450,14 @@ def test_two_splits_of_a_context_merge_through_shared_memory(ops, nh, nkv, hd, p
     lib = ops._attention_lib(hd)
     outs = []
     try:
-        for pair in (1, 0, 1):
+        for pair in (8, 0, 8):
             lib.ie_set_decode_pair(pair)
             got = torch.zeros_like(q)
             ops.paged_attention(q, k, v, tables, ctx, nh, nkv, hd, ps, hd ** -0.5, window, got)
             torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=2e-2)
             outs.append(got)
     finally:
-        lib.ie_set_decode_pair(1)
+        lib.ie_set_decode_pair(ops.decode_cluster_max)
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
     ops.check_errors()
 

@@ -13,19 +13,27 @@ import types
 from inference_engine_b200.kernels.cuda_ops import CudaOps
 
 
-def _ops(sm_count=148, balanced="auto", split_target=128):
-    ops = types.SimpleNamespace(sm_count=sm_count, decode_balanced=balanced, decode_split_target=split_target)
+def _ops(sm_count=148, balanced="auto", split_target=128, cluster_max=8):
+    ops = types.SimpleNamespace(sm_count=sm_count, decode_balanced=balanced, decode_split_target=split_target,
+                                decode_cluster_max=cluster_max, decode_cluster_tokens=4096)
     ops.decode_splits = lambda num_seqs, nkv: CudaOps.decode_splits(ops, num_seqs, nkv)
     return ops
 
 
 def test_contexts_are_cut_only_for_small_batches():
     ops = _ops()
-    assert CudaOps.decode_splits(ops, 1, 8) == 16
+    # 2, 4 or 8 parts merge inside a thread-block cluster: counts are rounded down to one of those
+    assert CudaOps.decode_splits(ops, 1, 8) == 8
+    assert CudaOps.decode_splits(ops, 3, 8) == 4   # (5 would fit the target)
     assert CudaOps.decode_splits(ops, 8, 8) == 2
     assert CudaOps.decode_splits(ops, 16, 8) == 1
     assert CudaOps.decode_splits(ops, 64, 8) == 1
-    assert CudaOps.decode_splits(ops, 1, 1) == 32  # never more than 32 parts
+    # ... except at the smallest batches when the tables hold long contexts: more parts, merged through memory
+    assert CudaOps.decode_splits(ops, 1, 8, table_tokens=8192) == 16
+    assert CudaOps.decode_splits(ops, 1, 8, table_tokens=2048) == 8
+    assert CudaOps.decode_splits(ops, 1, 1, table_tokens=32768) == 32  # never more than 32 parts
+    plain = _ops(cluster_max=0)
+    assert CudaOps.decode_splits(plain, 1, 8) == 16 and CudaOps.decode_splits(plain, 3, 8) == 5
 
 
 def test_work_is_dealt_by_length_only_where_that_pays():

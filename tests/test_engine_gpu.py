@@ -121,6 +121,26 @@ def test_preemption_with_few_pages_gives_the_same_tokens():
     assert tight.cache.num_free_pages == [24]
 
 
+def test_preemption_in_bfloat16_with_captured_steps():
+    """The same with the serving kernels and captured decode steps: requests that lose their pages
+    are prefilled again (through the prefill kernels, where the first time they decoded), so a
+    token may differ at a near tie; every token is the plain implementation's choice given the
+    tokens before it, or within a small gap of it, and every page comes back."""
+    from inference_engine_b200 import SamplingParams
+
+    cfg, weights = TINY_B, H.make_weights(TINY_B, seed=16)
+    prompts = {f"p{i}": H.random_tokens(cfg, n, 170 + i) for i, n in enumerate([20, 33, 14, 27, 9])}
+    params = SamplingParams(temperature=0, max_tokens=24)
+    tight = _engine(cfg, weights, "bfloat16", num_blocks=14, block_size=8, max_num_seqs=4,
+                    max_num_batched_tokens=24, enable_cuda_graphs=True)
+    got = tight.generate(prompts, params)
+    assert tight.scheduler.num_preemptions > 0 and tight.graphs.replays > 0
+    for rid, prompt in prompts.items():
+        assert len(got[rid]) == 24
+        _check_greedy(cfg, weights, prompt, got[rid], "bfloat16")
+    assert tight.cache.num_free_pages == [14]
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_steps_launched_ahead_give_the_same_tokens(dtype):
     """A decode step may start on the tokens the device is still sampling, before the host has

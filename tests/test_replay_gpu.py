@@ -14,10 +14,10 @@ import pytest
 import torch
 
 from tests import helpers as H
-from tests.tiny_configs import PAGE_SIZE, TINY_A, TINY_B, TINY_C
+from tests.tiny_configs import PAGE_SIZE, TINY_A, TINY_B, TINY_C, TINY_D
 
 pytestmark = pytest.mark.gpu
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 LENGTHS = [70, 45, 33, 90, 20, 60]
 
 

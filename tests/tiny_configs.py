@@ -30,4 +30,15 @@ TINY_C = {
     "rms_norm_eps": 3e-6, "tie_word_embeddings": False, "max_position_embeddings": 384,
 }
 
-PAGE_SIZE = {"A": 16, "B": 8, "C": 4}
+# A fourth that takes the ways around the fast paths: head size 80 (no tcgen05 attention), a width
+# and a feed-forward size that are no multiples of 16 (the gate and up rows cannot alternate in
+# blocks, the few-row product's inner dimension is no multiple of 64), pages of 32 tokens.
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"],
+    "num_hidden_layers": 2, "hidden_size": 120, "num_attention_heads": 6,
+    "num_key_value_heads": 3, "head_dim": 80, "intermediate_size": 200, "vocab_size": 1000,
+    "rope_theta": 1000000.0, "rms_norm_eps": 2e-5, "tie_word_embeddings": True,
+    "max_position_embeddings": 320,
+}
+
+PAGE_SIZE = {"A": 16, "B": 8, "C": 4, "D": 32}

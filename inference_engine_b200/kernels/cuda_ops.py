@@ -128,6 +128,8 @@ class CudaOps:
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.attn_tc5 = os.environ.get("IE_B200_ATTN_TC5", "1") != "0"  # tcgen05 prefill attention
         self.prefill_key_splits = os.environ.get("IE_B200_PREFILL_KEY_SPLITS", "1") != "0"
+        # up to this many query tiles x heads per SM a block takes two tiles of a request (a late and an early one)
+        self.prefill_paired_max = float(os.environ.get("IE_B200_PREFILL_PAIRED_MAX", 4))
         # the decode kernel cuts contexts until about this many blocks run (one block per SM)
         self.decode_split_target = int(os.environ.get("IE_B200_DECODE_SPLIT_TARGET", 128))
         # up to this many parts of a context merge inside a thread-block cluster (2, 4, 8; 0: never),
@@ -550,7 +552,7 @@ class CudaOps:
             # then much of the GPU would idle (a short portion of a long prompt), the keys of
             # every tile are shared among several blocks instead.
             ksplit = self.prefill_key_split(tiles * nh, hd, ctx.max_ctx_len) if self.prefill_key_splits else 1
-            paired = ksplit == 1 and tiles * nh <= 4 * self.sm_count
+            paired = ksplit == 1 and tiles * nh <= self.prefill_paired_max * self.sm_count
             if paired:
                 tiles = plan["tile_pairs"]
             scratch = tickets = None

@@ -221,6 +221,27 @@ def test_requests_that_cannot_fit_are_refused():
     assert engine.cache.num_free_pages == [4]
 
 
+def test_a_kernel_report_reaches_the_host_with_the_tokens():
+    """Without `debug_checks` too: the kernels' error word travels with every step's tokens, and
+    a step whose kernels reported a bad index (or a wait that ran out) raises instead of
+    handing out tokens; the word is cleared for the next report."""
+    from inference_engine_b200 import SamplingParams
+    from inference_engine_b200.kernels import KernelError
+
+    cfg, weights = TINY_A, H.make_weights(TINY_A, seed=9)
+    engine = _engine(cfg, weights, "bfloat16", num_blocks=16, block_size=16, max_num_seqs=2,
+                     max_num_batched_tokens=32, debug_checks=False)
+    engine.add_request("a", H.random_tokens(cfg, 9, 1), SamplingParams(temperature=0, max_tokens=8))
+    assert len(engine.step()) == 1  # prefill and first token: nothing reported
+    engine.ops.err.copy_(torch.tensor([2, 77, 3, 0], dtype=torch.int32))  # as a kernel would leave it
+    with pytest.raises(KernelError, match="page or slot outside the cache.*77"):
+        while engine.has_unfinished():
+            engine.step()
+    torch.cuda.synchronize()
+    assert engine.ops.err.tolist() == [0, 0, 0, 0]
+    engine.abort("a")
+
+
 def test_smoke_entry():
     import __graft_entry__
 

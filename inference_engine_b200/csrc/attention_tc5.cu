@@ -64,6 +64,33 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// Two 32-bit multiply-adds, or adds, in one instruction (the packed forms this architecture has):
+// the softmax warps are bound by the instructions they issue, not by a pipe.
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    unsigned long long ra, rb, rc, rd;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rc) : "f"(c.x), "f"(c.y));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
+    float2 d;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+    return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    unsigned long long ra, rb, rd;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
+    float2 d;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+    return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 // Instruction descriptor: bfloat16 x bfloat16 -> float, M = 128, N = 64; b_mn: B is MN-major.
 __device__ __forceinline__ unsigned instr_desc(bool b_mn) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
@@ -122,6 +149,13 @@ __device__ __forceinline__ void tmem_st32(const float (&v)[32], unsigned taddr) 
           "r"(taddr) : "memory");
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
+
+#ifdef IE_TC5_TIMING
+__device__ long long g_tc5_clocks[16];
+#define TC5_T(i) do { if (timing) { long long now_ = clock64(); g_tc5_clocks[i] += now_ - mark_; mark_ = now_; } } while (0)
+#else
+#define TC5_T(i) do { } while (0)
+#endif
 
 struct __align__(8) Barriers {
     unsigned long long q_full, kv_full[KV_STAGES], kv_empty[KV_STAGES], s_done[2], p_ready[2], o_done;
@@ -414,6 +448,10 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
         bool ok = true;
         int g = 0;
         ie_pdl_wait();
+#ifdef IE_TC5_TIMING
+        bool timing = tid == 0 && blockIdx.x == gridDim.x / 2 && blockIdx.y == 0;
+        long long mark_ = clock64();
+#endif
         for (int pi = 0; pi < nparts && ok; ++pi) {
             const Part& pt = parts[pi];
             int n_tiles = pt.n_tiles, qpos_lo = pt.qpos_lo, qpos_hi = pt.qpos_hi;
@@ -441,10 +479,13 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
             }
             for (int t = 0; t < n_tiles; ++t, ++g) {
                 int key0 = pt.key_begin + t * KT;
+                TC5_T(0);
                 if (!mbar_wait_compact(&bars->s_done[g & 1], (g >> 1) & 1)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                TC5_T(1);
                 float s[KT];
                 tmem_ld64(s, tmem + (g & 1) * KT + lane_addr);
+                TC5_T(2);
                 // inner tiles (every key visible to every row of the block) need no mask
                 bool inner = key0 + KT - 1 <= qpos_lo && (window <= 0 || key0 >= qpos_hi - window + 1);
                 if (!inner) {
@@ -454,12 +495,16 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
                         s[j] = (kpos <= qpos && kpos >= qlo) ? s[j] : -INFINITY;
                     }
                 }
-                float mx[8];  // eight independent chains: a warp has a scheduler to itself most of the time
+                float mx[8];  // eight independent chains of three-way maxima
 #pragma unroll
                 for (int j = 0; j < 8; ++j) mx[j] = s[j];
 #pragma unroll
-                for (int j = 8; j < KT; ++j) mx[j & 7] = fmaxf(mx[j & 7], s[j]);
-                float tile_max = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+                for (int j = 8; j + 16 <= KT; j += 16)
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) mx[i] = max3(mx[i], s[j + i], s[j + 8 + i]);
+#pragma unroll
+                for (int j = 8 + (KT - 8) / 16 * 16; j < KT; ++j) mx[j & 7] = fmaxf(mx[j & 7], s[j]);
+                float tile_max = fmaxf(max3(max3(mx[0], mx[1], mx[2]), max3(mx[3], mx[4], mx[5]), mx[6]), mx[7]);
                 float m_cand = fmaxf(m, tile_max * scale_log2);
                 bool rescale = __any_sync(0xffffffffu, m_cand > m + RESCALE_LAG);
                 float alpha = 1.f;
@@ -469,21 +514,26 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
                     l *= alpha;
                 }
                 float m_safe = (m == -INFINITY) ? 0.f : m;
+                TC5_T(3);
                 // weights, rounded to bfloat16 and packed two to a column, over this row of S: the
                 // second product's A operand
                 float pw[32];
                 unsigned* w = reinterpret_cast<unsigned*>(pw);
-                float ls[4] = {0.f, 0.f, 0.f, 0.f};
+                float2 ls[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+                const float2 scale2 = make_float2(scale_log2, scale_log2), minus_m = make_float2(-m_safe, -m_safe);
 #pragma unroll
                 for (int c = 0; c < KT / 2; ++c) {
-                    float p0 = fast_exp2(fmaf(s[2 * c], scale_log2, -m_safe));
-                    float p1 = fast_exp2(fmaf(s[2 * c + 1], scale_log2, -m_safe));
-                    ls[c & 3] += p0 + p1;
-                    __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+                    float2 x = fma2(make_float2(s[2 * c], s[2 * c + 1]), scale2, minus_m);
+                    float2 p = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+                    ls[c & 3] = add2(ls[c & 3], p);
+                    __nv_bfloat162 pk = __floats2bfloat162_rn(p.x, p.y);
                     w[c] = *reinterpret_cast<unsigned*>(&pk);
                 }
-                l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+                float2 lsum = add2(add2(ls[0], ls[1]), add2(ls[2], ls[3]));
+                l += lsum.x + lsum.y;
+                TC5_T(4);
                 tmem_st32(pw, tmem + (g & 1) * KT + lane_addr);
+                TC5_T(5);
                 if (t > 0) {
                     // the previous tile's product has had this tile's softmax to finish; waiting for
                     // it here every tile also keeps this barrier's phase in step
@@ -500,8 +550,13 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
                         }
                     }
                 }
+                TC5_T(6);
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 mbar_arrive(&bars->p_ready[g & 1]);
+                TC5_T(7);
+#ifdef IE_TC5_TIMING
+                if (timing) g_tc5_clocks[15] += 1;
+#endif
             }
             if (ok && n_tiles > 0 && !mbar_wait_compact(&bars->o_done, (g - 1) & 1)) ok = false;
             bf16* orow = out + ((size_t)(q0 + pt.t0 + row) * nh + head) * HD;
@@ -573,6 +628,15 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
 
 constexpr size_t SMEM_BYTES = 2 * KV_STAGES * KV_BYTES + MAX_TABLE * 4 + sizeof(Barriers) + 1024;
 }  // namespace
+
+#ifdef IE_TC5_TIMING
+IE_API int ie_tc5_timing(long long* out, int reset) {
+    long long zero[16] = {0};
+    cudaError_t e = cudaMemcpyFromSymbol(out, g_tc5_clocks, sizeof(zero));
+    if (e == cudaSuccess && reset) e = cudaMemcpyToSymbol(g_tc5_clocks, zero, sizeof(zero));
+    return (int)e;
+}
+#endif
 
 // 1 if the tcgen05 prefill kernel can take this geometry: pages of 8..64 tokens, at most
 // `MAX_TABLE` pages per 128-token tile's key range.

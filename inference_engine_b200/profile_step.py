@@ -7,6 +7,9 @@ name.  The reference has bench/profile_step.py in this role.
         python -m inference_engine_b200.profile_step --mode decode --batch 8 --layers 2 --steps 2
 
 With ``--events`` it prints the device time per step measured with CUDA events instead.
+``--phase-clocks`` (prefill, head sizes 64 and 128) builds the tcgen05 prefill attention with clock stamps
+around the phases of one softmax thread (``-DIE_TC5_TIMING``) and prints the clocks per key tile that thread
+spent in each: where a query row's time goes between two key tiles.
 """
 
 from __future__ import annotations
@@ -29,7 +32,13 @@ def main() -> int:
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--config", default=None, help="a config.json file (default: Llama 3.2 1B shape)")
     ap.add_argument("--graphs", action="store_true", help="replay captured decode steps")
+    ap.add_argument("--phase-clocks", action="store_true",
+                    help="prefill: clocks per key tile in each phase of a softmax thread of the tcgen05 attention")
     args = ap.parse_args()
+    if args.phase_clocks:  # (before the kernels are built: the flag is part of the library's name)
+        import os
+
+        os.environ["IE_B200_NVCC_FLAGS"] = (os.environ.get("IE_B200_NVCC_FLAGS", "") + " -DIE_TC5_TIMING").strip()
 
     import torch
 
@@ -122,6 +131,24 @@ def main() -> int:
             times.append(s.elapsed_time(e))
             pos += 1
     engine.ops.check_errors()
+    if args.phase_clocks and args.mode == "prefill":
+        import ctypes
+
+        lib = engine.ops._attention_lib(cfg["head_dim"])
+        clocks = (ctypes.c_longlong * 16)()
+        lib.ie_tc5_timing(clocks, 1)  # forget the warm-up
+        rid = "phase-clocks"
+        cache.add_request(rid)
+        cache.grow(rid, 0, args.tokens)
+        runner.step([StepEntry(rid, torch.randint(0, vocab, (args.tokens,), generator=g).tolist(), 0, [])])
+        torch.cuda.synchronize()
+        lib.ie_tc5_timing(clocks, 1)
+        tiles = max(clocks[15], 1)
+        names = ["loop top (with the stamps' own cost)", "wait for S = Q K^T", "read the row of S (tcgen05.ld)",
+                 "mask, maximum, vote", "exponentials, sum, pack", "write the weights (tcgen05.st)",
+                 "wait for the previous P V (and rescale)", "fence and arrive"]
+        print(json.dumps({"phase_clocks_per_key_tile": {n: round(clocks[i] / tiles) for i, n in enumerate(names)},
+                          "key_tiles_of_the_stamped_block": int(clocks[15]), "layers": args.layers}))
     steady = times[args.warmup:]
     print(json.dumps({"mode": args.mode, "batch": args.batch, "layers": args.layers,
                       "ms_per_step": [round(t, 4) for t in steady]}))

@@ -590,8 +590,10 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
         int row = (lane >> 2) + r * 8;
         bool exists = row < rows;
         int tok = exists ? row / G : 0, g = exists ? row - tok * G : 0;
-        qpos[0][r] = exists ? first_qpos + tok : -1;
-        qlo[0][r] = (window > 0 && qpos[0][r] - window + 1 > 0) ? qpos[0][r] - window + 1 : 0;
+        // (a row that does not exist sees every key: its result is never stored, and the tiles
+        // inside the context keep the path that masks nothing)
+        qpos[0][r] = exists ? first_qpos + tok : 0x7fffffff;
+        qlo[0][r] = (exists && window > 0 && qpos[0][r] - window + 1 > 0) ? qpos[0][r] - window + 1 : 0;
         const bf16* qrow = q + ((size_t)(q0 + tok) * nh + kvh * G + g) * HD;
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
@@ -1016,8 +1018,10 @@ attention_decode_balanced_kernel(const bf16* __restrict__ q, const bf16* __restr
             int row = (lane >> 2) + r * 8;
             bool exists = row < rows;
             int tok = exists ? row / G : 0, g = exists ? row - tok * G : 0;
-            qpos[0][r] = exists ? first_qpos + tok : -1;
-            qlo[0][r] = (window > 0 && qpos[0][r] - window + 1 > 0) ? qpos[0][r] - window + 1 : 0;
+            // (a row that does not exist sees every key: its result is never stored, and the tiles
+            // inside the context keep the path that masks nothing)
+            qpos[0][r] = exists ? first_qpos + tok : 0x7fffffff;
+            qlo[0][r] = (exists && window > 0 && qpos[0][r] - window + 1 > 0) ? qpos[0][r] - window + 1 : 0;
             const bf16* qrow = q + ((size_t)(q0 + tok) * nh + kvh * G + g) * HD;
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks) {

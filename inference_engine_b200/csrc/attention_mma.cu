@@ -331,6 +331,222 @@ __device__ __forceinline__ void finish_rows(RowState& st) {
     }
 }
 
+__device__ __forceinline__ unsigned movmatrix_trans(unsigned a) {
+    unsigned d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+    return d;
+}
+
+// The rows of one (request, key/value head) pair in a decode block: the group's query heads
+// for each of the request's tokens, row = token * G + head within the group.  Two layouts:
+//   wide   (up to 16 rows): the rows are the 16 rows of the instruction, keys its 8 columns;
+//   narrow (up to 8 rows):  the products are swapped.  Scores come out transposed, S^T = K Q^T
+//          (16 keys are the instruction's rows, the query rows its 8 columns), and so does the
+//          output, O^T = V^T P^T (16 dims x 8 rows); P^T reaches the second product through one
+//          movmatrix per 8 keys.  A decoded token with a group of 4 fills 4 of 8 columns instead
+//          of 4 of 16 rows: half the products and half the exponentials per key, which is what
+//          bounds the kernel on long contexts (it issues instructions faster than memory
+//          delivers keys only when there are few of them per key).
+// Both give the same m, l and o per row up to the order of the 32-bit sums.
+constexpr int NARROW_ROWS = 8;
+template <bool NARROW> struct DecodeRows;
+
+template <> struct DecodeRows<false> {
+    RowState st[1];
+    int qpos[1][2], qlo[1][2];
+    unsigned qf[1][KS][4];
+
+    __device__ __forceinline__ void load(const bf16* __restrict__ q, int q0, int rows, int G, int nh, int kvh,
+                                         int first_qpos, int window, int lane) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            int row = (lane >> 2) + r * 8;
+            bool exists = row < rows;
+            int tok = exists ? row / G : 0, g = exists ? row - tok * G : 0;
+            // (a row that does not exist sees every key: its result is never stored, and the tiles
+            // inside the context keep the path that masks nothing)
+            qpos[0][r] = exists ? first_qpos + tok : 0x7fffffff;
+            qlo[0][r] = (exists && window > 0 && qpos[0][r] - window + 1 > 0) ? qpos[0][r] - window + 1 : 0;
+            const bf16* qrow = q + ((size_t)(q0 + tok) * nh + kvh * G + g) * HD;
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+                int d = ks * 16 + (lane & 3) * 2;
+                qf[0][ks][r] = exists ? *reinterpret_cast<const unsigned*>(qrow + d) : 0u;
+                qf[0][ks][r + 2] = exists ? *reinterpret_cast<const unsigned*>(qrow + d + 8) : 0u;
+            }
+        }
+        st[0].init();
+    }
+    template <int KT>
+    __device__ __forceinline__ void tile(const bf16* ktile, const bf16* vtile, int key0, int key_hi,
+                                         float scale_log2, int lane) {
+        process_tile<KT, 1>(st, qf, ktile, vtile, key0, qpos, qlo, key_hi, scale_log2, lane);
+    }
+    // m, l to sm_ml[warp][row][2] and o to sm_o[warp][row][HD]
+    __device__ __forceinline__ void to_shared(float* sm_ml, float* sm_o, int warp, int lane) {
+        finish_rows(st[0]);
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            int row = (lane >> 2) + r * 8;
+            if ((lane & 3) == 0) {
+                sm_ml[(warp * MAX_ROWS + row) * 2] = st[0].m[r];
+                sm_ml[(warp * MAX_ROWS + row) * 2 + 1] = st[0].l[r];
+            }
+#pragma unroll
+            for (int d = 0; d < DT; ++d) {
+                float* dst = sm_o + ((size_t)(warp * MAX_ROWS + row)) * HD + d * 8 + (lane & 3) * 2;
+                dst[0] = st[0].o[d][r * 2];
+                dst[1] = st[0].o[d][r * 2 + 1];
+            }
+        }
+    }
+};
+
+template <> struct DecodeRows<true> {
+    // this thread's two columns (query rows) are 2 * (lane & 3) and the next
+    float m[2], l[2];        // running maximum (log2 units) and this thread's share of the sum
+    float o[KS][4];          // O^T: 16-dim tiles; [0],[1]: dim lane / 4, [2],[3]: dim lane / 4 + 8
+    int cpos[2], clo[2];     // the columns' query position and first visible key
+    unsigned qb[KS][2];      // Q^T as B fragments: query row lane / 4, dims 2 * (lane & 3) ..
+
+    __device__ __forceinline__ void load(const bf16* __restrict__ q, int q0, int rows, int G, int nh, int kvh,
+                                         int first_qpos, int window, int lane) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            int col = (lane & 3) * 2 + c;
+            bool exists = col < rows;
+            cpos[c] = exists ? first_qpos + col / G : 0x7fffffff;  // see the wide layout
+            clo[c] = (exists && window > 0 && cpos[c] - window + 1 > 0) ? cpos[c] - window + 1 : 0;
+            m[c] = -INFINITY;
+            l[c] = 0.f;
+        }
+        int col = lane >> 2;
+        bool exists = col < rows;
+        int tok = exists ? col / G : 0, g = exists ? col - tok * G : 0;
+        const bf16* qrow = q + ((size_t)(q0 + tok) * nh + kvh * G + g) * HD;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            int d = ks * 16 + (lane & 3) * 2;
+            qb[ks][0] = exists ? *reinterpret_cast<const unsigned*>(qrow + d) : 0u;
+            qb[ks][1] = exists ? *reinterpret_cast<const unsigned*>(qrow + d + 8) : 0u;
+            o[ks][0] = o[ks][1] = o[ks][2] = o[ks][3] = 0.f;
+        }
+    }
+
+    template <int KT>
+    __device__ __forceinline__ void tile(const bf16* ktile, const bf16* vtile, int key0, int key_hi,
+                                         float scale_log2, int lane) {
+        constexpr int MT = KT / 16;  // 16-key tiles of the scores
+        float s[MT][4];              // [0],[1]: key lane / 4, [2],[3]: key lane / 4 + 8; columns as above
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) s[mt][0] = s[mt][1] = s[mt][2] = s[mt][3] = 0.f;
+        {
+            const int arow = (lane & 7) + (((lane >> 3) & 1) << 3), achunk = lane >> 4;
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    unsigned a[4];
+                    int row = mt * 16 + arow, c = ks * 2 + achunk;
+                    ldmatrix_x4(a, ktile + (row * C + swz(row, c)) * 8);
+                    mma_bf16(s[mt], a, qb[ks][0], qb[ks][1]);
+                }
+            }
+        }
+        float tile_max[2] = {-INFINITY, -INFINITY};
+        int last = key0 + KT - 1;
+        bool all_visible = last <= key_hi && last <= cpos[0] && last <= cpos[1] && key0 >= clo[0] && key0 >= clo[1];
+        if (__all_sync(0xffffffffu, all_visible)) {  // an inner tile: nothing to mask
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                tile_max[0] = fmaxf(tile_max[0], fmaxf(s[mt][0], s[mt][2]));
+                tile_max[1] = fmaxf(tile_max[1], fmaxf(s[mt][1], s[mt][3]));
+            }
+        } else {
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    int c = j & 1;
+                    int kpos = key0 + mt * 16 + (lane >> 2) + ((j >> 1) << 3);
+                    bool valid = kpos <= cpos[c] && kpos >= clo[c] && kpos <= key_hi;
+                    float v = valid ? s[mt][j] : -INFINITY;
+                    s[mt][j] = v;
+                    tile_max[c] = fmaxf(tile_max[c], v);
+                }
+            }
+        }
+        float alpha[2], m_safe[2];
+        bool grew = false;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            float t = tile_max[c];  // over the keys of the tile: the lanes that share lane & 3
+            t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, 4));
+            t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, 8));
+            t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, 16));
+            float m_new = fmaxf(m[c], t * scale_log2);  // the scale is positive: max commutes
+            m_safe[c] = (m_new == -INFINITY) ? 0.f : m_new;
+            alpha[c] = fast_exp2(m[c] - m_safe[c]);  // 0 when nothing was seen before
+            grew = grew || m_new > m[c];
+            m[c] = m_new;
+        }
+        if (__any_sync(0xffffffffu, grew)) {
+            l[0] *= alpha[0];
+            l[1] *= alpha[1];
+#pragma unroll
+            for (int d = 0; d < KS; ++d) {
+                o[d][0] *= alpha[0]; o[d][1] *= alpha[1];
+                o[d][2] *= alpha[0]; o[d][3] *= alpha[1];
+            }
+        }
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float p = fast_exp2(fmaf(s[mt][j], scale_log2, -m_safe[j & 1]));  // -inf stays -inf -> 0
+                s[mt][j] = p;
+                l[j & 1] += p;
+            }
+        }
+        const int vrow = (lane & 7) + ((lane >> 4) << 3), vchunk = (lane >> 3) & 1;
+#pragma unroll
+        for (int kk = 0; kk < MT; ++kk) {
+            // P^T for 16 keys as B fragments: the weights rounded to bfloat16, 8 x 8 blocks transposed
+            unsigned b0 = movmatrix_trans(pack_bf16(s[kk][0], s[kk][1]));
+            unsigned b1 = movmatrix_trans(pack_bf16(s[kk][2], s[kk][3]));
+#pragma unroll
+            for (int d = 0; d < KS; ++d) {
+                unsigned a[4];  // V^T: 16 dims x 16 keys
+                int row = kk * 16 + vrow, c = d * 2 + vchunk;
+                ldmatrix_x4_trans(a, vtile + (row * C + swz(row, c)) * 8);
+                mma_bf16(o[d], a, b0, b1);
+            }
+        }
+    }
+
+    __device__ __forceinline__ void to_shared(float* sm_ml, float* sm_o, int warp, int lane) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            l[c] += __shfl_xor_sync(0xffffffffu, l[c], 4);
+            l[c] += __shfl_xor_sync(0xffffffffu, l[c], 8);
+            l[c] += __shfl_xor_sync(0xffffffffu, l[c], 16);
+            int col = (lane & 3) * 2 + c;
+            if ((lane >> 2) == 0) {
+                sm_ml[(warp * MAX_ROWS + col) * 2] = m[c];
+                sm_ml[(warp * MAX_ROWS + col) * 2 + 1] = l[c];
+            }
+        }
+#pragma unroll
+        for (int d = 0; d < KS; ++d) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                int col = (lane & 3) * 2 + (j & 1), dim = d * 16 + (lane >> 2) + ((j >> 1) << 3);
+                sm_o[((size_t)(warp * MAX_ROWS + col)) * HD + dim] = o[d][j];
+            }
+        }
+    }
+};
+
 // -------------------------------------------------------------------------------------------------
 // Decode: few rows per request.  grid = (requests, kv heads, splits), 8 warps, one block per SM.
 //
@@ -355,6 +571,38 @@ constexpr int DSTAGES = 3;
 template <int NWARPS>
 __device__ __forceinline__ void decode_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(NWARPS * 32) : "memory"); }
 
+// A warp's walk over its key tiles j0, j0 + stride, ... < n_tiles of one (request, key/value
+// head) pair.  The copies of the first DSTAGES - 1 tiles are in flight (one group each) and
+// `next` holds the block-table entries of tile j0 + (DSTAGES - 1) * stride: the copies of tile
+// i+2 use entries fetched one tile earlier, and the entries of tile i+3 are fetched now, so no
+// lookup is waited for.
+template <bool NARROW>
+__device__ __forceinline__ void decode_walk(DecodeRows<NARROW>& rs, TilePages<KT_DECODE, 32> next, bf16* ring,
+                                            const int* __restrict__ table, int table_width,
+                                            const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+                                            int j0, int stride, int n_tiles, int lo, int hi, int kvh, int nkv,
+                                            int page_shift, int total_pages, float scale_log2, int lane, int* err) {
+    constexpr int KT = KT_DECODE, TILE_ELEMS = KT * HD;
+    int i = 0;
+    for (int j = j0; j < n_tiles; j += stride, ++i) {
+        int pre = j + (DSTAGES - 1) * stride;
+        if (pre < n_tiles) {
+            bf16* st_k = ring + (size_t)((i + DSTAGES - 1) % DSTAGES) * 2 * TILE_ELEMS;
+            issue_kv<KT, 32, true>(st_k, st_k + TILE_ELEMS, next, k_cache, v_cache, lo + pre * KT, lo, hi,
+                                   kvh, nkv, page_shift, total_pages, lane, err);
+        }
+        cp_async_commit();
+        if (pre + stride < n_tiles)
+            fetch_pages<KT, 32>(next, table, table_width, lo + (pre + stride) * KT, lo, hi, page_shift, lane);
+        cp_async_wait<DSTAGES - 1>();
+        __syncwarp();
+        const bf16* cur = ring + (size_t)(i % DSTAGES) * 2 * TILE_ELEMS;
+        rs.template tile<KT>(cur, cur + TILE_ELEMS, lo + j * KT, hi, scale_log2, lane);
+        __syncwarp();
+    }
+    cp_async_wait<0>();
+}
+
 // The end of a decode block (its 8 x 32 compute threads call this together): the warps' partial
 // results are merged through shared memory; with one split the block writes the output, with
 // more it writes its partial result and the block that finishes last for this (request,
@@ -373,35 +621,21 @@ __device__ __forceinline__ void pair_store(float* stage, float v) {
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
 
-template <int NWARPS, bool PAIR = false>
-__device__ __forceinline__ void decode_merge_store(RowState& st, unsigned char* smem_raw, int* is_last, int warp,
+template <int NWARPS, bool PAIR = false, typename Rows>
+__device__ __forceinline__ void decode_merge_store(Rows& rs, unsigned char* smem_raw, int* is_last, int warp,
                                                    int lane, int rows, int G, int q0, int seq, int kvh, int split,
                                                    int num_splits, int nh, int nkv, bf16* __restrict__ out,
                                                    float* __restrict__ part_o, float* __restrict__ part_ml,
                                                    int* __restrict__ tickets) {
     constexpr int WARPS = NWARPS;
     int tid = warp * 32 + lane;
-    finish_rows(st);
     decode_barrier<NWARPS>();  // every warp is done with its tiles: the shared memory is reused below
     // [warp][row] m, l and [warp][row][HD] o in shared memory
     float* sm_ml = reinterpret_cast<float*>(smem_raw);            // [WARPS][16][2]
     float* sm_o = sm_ml + WARPS * MAX_ROWS * 2;                   // [WARPS][16][HD]
     float* pair_stage = reinterpret_cast<float*>(smem_raw + (size_t)WARPS * DSTAGES * 2 * KT_DECODE * HD * sizeof(bf16));
     (void)pair_stage;
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        int row = (lane >> 2) + r * 8;
-        if ((lane & 3) == 0) {
-            sm_ml[(warp * MAX_ROWS + row) * 2] = st.m[r];
-            sm_ml[(warp * MAX_ROWS + row) * 2 + 1] = st.l[r];
-        }
-#pragma unroll
-        for (int d = 0; d < DT; ++d) {
-            float* dst = sm_o + ((size_t)(warp * MAX_ROWS + row)) * HD + d * 8 + (lane & 3) * 2;
-            dst[0] = st.o[d][r * 2];
-            dst[1] = st.o[d][r * 2 + 1];
-        }
-    }
+    rs.to_shared(sm_ml, sm_o, warp, lane);
     decode_barrier<NWARPS>();
     for (int idx = tid; idx < rows * HD; idx += WARPS * 32) {
         int row = idx / HD, d = idx - row * HD;
@@ -509,7 +743,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
                         int table_width, const int* __restrict__ cu_q, const int* __restrict__ ctx_lens,
                         bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                         int* __restrict__ tickets, int nh, int nkv, int page_shift, int total_pages,
-                        float scale_log2, int window, int num_splits, int* err) {
+                        float scale_log2, int window, int num_splits, int narrow_rows, int* err) {
     constexpr int KT = KT_DECODE, TILE_ELEMS = KT * HD, WARPS = NWARPS;
     __shared__ int is_last;
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -582,52 +816,22 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
             cp_async_commit();
         }
     }
-    // 3. the queries (they needed cu_q) while those are in flight
-    int qpos[1][2], qlo[1][2];
-    unsigned qf[1][KS][4];
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        int row = (lane >> 2) + r * 8;
-        bool exists = row < rows;
-        int tok = exists ? row / G : 0, g = exists ? row - tok * G : 0;
-        // (a row that does not exist sees every key: its result is never stored, and the tiles
-        // inside the context keep the path that masks nothing)
-        qpos[0][r] = exists ? first_qpos + tok : 0x7fffffff;
-        qlo[0][r] = (exists && window > 0 && qpos[0][r] - window + 1 > 0) ? qpos[0][r] - window + 1 : 0;
-        const bf16* qrow = q + ((size_t)(q0 + tok) * nh + kvh * G + g) * HD;
-#pragma unroll
-        for (int ks = 0; ks < KS; ++ks) {
-            int d = ks * 16 + (lane & 3) * 2;
-            qf[0][ks][r] = exists ? *reinterpret_cast<const unsigned*>(qrow + d) : 0u;
-            qf[0][ks][r + 2] = exists ? *reinterpret_cast<const unsigned*>(qrow + d + 8) : 0u;
-        }
+    // 3. the queries (they needed cu_q) while those are in flight, 4. the ring, 5. the merge
+    if (rows <= narrow_rows) {
+        DecodeRows<true> rs;
+        rs.load(q, q0, rows, G, nh, kvh, first_qpos, window, lane);
+        decode_walk(rs, pg[DSTAGES - 1], ring, table, table_width, k_cache, v_cache, j0, stride, n_tiles, lo, hi, kvh,
+                    nkv, page_shift, total_pages, scale_log2, lane, err);
+        decode_merge_store<NWARPS, PAIR>(rs, smem_raw, &is_last, warp, lane, rows, G, q0, seq, kvh, split, num_splits,
+                                         nh, nkv, out, part_o, part_ml, tickets);
+    } else {
+        DecodeRows<false> rs;
+        rs.load(q, q0, rows, G, nh, kvh, first_qpos, window, lane);
+        decode_walk(rs, pg[DSTAGES - 1], ring, table, table_width, k_cache, v_cache, j0, stride, n_tiles, lo, hi, kvh,
+                    nkv, page_shift, total_pages, scale_log2, lane, err);
+        decode_merge_store<NWARPS, PAIR>(rs, smem_raw, &is_last, warp, lane, rows, G, q0, seq, kvh, split, num_splits,
+                                         nh, nkv, out, part_o, part_ml, tickets);
     }
-    RowState sts[1];
-    sts[0].init();
-    RowState& st = sts[0];
-    // 4. the ring: the copies of tile i+2 use block-table entries fetched one tile earlier, and
-    //    the entries of tile i+3 are fetched now, so no lookup is waited for
-    Pages next = pg[DSTAGES - 1];
-    int i = 0;
-    for (int j = j0; j < n_tiles; j += stride, ++i) {
-        int pre = j + (DSTAGES - 1) * stride;
-        if (pre < n_tiles) {
-            bf16* st_k = ring + (size_t)((i + DSTAGES - 1) % DSTAGES) * 2 * TILE_ELEMS;
-            issue_kv<KT, 32, true>(st_k, st_k + TILE_ELEMS, next, k_cache, v_cache, lo + pre * KT, lo, hi,
-                                   kvh, nkv, page_shift, total_pages, lane, err);
-        }
-        cp_async_commit();
-        if (pre + stride < n_tiles)
-            fetch_pages<KT, 32>(next, table, table_width, lo + (pre + stride) * KT, lo, hi, page_shift, lane);
-        cp_async_wait<DSTAGES - 1>();
-        __syncwarp();
-        const bf16* cur = ring + (size_t)(i % DSTAGES) * 2 * TILE_ELEMS;
-        process_tile<KT, 1>(sts, qf, cur, cur + TILE_ELEMS, lo + j * KT, qpos, qlo, hi, scale_log2, lane);
-        __syncwarp();
-    }
-    cp_async_wait<0>();
-    decode_merge_store<NWARPS, PAIR>(st, smem_raw, &is_last, warp, lane, rows, G, q0, seq, kvh, split, num_splits, nh,
-                                     nkv, out, part_o, part_ml, tickets);
 }
 
 // -------------------------------------------------------------------------------------------------
@@ -651,33 +855,19 @@ constexpr int MAX_BALANCED_SEQS = 512;  // requests a balanced launch takes (the
 // pair and writes the output.  Otherwise it writes its partial result to `slot`, and the block
 // that finishes last of the pair's `parts` blocks merges their slots first_slot, first_slot + 1,
 // ... in that order.  The ticket counter goes back to zero for the next launch.
-template <int NWARPS>
-__device__ __forceinline__ void decode_merge_slots(RowState& st, unsigned char* smem_raw, int* is_last, int warp,
+template <int NWARPS, typename Rows>
+__device__ __forceinline__ void decode_merge_slots(Rows& rs, unsigned char* smem_raw, int* is_last, int warp,
                                                    int lane, int rows, int G, int q0, int kvh, int nh, bool whole,
                                                    int slot, int first_slot, int parts, int* ticket,
                                                    bf16* __restrict__ out, float* __restrict__ part_o,
                                                    float* __restrict__ part_ml) {
     constexpr int WARPS = NWARPS;
     int tid = warp * 32 + lane;
-    finish_rows(st);
     decode_barrier<NWARPS>();  // every warp is done with its tiles: the shared memory is reused below
     // [warp][row] m, l and [warp][row][HD] o in shared memory
     float* sm_ml = reinterpret_cast<float*>(smem_raw);            // [WARPS][16][2]
     float* sm_o = sm_ml + WARPS * MAX_ROWS * 2;                   // [WARPS][16][HD]
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        int row = (lane >> 2) + r * 8;
-        if ((lane & 3) == 0) {
-            sm_ml[(warp * MAX_ROWS + row) * 2] = st.m[r];
-            sm_ml[(warp * MAX_ROWS + row) * 2 + 1] = st.l[r];
-        }
-#pragma unroll
-        for (int d = 0; d < DT; ++d) {
-            float* dst = sm_o + ((size_t)(warp * MAX_ROWS + row)) * HD + d * 8 + (lane & 3) * 2;
-            dst[0] = st.o[d][r * 2];
-            dst[1] = st.o[d][r * 2 + 1];
-        }
-    }
+    rs.to_shared(sm_ml, sm_o, warp, lane);
     decode_barrier<NWARPS>();
     for (int idx = tid; idx < rows * HD; idx += WARPS * 32) {
         int row = idx / HD, d = idx - row * HD;
@@ -786,7 +976,7 @@ attention_decode_balanced_kernel(const bf16* __restrict__ q, const bf16* __restr
                         int table_width, const int* __restrict__ cu_q, const int* __restrict__ ctx_lens,
                         bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                         int* __restrict__ tickets, int num_seqs, int nh, int nkv, int page_shift,
-                        int total_pages, float scale_log2, int window, int* err) {
+                        int total_pages, float scale_log2, int window, int narrow_rows, int* err) {
     constexpr int KT = KT_DECODE, TILE_ELEMS = KT * HD, WARPS = NWARPS;
     __shared__ int is_last;
     // balanced launches: tiles (of one head) and pieces (of all heads) of the requests before each request
@@ -1010,53 +1200,23 @@ attention_decode_balanced_kernel(const bf16* __restrict__ q, const bf16* __restr
                 cp_async_commit();
             }
         }
-        // 3. the queries while those are in flight
-        int qpos[1][2], qlo[1][2];
-        unsigned qf[1][KS][4];
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            int row = (lane >> 2) + r * 8;
-            bool exists = row < rows;
-            int tok = exists ? row / G : 0, g = exists ? row - tok * G : 0;
-            // (a row that does not exist sees every key: its result is never stored, and the tiles
-            // inside the context keep the path that masks nothing)
-            qpos[0][r] = exists ? first_qpos + tok : 0x7fffffff;
-            qlo[0][r] = (exists && window > 0 && qpos[0][r] - window + 1 > 0) ? qpos[0][r] - window + 1 : 0;
-            const bf16* qrow = q + ((size_t)(q0 + tok) * nh + kvh * G + g) * HD;
-#pragma unroll
-            for (int ks = 0; ks < KS; ++ks) {
-                int d = ks * 16 + (lane & 3) * 2;
-                qf[0][ks][r] = exists ? *reinterpret_cast<const unsigned*>(qrow + d) : 0u;
-                qf[0][ks][r + 2] = exists ? *reinterpret_cast<const unsigned*>(qrow + d + 8) : 0u;
-            }
+        // 3. the queries while those are in flight, 4. the ring, 5. merge the warps; write the
+        //    output or this block's partial result
+        if (rows <= narrow_rows) {
+            DecodeRows<true> rs;
+            rs.load(q, q0, rows, G, nh, kvh, first_qpos, window, lane);
+            decode_walk(rs, pg[DSTAGES - 1], ring, table, table_width, k_cache, v_cache, j0, stride, n_tiles, lo, hi,
+                        kvh, nkv, page_shift, total_pages, scale_log2, lane, err);
+            decode_merge_slots<NWARPS>(rs, smem_raw, &is_last, warp, lane, rows, G, q0, kvh, nh, whole, slot,
+                                       first_slot, parts, tickets + seq * nkv + kvh, out, part_o, part_ml);
+        } else {
+            DecodeRows<false> rs;
+            rs.load(q, q0, rows, G, nh, kvh, first_qpos, window, lane);
+            decode_walk(rs, pg[DSTAGES - 1], ring, table, table_width, k_cache, v_cache, j0, stride, n_tiles, lo, hi,
+                        kvh, nkv, page_shift, total_pages, scale_log2, lane, err);
+            decode_merge_slots<NWARPS>(rs, smem_raw, &is_last, warp, lane, rows, G, q0, kvh, nh, whole, slot,
+                                       first_slot, parts, tickets + seq * nkv + kvh, out, part_o, part_ml);
         }
-        RowState sts[1];
-        sts[0].init();
-        RowState& st = sts[0];
-        // 4. the ring: the copies of tile i+2 use block-table entries fetched one tile earlier, and
-        //    the entries of tile i+3 are fetched now, so no lookup is waited for
-        Pages next = pg[DSTAGES - 1];
-        int i = 0;
-        for (int j = j0; j < n_tiles; j += stride, ++i) {
-            int pre = j + (DSTAGES - 1) * stride;
-            if (pre < n_tiles) {
-                bf16* st_k = ring + (size_t)((i + DSTAGES - 1) % DSTAGES) * 2 * TILE_ELEMS;
-                issue_kv<KT, 32, true>(st_k, st_k + TILE_ELEMS, next, k_cache, v_cache, lo + pre * KT, lo, hi,
-                                       kvh, nkv, page_shift, total_pages, lane, err);
-            }
-            cp_async_commit();
-            if (pre + stride < n_tiles)
-                fetch_pages<KT, 32>(next, table, table_width, lo + (pre + stride) * KT, lo, hi, page_shift, lane);
-            cp_async_wait<DSTAGES - 1>();
-            __syncwarp();
-            const bf16* cur = ring + (size_t)(i % DSTAGES) * 2 * TILE_ELEMS;
-            process_tile<KT, 1>(sts, qf, cur, cur + TILE_ELEMS, lo + j * KT, qpos, qlo, hi, scale_log2, lane);
-            __syncwarp();
-        }
-        cp_async_wait<0>();
-        // 5. merge the warps; write the output or this block's partial result
-        decode_merge_slots<NWARPS>(st, smem_raw, &is_last, warp, lane, rows, G, q0, kvh, nh, whole, slot,
-                                   first_slot, parts, tickets + seq * nkv + kvh, out, part_o, part_ml);
         decode_barrier<NWARPS>();  // the merge read shared memory that the next pair's copies overwrite
         if (by_range) {
             int took = tile_end - tile0;
@@ -1211,8 +1371,16 @@ inline int& decode_pair_enabled() {
     return enabled;
 }
 
+// Requests with at most this many rows (tokens x group size) run the decode kernels' swapped
+// products (DecodeRows<true>); 0: all run the 16-row layout.
+inline int& decode_narrow_rows() {
+    static int rows = NARROW_ROWS;
+    return rows;
+}
+
 IE_API int ie_attention_head_dim() { return HD; }
 IE_API void ie_set_decode_pair(int max_splits) { decode_pair_enabled() = max_splits; }
+IE_API void ie_set_decode_narrow(int enabled) { decode_narrow_rows() = enabled ? NARROW_ROWS : 0; }
 // Query tokens one block of the prefill kernel takes (callers count tiles with it).
 IE_API int ie_attention_prefill_rows() { return BM; }
 IE_API void ie_set_pdl(int enabled) { ie_pdl_enabled() = enabled ? 1 : 0; }
@@ -1245,7 +1413,7 @@ int launch_decode_as(const void* q, const void* k_cache, const void* v_cache, co
                                  dim3(1, 1, (unsigned)num_splits),
                                  (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, tables, table_width, cu_q,
                                  ctx_lens, (bf16*)out, part_o, part_ml, tickets, nh, nkv, page_shift, total_pages,
-                                 scale * 1.4426950408889634f, window, num_splits, err);
+                                 scale * 1.4426950408889634f, window, num_splits, decode_narrow_rows(), err);
     }
     static IePerDevice configured;
     cudaError_t e = ie_allow_smem(configured, attention_decode_kernel<NWARPS>, decode_smem(NWARPS));
@@ -1253,7 +1421,7 @@ int launch_decode_as(const void* q, const void* k_cache, const void* v_cache, co
     return ie_launch(attention_decode_kernel<NWARPS>, grid, dim3(NWARPS * 32), decode_smem(NWARPS), s,
                      (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, tables, table_width, cu_q,
                      ctx_lens, (bf16*)out, part_o, part_ml, tickets, nh, nkv, page_shift, total_pages,
-                     scale * 1.4426950408889634f, window, num_splits, err);
+                     scale * 1.4426950408889634f, window, num_splits, decode_narrow_rows(), err);
 }
 
 // With at most one block per SM a block takes the SM's whole shared memory for tiles in flight;
@@ -1319,7 +1487,7 @@ int launch_balanced_as(const void* q, const void* k_cache, const void* v_cache, 
     return ie_launch(attention_decode_balanced_kernel<NWARPS>, dim3(blocks), dim3(NWARPS * 32), decode_smem(NWARPS), s,
                      (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, tables, table_width, cu_q, ctx_lens,
                      (bf16*)out, part_o, part_ml, tickets, num_seqs, nh, nkv, page_shift, total_pages,
-                     scale * 1.4426950408889634f, window, err);
+                     scale * 1.4426950408889634f, window, decode_narrow_rows(), err);
 }
 }  // namespace
 

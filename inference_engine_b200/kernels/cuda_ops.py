@@ -136,6 +136,9 @@ class CudaOps:
         # for steps whose block tables hold at most `decode_cluster_tokens` tokens per request
         self.decode_cluster_max = int(os.environ.get("IE_B200_DECODE_PAIR", 8))
         self.decode_cluster_tokens = int(os.environ.get("IE_B200_DECODE_CLUSTER_TOKENS", 4096))
+        # requests with at most 8 rows (tokens x query heads per key/value head) run the decode
+        # kernels' swapped products: keys are the instruction's rows ("0": the 16-row layout for all)
+        self.decode_narrow = os.environ.get("IE_B200_DECODE_NARROW", "1") != "0"
         # batches whose contexts differ much in length go to the decode kernel that deals key tiles
         # by length ("auto": when the step's context says so; "1": always; "0": never)
         self.decode_balanced = os.environ.get("IE_B200_DECODE_BALANCED", "auto")
@@ -392,6 +395,7 @@ class CudaOps:
             lib = ctypes.CDLL(str(build_attention(hd)))
             lib.ie_set_pdl(1 if self.pdl else 0)
             lib.ie_set_decode_pair(self.decode_cluster_max)
+            lib.ie_set_decode_narrow(1 if self.decode_narrow else 0)
             P, I, F = c_void_p, c_int, c_float
             lib.ie_attention_decode.argtypes = [P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, F, I, I, P, P]
             lib.ie_attention_prefill.argtypes = [P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P, P]

@@ -462,6 +462,43 @@ def test_splits_of_a_context_merge_through_shared_memory(ops, nh, nkv, hd, ps, s
     ops.check_errors()
 
 
+@pytest.mark.parametrize("nh,nkv,hd,ps", [(32, 8, 64, 16), (8, 2, 128, 16), (7, 1, 48, 8), (5, 5, 80, 4), (16, 2, 32, 16),
+                                          (6, 3, 16, 16)])
+@pytest.mark.parametrize("window", [0, 300])
+@pytest.mark.parametrize("by_length", ["0", "1"])
+def test_decode_attention_with_keys_as_the_rows_of_the_products(ops, nh, nkv, hd, ps, window, by_length, monkeypatch):
+    """Requests of at most 8 rows (tokens x query heads per key/value head) run the decode
+    kernels with the products swapped (keys are the instruction's rows); requests of 9 to 16 rows
+    keep the 16-row layout, in the same launch.  Both layouts give the plain attention's result
+    and differ from each other by rounding only (the order of 32-bit sums); a far key per
+    request stands out, so that a key or a row in the wrong place shows.  Contexts from one key
+    to thousands, at tile and page edges; portions of one to eight tokens, whose rows see
+    different last keys."""
+    group = nh // nkv
+    ctx_lens = [1, 2, 15, 16, 17, 31, 32, 33, 63, 64, 65, 257, 1000, 2049, 3000, 8, 640, 96]
+    q_lens = [min(1 + i % 8, c, max(1, 16 // group)) for i, c in enumerate(ctx_lens)]
+    assert any(ql * group <= 8 for ql in q_lens)
+    spike = [max(0, c - ql - window // 2) if window else (c - ql) // 3 for c, ql in zip(ctx_lens, q_lens)]
+    monkeypatch.setattr(ops, "decode_balanced", by_length)
+    q, k, v, tables, ctx = _attention_case(nh, nkv, hd, ps, q_lens, ctx_lens, torch.bfloat16, seed=13, spike=spike)
+    want = torch.empty_like(q)
+    RefOps().paged_attention(q, k, v, tables, ctx, nh, nkv, hd, ps, hd ** -0.5, window, want)
+    lib = ops._attention_lib(hd)
+    outs = []
+    try:
+        for narrow in (1, 0):
+            lib.ie_set_decode_narrow(narrow)
+            got = torch.zeros_like(q)
+            ops.paged_attention(q, k, v, tables, ctx, nh, nkv, hd, ps, hd ** -0.5, window, got)
+            torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+            outs.append(got)
+    finally:
+        lib.ie_set_decode_narrow(1 if ops.decode_narrow else 0)
+    # one rounding step of bfloat16 at most between the layouts
+    torch.testing.assert_close(outs[0].float(), outs[1].float(), atol=4e-3, rtol=8e-3)
+    ops.check_errors()
+
+
 @pytest.mark.parametrize("nh,nkv,hd,ps", [(32, 8, 64, 16), (8, 2, 128, 16), (4, 1, 64, 8)])
 @pytest.mark.parametrize("window", [0, 1000])
 @pytest.mark.parametrize("q_lens,ctx_lens", [([200], [3000]), ([130, 1, 260], [2600, 900, 260]), ([17], [1100])])

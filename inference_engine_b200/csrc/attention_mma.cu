@@ -1393,6 +1393,51 @@ IE_API long long ie_attention_decode_scratch_floats(int num_seqs, int nkv, int n
 }
 
 namespace {
+// How many clusters of `num_splits` decode blocks of NWARPS warps the current device runs at one
+// time (a cluster's blocks need room in one group of SMs together, so fewer than SMs over
+// num_splits): a grid with more clusters than that takes a second round.  0 if the splits do not
+// merge as a cluster or the runtime cannot say.
+template <int NWARPS>
+int max_decode_clusters(int num_splits) {
+    size_t smem = decode_smem(NWARPS) + (size_t)num_splits * PAIR_SLOT_BYTES;
+    if (!(num_splits == 2 || num_splits == 4 || num_splits == 8) || smem > MAX_DYNAMIC_SMEM) return 0;
+    auto kernel = attention_decode_kernel<NWARPS, true>;
+    size_t limit = decode_smem(NWARPS) + (size_t)8 * PAIR_SLOT_BYTES;
+    if (limit > MAX_DYNAMIC_SMEM) limit = MAX_DYNAMIC_SMEM;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)limit) != cudaSuccess) return 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1, 1, (unsigned)num_splits);
+    cfg.blockDim = dim3(NWARPS * 32);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = (unsigned)num_splits;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return 0;
+    }
+    return clusters;
+}
+
+// The same, asked once per device and cluster size.
+template <int NWARPS>
+int decode_clusters_at_once(int num_splits) {
+    static int known[IE_MAX_DEVICES][3] = {};  // 0: not asked yet, else the answer + 1
+    int dev = -1, slot = num_splits == 2 ? 0 : num_splits == 4 ? 1 : 2;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= IE_MAX_DEVICES) return max_decode_clusters<NWARPS>(num_splits);
+    if (known[dev][slot] == 0) known[dev][slot] = max_decode_clusters<NWARPS>(num_splits) + 1;
+    return known[dev][slot] - 1;
+}
+}  // namespace
+
+IE_API int ie_attention_decode_max_clusters(int num_splits) { return decode_clusters_at_once<DWARPS>(num_splits); }
+
+namespace {
 template <int NWARPS>
 int launch_decode_as(const void* q, const void* k_cache, const void* v_cache, const int* tables, int table_width,
                      const int* cu_q, const int* ctx_lens, void* out, float* part_o, float* part_ml, int* tickets,
@@ -1400,9 +1445,15 @@ int launch_decode_as(const void* q, const void* k_cache, const void* v_cache, co
                      int num_splits, int* err, cudaStream_t s) {
     dim3 grid(num_seqs, nkv, num_splits);
     size_t pair_smem = decode_smem(NWARPS) + (size_t)num_splits * PAIR_SLOT_BYTES;
-    if ((num_splits == 2 || num_splits == 4 || num_splits == 8) && num_splits <= decode_pair_enabled() &&
-        pair_smem <= MAX_DYNAMIC_SMEM) {
-        // the splits are a cluster that merges through shared memory
+    // the splits are a cluster that merges through shared memory, if all clusters run at one time
+    // (where the runtime cannot say how many do, it is taken that they do)
+    bool as_cluster = (num_splits == 2 || num_splits == 4 || num_splits == 8) && num_splits <= decode_pair_enabled() &&
+                      pair_smem <= MAX_DYNAMIC_SMEM;
+    if (as_cluster) {
+        int fit = decode_clusters_at_once<NWARPS>(num_splits);
+        as_cluster = fit <= 0 || (long long)num_seqs * nkv <= fit;
+    }
+    if (as_cluster) {
         static IePerDevice configured_pair;
         size_t smem = decode_smem(NWARPS) + (size_t)8 * PAIR_SLOT_BYTES;  // (what the function is set up for)
         if (smem > MAX_DYNAMIC_SMEM) smem = MAX_DYNAMIC_SMEM;

@@ -178,6 +178,7 @@ class CudaOps:
         self.nvtx = os.environ.get("IE_B200_NVTX", "0") == "1"  # an NVTX range around every kernel call
         self.launches = 0  # launches of this library's kernels (library matrix products not counted)
         self.launch_counts: dict[str, int] = {}  # the same, per kernel
+        self._cluster_fit: dict[tuple[int, int], int] = {}  # (head size, parts) -> clusters the device runs at once
 
     def _declare(self) -> None:
         P, I, F, L = c_void_p, c_int, c_float, ctypes.c_longlong
@@ -408,6 +409,7 @@ class CudaOps:
             lib.ie_attention_decode_balanced.argtypes = [P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, F, I, I, P, P]
             lib.ie_attention_decode_balanced_scratch_floats.argtypes = [I, I, I]
             lib.ie_attention_decode_balanced_scratch_floats.restype = ctypes.c_longlong
+            lib.ie_attention_decode_max_clusters.argtypes = [I]
             self._attn_libs[hd] = lib
         return lib
 
@@ -419,20 +421,39 @@ class CudaOps:
             self._tickets = self.torch.zeros(max(count, 16384), dtype=self.torch.int32, device=self.device)
         return self._tickets
 
-    def decode_splits(self, num_seqs: int, nkv: int, table_tokens: int = 0) -> int:
+    def _clusters_at_once(self, hd: int, parts: int) -> int:
+        """How many clusters of ``parts`` decode attention blocks the device runs at one time for
+        head size ``hd`` (a cluster's blocks must find room in one group of SMs at the same
+        time, so this is less than the SMs over ``parts``); 0: unknown."""
+        key = (hd, parts)
+        if key not in self._cluster_fit:
+            self._cluster_fit[key] = int(self._attention_lib(hd).ie_attention_decode_max_clusters(parts))
+        return self._cluster_fit[key]
+
+    def decode_splits(self, num_seqs: int, nkv: int, table_tokens: int = 0, hd: int | None = None) -> int:
         """Into how many parts the decode kernel cuts each context.  One block per (request,
         key/value head) streams at an SM's full rate, so contexts are only cut when there are
         few such blocks (small batches).  2, 4 or 8 parts run as one thread-block cluster and
         merge through shared memory, which is worth more than the last few blocks: the count is
-        rounded down to one of those, except for long contexts at the smallest batches
-        (``table_tokens``: what the step's block tables can hold), where 16 or 32 parts that
-        merge through memory stream faster.  The number depends on the batch and the tables'
+        rounded down to one of those (and to one of which the device runs all clusters at one
+        time, if the head size ``hd`` is given), except for long contexts (``table_tokens``: what
+        the step's block tables can hold), where as many parts as give nearly every SM a block
+        stream faster, whichever way they merge.  The number depends on the batch and the tables'
         width alone, never on the contexts' lengths, so that a captured launch stays valid."""
-        blocks = max(num_seqs * nkv, 1)
-        parts = max(1, min(self.decode_split_target // blocks, 32))
-        if self.decode_cluster_max < 2 or parts < 2 or (parts > 8 and table_tokens > self.decode_cluster_tokens):
+        pairs = max(num_seqs * nkv, 1)
+        if table_tokens > self.decode_cluster_tokens:
+            # long contexts: a block for nearly every SM counts for more than the way the parts merge
+            # (2 requests x 8 heads x 32,768 tokens: 9 parts 30.5 us, 8 parts 55, 4 parts 51)
+            return max(1, min(self.sm_count // pairs, 16 if pairs >= 8 else 32))
+        parts = max(1, min(self.decode_split_target // pairs, 32))
+        if self.decode_cluster_max < 2 or parts < 2:
             return parts
-        return min(8 if parts >= 8 else 4 if parts >= 4 else 2, self.decode_cluster_max)
+        parts = min(8 if parts >= 8 else 4 if parts >= 4 else 2, self.decode_cluster_max)
+        # all clusters have to run at one time (16 clusters of 8 do not: a second round of blocks
+        # doubled the kernel's time at batch 2); else the next smaller size
+        while hd is not None and parts > 2 and 0 < self._clusters_at_once(hd, parts) < pairs:
+            parts //= 2
+        return parts
 
     def decode_by_length(self, ctx_lens, nkv: int) -> bool:
         """Whether a decode step over contexts of these lengths should use the kernel that deals
@@ -531,7 +552,7 @@ class CudaOps:
                 total_pages, scale, window, per_pair, self._err_ptr, stream), "attention_decode_balanced")
             self.balanced_launches += 1
             return
-        splits = self.decode_splits(ctx.num_seqs, nkv, block_tables.shape[1] * page_size)
+        splits = self.decode_splits(ctx.num_seqs, nkv, block_tables.shape[1] * page_size, hd)
         floats = lib.ie_attention_decode_scratch_floats(ctx.num_seqs, nkv, splits)
         scratch = tickets = None
         if floats:

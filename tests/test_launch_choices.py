@@ -28,12 +28,27 @@ def test_contexts_are_cut_only_for_small_batches():
     assert CudaOps.decode_splits(ops, 8, 8) == 2
     assert CudaOps.decode_splits(ops, 16, 8) == 1
     assert CudaOps.decode_splits(ops, 64, 8) == 1
-    # ... except at the smallest batches when the tables hold long contexts: more parts, merged through memory
+    # ... except when the tables hold long contexts: as many parts as give nearly every SM a block
     assert CudaOps.decode_splits(ops, 1, 8, table_tokens=8192) == 16
     assert CudaOps.decode_splits(ops, 1, 8, table_tokens=2048) == 8
     assert CudaOps.decode_splits(ops, 1, 1, table_tokens=32768) == 32  # never more than 32 parts
+    assert CudaOps.decode_splits(ops, 2, 8, table_tokens=8192) == 9    # 144 blocks
+    assert CudaOps.decode_splits(ops, 3, 8, table_tokens=8192) == 6
+    assert CudaOps.decode_splits(ops, 5, 8, table_tokens=8192) == 3    # (the cluster sizes would leave it at 2)
+    assert CudaOps.decode_splits(ops, 8, 8, table_tokens=8192) == 2
+    assert CudaOps.decode_splits(ops, 32, 8, table_tokens=8192) == 1
     plain = _ops(cluster_max=0)
     assert CudaOps.decode_splits(plain, 1, 8) == 16 and CudaOps.decode_splits(plain, 3, 8) == 5
+    # all clusters of a launch have to run at one time: where the device fits fewer clusters of 8
+    # than there are (request, head) pairs, the parts are clusters of 4
+    ops._clusters_at_once = lambda hd, parts: {8: 14, 4: 33, 2: 70}[parts]
+    assert CudaOps.decode_splits(ops, 1, 8, hd=64) == 8      # 8 clusters of 8
+    assert CudaOps.decode_splits(ops, 2, 8, hd=64) == 4      # 16 clusters of 8 would take two rounds
+    assert CudaOps.decode_splits(ops, 2, 8) == 8             # (without a head size nothing is asked)
+    assert CudaOps.decode_splits(ops, 7, 2, hd=64) == 8      # 14 pairs
+    assert CudaOps.decode_splits(ops, 4, 8, hd=64) == 4
+    ops._clusters_at_once = lambda hd, parts: 0              # unknown: as before
+    assert CudaOps.decode_splits(ops, 2, 8, hd=64) == 8
 
 
 def test_work_is_dealt_by_length_only_where_that_pays():

@@ -61,6 +61,10 @@ def test_work_is_dealt_by_length_only_where_that_pays():
     assert not by_length([2304] * 32)
     assert not by_length([100, 2000, 700, 1500, 300, 900, 1200, 400])  # small differences do not pay for the set-up
     assert not by_length([64 + 31 * i for i in range(64)])  # 512 pairs: the hardware's dispatch evens them out
+    # equal lengths, a few blocks more than the device runs at once: a second round for those few
+    assert by_length([4096] * 40)
+    assert not by_length([4096] * 36)               # 288 blocks on 296 slots
+    assert not by_length([1024] * 48) and not by_length([1024] * 64)
     # the switch overrides the estimate
     assert CudaOps.decode_by_length(_ops(balanced="1"), [1024] * 8, 8)
     assert not CudaOps.decode_by_length(_ops(balanced="0"), [32768] + [256] * 31, 8)

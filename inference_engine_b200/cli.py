@@ -4,7 +4,7 @@ Option names and meanings are the reference's (engine/cli.py:142-197) where it h
 ``--model``, ``--prompt``, ``--temperature`` (0.7), ``--top-p`` (0.9), ``--max-tokens`` (256),
 ``--seed``, ``--device``, ``--gpu-mem`` and, from its ``serve`` command, ``--dtype``,
 ``--max-num-seqs``, ``--max-num-batched-tokens``, ``--block-size``, ``--num-blocks``,
-``--gpu-memory-utilization``, ``--no-chunked-prefill``, ``--no-cuda-graphs``.  There is no
+``--gpu-memory-utilization``, ``--no-chunked-prefill``, ``--no-cuda-graphs``, ``--no-mixed-graphs``.  There is no
 ``serve``.  ``generate`` takes token ids (``--prompt-ids``) when the model folder has no
 tokenizer, and can run a named-size random model (``--random-config FILE``).
 """
@@ -57,6 +57,7 @@ def _engine_config(args: argparse.Namespace):
         gpu_memory_utilization=args.gpu_memory_utilization,
         enable_chunked_prefill=not args.no_chunked_prefill,
         enable_cuda_graphs=False if args.no_cuda_graphs else None,
+        enable_mixed_graphs=False if args.no_cuda_graphs or args.no_mixed_graphs else None,
         max_model_len=args.max_model_len,
     )
 
@@ -156,6 +157,8 @@ def build_parser() -> argparse.ArgumentParser:
     gen.add_argument("--max-model-len", type=int, default=None)
     gen.add_argument("--no-chunked-prefill", action="store_true")
     gen.add_argument("--no-cuda-graphs", action="store_true")
+    gen.add_argument("--no-mixed-graphs", action="store_true",
+                     help="short steps with prompt portions run eagerly (decode steps stay captured)")
     gen.set_defaults(func=cmd_generate)
 
     rep = sub.add_parser("replay", help="feed token ids step by step (stdin) and write logits")

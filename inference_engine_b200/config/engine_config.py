@@ -17,6 +17,7 @@ class EngineConfig:
     enable_chunked_prefill: bool = True
     max_model_len: int | None = None
     enable_cuda_graphs: bool | None = None  # None: where they can be captured (a GPU, no state slots)
+    enable_mixed_graphs: bool | None = None  # short steps with prompt portions captured too; None: with the above
     debug_checks: bool = False
     profile_kernels: bool = False  # time every eagerly launched step per kind of kernel (into step_log)
 

@@ -1,4 +1,4 @@
-"""Decode steps as captured launch sequences (CUDA graphs).
+"""Decode steps, and short steps that hold prompt portions, as captured launch sequences (CUDA graphs).
 
 A decode-only step launches a hundred and more small kernels; at small batches their launch
 cost is a large part of the step.  For a few batch sizes (buckets) the whole forward pass is
@@ -12,11 +12,23 @@ engine allows (8,192 entries of 16 tokens at Llama 3.2's 131,072 positions) woul
 step copy megabytes of table to the device for contexts of a few hundred tokens, so the
 stride is part of what a capture is keyed by: the smallest of 64, 128, 256, ... entries
 (up to the engine's limit) that holds the step's longest context.
+
+Steps with prompt portions (`MixedGraphs`): an eager step costs the host about 13 us per kernel,
+1.9 ms for the sixteen layers of the 1B shape, whatever the step holds; up to a few hundred
+tokens the device needs half of that.  Such steps are captured too, per (tokens, sequences,
+wanted rows, block-table stride), each rounded up to a bucket: the tokens beyond the step's own
+are one more sequence (a prompt on the cache's scratch page), the sequences beyond that hold no
+tokens, and the attention is launched for the most query tiles any step within the bounds can
+have (`StepContext.bounds`).  The reference captures such steps piecewise, around an eager
+attention (engine/runtime/cuda_graphs.py:113-228); here the attention kernels take every length
+from device memory, so the whole step is one launch sequence.
 """
 
 from __future__ import annotations
 
 BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+TOKEN_BUCKETS = (16, 32, 64, 128, 256)  # captured steps with prompt portions: up to this many tokens
+SEQ_BUCKETS = (4, 16, 64)  # ... and their sequences, up to the largest decode bucket
 
 
 class DecodeGraphs:
@@ -132,3 +144,92 @@ class DecodeGraphs:
         graph.replay()
         self.replays += 1
         return logits[: len(entries)]
+
+
+class MixedGraphs:
+    """Short steps that hold prompt portions (beside decode tokens or not) as captured launch
+    sequences; see the module's text.  Shares the decode captures' bucket list and stride rule."""
+
+    def __init__(self, decode_graphs: DecodeGraphs, max_tokens: int = TOKEN_BUCKETS[-1]) -> None:
+        self.torch, self.runner, self.decode = decode_graphs.torch, decode_graphs.runner, decode_graphs
+        self.token_buckets = [t for t in TOKEN_BUCKETS if t <= max_tokens]
+        largest = decode_graphs.buckets[-1] + 1  # (all the engine's sequences and the one for the padding)
+        self.seq_buckets = [b for b in SEQ_BUCKETS if b < largest] + [largest]
+        self._graphs: dict[tuple, tuple] = {}
+        self._version = None
+        self.replays = 0
+
+    def _key(self, entries):
+        """(tokens, sequences, wanted rows, block-table stride) of the launch that serves these
+        entries, or None if none does."""
+        tokens = sum(len(e.tokens) for e in entries)
+        t_b = next((t for t in self.token_buckets if t >= tokens), None)
+        if t_b is None:
+            return None
+        # (one sequence more than the step's own: the one that takes the tokens beyond them; a
+        # sequence without tokens and a wanted row too many cost next to nothing, a capture costs
+        # memory and a first step of tens of milliseconds: few, coarse sizes)
+        s_b = next((b for b in self.seq_buckets if b >= len(entries) + 1), None)
+        if s_b is None:
+            return None
+        wanted = sum(len(e.want) for e in entries)
+        r_b = s_b if wanted <= s_b else self.decode.bucket_for(wanted)
+        if r_b is None:
+            return None
+        ps = self.runner.page_size
+        pages = max(max((e.start + len(e.tokens) - 1) // ps + 1 for e in entries), -(-t_b // ps))
+        width = self.decode.MIN_WIDTH
+        while width < pages:
+            width *= 2
+        if width > self.decode.table_width:
+            width = self.decode.table_width
+            if width < pages:
+                return None
+        return t_b, s_b, r_b, width
+
+    def can_run(self, entries) -> bool:
+        return bool(entries) and any(len(e.tokens) > 1 for e in entries) and self._key(entries) is not None
+
+    def run(self, entries):
+        """Returns the ``[wanted, vocab]`` logits of the step, in the order of the entries and
+        of their ``want`` lists, or None when nothing is wanted."""
+        torch, runner = self.torch, self.runner
+        if self._version != runner.ws.version:  # a buffer moved: captured addresses are stale
+            self._graphs.clear()
+            self._version = runner.ws.version
+        key = self._key(entries)
+        t_b, s_b, r_b, width = key
+        wanted = sum(len(e.want) for e in entries)
+
+        def build():
+            return runner.build_context(entries, pad_to_seqs=s_b, table_width=width, pad_to_tokens=t_b,
+                                        pad_to_rows=r_b)
+
+        ctx, rows = build()
+        if self._version != runner.ws.version:  # the staging buffer itself had to grow
+            self._graphs.clear()
+            self._version = runner.ws.version
+            ctx, rows = build()
+        if ctx.bounds != (t_b, s_b, width * runner.page_size):
+            raise RuntimeError(f"a step packed for {ctx.bounds} cannot replay the launch captured for {key}")
+        if key not in self._graphs:
+            # Run once outside a capture (buffers get allocated, libraries initialised) ...
+            stream = torch.cuda.Stream()
+            stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(stream):
+                runner.model.forward(ctx, rows)
+            torch.cuda.current_stream().wait_stream(stream)
+            torch.cuda.synchronize()
+            if self._version != runner.ws.version:
+                self._graphs.clear()
+                self._version = runner.ws.version
+                ctx, rows = build()
+            # ... then record the same launches.
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                logits = runner.model.forward(ctx, rows)
+            self._graphs[key] = (graph, logits)
+        graph, logits = self._graphs[key]
+        graph.replay()
+        self.replays += 1
+        return logits[:wanted] if wanted else None

@@ -28,7 +28,7 @@ from ..config.engine_config import EngineConfig
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
 from .batch import StepEntry
-from .graphs import DecodeGraphs
+from .graphs import DecodeGraphs, MixedGraphs
 from .model import Model
 from .output import OutputProcessor, RequestOutput
 from .runner import ModelRunner
@@ -41,7 +41,7 @@ class LLMEngine:
                  config: EngineConfig | None = None, *, ops=None, **settings) -> None:
         """``config``: the engine's settings; or give them by name (``num_blocks``,
         ``block_size``, ``max_num_seqs``, ``max_num_batched_tokens``, ``gpu_memory_utilization``,
-        ``enable_chunked_prefill``, ``enable_cuda_graphs``, ``max_model_len``,
+        ``enable_chunked_prefill``, ``enable_cuda_graphs``, ``enable_mixed_graphs``, ``max_model_len``,
         ``debug_checks``: the reference's argument names, engine/runtime/engine.py:47-66) and
         they are checked as an :class:`EngineConfig`."""
         import torch
@@ -84,6 +84,12 @@ class LLMEngine:
             use_graphs = (str(self.device).startswith("cuda") and torch.cuda.is_available()
                           and not model.state_groups)
         self.graphs = DecodeGraphs(self.runner, max_num_seqs, table_width) if use_graphs else None
+        use_mixed = config.enable_mixed_graphs
+        if use_mixed is None:
+            use_mixed = self.graphs is not None
+        if use_mixed and self.graphs is None:
+            raise ValueError("enable_mixed_graphs needs enable_cuda_graphs")
+        self.mixed_graphs = MixedGraphs(self.graphs) if use_mixed else None
         self.debug_checks = config.debug_checks
         self._seq_ids = itertools.count()
         self._requests: dict[str, Sequence] = {}
@@ -232,6 +238,9 @@ class LLMEngine:
             if self.graphs is not None and len(sampled) == len(entries) and self.graphs.can_run(entries):
                 logits = self.graphs.run(entries)
                 used_graph = True
+            elif (self.mixed_graphs is not None and not self.config.profile_kernels
+                  and self.mixed_graphs.can_run(entries)):
+                logits = self.mixed_graphs.run(entries)
             elif self.config.profile_kernels and hasattr(self.ops, "timed"):
                 # (the lead: about what the host needs to launch a layer's ten or so kernels, per layer)
                 with self.ops.timed(lead_ms=0.2 * len(self.model.spec.schedule)) as timer:

@@ -513,6 +513,14 @@ class CudaOps:
             if plans is None:
                 plans = ctx._attention_plans = {}
             plan = plans.get((groups, hd))
+            bounds = getattr(ctx, "bounds", None)
+            if plan is None and bounds is not None:
+                # a launch of fixed size (a captured step): both kernels, over as many query tiles
+                # as any step within the bounds can have; each kernel skips the other's requests
+                tokens, seqs, max_ctx = bounds
+                tiles = seqs + tokens // lib.ie_attention_prefill_rows()
+                plan = plans[(groups, hd)] = {"any": True, "all": False, "tiles": tiles, "tile_pairs": tiles,
+                                              "max_ctx": max_ctx}
             if plan is None:
                 small = [ql * groups <= 16 for ql in ctx.q_lens]
                 plan = {"small": small, "any": any(small), "all": all(small)}
@@ -526,7 +534,7 @@ class CudaOps:
             if plan["any"]:
                 if ragged is None:
                     ragged = any(getattr(ctx, "ragged", ()) or ())
-                self._decode_attention(lib, ragged, *args)
+                self._decode_attention(lib, ragged and bounds is None, *args)
             if not plan["all"]:
                 self._prefill_attention(lib, plan, *args)
             return
@@ -576,14 +584,16 @@ class CudaOps:
         """The requests with more than 16 rows, in query tiles of `ie_attention_prefill_rows` tokens."""
         total_pages, stream = k_cache.shape[0], self._stream()
         tiles = plan["tiles"]
-        if self.attn_tc5 and lib.ie_attention_prefill_tc5_ok(page_size, ctx.max_ctx_len):
+        fixed = "max_ctx" in plan  # a launch of fixed size: nothing is decided from the step's own lengths
+        max_ctx = plan["max_ctx"] if fixed else ctx.max_ctx_len
+        if self.attn_tc5 and lib.ie_attention_prefill_tc5_ok(page_size, max_ctx):
             # Head sizes 64 and 128, pages of 8 tokens or more: the tcgen05 / TMEM / TMA kernel.
             # While the blocks would fill the GPU less than about twice, a block takes two tiles
             # of a request, a late (long) and an early (short) one.  With so few tiles that even
             # then much of the GPU would idle (a short portion of a long prompt), the keys of
             # every tile are shared among several blocks instead.
-            ksplit = self.prefill_key_split(tiles * nh, hd, ctx.max_ctx_len) if self.prefill_key_splits else 1
-            paired = ksplit == 1 and tiles * nh <= self.prefill_paired_max * self.sm_count
+            ksplit = self.prefill_key_split(tiles * nh, hd, max_ctx) if self.prefill_key_splits and not fixed else 1
+            paired = not fixed and ksplit == 1 and tiles * nh <= self.prefill_paired_max * self.sm_count
             if paired:
                 tiles = plan["tile_pairs"]
             scratch = tickets = None

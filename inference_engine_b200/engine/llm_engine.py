@@ -200,6 +200,7 @@ class LLMEngine:
         started = time.perf_counter()
         preempted_before = self.scheduler.num_preemptions
         logits = kernel_times = None
+        captured_mixed = False  # the step held prompt portions and ran as a captured launch sequence
         ahead, self._ahead = self._ahead, None
         prepared, self._prepared = self._prepared, None
         if ahead is not None:
@@ -241,6 +242,7 @@ class LLMEngine:
             elif (self.mixed_graphs is not None and not self.config.profile_kernels
                   and self.mixed_graphs.can_run(entries)):
                 logits = self.mixed_graphs.run(entries)
+                captured_mixed = True
             elif self.config.profile_kernels and hasattr(self.ops, "timed"):
                 # (the lead: about what the host needs to launch a layer's ten or so kernels, per layer)
                 with self.ops.timed(lead_ms=0.2 * len(self.model.spec.schedule)) as timer:
@@ -263,7 +265,7 @@ class LLMEngine:
                     logits, params, [s.seed for s in sampled], [len(s.output_ids) for s in sampled],
                     [s.all_ids for s in sampled] if needs_history else None,
                     history_keys=[s.seq_id for s in sampled] if needs_history else None)
-            if used_graph and len(sampled) == len(seqs):
+            if (used_graph or captured_mixed) and len(sampled) == len(seqs):
                 # while the device is busy: start the next step on the tokens it is sampling,
                 # or at least pack that step's index data
                 self._ahead = self._launch_ahead(seqs, pending)

@@ -10,8 +10,8 @@ drives it (requests in, ``step()`` until done).  Three of them:
                                                    # other step holds a prompt beside up to 32 decoding requests
 
 ``--chunk`` sets the token budget of a step (the size of prompt portions); ``--no-mixed-graphs`` launches
-steps that hold prompt portions eagerly (decode steps stay captured).  Every workload runs twice;
-the second run (warm: kernels built, launch sequences captured) is the one to read.  One JSON line
+steps that hold prompt portions eagerly (decode steps stay captured).  Every workload runs three
+times; the last run (warm: kernels built, launch sequences captured) is the one to read.  One JSON line
 per run.
 """
 
@@ -45,7 +45,7 @@ def main() -> int:
     ap.add_argument("workload", choices=sorted(SHAPES) + ["chat"])
     ap.add_argument("--no-mixed-graphs", action="store_true")
     ap.add_argument("--chunk", type=int, default=None, help="token budget of a step (default: 4096; 3b: 512)")
-    ap.add_argument("--runs", type=int, default=2)
+    ap.add_argument("--runs", type=int, default=3)
     args = ap.parse_args()
 
     import torch

@@ -37,6 +37,8 @@ def test_contexts_are_cut_only_for_small_batches():
     assert CudaOps.decode_splits(ops, 5, 8, table_tokens=8192) == 3    # (the cluster sizes would leave it at 2)
     assert CudaOps.decode_splits(ops, 8, 8, table_tokens=8192) == 2
     assert CudaOps.decode_splits(ops, 32, 8, table_tokens=8192) == 1
+    assert CudaOps.decode_splits(ops, 12, 8, table_tokens=8192) == 3   # 288 half-size blocks on 296 slots, not 96 on 148
+    assert CudaOps.decode_splits(ops, 16, 8, table_tokens=8192) == 1   # (128 blocks either way)
     plain = _ops(cluster_max=0)
     assert CudaOps.decode_splits(plain, 1, 8) == 16 and CudaOps.decode_splits(plain, 3, 8) == 5
     # all clusters of a launch have to run at one time: where the device fits fewer clusters of 8

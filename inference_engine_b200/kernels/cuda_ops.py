@@ -165,6 +165,10 @@ class CudaOps:
         # 14336: 224 blocks) 33.6 against 25.4, and its K = 4096 products 13 to 45 % behind.
         # the gated feed-forward's first product with the activation in its kernel (IE_B200_GATED_GEMM=0: off)
         self.gated_gemm = os.environ.get("IE_B200_GATED_GEMM", "1") != "0"
+        # products of more than a few rows whose output is so narrow that the library's kernel would
+        # leave most SMs idle are cut along the inner dimension and run as one strided batched product
+        # (the parts are added by the consumer, like those of the few-row kernel)
+        self.blas_split_k = os.environ.get("IE_B200_BLAS_SPLIT_K", "1") != "0"
         self.batch_gemm = os.environ.get("IE_B200_BATCH_GEMM", "1") != "0"
         self.batch_gemm_rows = int(os.environ.get("IE_B200_BATCH_GEMM_ROWS", 64))
         self.batch_gemm_max_tiles = int(os.environ.get("IE_B200_BATCH_GEMM_MAX_TILES", 256))
@@ -315,6 +319,27 @@ class CudaOps:
                 break
         return per, -(-total // per)
 
+    def blas_split(self, m: int, n: int, k: int) -> int:
+        """Into how many parts along the inner dimension a bfloat16 product of ``m`` rows is cut before
+        it goes to the library (1: not at all).  The library's kernels take about 128 x 128 outputs per
+        block and do not cut the inner dimension themselves: the 64-row down projection of the 1B shape
+        runs as 16 blocks on 148 SMs, 13 us where its 33.5 MB would stream in 5.  As a batched product
+        over 8 slices of k it takes 8.5 us (measured, 1B shape, us: down at 17 / 64 / 256 / 512 rows
+        13.0 / 13.2 / 13.8 / 18.9 -> 8.1 / 8.5 / 10.6 / 15.4; output projection at 17 / 64 rows 5.6 / 5.8
+        -> 4.4 / 4.8; QKV 5.8 -> 5.0; products with many output features, gate-up and the head, lose).
+        A power of two, at most 8, with slices of at least 512; up to 256 rows (steps of more rows are
+        launched eagerly and bound by the host, where the batched call's extra preparation costs more
+        than its kernel saves: a 512-token step 2.16 -> 2.33 ms)."""
+        if not self.blas_split_k or m > 256:
+            return 1
+        blocks = -(-m // 128) * -(-n // 128)
+        parts = 1
+        while parts * 2 <= min(self.sm_count / blocks, 8) and k % (parts * 2 * 64) == 0 and k // (parts * 2) >= 512:
+            parts *= 2
+        if parts < 2 or (parts < 4 and k < 4096):
+            return 1
+        return parts
+
     @_kind(lambda kwargs: "linear:" + kwargs.get("tag", "linear"))
     def linear(self, x, w, out=None, *, ws=None, tag="linear", out_dtype=None, allow_split=False):
         """``x[M, K] @ w[N, K]^T``.  With ``out`` given the product is written there; otherwise a
@@ -337,6 +362,11 @@ class CudaOps:
         # The weight-streaming kernel pays where the library leaves SMs idle: few output
         # features (fewer 16-feature blocks than SMs) and a long inner dimension to split.
         few_rows = 0 < m <= self.FEW_ROWS and k % 8 == 0 and x.is_contiguous() and w.is_contiguous()
+        splittable = (allow_split and out is None and out_dtype == torch.float32 and m > 8
+                      and x.is_contiguous() and w.is_contiguous())
+        library_parts = self.blas_split(m, n, k) if splittable else 1
+        if few_rows and library_parts > 1 and k >= 4096:
+            few_rows = False  # (9 to 16 rows, long inner dimension: the batched library product is ahead, 8.0 against 9.5 us)
         if (few_rows and self.few_row_gemm == "tma"
                 and -(-n // 128) <= (self.tma_max_tiles if m <= 8 else self.tma_max_tiles_wide)):
             kbps, splits = self.tma_split(n, k) if allow_split and out is None else (-(-k // 64), 1)
@@ -350,6 +380,13 @@ class CudaOps:
                 self._check(self._gemm_tma_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), _dtype_code(out),
                                                 m, n, k, kbps, splits, self._err_ptr, self._stream()), "gemm_tma")
                 return out
+        if library_parts > 1:
+            parts, ks = library_parts, k // library_parts
+            out = ws.buffer(tag, parts * m, n, torch.float32).view(parts, m, n)
+            # slice p of the inner dimension: x[:, p ks : (p + 1) ks] and w[:, p ks : (p + 1) ks]^T, as views
+            torch.bmm(x.view(m, parts, ks).permute(1, 0, 2), w.view(n, parts, ks).permute(1, 2, 0),
+                      out_dtype=torch.float32, out=out)
+            return out
         # A batch of decode tokens (17 to 256 rows): still a stream of weights; the tcgen05
         # kernel with the operands' roles swapped, cut along k like the few-row kernel.
         if (self.batch_gemm and self.FEW_ROWS < m <= self.batch_gemm_rows and x.is_contiguous()

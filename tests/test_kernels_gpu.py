@@ -153,10 +153,12 @@ def test_linear_bf16(ops, out_dtype, m, n, k):
 
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
 @pytest.mark.parametrize("n,k", [(3072, 2048), (2048, 8192), (331, 80), (192, 64), (512, 96), (1000, 1032), (16384, 2048)])
-def test_tma_fed_gemm_for_few_rows(ops, m, n, k):
+def test_tma_fed_gemm_for_few_rows(ops, m, n, k, monkeypatch):
     """The TMA-fed weight-streaming product: any N (tiles of 128 with a ragged edge), any K
     that is a multiple of 8 (blocks of 64 with a ragged edge), with and without k splits."""
     from inference_engine_b200.engine.workspace import Workspace
+
+    monkeypatch.setattr(ops, "blas_split_k", False)  # (9 to 16 rows with a long inner dimension would go to the library)
 
     x = torch.randn(m, k, device="cuda").bfloat16()
     w = (torch.randn(n, k, device="cuda") * 0.05).bfloat16()
@@ -181,12 +183,13 @@ def test_tma_fed_gemm_for_few_rows(ops, m, n, k):
 
 @pytest.mark.parametrize("m", [17, 33, 64, 100, 128, 200, 256])
 @pytest.mark.parametrize("n,k", [(3072, 2048), (2048, 8192), (328, 128), (192, 64), (1000, 1024), (16384, 2048)])
-def test_tcgen05_gemm_for_a_batch_of_decode_tokens(ops, m, n, k):
+def test_tcgen05_gemm_for_a_batch_of_decode_tokens(ops, m, n, k, monkeypatch):
     """17 to 256 rows: features are the rows of tcgen05.mma, tokens its columns; any N (tiles of
     128 with a ragged edge), K a multiple of 64, with and without k splits, 32-bit and bfloat16
     results; twice, so that tensor memory must have been given back."""
     from inference_engine_b200.engine.workspace import Workspace
 
+    monkeypatch.setattr(ops, "blas_split_k", False)  # (the routing's first choice for these shapes: tested below)
     g = torch.Generator(device="cuda").manual_seed(m + n + k)
     x = torch.randn(m, k, device="cuda", generator=g).bfloat16()
     w = (torch.randn(n, k, device="cuda", generator=g) * 0.05).bfloat16()
@@ -213,6 +216,41 @@ def test_tcgen05_gemm_for_a_batch_of_decode_tokens(ops, m, n, k):
     finally:
         (ops.batch_gemm, ops.batch_gemm_rows, ops.batch_gemm_max_tiles, ops.batch_gemm_min_k,
          ops.batch_gemm_one_round) = saved
+
+
+@pytest.mark.parametrize("m", [9, 16, 17, 64, 130, 256, 512, 1024])
+@pytest.mark.parametrize("n,k", [(2048, 8192), (2048, 2048), (3072, 2048), (4096, 4096), (1000, 1536), (16384, 2048)])
+def test_narrow_products_are_cut_along_k_for_the_library(ops, m, n, k):
+    """Products of more than 8 rows with few output features go to the library as one batched
+    product over slices of the inner dimension (`CudaOps.blas_split`); the consumer adds the parts.
+    The parts sum to the product; shapes that are not cut come back whole."""
+    from inference_engine_b200.engine.workspace import Workspace
+
+    g = torch.Generator(device="cuda").manual_seed(m * 7 + n + k)
+    x = torch.randn(m, k, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(n, k, device="cuda", generator=g) * 0.05).bfloat16()
+    want = x.double() @ w.double().t()
+    ws = Workspace("cuda")
+    parts = ops.blas_split(m, n, k)
+    assert parts in (1, 2, 4, 8) and (parts == 1 or (k // parts >= 512 and k % parts == 0))
+    assert ops.blas_split(64, 2048, 8192) == 8 and ops.blas_split(256, 2048, 8192) == 4 and ops.blas_split(512, 2048, 8192) == 1
+    assert ops.blas_split(64, 16384, 2048) == 1 and ops.blas_split(2048, 2048, 8192) == 1
+    got = ops.linear(x, w, ws=ws, tag="t", out_dtype=torch.float32, allow_split=True)
+    if parts > 1 and not (m <= 16 and k < 4096):
+        assert got.shape == (parts, m, n)
+    total = got.sum(0) if got.dim() == 3 else got
+    torch.testing.assert_close(total.double(), want, atol=2e-4 * k ** 0.5, rtol=1e-5)
+    # the consumers add the parts in order: a norm over them gives the norm of the sum
+    if got.dim() == 3 and n % 8 == 0:
+        h = torch.randn(m, n, device="cuda", generator=g)
+        weight = torch.ones(n, device="cuda")
+        out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+        h_got = h.clone()
+        ops.rmsnorm(h_got, got, weight, 1e-5, out)
+        x_sum = h.double() + want
+        want_norm = x_sum * torch.rsqrt(x_sum.pow(2).mean(-1, keepdim=True) + 1e-5)
+        torch.testing.assert_close(out.double(), want_norm, atol=2e-2, rtol=2e-2)
+    ops.check_errors()
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

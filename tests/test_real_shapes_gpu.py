@@ -136,18 +136,25 @@ def test_real_shape_float32_is_the_same_however_it_is_cut(case):
             assert torch.equal(whole[rid], other[rid]), f"{cut}: request {rid} depends on the cutting"
 
 
-def test_real_shape_bfloat16_runs_the_kernels_it_is_meant_to(case):
-    """The portions above reach the tensor-core prefill attention, the split few-row products,
-    the tcgen05 product for batches of tokens and the decode attention (counted by the kernel
-    set's launch counters, so that a changed routing cannot quietly leave one untested)."""
+def test_real_shape_bfloat16_runs_the_kernels_it_is_meant_to(case, monkeypatch):
+    """The portions above reach the tensor-core prefill attention, the split few-row products
+    and the decode attention (counted by the kernel set's launch counters, so that a changed
+    routing cannot quietly leave one untested); with the library's products cut along k switched
+    off, portions of 17 to 64 tokens reach the tcgen05 product for batches of tokens, the
+    alternative to them, and the logits are right with it too."""
+    from inference_engine_b200.kernels import get_ops
+
     name, cfg, *_ = case
     cuts = _cuttings(case)
     _, launches = _run(case, "bfloat16", *cuts["portions"])
-    kernels = ["attention_prefill_tc5", "attention_decode", "gemm_tma"]
-    if cfg["hidden_size"] == 2048:
-        kernels.append("gemm_tc5")  # (at the 8B shape its blocks would not fit the SMs in one round)
-    for kernel in kernels:
+    for kernel in ["attention_prefill_tc5", "attention_decode", "gemm_tma"]:
         assert launches.get(kernel, 0) > 0, f"{kernel} never ran: {launches}"
+    assert launches.get("gemm_tc5", 0) == 0
+    if cfg["hidden_size"] == 2048:  # (at the 8B shape its blocks would not fit the SMs in one round)
+        monkeypatch.setattr(get_ops("cuda"), "blas_split_k", False)
+        _, launches = _run(case, "bfloat16", *cuts["portions"])
+        assert launches.get("gemm_tc5", 0) > 0, f"gemm_tc5 never ran: {launches}"
+        monkeypatch.undo()
     _, launches = _run(case, "bfloat16", *cuts["last 32 one by one"])
     assert launches.get("attention_decode", 0) >= 32 * cfg["num_hidden_layers"]
 

@@ -15,7 +15,8 @@ stride is part of what a capture is keyed by: the smallest of 64, 128, 256, ... 
 
 Steps with prompt portions (`MixedGraphs`): an eager step costs the host about 13 us per kernel,
 1.9 ms for the sixteen layers of the 1B shape, whatever the step holds; up to a few hundred
-tokens the device needs half of that.  Such steps are captured too, per (tokens, sequences,
+tokens the device needs half of that (a 384-token step 2.06 ms eager, 1.31 captured; 512 tokens 2.25
+and 1.62; 1,024 tokens 2.59 and 2.42: beyond that the device is the bound and steps stay eager).  Such steps are captured too, per (tokens, sequences,
 wanted rows, block-table stride), each rounded up to a bucket: the tokens beyond the step's own
 are one more sequence (a prompt on the cache's scratch page), the sequences beyond that hold no
 tokens, and the attention is launched for the most query tiles any step within the bounds can
@@ -27,7 +28,7 @@ from device memory, so the whole step is one launch sequence.
 from __future__ import annotations
 
 BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
-TOKEN_BUCKETS = (16, 32, 64, 128, 256)  # captured steps with prompt portions: up to this many tokens
+TOKEN_BUCKETS = (16, 32, 64, 128, 256, 384, 512, 768, 1024)  # captured steps with prompt portions: up to this many tokens
 SEQ_BUCKETS = (4, 16, 64)  # ... and their sequences, up to the largest decode bucket
 
 
@@ -153,6 +154,8 @@ class MixedGraphs:
     def __init__(self, decode_graphs: DecodeGraphs, max_tokens: int = TOKEN_BUCKETS[-1]) -> None:
         self.torch, self.runner, self.decode = decode_graphs.torch, decode_graphs.runner, decode_graphs
         self.token_buckets = [t for t in TOKEN_BUCKETS if t <= max_tokens]
+        if max_tokens < TOKEN_BUCKETS[-1] and max_tokens not in self.token_buckets:
+            self.token_buckets.append(max_tokens)  # (the engine's own limit of tokens per step)
         largest = decode_graphs.buckets[-1] + 1  # (all the engine's sequences and the one for the padding)
         self.seq_buckets = [b for b in SEQ_BUCKETS if b < largest] + [largest]
         self._graphs: dict[tuple, tuple] = {}

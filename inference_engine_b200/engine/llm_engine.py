@@ -89,7 +89,7 @@ class LLMEngine:
             use_mixed = self.graphs is not None
         if use_mixed and self.graphs is None:
             raise ValueError("enable_mixed_graphs needs enable_cuda_graphs")
-        self.mixed_graphs = MixedGraphs(self.graphs) if use_mixed else None
+        self.mixed_graphs = MixedGraphs(self.graphs, config.max_num_batched_tokens) if use_mixed else None
         self.debug_checks = config.debug_checks
         self._seq_ids = itertools.count()
         self._requests: dict[str, Sequence] = {}

@@ -238,7 +238,9 @@ class ModelRunner:
                 state_slots.append(self.cache.max_requests)
                 pos = np.arange(pad_tokens)
                 buf[v_tok[0] + cursor: v_tok[0] + cursor + pad_tokens] = 0
-                buf[v_pos[0] + cursor: v_pos[0] + cursor + pad_tokens] = pos
+                # (position 0 for the rotary table, whatever the engine's longest sequence: the attention
+                # kernels place the rows by the lengths, not by this)
+                buf[v_pos[0] + cursor: v_pos[0] + cursor + pad_tokens] = 0
                 buf[v_seq[0] + cursor: v_seq[0] + cursor + pad_tokens] = i
                 for g, st in enumerate(self.storage.paged):
                     buf[v_slots[g][0] + cursor: v_slots[g][0] + cursor + pad_tokens] = st.scratch_page * ps + pos % ps

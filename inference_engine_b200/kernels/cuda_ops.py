@@ -327,10 +327,9 @@ class CudaOps:
         over 8 slices of k it takes 8.5 us (measured, 1B shape, us: down at 17 / 64 / 256 / 512 rows
         13.0 / 13.2 / 13.8 / 18.9 -> 8.1 / 8.5 / 10.6 / 15.4; output projection at 17 / 64 rows 5.6 / 5.8
         -> 4.4 / 4.8; QKV 5.8 -> 5.0; products with many output features, gate-up and the head, lose).
-        A power of two, at most 8, with slices of at least 512; up to 256 rows (steps of more rows are
-        launched eagerly and bound by the host, where the batched call's extra preparation costs more
-        than its kernel saves: a 512-token step 2.16 -> 2.33 ms)."""
-        if not self.blas_split_k or m > 256:
+        A power of two, at most 8, with slices of at least 512; up to 512 rows (beyond that no shape
+        gains)."""
+        if not self.blas_split_k or m > 512:
             return 1
         blocks = -(-m // 128) * -(-n // 128)
         parts = 1

@@ -47,7 +47,7 @@ def _session(folder, dtype, max_tokens, page_size, captured: bool):
         def step(entries):
             if session.mixed.can_run(entries):
                 return session.mixed.run(entries)
-            assert all(len(e.tokens) == 1 for e in entries) or sum(len(e.tokens) for e in entries) > 256
+            assert all(len(e.tokens) == 1 for e in entries) or sum(len(e.tokens) for e in entries) > 1024
             return eager(entries)
 
         session.runner.step = step
@@ -93,7 +93,7 @@ def test_portions_beside_decoded_tokens_with_pages_used_again(cases, name, dtype
 
 def test_a_step_may_want_nothing_and_a_long_one_runs_eagerly(cases):
     cfg, folder, requests, want = cases["A"]
-    session = _session(folder, "bfloat16", 640, PAGE_SIZE["A"], captured=True)
+    session = _session(folder, "bfloat16", 1408, PAGE_SIZE["A"], captured=True)
     a, b = requests["r0"], requests["r1"]
     assert session.run_step({"step": 0, "entries": [{"id": "a", "tokens": a[:40], "want": []}], "end": []}) is None
     assert session.mixed.replays == 1
@@ -103,8 +103,8 @@ def test_a_step_may_want_nothing_and_a_long_one_runs_eagerly(cases):
     H.assert_close(out[1:], want["r1"][7:9], "bfloat16", "b beside a")
     assert session.mixed.replays == 2
     # more tokens than the largest capture holds: launched eagerly
-    long = H.random_tokens(cfg, 300, 5)
-    out = session.run_step({"step": 2, "entries": [{"id": "c", "tokens": long, "want": [299]}], "end": ["c"]})
+    long = H.random_tokens(cfg, 1100, 5)
+    out = session.run_step({"step": 2, "entries": [{"id": "c", "tokens": long, "want": [1099]}], "end": ["c"]})
     assert out is not None and session.mixed.replays == 2
     session.ops.check_errors()
 

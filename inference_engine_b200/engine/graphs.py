@@ -28,7 +28,7 @@ from device memory, so the whole step is one launch sequence.
 from __future__ import annotations
 
 BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
-TOKEN_BUCKETS = (16, 32, 64, 128, 256, 384, 512, 768, 1024)  # captured steps with prompt portions: up to this many tokens
+TOKEN_BUCKETS = (8, 16, 32, 64, 128, 256, 384, 512, 768, 1024)  # captured steps with prompt portions: up to this many tokens
 SEQ_BUCKETS = (4, 16, 64)  # ... and their sequences, up to the largest decode bucket
 
 

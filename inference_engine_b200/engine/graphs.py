@@ -18,8 +18,8 @@ Steps with prompt portions (`MixedGraphs`): an eager step costs the host about 1
 tokens the device needs half of that (a 384-token step 2.06 ms eager, 1.31 captured; 512 tokens 2.25
 and 1.62; 1,024 tokens 2.59 and 2.42: beyond that the device is the bound and steps stay eager).  Such steps are captured too, per (tokens, sequences,
 wanted rows, block-table stride), each rounded up to a bucket: the tokens beyond the step's own
-are one more sequence (a prompt on the cache's scratch page), the sequences beyond that hold no
-tokens, and the attention is launched for the most query tiles any step within the bounds can
+belong to no sequence (their keys and values go to the cache's scratch page), the sequences
+beyond the step's own hold no tokens, and the attention is launched for the most query tiles any step within the bounds can
 have (`StepContext.bounds`).  The reference captures such steps piecewise, around an eager
 attention (engine/runtime/cuda_graphs.py:113-228); here the attention kernels take every length
 from device memory, so the whole step is one launch sequence.

@@ -99,8 +99,8 @@ class ModelRunner:
         device vector of wanted rows.  ``pad_to_seqs``/``table_width`` give a launch of fixed
         size: missing sequences become single tokens that read and write the scratch page.
         With ``pad_to_tokens`` (and ``pad_to_rows`` wanted rows) the number of tokens is fixed
-        too: the tokens beyond the step's own are one more sequence, a prompt on the scratch
-        page, and the sequences beyond that one hold no tokens."""
+        too: the tokens beyond the step's own belong to no sequence (their keys and values go to
+        the scratch page), and the sequences beyond the step's own hold no tokens."""
         import numpy as np
 
         torch = self._torch
@@ -228,29 +228,24 @@ class ModelRunner:
                 buf[row] = st.scratch_page
                 buf[row + 1: row + width] = -1
             cursor += 1
+        last_token_of_a_sequence = n
         if pad_to_tokens is not None:
-            if pad_tokens:  # the tokens beyond the step's own: a prompt of that length on the scratch page
-                i = real_b
-                q_starts.append(cursor)
-                start_positions.append(0)
-                q_lens.append(pad_tokens)
-                ctx_lens.append(pad_tokens)
-                state_slots.append(self.cache.max_requests)
+            last_token_of_a_sequence = cursor
+            if pad_tokens:
+                # The tokens beyond the step's own: token 0 at position 0, their keys and values go to
+                # the scratch page.  They name the next sequence as theirs (`seq_of_token`: the kernel
+                # that walks tokens finds the scratch page's one key there), but that sequence, like
+                # those after it, holds no tokens by `cu_q`: the kernels that walk sequences do nothing
+                # for them, and their rows of the attention's output are never read.
                 pos = np.arange(pad_tokens)
                 buf[v_tok[0] + cursor: v_tok[0] + cursor + pad_tokens] = 0
-                # (position 0 for the rotary table, whatever the engine's longest sequence: the attention
-                # kernels place the rows by the lengths, not by this)
                 buf[v_pos[0] + cursor: v_pos[0] + cursor + pad_tokens] = 0
-                buf[v_seq[0] + cursor: v_seq[0] + cursor + pad_tokens] = i
+                buf[v_seq[0] + cursor: v_seq[0] + cursor + pad_tokens] = real_b
                 for g, st in enumerate(self.storage.paged):
                     buf[v_slots[g][0] + cursor: v_slots[g][0] + cursor + pad_tokens] = st.scratch_page * ps + pos % ps
-                    row = v_tables[g][0] + i * width
-                    held = -(-pad_tokens // ps)
-                    buf[row: row + held] = st.scratch_page
-                    buf[row + held: row + width] = -1
                 cursor += pad_tokens
             for i in range(len(q_starts), b):  # sequences without tokens
-                q_starts.append(cursor)
+                q_starts.append(last_token_of_a_sequence)
                 start_positions.append(0)
                 q_lens.append(0)
                 ctx_lens.append(0)
@@ -261,7 +256,7 @@ class ModelRunner:
                     buf[row + 1: row + width] = -1
             logit_rows += [0] * (rows - len(logit_rows))
         buf[v_cu[0]: v_cu[0] + b] = q_starts
-        buf[v_cu[0] + b] = n
+        buf[v_cu[0] + b] = last_token_of_a_sequence
         buf[v_ctx[0]: v_ctx[0] + b] = ctx_lens
         buf[v_state[0]: v_state[0] + b] = state_slots
         buf[v_rows[0]: v_rows[0] + rows] = logit_rows

@@ -357,6 +357,50 @@ class LLMEngine:
         return (not self.scheduler.waiting and self.scheduler.running == seqs
                 and all(s.num_computed == s.length - 1 for s in seqs))
 
+    def warm_up(self, max_tokens: int | None = None) -> int:
+        """Capture the launch sequences ahead of the first request, as the reference does when the
+        engine is built (engine/runtime/cuda_graphs.py:47, 159): one decode step per batch bucket
+        and one step with a prompt portion per token bucket up to ``max_tokens``, for short
+        contexts (captures for longer block tables are made when a step first needs one).  Uses
+        requests of its own on an idle engine and gives their pages back.  Returns how many
+        launch sequences are captured afterwards; 0 without captured steps."""
+        if self.graphs is None:
+            return 0
+        if self.has_unfinished():
+            raise RuntimeError("warm_up() wants an idle engine")
+        from .batch import StepEntry
+
+        cache, ps = self.cache, self.cache.page_size
+
+        def run(lengths, step) -> None:
+            ids = [("warm-up", i) for i in range(len(lengths))]
+            held = []
+            try:
+                for rid, n in zip(ids, lengths):
+                    cache.add_request(rid)
+                    held.append(rid)
+                    cache.grow(rid, 0, n)
+                step([StepEntry(rid, [0] * n, 0, [n - 1]) for rid, n in zip(ids, lengths)])
+            finally:
+                for rid in held:
+                    cache.free(rid)
+
+        # (twice, the largest first: a capture holds the addresses of the step's buffers, and a buffer
+        # that has to grow for a later step makes the earlier captures stale; the second round finds
+        # every buffer as large as these steps need it and captures again what the first lost)
+        free_pages = min(cache.num_free_pages)
+        for _ in range(2):
+            if self.mixed_graphs is not None:
+                limit = min(max_tokens or self.config.max_num_batched_tokens, free_pages * ps)
+                for tokens in sorted(self.mixed_graphs.token_buckets, reverse=True):
+                    if 2 <= tokens <= limit:
+                        run([tokens], self.mixed_graphs.run)
+            for bucket in sorted(self.graphs.buckets, reverse=True):
+                if bucket <= min(free_pages, cache.max_requests):
+                    run([1] * bucket, self.graphs.run)
+        self.ops.check_errors()
+        return len(self.graphs._graphs) + (len(self.mixed_graphs._graphs) if self.mixed_graphs else 0)
+
     def generate(self, prompts: dict[str, list[int]], params: SamplingParams) -> dict[str, list[int]]:
         """Run ``prompts`` (request id -> token ids) to their end with the same ``params``;
         returns the produced ids per request."""

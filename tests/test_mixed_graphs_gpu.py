@@ -131,3 +131,30 @@ def test_the_engine_captures_short_steps_by_default():
     eager = LLMEngine(model, None, (), num_blocks=60, block_size=8, max_num_seqs=4, max_num_batched_tokens=32,
                       enable_mixed_graphs=False)
     assert eager.mixed_graphs is None and eager.graphs is not None
+
+
+def test_warm_up_captures_ahead_of_the_first_request():
+    """`LLMEngine.warm_up()`: the decode buckets and the token buckets are captured on an idle engine,
+    every page comes back, and a generation afterwards replays those captures instead of making its own."""
+    from inference_engine_b200 import SamplingParams
+    from inference_engine_b200.engine.llm_engine import LLMEngine
+    from inference_engine_b200.engine.loading import model_from_tensors
+    from tests.test_engine_gpu import _check_greedy
+
+    cfg, weights = TINY_B, H.make_weights(TINY_B, seed=32)
+    model, _ = model_from_tensors(cfg, weights, "bfloat16", "cuda", cfg["max_position_embeddings"])
+    engine = LLMEngine(model, None, (), num_blocks=60, block_size=8, max_num_seqs=4, max_num_batched_tokens=48,
+                       debug_checks=True)
+    captured = engine.warm_up()
+    assert captured == len(engine.graphs.buckets) + len([t for t in engine.mixed_graphs.token_buckets if t >= 2])
+    assert engine.cache.num_free_pages == [60] and not engine.has_unfinished()
+    decode_keys, mixed_keys = set(engine.graphs._graphs), set(engine.mixed_graphs._graphs)
+    prompts = {f"p{i}": H.random_tokens(cfg, n, 400 + i) for i, n in enumerate([30, 7, 2])}
+    got = engine.generate(prompts, SamplingParams(temperature=0, max_tokens=8))
+    for rid, prompt in prompts.items():
+        _check_greedy(cfg, weights, prompt, got[rid], "bfloat16")
+    assert set(engine.graphs._graphs) == decode_keys  # (decode steps of 1 to 3 requests: buckets 1, 2, 4)
+    assert len(set(engine.mixed_graphs._graphs) - mixed_keys) <= 1  # (at most the step that needed a larger sequence bucket)
+    with pytest.raises(RuntimeError):
+        engine.add_request("x", [1, 2, 3], SamplingParams(temperature=0, max_tokens=4))
+        engine.warm_up()

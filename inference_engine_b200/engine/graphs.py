@@ -180,7 +180,7 @@ class MixedGraphs:
         if r_b is None:
             return None
         ps = self.runner.page_size
-        pages = max(max((e.start + len(e.tokens) - 1) // ps + 1 for e in entries), -(-t_b // ps))
+        pages = max((e.start + len(e.tokens) - 1) // ps + 1 for e in entries)
         width = self.decode.MIN_WIDTH
         while width < pages:
             width *= 2

@@ -504,7 +504,7 @@ class CudaOps:
         as the longest context over its splits (or the whole work over the blocks the device
         runs at once, if that is more); dealt by length, the work over those blocks, plus the
         set-up that kernel pays (measured: about 600 tokens' worth, and 15 % for second pairs in
-        a block)."""
+        a block; 50 % with more pairs than SMs)."""
         if self.decode_balanced in ("0", "1"):
             return self.decode_balanced == "1"
         pairs = len(ctx_lens) * nkv
@@ -518,7 +518,10 @@ class CudaOps:
         rounds = pairs * splits / slots
         last_round = (-(-pairs * splits // slots) - rounds) * work / (pairs * splits)
         by_request = max(longest / splits, work / slots + last_round)
-        return by_request > 1.15 * work / slots + 600
+        # (with more pairs than SMs that kernel runs half-size blocks, two to an SM, and stays a half
+        # behind its even share: 40 requests of 128 to 2,048 tokens took 34 us dealt by length, 26 by request)
+        behind = 1.15 if pairs <= self.sm_count else 1.5
+        return by_request > behind * work / slots + 600
 
     def prefill_key_split(self, blocks: int, hd: int, max_ctx_len: int) -> int:
         """Among how many blocks the tcgen05 prefill kernel shares the keys of a query tile: the

@@ -63,6 +63,8 @@ def test_work_is_dealt_by_length_only_where_that_pays():
     assert not by_length([2304] * 32)
     assert not by_length([100, 2000, 700, 1500, 300, 900, 1200, 400])  # small differences do not pay for the set-up
     assert not by_length([64 + 31 * i for i in range(64)])  # 512 pairs: the hardware's dispatch evens them out
+    # more pairs than block slots and lengths that differ by a factor: the hardware's dispatch fills the gaps
+    assert not by_length([128 + (1920 * ((7 * i) % 40)) // 39 for i in range(40)])
     # equal lengths, a few blocks more than the device runs at once: a second round for those few
     assert by_length([4096] * 40)
     assert not by_length([4096] * 36)               # 288 blocks on 296 slots

@@ -3,8 +3,12 @@ the fraction of a memory bandwidth at which it reads the keys and values it must
 
     python -m inference_engine_b200.profile_attention --cases 8x1024,64x1024,64x4096,16x16384,1x32768
     IE_B200_DECODE_NARROW=0 python -m inference_engine_b200.profile_attention   # the 16-row layout for all
+    python -m inference_engine_b200.profile_attention --cases 32x128-4352       # 32 contexts of 128 to 4,352 tokens
+    IE_B200_DECODE_BALANCED=0 python -m inference_engine_b200.profile_attention --cases 32x128-4352   # dealt by request
 
-Every request brings one token.  A launch stands for one layer of a step: it runs on a cache of its own
+Every request brings one token.  ``BxL`` is B requests of L cached tokens, ``BxL1-L2`` B requests whose lengths
+are drawn evenly from L1 to L2 (seeded); which of the two decode kernels runs is the engine's own choice
+(``CudaOps.decode_by_length``) unless ``IE_B200_DECODE_BALANCED`` says otherwise.  A launch stands for one layer of a step: it runs on a cache of its own
 (several caches, together larger than L2, taken in turn), block tables point at shuffled pages.  The launches
 of four rounds over the caches are captured in one CUDA graph and timed with CUDA events; the best of
 three replays counts.  ``--peak-gbs`` is the bandwidth the fraction is of (default: the copy rate in
@@ -37,6 +41,7 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--window", type=int, default=0)
     ap.add_argument("--peak-gbs", type=float, default=None)
+    ap.add_argument("--caches", type=int, default=0, help="caches taken in turn (default: 2 to 8, about 1 GB in all)")
     args = ap.parse_args()
 
     import torch
@@ -48,28 +53,42 @@ def main() -> int:
     nh, nkv, hd, ps = args.heads, args.kv_heads, args.head_dim, args.page_size
     peak = args.peak_gbs or _peak_gbs()
 
-    def case(batch: int, ctx_len: int, ws):
-        pages_per = -(-ctx_len // ps)
-        total = batch * pages_per + 2
+    def case(lengths: list[int], ws):
+        batch = len(lengths)
+        pages = [-(-n // ps) for n in lengths]
+        total, width = sum(pages) + 2, max(pages)
         perm = torch.randperm(total, device="cuda").to(torch.int32)
-        tables = perm[: batch * pages_per].view(batch, pages_per).contiguous()
+        tables = torch.full((batch, width), -1, dtype=torch.int32, device="cuda")
+        at = 0
+        for i, n in enumerate(pages):
+            tables[i, :n] = perm[at: at + n]
+            at += n
         k = torch.randn(total, nkv, ps, hd, device="cuda").bfloat16()
         v = torch.randn_like(k)
         q = torch.randn(batch, nh * hd, device="cuda").bfloat16()
+        ragged = bool(ops.decode_by_length(lengths, nkv)) if batch > 1 else False
         ctx = types.SimpleNamespace(
-            num_tokens=batch, num_seqs=batch, q_lens=[1] * batch, max_q_len=1, max_ctx_len=ctx_len, ws=ws,
-            positions=torch.full((batch,), ctx_len - 1, dtype=torch.int32, device="cuda"),
+            num_tokens=batch, num_seqs=batch, q_lens=[1] * batch, max_q_len=1, max_ctx_len=max(lengths), ws=ws,
+            positions=torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device="cuda"),
             seq_of_token=torch.arange(batch, dtype=torch.int32, device="cuda"),
             cu_q=torch.arange(batch + 1, dtype=torch.int32, device="cuda"),
-            ctx_lens=torch.full((batch,), ctx_len, dtype=torch.int32, device="cuda"))
+            ctx_lens=torch.tensor(lengths, dtype=torch.int32, device="cuda"), ragged=(ragged,))
         return q, k, v, tables, ctx
 
     for item in args.cases.split(","):
-        batch, ctx_len = (int(x) for x in item.lower().split("x"))
+        count, length = item.lower().split("x")
+        batch = int(count)
+        if "-" in length:
+            low, high = (int(x) for x in length.split("-"))
+            lengths = torch.randint(low, high + 1, (batch,), generator=torch.Generator().manual_seed(0)).tolist()
+        else:
+            lengths = [int(length)] * batch
+        ctx_len = max(lengths)
         ws = Workspace("cuda")
-        visible = min(ctx_len, args.window) if args.window > 0 else ctx_len  # keys a request's token sees
-        kv_bytes = batch * visible * nkv * hd * 2 * 2
-        cases = [case(batch, ctx_len, ws) for _ in range(max(2, min(8, int(1.0e9 // (batch * ctx_len * nkv * hd * 4)))))]
+        visible = [min(n, args.window) if args.window > 0 else n for n in lengths]  # keys a request's token sees
+        kv_bytes = sum(visible) * nkv * hd * 2 * 2
+        copies = args.caches or max(2, min(8, int(1.0e9 // (sum(lengths) * nkv * hd * 4))))
+        cases = [case(lengths, ws) for _ in range(copies)]
         out = torch.empty_like(cases[0][0])
 
         def run(i: int) -> None:
@@ -95,7 +114,7 @@ def main() -> int:
             torch.cuda.synchronize()
             best = min(best, start.elapsed_time(end) / iters * 1e3)
         gbs = kv_bytes / best / 1e3
-        row = {"requests": batch, "context": ctx_len, "us": round(best, 2), "gbs": round(gbs, 1),
+        row = {"requests": batch, "context": length, "by_length": cases[0][4].ragged[0], "us": round(best, 2), "gbs": round(gbs, 1),
                "caches": len(cases), "kv_mb_per_launch": round(kv_bytes / 1e6, 1)}
         if peak:
             row["frac"] = round(gbs / peak, 3)

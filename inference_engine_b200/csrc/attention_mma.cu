@@ -743,12 +743,16 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
                         int table_width, const int* __restrict__ cu_q, const int* __restrict__ ctx_lens,
                         bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                         int* __restrict__ tickets, int nh, int nkv, int page_shift, int total_pages,
-                        float scale_log2, int window, int num_splits, int narrow_rows, int* err) {
+                        float scale_log2, int window, int num_splits, int narrow_rows, const int* __restrict__ order,
+                        int* err) {
     constexpr int KT = KT_DECODE, TILE_ELEMS = KT * HD, WARPS = NWARPS;
     __shared__ int is_last;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
-    int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    // Blocks start in the order of their number: the heads of a request side by side, the requests
+    // in the order the caller gives (`order`: the longest first, so that with more blocks than the
+    // device runs at once the short ones fill the end) or as they are numbered.
+    int kvh = blockIdx.x, seq = order ? order[blockIdx.y] : blockIdx.y, split = blockIdx.z;
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int G = nh / nkv;
     const int* table = tables + (size_t)seq * table_width;
@@ -1442,8 +1446,8 @@ template <int NWARPS>
 int launch_decode_as(const void* q, const void* k_cache, const void* v_cache, const int* tables, int table_width,
                      const int* cu_q, const int* ctx_lens, void* out, float* part_o, float* part_ml, int* tickets,
                      int num_seqs, int nh, int nkv, int page_shift, int total_pages, float scale, int window,
-                     int num_splits, int* err, cudaStream_t s) {
-    dim3 grid(num_seqs, nkv, num_splits);
+                     int num_splits, const int* order, int* err, cudaStream_t s) {
+    dim3 grid(nkv, num_seqs, num_splits);
     size_t pair_smem = decode_smem(NWARPS) + (size_t)num_splits * PAIR_SLOT_BYTES;
     // the splits are a cluster that merges through shared memory, if all clusters run at one time
     // (where the runtime cannot say how many do, it is taken that they do)
@@ -1464,7 +1468,7 @@ int launch_decode_as(const void* q, const void* k_cache, const void* v_cache, co
                                  dim3(1, 1, (unsigned)num_splits),
                                  (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, tables, table_width, cu_q,
                                  ctx_lens, (bf16*)out, part_o, part_ml, tickets, nh, nkv, page_shift, total_pages,
-                                 scale * 1.4426950408889634f, window, num_splits, decode_narrow_rows(), err);
+                                 scale * 1.4426950408889634f, window, num_splits, decode_narrow_rows(), order, err);
     }
     static IePerDevice configured;
     cudaError_t e = ie_allow_smem(configured, attention_decode_kernel<NWARPS>, decode_smem(NWARPS));
@@ -1472,7 +1476,7 @@ int launch_decode_as(const void* q, const void* k_cache, const void* v_cache, co
     return ie_launch(attention_decode_kernel<NWARPS>, grid, dim3(NWARPS * 32), decode_smem(NWARPS), s,
                      (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, tables, table_width, cu_q,
                      ctx_lens, (bf16*)out, part_o, part_ml, tickets, nh, nkv, page_shift, total_pages,
-                     scale * 1.4426950408889634f, window, num_splits, decode_narrow_rows(), err);
+                     scale * 1.4426950408889634f, window, num_splits, decode_narrow_rows(), order, err);
 }
 
 // With at most one block per SM a block takes the SM's whole shared memory for tiles in flight;
@@ -1481,16 +1485,16 @@ int launch_decode_as(const void* q, const void* k_cache, const void* v_cache, co
 int launch_decode(const void* q, const void* k_cache, const void* v_cache, const int* tables, int table_width,
                   const int* cu_q, const int* ctx_lens, void* out, float* part_o, float* part_ml, int* tickets,
                   int num_seqs, int nh, int nkv, int page_shift, int total_pages, float scale, int window,
-                  int num_splits, int* err, cudaStream_t s) {
+                  int num_splits, const int* order, int* err, cudaStream_t s) {
     int sms = ie_sm_count();
     long long blocks = (long long)num_seqs * nkv * num_splits;
     if (blocks > sms)
         return launch_decode_as<DWARPS_SHARED>(q, k_cache, v_cache, tables, table_width, cu_q, ctx_lens, out, part_o,
                                                part_ml, tickets, num_seqs, nh, nkv, page_shift, total_pages, scale,
-                                               window, num_splits, err, s);
+                                               window, num_splits, order, err, s);
     return launch_decode_as<DWARPS>(q, k_cache, v_cache, tables, table_width, cu_q, ctx_lens, out, part_o, part_ml,
                                     tickets, num_seqs, nh, nkv, page_shift, total_pages, scale, window, num_splits,
-                                    err, s);
+                                    order, err, s);
 }
 }  // namespace
 
@@ -1512,7 +1516,29 @@ IE_API int ie_attention_decode(const void* q, const void* k_cache, const void* v
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)num_seqs * nkv * num_splits * MAX_ROWS * HD : nullptr;
     return launch_decode(q, k_cache, v_cache, tables, table_width, cu_q, ctx_lens, out, part_o, part_ml, tickets,
-                         num_seqs, nh, nkv, page_shift, total_pages, scale, window, num_splits, err,
+                         num_seqs, nh, nkv, page_shift, total_pages, scale, window, num_splits, nullptr, err,
+                         (cudaStream_t)stream);
+}
+
+// The same with the order in which the requests' blocks start: `order[i]` is the request that is
+// i-th (every request once; the longest first pays when the step has more blocks than the device
+// runs at once and contexts of different lengths).
+IE_API int ie_attention_decode_ordered(const void* q, const void* k_cache, const void* v_cache,
+                                       const int* tables, int table_width, const int* cu_q,
+                                       const int* ctx_lens, void* out, float* scratch, int* tickets,
+                                       int num_seqs, int nh, int nkv, int page_size, int total_pages,
+                                       float scale, int window, int num_splits, const int* order, int* err,
+                                       void* stream) {
+    if (num_seqs <= 0) return 0;
+    if (nkv <= 0 || nh % nkv != 0 || (page_size & (page_size - 1)) != 0 || num_splits < 1 ||
+        (num_splits > 1 && (scratch == nullptr || tickets == nullptr)))
+        return (int)cudaErrorInvalidValue;
+    int page_shift = 0;
+    while ((1 << page_shift) < page_size) ++page_shift;
+    float* part_o = scratch;
+    float* part_ml = scratch ? scratch + (size_t)num_seqs * nkv * num_splits * MAX_ROWS * HD : nullptr;
+    return launch_decode(q, k_cache, v_cache, tables, table_width, cu_q, ctx_lens, out, part_o, part_ml, tickets,
+                         num_seqs, nh, nkv, page_shift, total_pages, scale, window, num_splits, order, err,
                          (cudaStream_t)stream);
 }
 

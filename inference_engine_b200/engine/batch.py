@@ -64,6 +64,7 @@ class StepContext:
     max_ctx_len: int
     padded: bool = False  # a fixed-size launch: sizes above are upper bounds
     ragged: tuple = ()  # per paged group: its ``ragged`` hint (part of what a captured launch is keyed by)
+    decode_order: Any = None  # int32 [B] on the device: the sequences by context length, the longest first
     # A launch of fixed size that must serve every step that fits (a captured step with prompt
     # portions): (tokens, sequences, context length) the launch is sized for.  Launch decisions are
     # then taken from these bounds alone, never from the step's own lengths.

@@ -32,6 +32,23 @@ TOKEN_BUCKETS = (8, 16, 32, 64, 128, 256, 384, 512, 768, 1024)  # captured steps
 SEQ_BUCKETS = (4, 16, 64)  # ... and their sequences, up to the largest decode bucket
 
 
+def _capture(torch, graph, forward):
+    """Record ``forward()``'s launches into ``graph``.  The garbage collector stays off meanwhile
+    (and runs once before): an object it frees may own captured launch sequences or device
+    memory, and giving those back while a stream is capturing makes the capture invalid."""
+    import gc
+
+    gc.collect()
+    was_enabled = gc.isenabled()
+    gc.disable()
+    try:
+        with torch.cuda.graph(graph):
+            return forward()
+    finally:
+        if was_enabled:
+            gc.enable()
+
+
 class DecodeGraphs:
     def __init__(self, runner, max_num_seqs: int, table_width: int) -> None:
         import torch
@@ -138,8 +155,7 @@ class DecodeGraphs:
             # ... then record the same launches.
             graph = torch.cuda.CUDAGraph()
             before = getattr(runner.ops, "launches", 0)
-            with torch.cuda.graph(graph):
-                logits = runner.model.forward(ctx, rows)
+            logits = _capture(torch, graph, lambda: runner.model.forward(ctx, rows))
             self._graphs[key] = (graph, logits, getattr(runner.ops, "launches", 0) - before)
         graph, logits, _ = self._graphs[key]
         graph.replay()
@@ -229,8 +245,7 @@ class MixedGraphs:
                 ctx, rows = build()
             # ... then record the same launches.
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                logits = runner.model.forward(ctx, rows)
+            logits = _capture(torch, graph, lambda: runner.model.forward(ctx, rows))
             self._graphs[key] = (graph, logits)
         graph, logits = self._graphs[key]
         graph.replay()

@@ -63,7 +63,7 @@ class ModelRunner:
     def _staging_ints(self, n: int, b: int, r: int, width: int) -> int:
         groups = len(self.cache.paged_groups)
         per_group = _align4(n) + _align4(b * width)
-        return (3 * _align4(n) + _align4(b + 1) + 2 * _align4(b) + _align4(r)
+        return (3 * _align4(n) + _align4(b + 1) + 3 * _align4(b) + _align4(r)
                 + groups * per_group + 16)
 
     RING = 4  # pinned host buffers in rotation: a step may be packed while earlier copies wait
@@ -145,6 +145,7 @@ class ModelRunner:
 
         v_tok, v_pos, v_seq = take(n), take(n), take(n)
         v_cu, v_ctx, v_state, v_rows = take(b + 1), take(b), take(b), take(rows)
+        v_order = take(b)
         v_slots = [take(n) for _ in tables]
         v_tables = [take(b * width) for _ in tables]
 
@@ -260,6 +261,9 @@ class ModelRunner:
         buf[v_ctx[0]: v_ctx[0] + b] = ctx_lens
         buf[v_state[0]: v_state[0] + b] = state_slots
         buf[v_rows[0]: v_rows[0] + rows] = logit_rows
+        # the sequences by context length, the longest first: the order in which the decode attention
+        # starts their blocks (with more blocks than the device runs at once the short ones fill the end)
+        buf[v_order[0]: v_order[0] + b] = np.argsort(-np.asarray(ctx_lens, dtype=np.int64), kind="stable")
 
         self._staging_dev[:off].copy_(self._staging_host[turn][:off], non_blocking=True)
         if self._staging_events[turn] is not None:
@@ -289,7 +293,7 @@ class ModelRunner:
             cu_q=dview(v_cu), ctx_lens=dview(v_ctx), groups=groups,
             q_starts=q_starts, q_lens=q_lens, start_positions=start_positions,
             max_q_len=max(q_lens), max_ctx_len=max(ctx_lens), padded=pad_to_seqs is not None,
-            ragged=ragged,
+            ragged=ragged, decode_order=dview(v_order),
             bounds=None if pad_to_tokens is None else (n, b, width * ps),
         )
         return ctx, dview(v_rows)
@@ -349,6 +353,7 @@ class ModelRunner:
 
         v_tok, v_pos, v_seq = take(b), take(b), take(b)
         v_cu, v_ctx, v_state, v_rows = take(b + 1), take(b), take(b), take(rows)
+        v_order = take(b)
         v_slots = [take(b) for _ in cache.paged_groups]
         v_tables = [take(b * width) for _ in cache.paged_groups]
         buf[v_tok[0]: v_tok[0] + real_b] = [e.tokens[0] for e in entries]
@@ -358,7 +363,10 @@ class ModelRunner:
         buf[v_ctx[0]: v_ctx[0] + real_b] = positions + 1
         buf[v_state[0]: v_state[0] + real_b] = slots_arr
         buf[v_rows[0]: v_rows[0] + rows] = logit_rows
+        # (the sequences by context length, the longest first; the padding's last: see build_context)
+        buf[v_order[0]: v_order[0] + real_b] = np.argsort(-positions, kind="stable")
         if pad:
+            buf[v_order[0] + real_b: v_order[0] + b] = np.arange(real_b, b)
             buf[v_tok[0] + real_b: v_tok[0] + b] = 0
             buf[v_pos[0] + real_b: v_pos[0] + b] = 0
             buf[v_ctx[0] + real_b: v_ctx[0] + b] = 1
@@ -413,7 +421,7 @@ class ModelRunner:
             cu_q=dview(v_cu), ctx_lens=dview(v_ctx), groups=groups,
             q_starts=list(range(b)), q_lens=[1] * b, start_positions=start_positions,
             max_q_len=1, max_ctx_len=int(positions.max()) + 1, padded=pad_to_seqs is not None,
-            ragged=ragged,
+            ragged=ragged, decode_order=dview(v_order),
         )
         return ctx, dview(v_rows)
 

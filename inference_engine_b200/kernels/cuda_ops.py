@@ -443,6 +443,7 @@ class CudaOps:
             lib.ie_attention_decode_scratch_floats.argtypes = [I, I, I]
             lib.ie_attention_decode_scratch_floats.restype = ctypes.c_longlong
             lib.ie_attention_decode_balanced.argtypes = [P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, F, I, I, P, P]
+            lib.ie_attention_decode_ordered.argtypes = [P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, F, I, I, P, P, P]
             lib.ie_attention_decode_balanced_scratch_floats.argtypes = [I, I, I]
             lib.ie_attention_decode_balanced_scratch_floats.restype = ctypes.c_longlong
             lib.ie_attention_decode_max_clusters.argtypes = [I]
@@ -618,11 +619,12 @@ class CudaOps:
         if floats:
             scratch = self._scratch(ctx, "attn.partial", floats, q.device)
             tickets = self._decode_tickets(ctx.num_seqs * nkv)
-        self._check(lib.ie_attention_decode(
+        self._check(lib.ie_attention_decode_ordered(
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
             block_tables.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_lens.data_ptr(), out.data_ptr(),
             self._ptr(scratch), self._ptr(tickets), ctx.num_seqs, nh, nkv, page_size,
-            total_pages, scale, window, splits, self._err_ptr, stream), "attention_decode")
+            total_pages, scale, window, splits, self._ptr(getattr(ctx, "decode_order", None)),
+            self._err_ptr, stream), "attention_decode")
 
     @_kind("attention.prefill")
     def _prefill_attention(self, lib, plan, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, page_size,

@@ -72,7 +72,9 @@ def main() -> int:
             positions=torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device="cuda"),
             seq_of_token=torch.arange(batch, dtype=torch.int32, device="cuda"),
             cu_q=torch.arange(batch + 1, dtype=torch.int32, device="cuda"),
-            ctx_lens=torch.tensor(lengths, dtype=torch.int32, device="cuda"), ragged=(ragged,))
+            ctx_lens=torch.tensor(lengths, dtype=torch.int32, device="cuda"), ragged=(ragged,),
+            # (as the engine packs a step: the by-request kernel starts the longest requests' blocks first)
+            decode_order=torch.tensor(sorted(range(batch), key=lambda i: -lengths[i]), dtype=torch.int32, device="cuda"))
         return q, k, v, tables, ctx
 
     for item in args.cases.split(","):

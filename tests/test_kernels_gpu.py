@@ -434,6 +434,28 @@ def test_decode_attention_with_many_splits_is_the_same_as_one(ops):
     torch.testing.assert_close(got.float(), want.float(), atol=1e-2, rtol=1e-2)
 
 
+@pytest.mark.parametrize("nh,nkv,hd,ps", [(32, 8, 64, 16), (8, 2, 128, 16), (5, 5, 48, 4)])
+def test_decode_attention_starts_the_requests_blocks_in_a_given_order(ops, nh, nkv, hd, ps, monkeypatch):
+    """The by-request decode attention takes the order in which the requests' blocks start (the
+    runner gives the longest first): whatever the order, every request gets its own result, bit for
+    bit the same (50 requests of one key to thousands: more blocks than the device runs at once)."""
+    monkeypatch.setattr(ops, "decode_balanced", "0")
+    g = torch.Generator().manual_seed(7)
+    ctx_lens = torch.randint(1, 3000, (50,), generator=g).tolist()
+    q, k, v, tables, ctx = _attention_case(nh, nkv, hd, ps, [1] * 50, ctx_lens, torch.bfloat16, seed=9)
+    want = torch.empty_like(q)
+    RefOps().paged_attention(q, k, v, tables, ctx, nh, nkv, hd, ps, hd ** -0.5, 0, want)
+    outs = []
+    for order in (None, torch.argsort(ctx.ctx_lens, descending=True), torch.randperm(50, generator=g).cuda()):
+        ctx.decode_order = None if order is None else order.to(torch.int32)
+        got = torch.zeros_like(q)
+        ops.paged_attention(q, k, v, tables, ctx, nh, nkv, hd, ps, hd ** -0.5, 0, got)
+        torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+        outs.append(got)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    ops.check_errors()
+
+
 @pytest.mark.parametrize("nh,nkv,hd,ps", [(32, 8, 64, 16), (8, 2, 128, 16), (6, 3, 80, 8), (4, 4, 32, 4)])
 @pytest.mark.parametrize("window", [0, 300])
 @pytest.mark.parametrize("blocks_per_pair", [1, 2, 3, 32])

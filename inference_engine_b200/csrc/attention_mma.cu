@@ -1385,6 +1385,7 @@ inline int& decode_narrow_rows() {
 IE_API int ie_attention_head_dim() { return HD; }
 IE_API void ie_set_decode_pair(int max_splits) { decode_pair_enabled() = max_splits; }
 IE_API void ie_set_decode_narrow(int enabled) { decode_narrow_rows() = enabled ? NARROW_ROWS : 0; }
+
 // Query tokens one block of the prefill kernel takes (callers count tiles with it).
 IE_API int ie_attention_prefill_rows() { return BM; }
 IE_API void ie_set_pdl(int enabled) { ie_pdl_enabled() = enabled ? 1 : 0; }
@@ -1479,15 +1480,34 @@ int launch_decode_as(const void* q, const void* k_cache, const void* v_cache, co
                      scale * 1.4426950408889634f, window, num_splits, decode_narrow_rows(), order, err);
 }
 
+// Blocks of `warps` warps an SM holds at one time (by their shared memory).
+constexpr int blocks_per_sm(int warps) {
+    size_t n = (MAX_DYNAMIC_SMEM + 1024) / (decode_smem(warps) + 1024);
+    return n > 8 ? 8 : (int)n;
+}
+
 // With at most one block per SM a block takes the SM's whole shared memory for tiles in flight;
 // with more blocks than SMs, blocks of half the size run two to an SM, so that one block's
 // start-up and merge overlap the other's streaming.  The choice depends on the grid alone.
+// `small_blocks` (the caller's choice): blocks of 3 or 2 warps, three or four to an SM at head size
+// 64, so that a grid of more than two blocks per SM still runs in one round (40 requests x 8 heads
+// of 1,024 tokens: 320 blocks, 25.8 us in two rounds of four-warp blocks, 17.9 us in one round of
+// three-warp blocks; 64 requests: 27.3 us, 24.8 us in two-warp blocks).  Requests of very different
+// lengths lose: the longest one's block has fewer warps to walk it.
 int launch_decode(const void* q, const void* k_cache, const void* v_cache, const int* tables, int table_width,
                   const int* cu_q, const int* ctx_lens, void* out, float* part_o, float* part_ml, int* tickets,
                   int num_seqs, int nh, int nkv, int page_shift, int total_pages, float scale, int window,
-                  int num_splits, const int* order, int* err, cudaStream_t s) {
+                  int num_splits, const int* order, int small_blocks, int* err, cudaStream_t s) {
     int sms = ie_sm_count();
     long long blocks = (long long)num_seqs * nkv * num_splits;
+    if (small_blocks == 3 && blocks > sms)
+        return launch_decode_as<3>(q, k_cache, v_cache, tables, table_width, cu_q, ctx_lens, out, part_o,
+                                   part_ml, tickets, num_seqs, nh, nkv, page_shift, total_pages, scale,
+                                   window, num_splits, order, err, s);
+    if (small_blocks == 2 && blocks > sms)
+        return launch_decode_as<2>(q, k_cache, v_cache, tables, table_width, cu_q, ctx_lens, out, part_o,
+                                   part_ml, tickets, num_seqs, nh, nkv, page_shift, total_pages, scale,
+                                   window, num_splits, order, err, s);
     if (blocks > sms)
         return launch_decode_as<DWARPS_SHARED>(q, k_cache, v_cache, tables, table_width, cu_q, ctx_lens, out, part_o,
                                                part_ml, tickets, num_seqs, nh, nkv, page_shift, total_pages, scale,
@@ -1516,19 +1536,23 @@ IE_API int ie_attention_decode(const void* q, const void* k_cache, const void* v
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)num_seqs * nkv * num_splits * MAX_ROWS * HD : nullptr;
     return launch_decode(q, k_cache, v_cache, tables, table_width, cu_q, ctx_lens, out, part_o, part_ml, tickets,
-                         num_seqs, nh, nkv, page_shift, total_pages, scale, window, num_splits, nullptr, err,
+                         num_seqs, nh, nkv, page_shift, total_pages, scale, window, num_splits, nullptr, 0, err,
                          (cudaStream_t)stream);
 }
 
+// How many decode blocks of `warps` warps an SM holds at one time.
+IE_API int ie_attention_decode_blocks_per_sm(int warps) { return warps >= 1 && warps <= 8 ? blocks_per_sm(warps) : 0; }
+
 // The same with the order in which the requests' blocks start: `order[i]` is the request that is
 // i-th (every request once; the longest first pays when the step has more blocks than the device
-// runs at once and contexts of different lengths).
+// runs at once and contexts of different lengths), and with the choice of blocks of 3 or 2 warps
+// (`small_blocks` 3, 2; 0: four or eight, by the grid) for grids of more blocks than SMs.
 IE_API int ie_attention_decode_ordered(const void* q, const void* k_cache, const void* v_cache,
                                        const int* tables, int table_width, const int* cu_q,
                                        const int* ctx_lens, void* out, float* scratch, int* tickets,
                                        int num_seqs, int nh, int nkv, int page_size, int total_pages,
-                                       float scale, int window, int num_splits, const int* order, int* err,
-                                       void* stream) {
+                                       float scale, int window, int num_splits, const int* order,
+                                       int small_blocks, int* err, void* stream) {
     if (num_seqs <= 0) return 0;
     if (nkv <= 0 || nh % nkv != 0 || (page_size & (page_size - 1)) != 0 || num_splits < 1 ||
         (num_splits > 1 && (scratch == nullptr || tickets == nullptr)))
@@ -1538,8 +1562,8 @@ IE_API int ie_attention_decode_ordered(const void* q, const void* k_cache, const
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)num_seqs * nkv * num_splits * MAX_ROWS * HD : nullptr;
     return launch_decode(q, k_cache, v_cache, tables, table_width, cu_q, ctx_lens, out, part_o, part_ml, tickets,
-                         num_seqs, nh, nkv, page_shift, total_pages, scale, window, num_splits, order, err,
-                         (cudaStream_t)stream);
+                         num_seqs, nh, nkv, page_shift, total_pages, scale, window, num_splits, order, small_blocks,
+                         err, (cudaStream_t)stream);
 }
 
 namespace {

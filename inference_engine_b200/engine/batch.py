@@ -34,7 +34,7 @@ class PagedGroupView:
     block_tables: Any  # int32 [B, table_width]; -1 where a window has passed
     table_width: int
     slot_mapping: Any  # int32 [N]: flat slot (page * page_size + offset) of each new token
-    ragged: bool = False  # the contexts this group's mixers see differ much in length (a launch hint)
+    ragged: int = 0  # a launch hint: 1 the contexts this group's mixers see differ much in length; 2, 3 so many that blocks of as many warps pay
 
 
 @dataclass

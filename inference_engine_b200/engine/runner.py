@@ -42,20 +42,21 @@ class ModelRunner:
         self.last_h2d_bytes = 0
         self._ensure_staging(self._staging_ints(self.max_tokens, self.max_seqs, self.max_seqs, 8))
 
-    def contexts_are_ragged(self, ctx_lens) -> tuple[bool, ...]:
-        """A hint for the attention's launch, one answer per paged cache group: whether these
+    def contexts_are_ragged(self, ctx_lens) -> tuple[int, ...]:
+        """A hint for the attention's launch, one answer per paged cache group: 1 if these
         requests' contexts (what a group's window leaves of them) differ so much in length that
-        work dealt request by request would leave most of the GPU waiting for the longest one.
+        work dealt request by request would leave most of the GPU waiting for the longest one,
+        2 or 3 if they are so many and so alike that blocks of as many warps pay, else 0.
         The kernels' side decides (it knows how many requests the device takes at once and the
-        group's number of key/value heads); without such kernels the answer is no."""
-        decide = getattr(self.ops, "decode_by_length", None)
+        group's number of key/value heads and head size); without such kernels the answer is 0."""
+        decide = getattr(self.ops, "decode_dealing", None)
         groups = self.cache.paged_groups
         if decide is None or len(ctx_lens) < 2:
-            return (False,) * len(groups)
+            return (0,) * len(groups)
         answers = []
         for g in groups:
             seen = ctx_lens if g.window is None else [min(c, g.window) for c in ctx_lens]
-            answers.append(bool(decide(seen, g.num_kv_heads)))
+            answers.append(int(decide(seen, g.num_kv_heads, getattr(g, "head_dim", None))))
         return tuple(answers)
 
     # --- staging ----------------------------------------------------------------------------
@@ -279,7 +280,7 @@ class ModelRunner:
         # (of the requests that bring one token: the others are not the decode kernel's)
         ragged = self.contexts_are_ragged([c for c, ql in zip(ctx_lens[:real_b], q_lens) if ql == 1])
         if pad_to_tokens is not None:  # (a launch that serves every step that fits knows no lengths)
-            ragged = tuple(False for _ in ragged)
+            ragged = tuple(0 for _ in ragged)
         groups: list[Any] = []
         for g, st in enumerate(self.storage.paged):
             groups.append(PagedGroupView(st.k, st.v, ps, st.window, dview(v_tables[g], (b, width)),

@@ -143,6 +143,9 @@ class CudaOps:
         # by length ("auto": when the step's context says so; "1": always; "0": never)
         self.decode_balanced = os.environ.get("IE_B200_DECODE_BALANCED", "auto")
         self.decode_balanced_blocks_per_pair = 32
+        # by-request decode attention in two-warp blocks where that saves a round ("0": never)
+        self.decode_small = os.environ.get("IE_B200_DECODE_SMALL", "1") != "0"
+        self._small_per_sm: dict[tuple[int, int], int] = {}
         self.balanced_launches = 0
         # which kernel takes few-row bfloat16 products: "tma" (the TMA-fed weight-streaming kernel)
         # or "lib" (the vendor library, for comparisons)
@@ -443,7 +446,7 @@ class CudaOps:
             lib.ie_attention_decode_scratch_floats.argtypes = [I, I, I]
             lib.ie_attention_decode_scratch_floats.restype = ctypes.c_longlong
             lib.ie_attention_decode_balanced.argtypes = [P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, F, I, I, P, P]
-            lib.ie_attention_decode_ordered.argtypes = [P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, F, I, I, P, P, P]
+            lib.ie_attention_decode_ordered.argtypes = [P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, F, I, I, P, I, P, P]
             lib.ie_attention_decode_balanced_scratch_floats.argtypes = [I, I, I]
             lib.ie_attention_decode_balanced_scratch_floats.restype = ctypes.c_longlong
             lib.ie_attention_decode_max_clusters.argtypes = [I]
@@ -498,6 +501,51 @@ class CudaOps:
         while hd is not None and parts > 2 and 0 < self._clusters_at_once(hd, parts) < pairs:
             parts //= 2
         return parts
+
+    BY_REQUEST, BY_LENGTH, SMALL_2, SMALL_3 = 0, 1, 2, 3  # how a decode step's attention is dealt (StepContext.ragged)
+
+    def _decode_blocks_per_sm(self, hd: int, warps: int) -> int:
+        key = (hd, warps)
+        if key not in self._small_per_sm:
+            self._small_per_sm[key] = int(self._attention_lib(hd).ie_attention_decode_blocks_per_sm(warps))
+        return self._small_per_sm[key]
+
+    def decode_dealing(self, ctx_lens, nkv: int, hd: int | None = None) -> int:
+        """How the decode attention of a step over contexts of these lengths is dealt: key tiles by
+        length (:meth:`decode_by_length`), or by request, and then in blocks of 3 or 2 warps (3 or 4 of
+        them to an SM at head size 64) where that brings all blocks onto the device in one round instead
+        of two of the four-warp blocks.  In tokens a four-warp block walks, with a block's set-up worth
+        600: the small blocks take the set-up and the longest context times 4 / warps; the four-warp
+        blocks, which start longest first, as long as the last of the second round needs, each of those
+        starting when a block of the first round ends.  The small blocks must be a tenth ahead
+        (48 requests of 512 to 1,536 tokens: 19.5 us in four-warp blocks, 23.1 in three-warp blocks; 40
+        of 768 to 1,280: 22.1 and 19.8).  Measured at head size 64, us per
+        layer: 40 requests x 1,024 tokens 25.8 -> 17.9 (3 warps), 48 x 1,024 26.7 -> 18.4, 55 x 1,024 ->
+        19.6 (0.90 of the copy rate), 64 x 1,024 27.3 -> 24.8 (2 warps), 72 x 1,024 28.5 -> 25.8, 64 x 4,096
+        96.4 -> 90.4, 64 x 256 10.4 -> 8.3; 64 requests of 64 to 2,048 tokens would take 43.6 instead of
+        27.1 and stay with the four-warp blocks, the longest first."""
+        if self.decode_by_length(ctx_lens, nkv):
+            return self.BY_LENGTH
+        if not self.decode_small or hd is None or hd not in ATTENTION_HEAD_DIMS or not ctx_lens:
+            return self.BY_REQUEST
+        pairs = len(ctx_lens) * nkv
+        if pairs <= 2 * self.sm_count:
+            return self.BY_REQUEST
+        warps = next((w for w in (3, 2) if self._decode_blocks_per_sm(hd, w) >= 3
+                      and pairs <= self._decode_blocks_per_sm(hd, w) * self.sm_count), 0)
+        if not warps:
+            return self.BY_REQUEST
+        # the four-warp blocks, longest first, two to an SM: the requests beyond the first round start as
+        # those of the first round end, the shortest of them first (a request's heads together)
+        setup = 600
+        by_length = sorted(ctx_lens, reverse=True)
+        at_once = max(1, 2 * self.sm_count // nkv)
+        first, rest = by_length[:at_once], by_length[at_once:]
+        larger = max([first[0] + setup] + [a + b + 2 * setup for a, b in zip(reversed(first), rest)])
+        small = setup + by_length[0] * 4 / warps
+        if small > 0.9 * larger:
+            return self.BY_REQUEST
+        return self.SMALL_3 if warps == 3 else self.SMALL_2
 
     def decode_by_length(self, ctx_lens, nkv: int) -> bool:
         """Whether a decode step over contexts of these lengths should use the kernel that deals
@@ -580,8 +628,8 @@ class CudaOps:
             args = (q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, page_size, scale, window, out)
             if plan["any"]:
                 if ragged is None:
-                    ragged = any(getattr(ctx, "ragged", ()) or ())
-                self._decode_attention(lib, ragged and bounds is None, *args)
+                    ragged = max(getattr(ctx, "ragged", ()) or (0,))
+                self._decode_attention(lib, int(ragged) if bounds is None else self.BY_REQUEST, *args)
             if not plan["all"]:
                 self._prefill_attention(lib, plan, *args)
             return
@@ -600,7 +648,7 @@ class CudaOps:
         """The requests with few rows (the kernels skip the others): key tiles dealt by length
         when the step's context says its lengths differ much, else by request."""
         total_pages, stream = k_cache.shape[0], self._stream()
-        by_length = self.decode_balanced == "1" or (self.decode_balanced == "auto" and bool(ragged))
+        by_length = self.decode_balanced == "1" or (self.decode_balanced == "auto" and ragged == self.BY_LENGTH)
         if by_length and ctx.num_seqs <= lib.ie_attention_decode_balanced_max_seqs():
             per_pair = self.decode_balanced_blocks_per_pair
             floats = lib.ie_attention_decode_balanced_scratch_floats(ctx.num_seqs, nkv, per_pair)
@@ -624,7 +672,8 @@ class CudaOps:
             block_tables.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_lens.data_ptr(), out.data_ptr(),
             self._ptr(scratch), self._ptr(tickets), ctx.num_seqs, nh, nkv, page_size,
             total_pages, scale, window, splits, self._ptr(getattr(ctx, "decode_order", None)),
-            self._err_ptr, stream), "attention_decode")
+            ragged if ragged in (self.SMALL_2, self.SMALL_3) and splits == 1 else 0, self._err_ptr, stream),
+            "attention_decode")
 
     @_kind("attention.prefill")
     def _prefill_attention(self, lib, plan, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, page_size,

@@ -8,7 +8,7 @@ the fraction of a memory bandwidth at which it reads the keys and values it must
 
 Every request brings one token.  ``BxL`` is B requests of L cached tokens, ``BxL1-L2`` B requests whose lengths
 are drawn evenly from L1 to L2 (seeded); which of the two decode kernels runs is the engine's own choice
-(``CudaOps.decode_by_length``) unless ``IE_B200_DECODE_BALANCED`` says otherwise.  A launch stands for one layer of a step: it runs on a cache of its own
+(``CudaOps.decode_dealing``) unless ``IE_B200_DECODE_BALANCED`` (by length: 0, 1) or ``IE_B200_DECODE_SMALL`` (no blocks of 2 or 3 warps: 0) says otherwise.  A launch stands for one layer of a step: it runs on a cache of its own
 (several caches, together larger than L2, taken in turn), block tables point at shuffled pages.  The launches
 of four rounds over the caches are captured in one CUDA graph and timed with CUDA events; the best of
 three replays counts.  ``--peak-gbs`` is the bandwidth the fraction is of (default: the copy rate in
@@ -66,7 +66,7 @@ def main() -> int:
         k = torch.randn(total, nkv, ps, hd, device="cuda").bfloat16()
         v = torch.randn_like(k)
         q = torch.randn(batch, nh * hd, device="cuda").bfloat16()
-        ragged = bool(ops.decode_by_length(lengths, nkv)) if batch > 1 else False
+        ragged = int(ops.decode_dealing(lengths, nkv, hd)) if batch > 1 else 0
         ctx = types.SimpleNamespace(
             num_tokens=batch, num_seqs=batch, q_lens=[1] * batch, max_q_len=1, max_ctx_len=max(lengths), ws=ws,
             positions=torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device="cuda"),
@@ -116,7 +116,7 @@ def main() -> int:
             torch.cuda.synchronize()
             best = min(best, start.elapsed_time(end) / iters * 1e3)
         gbs = kv_bytes / best / 1e3
-        row = {"requests": batch, "context": length, "by_length": cases[0][4].ragged[0], "us": round(best, 2), "gbs": round(gbs, 1),
+        row = {"requests": batch, "context": length, "dealt": ("by request", "by length", "by request, 2-warp blocks", "by request, 3-warp blocks")[cases[0][4].ragged[0]], "us": round(best, 2), "gbs": round(gbs, 1),
                "caches": len(cases), "kv_mb_per_launch": round(kv_bytes / 1e6, 1)}
         if peak:
             row["frac"] = round(gbs / peak, 3)

@@ -456,6 +456,33 @@ def test_decode_attention_starts_the_requests_blocks_in_a_given_order(ops, nh, n
     ops.check_errors()
 
 
+@pytest.mark.parametrize("nh,nkv,hd,ps,window", [(32, 8, 64, 16, 0), (16, 8, 128, 16, 0), (12, 6, 80, 8, 200), (8, 8, 32, 4, 0)])
+def test_decode_attention_in_small_blocks(ops, nh, nkv, hd, ps, window):
+    """Many requests of about one length, dealt by request to blocks of two or three warps (the launch hints 2, 3):
+    the same result as in the larger blocks, against the plain formula; one far key per request
+    stands out.  Requests of two tokens and a request the prefill kernel takes are among them."""
+    n = 300 // nkv + 3  # (more blocks than two per SM)
+    g = torch.Generator().manual_seed(3)
+    ctx_lens = torch.randint(500, 600, (n,), generator=g).tolist()
+    group = nh // nkv
+    q_lens = [1] * n
+    q_lens[5], q_lens[n // 2] = (2 if 2 * group <= 16 else 1), 40
+    spike = [(c - ql) // 3 for c, ql in zip(ctx_lens, q_lens)]
+    q, k, v, tables, ctx = _attention_case(nh, nkv, hd, ps, q_lens, ctx_lens, torch.bfloat16, seed=13, spike=spike)
+    want = torch.empty_like(q)
+    RefOps().paged_attention(q, k, v, tables, ctx, nh, nkv, hd, ps, hd ** -0.5, window, want)
+    outs = []
+    for hint in (ops.BY_REQUEST, ops.SMALL_2, ops.SMALL_3):
+        got = torch.zeros_like(q)
+        ops.paged_attention(q, k, v, tables, ctx, nh, nkv, hd, ps, hd ** -0.5, window, got, ragged=hint)
+        torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+        outs.append(got)
+    small = [i for i, ql in enumerate(q_lens) if ql * group <= 16]
+    rows = torch.cat([torch.arange(int(ctx.cu_q[i]), int(ctx.cu_q[i + 1])) for i in small]).cuda()
+    assert max((outs[0][rows] - o[rows]).abs().max() for o in outs[1:]) < 2e-2  # (other warps, another order of the tiles' sums)
+    ops.check_errors()
+
+
 @pytest.mark.parametrize("nh,nkv,hd,ps", [(32, 8, 64, 16), (8, 2, 128, 16), (6, 3, 80, 8), (4, 4, 32, 4)])
 @pytest.mark.parametrize("window", [0, 300])
 @pytest.mark.parametrize("blocks_per_pair", [1, 2, 3, 32])

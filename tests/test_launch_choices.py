@@ -123,3 +123,31 @@ def test_the_history_masks_of_the_repetition_penalty_grow_with_the_histories():
     # without keys every mask is built from the whole history
     got = sampler._seen_bits(params, histories).numpy().view(np.uint32)
     assert (got == expected(histories)).all()
+
+
+def test_many_requests_of_one_length_run_in_small_blocks():
+    """`CudaOps.decode_dealing`: by request in blocks of 3 or 2 warps when the (request, head) pairs
+    are more than two per SM, no more than the device holds of the small blocks, and no context so much
+    longer than the others that its block would be the last by far; by length or in the larger
+    blocks otherwise."""
+    ops = _ops()
+    fits = {(64, 3): 3, (64, 2): 4, (128, 3): 1, (128, 2): 2}
+    ops.decode_small, ops._decode_blocks_per_sm = True, lambda hd, warps: fits[(hd, warps)]
+    ops.decode_by_length = lambda lens, nkv: CudaOps.decode_by_length(ops, lens, nkv)
+    for name in ("BY_REQUEST", "BY_LENGTH", "SMALL_2", "SMALL_3"):
+        setattr(ops, name, getattr(CudaOps, name))
+    deal = lambda lens, nkv=8, hd=64: CudaOps.decode_dealing(ops, lens, nkv, hd)
+    assert deal([1024] * 40) == CudaOps.SMALL_3 and deal([1024] * 55) == CudaOps.SMALL_3  # up to 444 blocks
+    assert deal([1024] * 56) == CudaOps.SMALL_2 and deal([1024] * 74) == CudaOps.SMALL_2  # up to 592
+    assert deal([800 + 8 * i for i in range(48)]) == CudaOps.SMALL_3    # (lengths that differ a little)
+    assert deal([1024] * 37) == CudaOps.BY_REQUEST       # 296 blocks: one round of the larger ones
+    assert deal([1024] * 75) == CudaOps.BY_REQUEST       # 600 blocks: more than 4 x 148
+    assert deal([1024] * 64, hd=128) == CudaOps.BY_REQUEST  # two small blocks per SM: nothing gained
+    assert deal([1024] * 64, hd=None) == CudaOps.BY_REQUEST
+    import random
+    rng = random.Random(0)
+    assert deal([rng.randint(64, 2048) for _ in range(64)]) == CudaOps.BY_REQUEST
+    assert deal([rng.randint(128, 2048) for _ in range(40)]) == CudaOps.BY_REQUEST
+    assert deal([256] * 39 + [32768]) == CudaOps.BY_LENGTH
+    ops.decode_small = False
+    assert deal([1024] * 64) == CudaOps.BY_REQUEST

@@ -143,3 +143,39 @@ def test_sampling_params_are_validated():
         with pytest.raises(ValueError):
             SamplingParams(**bad)
     assert SamplingParams(temperature=0).greedy and not SamplingParams().greedy
+
+
+def test_the_garbage_collector_is_off_while_a_step_is_captured():
+    """An object the collector frees may own captured launch sequences or device memory; giving those
+    back while a stream is capturing makes the capture invalid.  `graphs._capture` collects before
+    and keeps the collector off until the capture has ended, also when the forward pass raises."""
+    import contextlib
+    import gc
+    import types
+
+    from inference_engine_b200.engine.graphs import _capture
+
+    seen = []
+
+    @contextlib.contextmanager
+    def graph(_):
+        seen.append(gc.isenabled())
+        yield
+
+    fake_torch = types.SimpleNamespace(cuda=types.SimpleNamespace(graph=graph))
+    assert gc.isenabled()
+    assert _capture(fake_torch, object(), lambda: (seen.append(gc.isenabled()), 7)[1]) == 7
+    assert seen == [False, False] and gc.isenabled()
+
+    def fails():
+        raise RuntimeError("no")
+
+    with pytest.raises(RuntimeError):
+        _capture(fake_torch, object(), fails)
+    assert gc.isenabled()
+    gc.disable()
+    try:  # (a caller that had it off gets it back off)
+        _capture(fake_torch, object(), lambda: None)
+        assert not gc.isenabled()
+    finally:
+        gc.enable()

@@ -145,6 +145,7 @@ class CudaOps:
         self.decode_balanced_blocks_per_pair = 32
         # by-request decode attention in two-warp blocks where that saves a round ("0": never)
         self.decode_small = os.environ.get("IE_B200_DECODE_SMALL", "1") != "0"
+        self._force_small = int(os.environ.get("IE_B200_DECODE_SMALL", "1")) if os.environ.get("IE_B200_DECODE_SMALL", "1") in ("2", "3") else 0
         self._small_per_sm: dict[tuple[int, int], int] = {}
         self.balanced_launches = 0
         # which kernel takes few-row bfloat16 products: "tma" (the TMA-fed weight-streaming kernel)
@@ -510,42 +511,56 @@ class CudaOps:
             self._small_per_sm[key] = int(self._attention_lib(hd).ie_attention_decode_blocks_per_sm(warps))
         return self._small_per_sm[key]
 
+    @staticmethod
+    def _by_request_estimate(by_length, at_once: int, scale: float, setup: float) -> float:
+        """How long blocks dealt by request take, in tokens a four-warp block walks: ``by_length`` the
+        contexts, the longest first, ``at_once`` of them on the device at one time, a block's time
+        ``setup + scale * length``.  The requests beyond the first round start as those of the round
+        before end, the shortest of them first."""
+        if by_length[0] <= 1.1 * by_length[-1]:  # (about one length: whole rounds)
+            return -(-len(by_length) // at_once) * (setup + scale * by_length[0])
+        finish = []
+        for i, n in enumerate(by_length):
+            r, k = divmod(i, at_once)
+            finish.append((finish[r * at_once - 1 - k] if r else 0.0) + setup + scale * n)
+        return max(finish)
+
     def decode_dealing(self, ctx_lens, nkv: int, hd: int | None = None) -> int:
         """How the decode attention of a step over contexts of these lengths is dealt: key tiles by
         length (:meth:`decode_by_length`), or by request, and then in blocks of 3 or 2 warps (3 or 4 of
-        them to an SM at head size 64) where that brings all blocks onto the device in one round instead
-        of two of the four-warp blocks.  In tokens a four-warp block walks, with a block's set-up worth
-        600: the small blocks take the set-up and the longest context times 4 / warps; the four-warp
-        blocks, which start longest first, as long as the last of the second round needs, each of those
-        starting when a block of the first round ends.  The small blocks must be a tenth ahead
-        (48 requests of 512 to 1,536 tokens: 19.5 us in four-warp blocks, 23.1 in three-warp blocks; 40
-        of 768 to 1,280: 22.1 and 19.8).  Measured at head size 64, us per
-        layer: 40 requests x 1,024 tokens 25.8 -> 17.9 (3 warps), 48 x 1,024 26.7 -> 18.4, 55 x 1,024 ->
-        19.6 (0.90 of the copy rate), 64 x 1,024 27.3 -> 24.8 (2 warps), 72 x 1,024 28.5 -> 25.8, 64 x 4,096
-        96.4 -> 90.4, 64 x 256 10.4 -> 8.3; 64 requests of 64 to 2,048 tokens would take 43.6 instead of
-        27.1 and stay with the four-warp blocks, the longest first."""
+        them to an SM at head size 64, against 2 of the four-warp blocks) where the step's blocks then
+        need fewer rounds over the device.  A block of w warps takes a set-up worth 300 tokens and
+        4 / w of its context (in tokens a four-warp block walks; measured at 1,024 tokens: a round of
+        four-warp blocks 13 us, of three-warp blocks 18, of two-warp blocks 24); the rounds are
+        estimated by :meth:`_by_request_estimate`, and smaller blocks must be 7 % ahead.  Measured at
+        head size 64, us per layer, four-warp blocks -> the choice: 40 requests x 1,024 tokens 25.8 ->
+        17.9 (3 warps), 55 x 1,024 26.9 -> 19.6 (0.90 of the copy rate), 64 x 1,024 27.3 -> 24.8 (2 warps),
+        80 x 1,024 40.0 -> 35.9 (3), 128 x 1,024 54.6 -> 49.4 (2), 160 x 1,024 68.1 -> 56.4 (3), 64 x 4,096
+        96.4 -> 90.4, 64 x 256 10.4 -> 8.3, 40 of 768 to 1,280 tokens 22.1 -> 19.8; kept in four-warp blocks,
+        the longest first: 48 of 512 to 1,536 tokens (19.5; 23.1 in three-warp blocks), 64 of 64 to 2,048
+        (27.1; 43.6 in two-warp blocks)."""
         if self.decode_by_length(ctx_lens, nkv):
             return self.BY_LENGTH
         if not self.decode_small or hd is None or hd not in ATTENTION_HEAD_DIMS or not ctx_lens:
             return self.BY_REQUEST
         pairs = len(ctx_lens) * nkv
-        if pairs <= 2 * self.sm_count:
+        if self._force_small and pairs > self.sm_count:
+            return self._force_small
+        usual = self._decode_blocks_per_sm(hd, 4)
+        if pairs <= max(usual, 1) * self.sm_count:  # (one round anyway; up to one block per SM: eight warps)
             return self.BY_REQUEST
-        warps = next((w for w in (3, 2) if self._decode_blocks_per_sm(hd, w) >= 3
-                      and pairs <= self._decode_blocks_per_sm(hd, w) * self.sm_count), 0)
-        if not warps:
-            return self.BY_REQUEST
-        # the four-warp blocks, longest first, two to an SM: the requests beyond the first round start as
-        # those of the first round end, the shortest of them first (a request's heads together)
-        setup = 600
         by_length = sorted(ctx_lens, reverse=True)
-        at_once = max(1, 2 * self.sm_count // nkv)
-        first, rest = by_length[:at_once], by_length[at_once:]
-        larger = max([first[0] + setup] + [a + b + 2 * setup for a, b in zip(reversed(first), rest)])
-        small = setup + by_length[0] * 4 / warps
-        if small > 0.9 * larger:
-            return self.BY_REQUEST
-        return self.SMALL_3 if warps == 3 else self.SMALL_2
+        setup = 300.0
+        best, best_time = self.BY_REQUEST, 0.93 * self._by_request_estimate(
+            by_length, max(1, usual * self.sm_count // nkv), 1.0, setup)
+        for warps, code in ((3, self.SMALL_3), (2, self.SMALL_2)):
+            per_sm = self._decode_blocks_per_sm(hd, warps)
+            if per_sm <= usual:
+                continue
+            time = self._by_request_estimate(by_length, max(1, per_sm * self.sm_count // nkv), 4.0 / warps, setup)
+            if time < best_time:
+                best, best_time = code, time
+        return best
 
     def decode_by_length(self, ctx_lens, nkv: int) -> bool:
         """Whether a decode step over contexts of these lengths should use the kernel that deals

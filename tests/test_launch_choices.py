@@ -126,28 +126,35 @@ def test_the_history_masks_of_the_repetition_penalty_grow_with_the_histories():
 
 
 def test_many_requests_of_one_length_run_in_small_blocks():
-    """`CudaOps.decode_dealing`: by request in blocks of 3 or 2 warps when the (request, head) pairs
-    are more than two per SM, no more than the device holds of the small blocks, and no context so much
-    longer than the others that its block would be the last by far; by length or in the larger
-    blocks otherwise."""
+    """`CudaOps.decode_dealing`: by request in blocks of 3 or 2 warps when the step's (request, head)
+    pairs then need fewer rounds over the device and no context is so much longer than the others
+    that its block would be the last by far; by length or in the larger blocks otherwise."""
     ops = _ops()
-    fits = {(64, 3): 3, (64, 2): 4, (128, 3): 1, (128, 2): 2}
-    ops.decode_small, ops._decode_blocks_per_sm = True, lambda hd, warps: fits[(hd, warps)]
+    fits = {(64, 4): 2, (64, 3): 3, (64, 2): 4, (128, 4): 1, (128, 3): 1, (128, 2): 2}
+    ops.decode_small, ops._force_small, ops._decode_blocks_per_sm = True, 0, lambda hd, warps: fits[(hd, warps)]
     ops.decode_by_length = lambda lens, nkv: CudaOps.decode_by_length(ops, lens, nkv)
+    ops._by_request_estimate = CudaOps._by_request_estimate
     for name in ("BY_REQUEST", "BY_LENGTH", "SMALL_2", "SMALL_3"):
         setattr(ops, name, getattr(CudaOps, name))
     deal = lambda lens, nkv=8, hd=64: CudaOps.decode_dealing(ops, lens, nkv, hd)
-    assert deal([1024] * 40) == CudaOps.SMALL_3 and deal([1024] * 55) == CudaOps.SMALL_3  # up to 444 blocks
+    assert deal([1024] * 40) == CudaOps.SMALL_3 and deal([1024] * 55) == CudaOps.SMALL_3  # up to 444 blocks: one round
     assert deal([1024] * 56) == CudaOps.SMALL_2 and deal([1024] * 74) == CudaOps.SMALL_2  # up to 592
+    assert deal([1024] * 80) == CudaOps.SMALL_3     # two rounds of three-warp blocks against three of four-warp ones
+    assert deal([1024] * 128) == CudaOps.SMALL_2    # two rounds against four
+    assert deal([1024] * 160) == CudaOps.SMALL_3    # three against five
     assert deal([800 + 8 * i for i in range(48)]) == CudaOps.SMALL_3    # (lengths that differ a little)
     assert deal([1024] * 37) == CudaOps.BY_REQUEST       # 296 blocks: one round of the larger ones
-    assert deal([1024] * 75) == CudaOps.BY_REQUEST       # 600 blocks: more than 4 x 148
-    assert deal([1024] * 64, hd=128) == CudaOps.BY_REQUEST  # two small blocks per SM: nothing gained
     assert deal([1024] * 64, hd=None) == CudaOps.BY_REQUEST
     import random
     rng = random.Random(0)
     assert deal([rng.randint(64, 2048) for _ in range(64)]) == CudaOps.BY_REQUEST
     assert deal([rng.randint(128, 2048) for _ in range(40)]) == CudaOps.BY_REQUEST
+    assert deal([rng.randint(512, 1536) for _ in range(48)]) == CudaOps.BY_REQUEST
+    assert deal([rng.randint(768, 1280) for _ in range(40)]) == CudaOps.SMALL_3
     assert deal([256] * 39 + [32768]) == CudaOps.BY_LENGTH
+    # the estimate itself: whole rounds for one length; else every later request starts as one of the round before ends
+    est = CudaOps._by_request_estimate
+    assert est([1000] * 80, 37, 1.0, 300.0) == 3 * 1300
+    assert est([900, 800, 700, 100, 50], 3, 1.0, 0.0) == max(700 + 100, 800 + 50, 900)
     ops.decode_small = False
     assert deal([1024] * 64) == CudaOps.BY_REQUEST

@@ -361,7 +361,8 @@ class LLMEngine:
         """Capture the launch sequences ahead of the first request, as the reference does when the
         engine is built (engine/runtime/cuda_graphs.py:47, 159): one decode step per batch bucket
         and one step with a prompt portion per token bucket up to ``max_tokens``, for short
-        contexts (captures for longer block tables are made when a step first needs one).  Uses
+        contexts of one length (captures for longer block tables, and for the other ways the decode
+        attention deals contexts of very different lengths, are made when a step first needs one).  Uses
         requests of its own on an idle engine and gives their pages back.  Returns how many
         launch sequences are captured afterwards; 0 without captured steps."""
         if self.graphs is None:

@@ -144,8 +144,10 @@ class CudaOps:
         self.decode_balanced = os.environ.get("IE_B200_DECODE_BALANCED", "auto")
         self.decode_balanced_blocks_per_pair = 32
         # by-request decode attention in two-warp blocks where that saves a round ("0": never)
-        self.decode_small = os.environ.get("IE_B200_DECODE_SMALL", "1") != "0"
-        self._force_small = int(os.environ.get("IE_B200_DECODE_SMALL", "1")) if os.environ.get("IE_B200_DECODE_SMALL", "1") in ("2", "3") else 0
+        # ("2", "3": always blocks of as many warps when there are more blocks than SMs, for comparisons)
+        small = os.environ.get("IE_B200_DECODE_SMALL", "1")
+        self.decode_small = small != "0"
+        self._force_small = int(small) if small in ("2", "3") else 0
         self._small_per_sm: dict[tuple[int, int], int] = {}
         self.balanced_launches = 0
         # which kernel takes few-row bfloat16 products: "tma" (the TMA-fed weight-streaming kernel)

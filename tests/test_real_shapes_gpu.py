@@ -200,3 +200,46 @@ def test_engine_at_1b_shape_with_padded_captured_steps(num_requests):
             gap = float(logits[best] - logits[token])
             assert token == best or gap < 0.1, f"{rid} token {i}: engine {token}, plain {best} (gap {gap:.4f})"
             ids.append(token)
+
+
+def test_many_live_requests_with_preemption_twice_the_same():
+    """300 requests of 1 to 300 prompt tokens and 1 to 60 new ones, ten arriving per step, as many
+    live as a cache that cannot hold them all lets in (preemption): captured steps launched ahead of the
+    host, the decode attention in blocks of 2 or 3 warps for the large batches.  Every request gets its
+    tokens, every page comes back, and the same schedule run again gives the same tokens."""
+    import random
+
+    from inference_engine_b200 import SamplingParams
+    from inference_engine_b200.engine.llm_engine import LLMEngine
+    from inference_engine_b200.engine.loading import model_from_tensors
+
+    cfg = SHAPE_1B_2L
+    weights = _weights(cfg, seed=11)
+    rng = random.Random(5)
+    requests = {f"r{i}": (H.random_tokens(cfg, rng.randint(1, 300), 1000 + i), rng.randint(1, 60)) for i in range(300)}
+    num_blocks = 700
+    runs, dealt = [], set()
+    for _ in range(2):
+        model, _ = model_from_tensors(cfg, weights, "bfloat16", "cuda", 512)
+        engine = LLMEngine(model, None, (), num_blocks=num_blocks, block_size=PAGE, max_num_seqs=128,
+                           max_num_batched_tokens=512, max_model_len=400, enable_cuda_graphs=True, debug_checks=True)
+        out = {rid: [] for rid in requests}
+        pending = list(requests.items())
+        most_live = 0
+        while pending or engine.has_unfinished():
+            for rid, (prompt, n) in pending[:10]:
+                engine.add_request(rid, prompt, SamplingParams(temperature=0, max_tokens=n))
+            del pending[:10]
+            for o in engine.step():
+                out[o.request_id].append(o.token_id)
+            most_live = max(most_live, len(engine.scheduler.running))
+        engine.ops.check_errors()
+        assert engine.cache.num_free_pages == [num_blocks]
+        assert all(len(out[rid]) == n for rid, (_, n) in requests.items())
+        assert most_live > 55 and engine.snapshot()["totals"]["preemptions"] > 0  # (more than 444 attention blocks)
+        dealt |= {key[1] for key in engine.graphs._graphs}
+        runs.append(out)
+        del engine, model
+        torch.cuda.empty_cache()
+    assert runs[0] == runs[1]
+    assert dealt & {(2,), (3,)}  # (large batches of contexts alike: the small blocks ran)

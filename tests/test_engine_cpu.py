@@ -147,8 +147,8 @@ def test_sampling_params_are_validated():
 
 def test_the_garbage_collector_is_off_while_a_step_is_captured():
     """An object the collector frees may own captured launch sequences or device memory; giving those
-    back while a stream is capturing makes the capture invalid.  `graphs._capture` collects before
-    and keeps the collector off until the capture has ended, also when the forward pass raises."""
+    back while a stream is capturing makes the capture invalid.  `graphs._capture` keeps the
+    collector off until the capture has ended, also when the forward pass raises."""
     import contextlib
     import gc
     import types

@@ -541,20 +541,23 @@ class CudaOps:
         96.4 -> 90.4, 64 x 256 10.4 -> 8.3, 40 of 768 to 1,280 tokens 22.1 -> 19.8; kept in four-warp blocks,
         the longest first: 48 of 512 to 1,536 tokens (19.5; 23.1 in three-warp blocks), 64 of 64 to 2,048
         (27.1; 43.6 in two-warp blocks)."""
-        if self.decode_by_length(ctx_lens, nkv):
-            return self.BY_LENGTH
+        dealt_by_length = self.decode_by_length(ctx_lens, nkv)
+        first = self.BY_LENGTH if dealt_by_length else self.BY_REQUEST
         if not self.decode_small or hd is None or hd not in ATTENTION_HEAD_DIMS or not ctx_lens:
-            return self.BY_REQUEST
+            return first
         pairs = len(ctx_lens) * nkv
         if self._force_small and pairs > self.sm_count:
             return self._force_small
         usual = self._decode_blocks_per_sm(hd, 4)
-        if pairs <= max(usual, 1) * self.sm_count:  # (one round anyway; up to one block per SM: eight warps)
-            return self.BY_REQUEST
+        if pairs <= max(usual, 1) * self.sm_count or self.decode_balanced == "1":
+            return first  # (one round of the usual blocks anyway; up to one block per SM: eight warps)
         by_length = sorted(ctx_lens, reverse=True)
         setup = 300.0
         best, best_time = self.BY_REQUEST, 0.93 * self._by_request_estimate(
             by_length, max(1, usual * self.sm_count // nkv), 1.0, setup)
+        if dealt_by_length:  # (the smaller blocks then have to beat that kernel: 48 requests x 4,096 tokens
+            # take 75.9 us dealt by length, 64.4 in three-warp blocks)
+            best, best_time = self.BY_LENGTH, self._dealt_estimates(ctx_lens, nkv)[1]
         for warps, code in ((3, self.SMALL_3), (2, self.SMALL_2)):
             per_sm = self._decode_blocks_per_sm(hd, warps)
             if per_sm <= usual:
@@ -564,15 +567,19 @@ class CudaOps:
                 best, best_time = code, time
         return best
 
-    def decode_by_length(self, ctx_lens, nkv: int) -> bool:
-        """Whether a decode step over contexts of these lengths should use the kernel that deals
-        key tiles by length.  In tokens one block walks: dealt by request the step lasts as long
-        as the longest context over its splits (or the whole work over the blocks the device
-        runs at once, if that is more); dealt by length, the work over those blocks, plus the
-        set-up that kernel pays (measured: about 600 tokens' worth, and 15 % for second pairs in
-        a block; 50 % with more pairs than SMs)."""
-        if self.decode_balanced in ("0", "1"):
-            return self.decode_balanced == "1"
+    def _dealt_estimates(self, ctx_lens, nkv: int) -> tuple[float, float]:
+        """(dealt by request, dealt by length): how long the two decode attention kernels take for
+        contexts of these lengths, in tokens one block walks.  By request the step lasts as long as the
+        longest context over its splits, or the whole work over the blocks the device runs at once, if
+        that is more.  By length: the work over those blocks, plus the set-up that kernel pays -- up
+        to one block per SM about 600 tokens' worth and 15 % for second pairs in a block; with more
+        pairs than SMs (blocks of four warps, two to an SM) a block's equal share of the tiles lies in
+        1 + pairs / blocks stretches of different (request, head) pairs on average, and every stretch
+        costs what 768 tokens do (six tiles per warp).  Measured, us per layer, by request / by length,
+        with the estimate's answer: 24 requests x 8,192 tokens 92.8 / 74.4 (by length), 28 x 8,192 94.3 /
+        85.6 (by length), 32 x 8,192 95.4 / 97.0 (by request), 20 x 4,096 47.6 / 37.3 (by length),
+        24 x 4,096 48.0 / 41.9 (by length), 28 x 4,096 48.5 / 47.8 (by request), 24 x 2,048 25.4 / 35.0
+        (by request), 40 of 128 to 2,048 tokens 26 / 34 (by request)."""
         pairs = len(ctx_lens) * nkv
         work = sum(ctx_lens) * nkv
         longest = max(ctx_lens)
@@ -584,10 +591,17 @@ class CudaOps:
         rounds = pairs * splits / slots
         last_round = (-(-pairs * splits // slots) - rounds) * work / (pairs * splits)
         by_request = max(longest / splits, work / slots + last_round)
-        # (with more pairs than SMs that kernel runs half-size blocks, two to an SM, and stays a half
-        # behind its even share: 40 requests of 128 to 2,048 tokens took 34 us dealt by length, 26 by request)
-        behind = 1.15 if pairs <= self.sm_count else 1.5
-        return by_request > behind * work / slots + 600
+        if pairs <= self.sm_count:
+            return by_request, 1.15 * work / slots + 600
+        return by_request, work / slots + 768 * (1 + pairs / slots)
+
+    def decode_by_length(self, ctx_lens, nkv: int) -> bool:
+        """Whether a decode step over contexts of these lengths should use the kernel that deals
+        key tiles by length (:meth:`_dealt_estimates`)."""
+        if self.decode_balanced in ("0", "1"):
+            return self.decode_balanced == "1"
+        by_request, by_length = self._dealt_estimates(ctx_lens, nkv)
+        return by_request > by_length
 
     def prefill_key_split(self, blocks: int, hd: int, max_ctx_len: int) -> int:
         """Among how many blocks the tcgen05 prefill kernel shares the keys of a query tile: the

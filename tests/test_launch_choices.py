@@ -17,6 +17,7 @@ def _ops(sm_count=148, balanced="auto", split_target=128, cluster_max=8):
     ops = types.SimpleNamespace(sm_count=sm_count, decode_balanced=balanced, decode_split_target=split_target,
                                 decode_cluster_max=cluster_max, decode_cluster_tokens=4096)
     ops.decode_splits = lambda num_seqs, nkv: CudaOps.decode_splits(ops, num_seqs, nkv)
+    ops._dealt_estimates = lambda lens, nkv: CudaOps._dealt_estimates(ops, lens, nkv)
     return ops
 
 
@@ -133,6 +134,7 @@ def test_many_requests_of_one_length_run_in_small_blocks():
     fits = {(64, 4): 2, (64, 3): 3, (64, 2): 4, (128, 4): 1, (128, 3): 1, (128, 2): 2}
     ops.decode_small, ops._force_small, ops._decode_blocks_per_sm = True, 0, lambda hd, warps: fits[(hd, warps)]
     ops.decode_by_length = lambda lens, nkv: CudaOps.decode_by_length(ops, lens, nkv)
+    ops._dealt_estimates = lambda lens, nkv: CudaOps._dealt_estimates(ops, lens, nkv)
     ops._by_request_estimate = CudaOps._by_request_estimate
     for name in ("BY_REQUEST", "BY_LENGTH", "SMALL_2", "SMALL_3"):
         setattr(ops, name, getattr(CudaOps, name))
@@ -152,6 +154,10 @@ def test_many_requests_of_one_length_run_in_small_blocks():
     assert deal([rng.randint(512, 1536) for _ in range(48)]) == CudaOps.BY_REQUEST
     assert deal([rng.randint(768, 1280) for _ in range(40)]) == CudaOps.SMALL_3
     assert deal([256] * 39 + [32768]) == CudaOps.BY_LENGTH
+    # long contexts, more pairs than SMs but fewer than block slots: the blocks' shares by length are more even
+    assert deal([8192] * 24) == CudaOps.BY_LENGTH and deal([4096] * 24) == CudaOps.BY_LENGTH
+    assert deal([8192] * 32) == CudaOps.BY_REQUEST and deal([4096] * 28) == CudaOps.BY_REQUEST and deal([2048] * 24) == CudaOps.BY_REQUEST
+    assert deal([4096] * 48) == CudaOps.SMALL_3   # (by length would beat the four-warp blocks' two rounds, not these)
     # the estimate itself: whole rounds for one length; else every later request starts as one of the round before ends
     est = CudaOps._by_request_estimate
     assert est([1000] * 80, 37, 1.0, 300.0) == 3 * 1300

@@ -541,7 +541,7 @@ class CudaOps:
         96.4 -> 90.4, 64 x 256 10.4 -> 8.3, 40 of 768 to 1,280 tokens 22.1 -> 19.8; kept in four-warp blocks,
         the longest first: 48 of 512 to 1,536 tokens (19.5; 23.1 in three-warp blocks), 64 of 64 to 2,048
         (27.1; 43.6 in two-warp blocks)."""
-        dealt_by_length = self.decode_by_length(ctx_lens, nkv)
+        dealt_by_length = self.decode_by_length(ctx_lens, nkv, hd)
         first = self.BY_LENGTH if dealt_by_length else self.BY_REQUEST
         if not self.decode_small or hd is None or hd not in ATTENTION_HEAD_DIMS or not ctx_lens:
             return first
@@ -557,7 +557,7 @@ class CudaOps:
             by_length, max(1, usual * self.sm_count // nkv), 1.0, setup)
         if dealt_by_length:  # (the smaller blocks then have to beat that kernel: 48 requests x 4,096 tokens
             # take 75.9 us dealt by length, 64.4 in three-warp blocks)
-            best, best_time = self.BY_LENGTH, self._dealt_estimates(ctx_lens, nkv)[1]
+            best, best_time = self.BY_LENGTH, self._dealt_estimates(ctx_lens, nkv, hd)[1]
         for warps, code in ((3, self.SMALL_3), (2, self.SMALL_2)):
             per_sm = self._decode_blocks_per_sm(hd, warps)
             if per_sm <= usual:
@@ -567,40 +567,54 @@ class CudaOps:
                 best, best_time = code, time
         return best
 
-    def _dealt_estimates(self, ctx_lens, nkv: int) -> tuple[float, float]:
+    def _dealt_estimates(self, ctx_lens, nkv: int, hd: int | None = None) -> tuple[float, float]:
         """(dealt by request, dealt by length): how long the two decode attention kernels take for
-        contexts of these lengths, in tokens one block walks.  By request the step lasts as long as the
-        longest context over its splits, or the whole work over the blocks the device runs at once, if
-        that is more.  By length: the work over those blocks, plus the set-up that kernel pays -- up
-        to one block per SM about 600 tokens' worth and 15 % for second pairs in a block; with more
-        pairs than SMs (blocks of four warps, two to an SM) a block's equal share of the tiles lies in
-        1 + pairs / blocks stretches of different (request, head) pairs on average, and every stretch
-        costs what 768 tokens do (six tiles per warp).  Measured, us per layer, by request / by length,
-        with the estimate's answer: 24 requests x 8,192 tokens 92.8 / 74.4 (by length), 28 x 8,192 94.3 /
-        85.6 (by length), 32 x 8,192 95.4 / 97.0 (by request), 20 x 4,096 47.6 / 37.3 (by length),
-        24 x 4,096 48.0 / 41.9 (by length), 28 x 4,096 48.5 / 47.8 (by request), 24 x 2,048 25.4 / 35.0
-        (by request), 40 of 128 to 2,048 tokens 26 / 34 (by request)."""
+        contexts of these lengths, in tokens one block walks (a block of eight warps up to one (request,
+        head) pair per SM, of four warps, two to an SM, beyond).  By request the step lasts as long as
+        the longest context over its splits (twice that where the splits make more blocks than SMs:
+        those blocks have four warps; and a set-up more where they merge through memory), or the whole
+        work over the blocks the device runs at once, if that is more.  By length: the work over those
+        blocks, plus that kernel's set-ups: a block's equal share of the tiles lies in 1 + pairs / blocks
+        stretches of different (request, head) pairs on average, and every stretch costs what six tiles
+        per warp do (1,536 tokens for a block of eight warps, 768 for one of four).  Measured, us per
+        layer, by request / by length, with the estimate's answer: 12 requests x 4,096 tokens 25.8 / 33.4
+        (by request), 11 x 2,048 12.8 / 19.5 (by request), 7 x 32,768 98.7 / 85.9 (by length), 10 x 8,192
+        41.0 / 36.4 (by length), 24 x 8,192 92.8 / 74.4 (by length), 28 x 8,192 94.3 / 85.6 (by length),
+        32 x 8,192 95.4 / 97.0 (by request), 20 x 4,096 47.6 / 37.3 (by length), 24 x 4,096 48.0 / 41.9 (by
+        length), 28 x 4,096 48.5 / 47.8 (by request), 24 x 2,048 25.4 / 35.0 (by request), 40 of 128 to
+        2,048 tokens 26 / 34 (by request); 14 x 8,192 49.5 / 47.1 is answered by request."""
         pairs = len(ctx_lens) * nkv
         work = sum(ctx_lens) * nkv
         longest = max(ctx_lens)
         slots = self.sm_count if pairs <= self.sm_count else 2 * self.sm_count
-        splits = self.decode_splits(len(ctx_lens), nkv)
+        table_tokens = 1024  # (what the step's block tables hold: widths double from 64 pages of 16 tokens)
+        while table_tokens < longest:
+            table_tokens *= 2
+        splits = self.decode_splits(len(ctx_lens), nkv, table_tokens, hd)
         # blocks run in rounds over the slots; the last round is as long as a block even when few
         # blocks are in it (40 requests x 8 heads of 4,096 tokens, 320 blocks on 296 slots: 93 us by
         # request, 65 us by length)
-        rounds = pairs * splits / slots
-        last_round = (-(-pairs * splits // slots) - rounds) * work / (pairs * splits)
-        by_request = max(longest / splits, work / slots + last_round)
         if pairs <= self.sm_count:
-            return by_request, 1.15 * work / slots + 600
-        return by_request, work / slots + 768 * (1 + pairs / slots)
+            stretch = 1536
+            by_request = longest / splits
+            if pairs * splits > self.sm_count:   # (the splits' blocks have four warps)
+                by_request = 2 * by_request * -(-pairs * splits // (2 * self.sm_count))
+            if splits not in (1, 2, 4, 8):       # (merged through memory by the block that ends last)
+                by_request += stretch
+            by_request = max(by_request, work / slots)
+        else:
+            stretch = 768
+            rounds = pairs * splits / slots
+            last_round = (-(-pairs * splits // slots) - rounds) * work / (pairs * splits)
+            by_request = max(longest / splits, work / slots + last_round)
+        return by_request, work / slots + stretch * (1 + pairs / slots)
 
-    def decode_by_length(self, ctx_lens, nkv: int) -> bool:
+    def decode_by_length(self, ctx_lens, nkv: int, hd: int | None = None) -> bool:
         """Whether a decode step over contexts of these lengths should use the kernel that deals
         key tiles by length (:meth:`_dealt_estimates`)."""
         if self.decode_balanced in ("0", "1"):
             return self.decode_balanced == "1"
-        by_request, by_length = self._dealt_estimates(ctx_lens, nkv)
+        by_request, by_length = self._dealt_estimates(ctx_lens, nkv, hd)
         return by_request > by_length
 
     def prefill_key_split(self, blocks: int, hd: int, max_ctx_len: int) -> int:

@@ -16,8 +16,8 @@ from inference_engine_b200.kernels.cuda_ops import CudaOps
 def _ops(sm_count=148, balanced="auto", split_target=128, cluster_max=8):
     ops = types.SimpleNamespace(sm_count=sm_count, decode_balanced=balanced, decode_split_target=split_target,
                                 decode_cluster_max=cluster_max, decode_cluster_tokens=4096)
-    ops.decode_splits = lambda num_seqs, nkv: CudaOps.decode_splits(ops, num_seqs, nkv)
-    ops._dealt_estimates = lambda lens, nkv: CudaOps._dealt_estimates(ops, lens, nkv)
+    ops.decode_splits = lambda num_seqs, nkv, table_tokens=0, hd=None: CudaOps.decode_splits(ops, num_seqs, nkv, table_tokens, hd)
+    ops._dealt_estimates = lambda lens, nkv, hd=None: CudaOps._dealt_estimates(ops, lens, nkv, hd)
     return ops
 
 
@@ -70,6 +70,10 @@ def test_work_is_dealt_by_length_only_where_that_pays():
     assert by_length([4096] * 40)
     assert not by_length([4096] * 36)               # 288 blocks on 296 slots
     assert not by_length([1024] * 48) and not by_length([1024] * 64)
+    # up to one pair per SM: that kernel's blocks start again for every stretch of another pair
+    assert not by_length([4096] * 12) and not by_length([2048] * 11)
+    assert by_length([32768] * 7) and by_length([8192] * 10) and by_length([32768, 256, 256, 256])
+    assert not by_length([8192] * 16) and not by_length([4096] * 18)
     # the switch overrides the estimate
     assert CudaOps.decode_by_length(_ops(balanced="1"), [1024] * 8, 8)
     assert not CudaOps.decode_by_length(_ops(balanced="0"), [32768] + [256] * 31, 8)
@@ -133,8 +137,8 @@ def test_many_requests_of_one_length_run_in_small_blocks():
     ops = _ops()
     fits = {(64, 4): 2, (64, 3): 3, (64, 2): 4, (128, 4): 1, (128, 3): 1, (128, 2): 2}
     ops.decode_small, ops._force_small, ops._decode_blocks_per_sm = True, 0, lambda hd, warps: fits[(hd, warps)]
-    ops.decode_by_length = lambda lens, nkv: CudaOps.decode_by_length(ops, lens, nkv)
-    ops._dealt_estimates = lambda lens, nkv: CudaOps._dealt_estimates(ops, lens, nkv)
+    ops.decode_by_length = lambda lens, nkv, hd=None: CudaOps.decode_by_length(ops, lens, nkv, hd)
+    ops._clusters_at_once = lambda hd, parts: 0
     ops._by_request_estimate = CudaOps._by_request_estimate
     for name in ("BY_REQUEST", "BY_LENGTH", "SMALL_2", "SMALL_3"):
         setattr(ops, name, getattr(CudaOps, name))

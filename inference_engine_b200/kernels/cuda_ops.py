@@ -573,16 +573,15 @@ class CudaOps:
         head) pair per SM, of four warps, two to an SM, beyond).  By request the step lasts as long as
         the longest context over its splits (twice that where the splits make more blocks than SMs:
         those blocks have four warps; and a set-up more where they merge through memory), or the whole
-        work over the blocks the device runs at once, if that is more.  By length: the work over those
-        blocks, plus that kernel's set-ups: a block's equal share of the tiles lies in 1 + pairs / blocks
-        stretches of different (request, head) pairs on average, and every stretch costs what six tiles
-        per warp do (1,536 tokens for a block of eight warps, 768 for one of four).  Measured, us per
+        work over the blocks the device runs at once, if that is more.  By length: what that kernel's own
+        dealing gives the slowest block (below).  Measured, us per
         layer, by request / by length, with the estimate's answer: 12 requests x 4,096 tokens 25.8 / 33.4
         (by request), 11 x 2,048 12.8 / 19.5 (by request), 7 x 32,768 98.7 / 85.9 (by length), 10 x 8,192
         41.0 / 36.4 (by length), 24 x 8,192 92.8 / 74.4 (by length), 28 x 8,192 94.3 / 85.6 (by length),
         32 x 8,192 95.4 / 97.0 (by request), 20 x 4,096 47.6 / 37.3 (by length), 24 x 4,096 48.0 / 41.9 (by
         length), 28 x 4,096 48.5 / 47.8 (by request), 24 x 2,048 25.4 / 35.0 (by request), 40 of 128 to
-        2,048 tokens 26 / 34 (by request); 14 x 8,192 49.5 / 47.1 is answered by request."""
+        2,048 tokens 26 / 34 (by request), 9 x 4,096 25.1 / 18.5 (by length: two pieces per pair, one
+        round); 14 x 8,192 49.5 / 47.1 is answered by request."""
         pairs = len(ctx_lens) * nkv
         work = sum(ctx_lens) * nkv
         longest = max(ctx_lens)
@@ -595,19 +594,32 @@ class CudaOps:
         # blocks are in it (40 requests x 8 heads of 4,096 tokens, 320 blocks on 296 slots: 93 us by
         # request, 65 us by length)
         if pairs <= self.sm_count:
-            stretch = 1536
             by_request = longest / splits
             if pairs * splits > self.sm_count:   # (the splits' blocks have four warps)
                 by_request = 2 * by_request * -(-pairs * splits // (2 * self.sm_count))
             if splits not in (1, 2, 4, 8):       # (merged through memory by the block that ends last)
-                by_request += stretch
+                by_request += 1536
             by_request = max(by_request, work / slots)
         else:
-            stretch = 768
             rounds = pairs * splits / slots
             last_round = (-(-pairs * splits // slots) - rounds) * work / (pairs * splits)
             by_request = max(longest / splits, work / slots + last_round)
-        return by_request, work / slots + stretch * (1 + pairs / slots)
+        # By length, as that kernel deals (attention_mma.cu): every pair's tiles in pieces of about an
+        # even share, dealt in rounds over the blocks, or, where the pieces would leave the slowest block
+        # well behind, equal ranges of the list of all tiles, which lie in 1 + pairs / blocks stretches
+        # of different pairs on average.  A piece or stretch costs six tiles per warp to set up.
+        warps, keys = (8 if pairs <= self.sm_count else 4), 32
+        tiles = [-(-c // keys) for c in ctx_lens]
+        share = max(-(-sum(tiles) * nkv // slots), warps)
+        pieces = [max(1, min((n + share // 2) // share, n // warps)) for n in tiles]
+        largest = max(-(-n // k) for n, k in zip(tiles, pieces))
+        piece_rounds = -(-sum(pieces) * nkv // slots)
+        setup = 6 * warps
+        if piece_rounds * largest > share + setup:
+            by_length = share + setup * (1 + pairs / slots)
+        else:  # (the blocks that take a second piece are few when the pieces are few more than the blocks)
+            by_length = max(1.0, sum(pieces) * nkv / slots) * (largest + setup)
+        return by_request, by_length * keys
 
     def decode_by_length(self, ctx_lens, nkv: int, hd: int | None = None) -> bool:
         """Whether a decode step over contexts of these lengths should use the kernel that deals

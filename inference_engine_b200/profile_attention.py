@@ -4,6 +4,7 @@ the fraction of a memory bandwidth at which it reads the keys and values it must
     python -m inference_engine_b200.profile_attention --cases 8x1024,64x1024,64x4096,16x16384,1x32768
     IE_B200_DECODE_NARROW=0 python -m inference_engine_b200.profile_attention   # the 16-row layout for all
     python -m inference_engine_b200.profile_attention --cases 32x128-4352       # 32 contexts of 128 to 4,352 tokens
+    python -m inference_engine_b200.profile_attention --cases 8000+7*500        # one of 8,000 tokens and seven of 500
     IE_B200_DECODE_BALANCED=0 python -m inference_engine_b200.profile_attention --cases 32x128-4352   # dealt by request
 
 Every request brings one token.  ``BxL`` is B requests of L cached tokens, ``BxL1-L2`` B requests whose lengths
@@ -78,9 +79,18 @@ def main() -> int:
         return q, k, v, tables, ctx
 
     for item in args.cases.split(","):
-        count, length = item.lower().split("x")
-        batch = int(count)
-        if "-" in length:
+        if "+" in item:  # the lengths themselves, and "7*500" for seven of one length
+            lengths = []
+            for part in item.split("+"):
+                times, _, n = part.rpartition("*")
+                lengths += [int(n)] * (int(times) if times else 1)
+            batch, length = len(lengths), item
+        else:
+            count, length = item.lower().split("x")
+            batch = int(count)
+        if "+" in item:
+            pass
+        elif "-" in length:
             low, high = (int(x) for x in length.split("-"))
             lengths = torch.randint(low, high + 1, (batch,), generator=torch.Generator().manual_seed(0)).tolist()
         else:

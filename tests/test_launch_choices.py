@@ -74,6 +74,7 @@ def test_work_is_dealt_by_length_only_where_that_pays():
     assert not by_length([4096] * 12) and not by_length([2048] * 11)
     assert by_length([32768] * 7) and by_length([8192] * 10) and by_length([32768, 256, 256, 256])
     assert not by_length([8192] * 16) and not by_length([4096] * 18)
+    assert by_length([4096] * 9)   # 72 pairs on 148 SMs: two pieces per pair, all at once
     # the switch overrides the estimate
     assert CudaOps.decode_by_length(_ops(balanced="1"), [1024] * 8, 8)
     assert not CudaOps.decode_by_length(_ops(balanced="0"), [32768] + [256] * 31, 8)

@@ -333,13 +333,14 @@ class CudaOps:
         over 8 slices of k it takes 8.5 us (measured, 1B shape, us: down at 17 / 64 / 256 / 512 rows
         13.0 / 13.2 / 13.8 / 18.9 -> 8.1 / 8.5 / 10.6 / 15.4; output projection at 17 / 64 rows 5.6 / 5.8
         -> 4.4 / 4.8; QKV 5.8 -> 5.0; products with many output features, gate-up and the head, lose).
-        A power of two, at most 8, with slices of at least 512; up to 512 rows (beyond that no shape
-        gains)."""
+        A power of two, at most 8 (4 beyond 64 rows), with slices of at least 512; up to 512 rows (beyond
+        that no shape gains)."""
         if not self.blas_split_k or m > 512:
             return 1
         blocks = -(-m // 128) * -(-n // 128)
         parts = 1
-        while parts * 2 <= min(self.sm_count / blocks, 8) and k % (parts * 2 * 64) == 0 and k // (parts * 2) >= 512:
+        most = 8 if m <= 64 else 4  # (96 rows of the down projection: 9.6 us in 8 parts, 8.6 in 4; 128 rows 9.9 and 9.4)
+        while parts * 2 <= min(self.sm_count / blocks, most) and k % (parts * 2 * 64) == 0 and k // (parts * 2) >= 512:
             parts *= 2
         if parts < 2 or (parts < 4 and k < 4096):
             return 1

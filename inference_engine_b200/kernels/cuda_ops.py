@@ -368,10 +368,10 @@ class CudaOps:
         # The weight-streaming kernel pays where the library leaves SMs idle: few output
         # features (fewer 16-feature blocks than SMs) and a long inner dimension to split.
         few_rows = 0 < m <= self.FEW_ROWS and k % 8 == 0 and x.is_contiguous() and w.is_contiguous()
-        splittable = (allow_split and out is None and out_dtype == torch.float32 and m > 8
+        splittable = (allow_split and out is None and out_dtype == torch.float32 and m > 0
                       and x.is_contiguous() and w.is_contiguous())
         library_parts = self.blas_split(m, n, k) if splittable else 1
-        if few_rows and library_parts > 1 and k >= 4096:
+        if few_rows and m > 8 and library_parts > 1 and k >= 4096:
             few_rows = False  # (9 to 16 rows, long inner dimension: the batched library product is ahead, 8.0 against 9.5 us)
         if (few_rows and self.few_row_gemm == "tma"
                 and -(-n // 128) <= (self.tma_max_tiles if m <= 8 else self.tma_max_tiles_wide)):

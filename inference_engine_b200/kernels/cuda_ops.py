@@ -333,17 +333,18 @@ class CudaOps:
         over 8 slices of k it takes 8.5 us (measured, 1B shape, us: down at 17 / 64 / 256 / 512 rows
         13.0 / 13.2 / 13.8 / 18.9 -> 8.1 / 8.5 / 10.6 / 15.4; output projection at 17 / 64 rows 5.6 / 5.8
         -> 4.4 / 4.8; QKV 5.8 -> 5.0; products with many output features, gate-up and the head, lose).
-        A power of two, at most 8 (4 beyond 64 rows), with slices of at least 512; up to 512 rows (beyond
-        that no shape gains)."""
+        A power of two: at most 8 up to 32 rows, 4 up to 256, 2 up to 512 (the parts' sums are written and
+        read again: 96 rows of the down projection take 9.6 us in 8 parts, 8.6 in 4); no more parts than
+        bring the library's blocks to about 1.2 per SM; slices of at least 256.  The rule was set against
+        `profile_gemm`'s tables of the 1B, 3B and 8B shapes' products at 9 to 512 rows: it is 0.6 %, 1.4 %
+        and 1.8 % behind the best of 1, 2, 4, 8 parts on average, 4 %, 8 % and 15 % at worst."""
         if not self.blas_split_k or m > 512:
             return 1
         blocks = -(-m // 128) * -(-n // 128)
         parts = 1
-        most = 8 if m <= 64 else 4  # (96 rows of the down projection: 9.6 us in 8 parts, 8.6 in 4; 128 rows 9.9 and 9.4)
-        while parts * 2 <= min(self.sm_count / blocks, most) and k % (parts * 2 * 64) == 0 and k // (parts * 2) >= 512:
+        most = 8 if m <= 32 else 4 if m <= 256 else 2
+        while parts * 2 <= min(1.2 * self.sm_count / blocks, most) and k % (parts * 2 * 64) == 0 and k // (parts * 2) >= 256:
             parts *= 2
-        if parts < 2 or (parts < 4 and k < 4096):
-            return 1
         return parts
 
     @_kind(lambda kwargs: "linear:" + kwargs.get("tag", "linear"))
@@ -371,8 +372,10 @@ class CudaOps:
         splittable = (allow_split and out is None and out_dtype == torch.float32 and m > 0
                       and x.is_contiguous() and w.is_contiguous())
         library_parts = self.blas_split(m, n, k) if splittable else 1
-        if few_rows and m > 8 and library_parts > 1 and k >= 4096:
-            few_rows = False  # (9 to 16 rows, long inner dimension: the batched library product is ahead, 8.0 against 9.5 us)
+        if few_rows and m > 8 and library_parts > 1 and (k >= 4096 or n * k >= 12 << 20):
+            # (9 to 16 rows, a long inner dimension or a large matrix: the batched library product is ahead,
+            # 8.0 against 9.5 us on the 1B shape's down projection, 7.9 against 9.1 on the 3B shape's QKV)
+            few_rows = False
         if (few_rows and self.few_row_gemm == "tma"
                 and -(-n // 128) <= (self.tma_max_tiles if m <= 8 else self.tma_max_tiles_wide)):
             kbps, splits = self.tma_split(n, k) if allow_split and out is None else (-(-k // 64), 1)

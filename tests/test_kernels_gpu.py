@@ -232,8 +232,9 @@ def test_narrow_products_are_cut_along_k_for_the_library(ops, m, n, k):
     want = x.double() @ w.double().t()
     ws = Workspace("cuda")
     parts = ops.blas_split(m, n, k)
-    assert parts in (1, 2, 4, 8) and (parts == 1 or (k // parts >= 512 and k % parts == 0))
-    assert ops.blas_split(64, 2048, 8192) == 8 and ops.blas_split(256, 2048, 8192) == 4 and ops.blas_split(512, 2048, 8192) == 2 and ops.blas_split(513, 2048, 8192) == 1
+    assert parts in (1, 2, 4, 8) and (parts == 1 or (k // parts >= 256 and k % parts == 0))
+    assert ops.blas_split(32, 2048, 8192) == 8 and ops.blas_split(64, 2048, 8192) == 4 and ops.blas_split(256, 2048, 8192) == 4
+    assert ops.blas_split(512, 2048, 8192) == 2 and ops.blas_split(513, 2048, 8192) == 1
     assert ops.blas_split(64, 16384, 2048) == 1 and ops.blas_split(2048, 2048, 8192) == 1
     got = ops.linear(x, w, ws=ws, tag="t", out_dtype=torch.float32, allow_split=True)
     if parts > 1 and not (m <= 16 and k < 4096):

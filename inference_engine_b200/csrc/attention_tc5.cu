@@ -51,7 +51,9 @@ constexpr int THREADS = SPLIT_ISSUE ? 224 : 192;  // + the copy warp and the ten
 constexpr int KV_STAGES = HD == 64 ? 3 : 4;   // head size 128: 132 KB of shared memory, one block per SM as its tensor memory asks
 constexpr int KV_BYTES = KT * HD * 2;       // K (and as much V) of a stage: HALVES tiles of 64 keys x 64 dims, 8 KB each
 constexpr int HALF_BYTES = KT * 128;
-constexpr int MAX_TABLE = 1024;             // block-table entries cached in shared memory
+// block-table entries a block keeps in shared memory (a late query tile needs the request's whole table: 131,072
+// tokens in pages of 16; 32 KB of the 80 KB a block of head size 64 takes, two blocks to an SM)
+constexpr int MAX_TABLE = 8192;
 // tensor memory: S (then P, packed) in columns 0..63 and 64..127, O in the next HD, Q (two dims to a
 // column) in the next HD / 2: 224 columns for head size 64 (two blocks per SM), 320 for 128 (one)
 constexpr int TMEM_COLS = HD == 64 ? 256 : 512;
@@ -643,7 +645,7 @@ IE_API int ie_tc5_timing(long long* out, int reset) {
 IE_API int ie_attention_prefill_tc5_ok(int page_size, int max_ctx) {
     if (encode_fn() == nullptr) return 0;
     if (page_size < 8 || page_size > KT || (page_size & (page_size - 1)) != 0) return 0;
-    return (max_ctx + KT) / page_size <= MAX_TABLE ? 1 : 0;
+    return ((max_ctx + KT - 1) / KT * KT + page_size - 1) / page_size <= MAX_TABLE ? 1 : 0;  // (whole key tiles)
 }
 
 // Floats of scratch for `ksplit` > 1: a partial result per (work item, head, share of the keys).

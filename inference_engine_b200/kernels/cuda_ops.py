@@ -752,6 +752,12 @@ class CudaOps:
             # every tile are shared among several blocks instead.
             ksplit = self.prefill_key_split(tiles * nh, hd, max_ctx) if self.prefill_key_splits and not fixed else 1
             paired = not fixed and ksplit == 1 and tiles * nh <= self.prefill_paired_max * self.sm_count
+            # (portions at the end of long contexts: their tiles see about as many keys each, and pairs
+            # would only halve the blocks where those do not fill the device anyway: two 512-token
+            # portions at 65,536 tokens took 1,602 us in 128 blocks of two tiles, 944 in 256 of one)
+            slots = self.sm_count * (2 if hd == 64 else 1)
+            if paired and ctx.max_ctx_len >= 2 * max(ctx.q_lens) and plan["tile_pairs"] * nh < slots:
+                paired = False
             if paired:
                 tiles = plan["tile_pairs"]
             scratch = tickets = None

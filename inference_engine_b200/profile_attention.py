@@ -7,7 +7,8 @@ the fraction of a memory bandwidth at which it reads the keys and values it must
     python -m inference_engine_b200.profile_attention --cases 8000+7*500        # one of 8,000 tokens and seven of 500
     IE_B200_DECODE_BALANCED=0 python -m inference_engine_b200.profile_attention --cases 32x128-4352   # dealt by request
 
-Every request brings one token.  ``BxL`` is B requests of L cached tokens, ``BxL1-L2`` B requests whose lengths
+Every request brings one token (``--portion T``: its last T tokens, a prompt portion for the prefill kernel; the row
+then gives TFLOP/s).  ``BxL`` is B requests of L cached tokens, ``BxL1-L2`` B requests whose lengths
 are drawn evenly from L1 to L2 (seeded); which of the two decode kernels runs is the engine's own choice
 (``CudaOps.decode_dealing``) unless ``IE_B200_DECODE_BALANCED`` (by length: 0, 1) or ``IE_B200_DECODE_SMALL`` (no blocks of 2 or 3 warps: 0) says otherwise.  A launch stands for one layer of a step: it runs on a cache of its own
 (several caches, together larger than L2, taken in turn), block tables point at shuffled pages.  The launches
@@ -43,6 +44,8 @@ def main() -> int:
     ap.add_argument("--window", type=int, default=0)
     ap.add_argument("--peak-gbs", type=float, default=None)
     ap.add_argument("--caches", type=int, default=0, help="caches taken in turn (default: 2 to 8, about 1 GB in all)")
+    ap.add_argument("--portion", type=int, default=1,
+                    help="tokens every request brings, the last of its context (more than 16 / heads per group: the prefill kernel)")
     args = ap.parse_args()
 
     import torch
@@ -66,13 +69,14 @@ def main() -> int:
             at += n
         k = torch.randn(total, nkv, ps, hd, device="cuda").bfloat16()
         v = torch.randn_like(k)
-        q = torch.randn(batch, nh * hd, device="cuda").bfloat16()
-        ragged = int(ops.decode_dealing(lengths, nkv, hd)) if batch > 1 else 0
+        t = args.portion
+        q = torch.randn(batch * t, nh * hd, device="cuda").bfloat16()
+        ragged = int(ops.decode_dealing(lengths, nkv, hd)) if batch > 1 and t == 1 else 0
         ctx = types.SimpleNamespace(
-            num_tokens=batch, num_seqs=batch, q_lens=[1] * batch, max_q_len=1, max_ctx_len=max(lengths), ws=ws,
-            positions=torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device="cuda"),
-            seq_of_token=torch.arange(batch, dtype=torch.int32, device="cuda"),
-            cu_q=torch.arange(batch + 1, dtype=torch.int32, device="cuda"),
+            num_tokens=batch * t, num_seqs=batch, q_lens=[t] * batch, max_q_len=t, max_ctx_len=max(lengths), ws=ws,
+            positions=torch.tensor([n - t + i for n in lengths for i in range(t)], dtype=torch.int32, device="cuda"),
+            seq_of_token=torch.arange(batch, dtype=torch.int32, device="cuda").repeat_interleave(t),
+            cu_q=torch.arange(batch + 1, dtype=torch.int32, device="cuda") * t,
             ctx_lens=torch.tensor(lengths, dtype=torch.int32, device="cuda"), ragged=(ragged,),
             # (as the engine packs a step: the by-request kernel starts the longest requests' blocks first)
             decode_order=torch.tensor(sorted(range(batch), key=lambda i: -lengths[i]), dtype=torch.int32, device="cuda"))
@@ -128,7 +132,11 @@ def main() -> int:
         gbs = kv_bytes / best / 1e3
         row = {"requests": batch, "context": length, "dealt": ("by request", "by length", "by request, 2-warp blocks", "by request, 3-warp blocks")[cases[0][4].ragged[0]], "us": round(best, 2), "gbs": round(gbs, 1),
                "caches": len(cases), "kv_mb_per_launch": round(kv_bytes / 1e6, 1)}
-        if peak:
+        if args.portion > 1:  # (a portion's cost is its products: two per query and visible key, 2 hd flops each)
+            seen = sum(min(n - args.portion + i + 1, args.window or n) for n in lengths for i in range(args.portion))
+            row = {"requests": batch, "context": length, "portion": args.portion, "us": round(best, 2),
+                   "tflops": round(4 * hd * nh * seen / best / 1e6, 1), "caches": len(cases)}
+        elif peak:
             row["frac"] = round(gbs / peak, 3)
         print(json.dumps(row), flush=True)
         del cases, graph

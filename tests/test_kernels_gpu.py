@@ -435,6 +435,30 @@ def test_decode_attention_with_many_splits_is_the_same_as_one(ops):
     torch.testing.assert_close(got.float(), want.float(), atol=1e-2, rtol=1e-2)
 
 
+@pytest.mark.parametrize("nh,nkv,hd,ps", [(4, 2, 64, 16), (2, 1, 128, 16)])
+@pytest.mark.parametrize("far", [True, False])
+def test_prefill_attention_over_a_long_context(ops, nh, nkv, hd, ps, far):
+    """Prompt portions at the end of contexts of 40,000 and 20,500 tokens (2,500 block-table entries:
+    a late query tile needs them all).  One key per request stands out, near the context's start or
+    24,000 tokens in: the output must be that key's value, whichever page it lies in."""
+    ctx_lens, q_lens = [40000, 20500], [300, 140]
+    spike = [77, 1031] if far else [24000, 20400]
+    q, k, v, tables, ctx = _attention_case(nh, nkv, hd, ps, q_lens, ctx_lens, torch.bfloat16, seed=21, spike=spike)
+    got = torch.empty_like(q)
+    before = ops.launch_counts.get("attention_prefill_tc5", 0)
+    ops.paged_attention(q, k, v, tables, ctx, nh, nkv, hd, ps, hd ** -0.5, 0, got)
+    assert ops.launch_counts.get("attention_prefill_tc5", 0) == before + 1  # (the tcgen05 kernel, not the fallback)
+    want = torch.empty_like(q)
+    RefOps().paged_attention(q, k, v, tables, ctx, nh, nkv, hd, ps, hd ** -0.5, 0, want)
+    torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+    # (the output is that key's value)
+    for i, (key_pos, last) in enumerate(zip(spike, (q_lens[0] - 1, sum(q_lens) - 1))):  # (a request's last token sees every key)
+        page, off = int(tables[i, key_pos // ps]), key_pos % ps
+        value = v[page, :, off].float().repeat_interleave(nh // nkv, dim=0).reshape(-1)
+        torch.testing.assert_close(got[last].float(), value, atol=3e-2, rtol=3e-2)
+    ops.check_errors()
+
+
 @pytest.mark.parametrize("nh,nkv,hd,ps", [(32, 8, 64, 16), (8, 2, 128, 16), (5, 5, 48, 4)])
 def test_decode_attention_starts_the_requests_blocks_in_a_given_order(ops, nh, nkv, hd, ps, monkeypatch):
     """The by-request decode attention takes the order in which the requests' blocks start (the

@@ -169,45 +169,98 @@ struct __align__(8) Barriers {
 // The last block of a tile and head merges the shares of the tile's keys that `ksplit` blocks
 // left in scratch, in their order: one thread per query row.  Kept out of line: inlined, its
 // registers slowed the kernel's main path down.
-__device__ __noinline__ void merge_key_shares(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                              size_t first, int ksplit, bf16* __restrict__ orow) {
-    __threadfence();
-    float m_all = -INFINITY;
-    for (int z = 0; z < ksplit; ++z) m_all = fmaxf(m_all, __ldcg(part_ml + (first + (size_t)z * BM) * 2));
-    float m_safe = (m_all == -INFINITY) ? 0.f : m_all;
-    float l_all = 0.f;
-    for (int z = 0; z < ksplit; ++z) {
-        size_t p = first + (size_t)z * BM;
-        l_all += __ldcg(part_ml + p * 2 + 1) * exp2f(__ldcg(part_ml + p * 2) - m_safe);
-    }
-    float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
+template <int C>
+__device__ __forceinline__ void merge_rows(const float* __restrict__ part_o, size_t first, int ksplit,
+                                           bf16* __restrict__ out0, size_t row_stride, int rows,
+                                           const float* __restrict__ factor_s, int tid) {
+    constexpr int TPR = HD / 4;               // threads per row
+    constexpr int ROWS_AT_ONCE = SOFTMAX_THREADS / TPR;
+    constexpr int U = 16 / C;                 // row groups at a time
+    int d4 = tid % TPR, r0 = tid / TPR;
 #pragma unroll 1
-    for (int half = 0; half < HD / 32; ++half) {
-        float acc[32];
+    for (int rb = 0; rb < BM; rb += U * ROWS_AT_ONCE) {
+        float4 acc[U];
 #pragma unroll
-        for (int d = 0; d < 32; ++d) acc[d] = 0.f;
-        for (int z = 0; z < ksplit; ++z) {
-            size_t p = first + (size_t)z * BM;
-            float f = exp2f(__ldcg(part_ml + p * 2) - m_safe);
-            const float4* src = reinterpret_cast<const float4*>(part_o + p * HD + half * 32);
+        for (int u = 0; u < U; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int z0 = 0; z0 < ksplit; z0 += C) {
+            float4 v[U][C];
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                float4 v = __ldcg(src + c);
-                acc[4 * c] += v.x * f; acc[4 * c + 1] += v.y * f;
-                acc[4 * c + 2] += v.z * f; acc[4 * c + 3] += v.w * f;
-            }
+            for (int u = 0; u < U; ++u)
+#pragma unroll
+                for (int j = 0; j < C; ++j) {
+                    int row = rb + u * ROWS_AT_ONCE + r0;
+                    bool in = z0 + j < ksplit;
+                    size_t p = first + (size_t)(in ? z0 + j : 0) * BM + row;
+                    v[u][j] = in ? __ldcg(reinterpret_cast<const float4*>(part_o + p * HD) + d4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+#pragma unroll
+                for (int j = 0; j < C; ++j)    // (in the shares' order)
+                    if (z0 + j < ksplit) {
+                        float f = factor_s[(z0 + j) * BM + rb + u * ROWS_AT_ONCE + r0];
+                        acc[u].x += v[u][j].x * f; acc[u].y += v[u][j].y * f;
+                        acc[u].z += v[u][j].z * f; acc[u].w += v[u][j].w * f;
+                    }
         }
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            unsigned w[4];
-#pragma unroll
-            for (int h = 0; h < 4; ++h) {
-                __nv_bfloat162 pk = __floats2bfloat162_rn(acc[c * 8 + 2 * h] * inv, acc[c * 8 + 2 * h + 1] * inv);
-                w[h] = *reinterpret_cast<unsigned*>(&pk);
+        for (int u = 0; u < U; ++u) {
+            int row = rb + u * ROWS_AT_ONCE + r0;
+            if (row < rows) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(acc[u].x, acc[u].y), hi = __floats2bfloat162_rn(acc[u].z, acc[u].w);
+                *reinterpret_cast<uint2*>(out0 + (size_t)row * row_stride + d4 * 4) =
+                    make_uint2(*reinterpret_cast<unsigned*>(&lo), *reinterpret_cast<unsigned*>(&hi));
             }
-            *reinterpret_cast<uint4*>(orow + half * 32 + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
         }
     }
+}
+
+__device__ __noinline__ void merge_key_shares(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                              size_t first, int ksplit, bf16* __restrict__ out0, size_t row_stride,
+                                              int rows, float* __restrict__ factor_s, int tid) {
+    // Called by the 128 softmax threads of the block that ends last.  `first`: the pair's first row in
+    // scratch (share z's row r at first + z * BM + r); `out0`: the tile's first output row of this head.
+    // 1. A thread per row: the shares' maxima and sums (eight shares' loads in flight at a time) give
+    //    every share's factor exp2(m_z - m) / l for the row, left in shared memory.
+    __threadfence();
+    {
+        size_t at = first + tid;
+        float m_all = -INFINITY;
+        for (int z0 = 0; z0 < ksplit; z0 += 8) {
+            float t[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                t[j] = z0 + j < ksplit ? __ldcg(part_ml + (at + (size_t)(z0 + j) * BM) * 2) : -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) m_all = fmaxf(m_all, t[j]);
+        }
+        float m_safe = (m_all == -INFINITY) ? 0.f : m_all;
+        float l_all = 0.f;
+        for (int z0 = 0; z0 < ksplit; z0 += 8) {
+            float tm[8], tl[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                size_t p = at + (size_t)(z0 + j < ksplit ? z0 + j : 0) * BM;
+                tm[j] = z0 + j < ksplit ? __ldcg(part_ml + p * 2) : -INFINITY;
+                tl[j] = z0 + j < ksplit ? __ldcg(part_ml + p * 2 + 1) : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (z0 + j < ksplit) {   // (in the shares' order)
+                    float f = exp2f(tm[j] - m_safe);
+                    l_all += tl[j] * f;
+                    factor_s[(z0 + j) * BM + tid] = f;
+                }
+        }
+        float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
+        for (int z = 0; z < ksplit; ++z) factor_s[z * BM + tid] *= inv;
+    }
+    named_barrier(2, SOFTMAX_THREADS);
+    // 2. The rows' sums: a thread takes four dims of the rows tid / (HD / 4) + k * 128 / (HD / 4), so that
+    //    a warp reads whole rows; sixteen loads in flight: C shares of 16 / C rows at a time.
+    if (ksplit <= 2) merge_rows<2>(part_o, first, ksplit, out0, row_stride, rows, factor_s, tid);
+    else if (ksplit <= 4) merge_rows<4>(part_o, first, ksplit, out0, row_stride, rows, factor_s, tid);
+    else merge_rows<8>(part_o, first, ksplit, out0, row_stride, rows, factor_s, tid);
 }
 
 // SPLIT: the keys of a tile are shared among gridDim.z blocks (an instance of its own: the code
@@ -616,7 +669,11 @@ attention_prefill_tc5_kernel(const bf16* __restrict__ q, const __grid_constant__
                     if (bars->is_last) tickets[pair] = 0;  // zero again for the next launch
                 }
                 named_barrier(2, SOFTMAX_THREADS);
-                if (bars->is_last && exists) merge_key_shares(part_o, part_ml, pair * ksplit * BM + row, ksplit, orow);
+                // (the ring of K and V tiles is free by now: the shares' factors go there)
+                if (bars->is_last)
+                    merge_key_shares(part_o, part_ml, pair * ksplit * BM, ksplit,
+                                     out + ((size_t)(q0 + pt.t0) * nh + head) * HD, (size_t)nh * HD, pt.rows,
+                                     reinterpret_cast<float*>(k_s), tid);
             }
         }
         if (!ok) bars->failed = 1;

@@ -635,17 +635,25 @@ class CudaOps:
 
     def prefill_key_split(self, blocks: int, hd: int, max_ctx_len: int) -> int:
         """Among how many blocks the tcgen05 prefill kernel shares the keys of a query tile: the
-        count that needs the fewest rounds of blocks over the device per share of the keys, if
-        that saves a quarter of the time and leaves every block four key tiles of the longest
-        context; 1 when the tiles fill the device anyway."""
+        count that costs least by this estimate, in key tiles one block walks: rounds of blocks over
+        the device, each block its share of the longest context's key tiles plus a start and end
+        worth six, and for the block that adds the shares three key tiles and 1.1 per share
+        (measured, a 128-token portion at 2,048 tokens, us for 1 / 2 / 4 / 8 shares: 23.9 / 18.5 / 17.0 /
+        19.0; at 8,192 tokens: 81 / 47.6 / 36.8 / 29.5; a 512-token portion at 8,192: 103 / 65 / 72 / 82);
+        if that saves a quarter of the time and leaves every block four key tiles; 1 when the tiles
+        fill the device anyway."""
         slots = self.sm_count * (2 if hd == 64 else 1)
         if blocks <= 0 or blocks >= slots:
             return 1
         key_tiles = max(max_ctx_len // 64, 1)
-        # rounds of blocks over the device, each block 1 / ks of a tile's keys plus a set-up worth two key tiles
-        cost = lambda ks: -(-blocks * ks // slots) * (1.0 / ks + 2.0 / key_tiles)
+
+        def cost(ks: int) -> float:
+            rounds = -(-blocks * ks // slots)
+            return rounds * (key_tiles / ks + 6.0) + (3.0 + 1.1 * ks if ks > 1 else 0.0)
+
         limit = max(1, min(16, max_ctx_len // 256))
-        best = min(range(1, limit + 1), key=lambda ks: (cost(ks), ks))
+        least = min(cost(ks) for ks in range(1, limit + 1))
+        best = next(ks for ks in range(1, limit + 1) if cost(ks) <= 1.05 * least)  # (the fewest shares among the near-best)
         return best if cost(best) <= 0.75 * cost(1) else 1
 
     def paged_attention(self, q, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, page_size,
@@ -751,11 +759,13 @@ class CudaOps:
             # then much of the GPU would idle (a short portion of a long prompt), the keys of
             # every tile are shared among several blocks instead.
             ksplit = self.prefill_key_split(tiles * nh, hd, max_ctx) if self.prefill_key_splits and not fixed else 1
-            paired = not fixed and ksplit == 1 and tiles * nh <= self.prefill_paired_max * self.sm_count
+            # (pairs of tiles only where single tiles would take more than one round of blocks: two
+            # prompts of 256 tokens took 11.2 us in pairs, 8.3 in single tiles; eight of them 14.9 and 17.5)
+            slots = self.sm_count * (2 if hd == 64 else 1)
+            paired = (not fixed and ksplit == 1 and slots < tiles * nh <= self.prefill_paired_max * self.sm_count)
             # (portions at the end of long contexts: their tiles see about as many keys each, and pairs
             # would only halve the blocks where those do not fill the device anyway: two 512-token
-            # portions at 65,536 tokens took 1,602 us in 128 blocks of two tiles, 944 in 256 of one)
-            slots = self.sm_count * (2 if hd == 64 else 1)
+            # portions at 65,536 tokens took 1,602 us in 128 blocks of two tiles, 826 in 256 of one)
             if paired and ctx.max_ctx_len >= 2 * max(ctx.q_lens) and plan["tile_pairs"] * nh < slots:
                 paired = False
             if paired:

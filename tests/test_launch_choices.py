@@ -84,7 +84,9 @@ def test_keys_of_a_query_tile_are_shared_when_tiles_are_few_and_contexts_long():
     ops = _ops()
     split = lambda blocks, hd, ctx: CudaOps.prefill_key_split(ops, blocks, hd, ctx)
     assert split(128, 64, 4096) == 2      # 4 tiles x 32 heads on 296 block slots
-    assert split(96, 128, 4096) == 3      # head size 128: one block per SM, 148 slots
+    assert split(96, 128, 4096) == 1      # head size 128: one block per SM, 148 slots; three shares would take two rounds
+    assert split(32, 64, 2048) == 4 and split(32, 64, 8192) == 8   # one tile: 17.0 us (23.9 unshared), 29.5 (81)
+    assert split(128, 64, 512) == 1       # a whole 512-token prompt: few keys per tile (11.1 us; 19.0 in two shares)
     assert split(512, 64, 4096) == 1      # the tiles fill the device
     assert split(200, 64, 4000) == 1      # two thirds full: sharing would not save a quarter
     assert split(128, 64, 200) == 1       # too short a context to share

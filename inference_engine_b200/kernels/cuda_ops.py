@@ -682,9 +682,14 @@ class CudaOps:
                 # a launch of fixed size (a captured step): both kernels, over as many query tiles
                 # as any step within the bounds can have; each kernel skips the other's requests
                 tokens, seqs, max_ctx = bounds
-                tiles = seqs + tokens // lib.ie_attention_prefill_rows()
+                rows = lib.ie_attention_prefill_rows()
+                tiles = seqs + tokens // rows
+                # (the keys of a tile may be shared among blocks here too: how many is decided from the
+                # bounds alone, for the tiles a step of so many tokens usually has: one request's portion
+                # and little else; blocks for tiles that a step does not have leave at once)
+                likely = tokens // rows + min(seqs, 2)
                 plan = plans[(groups, hd)] = {"any": True, "all": False, "tiles": tiles, "tile_pairs": tiles,
-                                              "max_ctx": max_ctx}
+                                              "max_ctx": max_ctx, "likely_tiles": likely}
             if plan is None:
                 small = [ql * groups <= 16 for ql in ctx.q_lens]
                 plan = {"small": small, "any": any(small), "all": all(small)}
@@ -758,7 +763,9 @@ class CudaOps:
             # of a request, a late (long) and an early (short) one.  With so few tiles that even
             # then much of the GPU would idle (a short portion of a long prompt), the keys of
             # every tile are shared among several blocks instead.
-            ksplit = self.prefill_key_split(tiles * nh, hd, max_ctx) if self.prefill_key_splits and not fixed else 1
+            ksplit = 1
+            if self.prefill_key_splits:
+                ksplit = self.prefill_key_split((plan["likely_tiles"] if fixed else tiles) * nh, hd, max_ctx)
             # (pairs of tiles only where single tiles would take more than one round of blocks: two
             # prompts of 256 tokens took 11.2 us in pairs, 8.3 in single tiles; eight of them 14.9 and 17.5)
             slots = self.sm_count * (2 if hd == 64 else 1)

@@ -612,7 +612,7 @@ class CudaOps:
         # even share, dealt in rounds over the blocks, or, where the pieces would leave the slowest block
         # well behind, equal ranges of the list of all tiles, which lie in 1 + pairs / blocks stretches
         # of different pairs on average.  A piece or stretch costs six tiles per warp to set up.
-        warps, keys = (8 if pairs <= self.sm_count else 4), 32
+        warps, keys = (8 if pairs <= self.sm_count else 4), (32 if hd is None or hd <= 64 else 16)  # (keys per tile)
         tiles = [-(-c // keys) for c in ctx_lens]
         share = max(-(-sum(tiles) * nkv // slots), warps)
         pieces = [max(1, min((n + share // 2) // share, n // warps)) for n in tiles]

@@ -713,7 +713,10 @@ class CudaOps:
     def _scratch(self, ctx, name: str, floats: int, device):
         ws = getattr(ctx, "ws", None)
         if ws is not None:
-            return ws.buffer(name, 1, floats, self.torch.float32)
+            # (one row of exactly what is asked for, rounded up so that it seldom has to grow: the
+            # workspace's own floor of rows is for per-token buffers)
+            size = max(1 << max(int(floats) - 1, 0).bit_length(), 1 << 22)  # (16 MB at least: most steps never outgrow it)
+            return ws.buffer(name, 1, size, self.torch.float32, rows_cap=None)[:, :floats]
         return self.torch.empty(floats, dtype=self.torch.float32, device=device)
 
     @_kind("attention.decode")

@@ -171,3 +171,21 @@ def test_many_requests_of_one_length_run_in_small_blocks():
     assert est([900, 800, 700, 100, 50], 3, 1.0, 0.0) == max(700 + 100, 800 + 50, 900)
     ops.decode_small = False
     assert deal([1024] * 64) == CudaOps.BY_REQUEST
+
+
+def test_scratch_buffers_are_sized_as_asked():
+    """The attention kernels' scratch is one row of what they ask for (rounded up, 16 MB at least), not
+    the workspace's floor of rows for per-token buffers; a larger request grows it once."""
+    import torch
+
+    from inference_engine_b200.engine.workspace import Workspace
+
+    ops = types.SimpleNamespace(torch=torch)
+    ctx = types.SimpleNamespace(ws=Workspace("cpu", min_rows=4096))
+    small = CudaOps._scratch(ops, ctx, "attn.partial", 1000, "cpu")
+    assert tuple(small.shape) == (1, 1000) and ctx.ws.bytes() == 4 << 22
+    version = ctx.ws.version
+    again = CudaOps._scratch(ops, ctx, "attn.partial", 3_000_000, "cpu")
+    assert tuple(again.shape) == (1, 3_000_000) and ctx.ws.version == version and again.data_ptr() == small.data_ptr()
+    large = CudaOps._scratch(ops, ctx, "attn.partial", 5_000_000, "cpu")
+    assert tuple(large.shape) == (1, 5_000_000) and ctx.ws.version == version + 1 and ctx.ws.bytes() == 4 << 23

@@ -282,3 +282,26 @@ def test_a_long_prompt_in_captured_portions_shares_its_tiles_keys():
             assert float(logits[best] - logits[outs[1][i]]) < 0.1
             break
         ids.append(token)
+
+
+def test_the_workspace_stays_small_with_many_sequences_and_long_tables():
+    """An engine for 64 sequences of up to 8,192 tokens (the benchmark's settings) that runs prompts as
+    captured short steps: the attention kernels' scratch is sized for what a step can need, not for the
+    workspace's floor of rows (which had asked for hundreds of gigabytes here)."""
+    from inference_engine_b200 import SamplingParams
+    from inference_engine_b200.engine.llm_engine import LLMEngine
+    from inference_engine_b200.engine.loading import model_from_tensors
+
+    cfg = SHAPE_1B_2L
+    weights = _weights(cfg, seed=3)
+    model, _ = model_from_tensors(cfg, weights, "bfloat16", "cuda", 8192)
+    engine = LLMEngine(model, None, (), num_blocks=2048, block_size=PAGE, max_num_seqs=64,
+                       max_num_batched_tokens=512, max_model_len=8192, enable_cuda_graphs=True)
+    prompts = {f"p{i}": H.random_tokens(cfg, n, 900 + i) for i, n in enumerate([1024, 700, 130, 60, 9, 2])}
+    got = engine.generate(prompts, SamplingParams(temperature=0, max_tokens=3))
+    assert all(len(v) == 3 for v in got.values()) and engine.mixed_graphs.replays > 0
+    scratch = {name: buf.numel() * buf.element_size() for (name, _), buf in engine.runner.ws._buffers.items()
+               if name.startswith("attn.") and "partial" in name}
+    assert scratch and max(scratch.values()) < 1 << 30, scratch
+    assert engine.runner.ws.bytes() < 8 << 30
+    engine.ops.check_errors()

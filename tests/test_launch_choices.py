@@ -145,6 +145,8 @@ def test_many_requests_of_one_length_run_in_small_blocks():
     ops._by_request_estimate = CudaOps._by_request_estimate
     for name in ("BY_REQUEST", "BY_LENGTH", "SMALL_2", "SMALL_3"):
         setattr(ops, name, getattr(CudaOps, name))
+    ops._dealing_look, ops._dealing_answer = None, 0
+    ops._decode_dealing = lambda lens, nkv, hd=None: CudaOps._decode_dealing(ops, lens, nkv, hd)
     deal = lambda lens, nkv=8, hd=64: CudaOps.decode_dealing(ops, lens, nkv, hd)
     assert deal([1024] * 40) == CudaOps.SMALL_3 and deal([1024] * 55) == CudaOps.SMALL_3  # up to 444 blocks: one round
     assert deal([1024] * 56) == CudaOps.SMALL_2 and deal([1024] * 74) == CudaOps.SMALL_2  # up to 592
@@ -169,6 +171,11 @@ def test_many_requests_of_one_length_run_in_small_blocks():
     est = CudaOps._by_request_estimate
     assert est([1000] * 80, 37, 1.0, 300.0) == 3 * 1300
     assert est([900, 800, 700, 100, 50], 3, 1.0, 0.0) == max(700 + 100, 800 + 50, 900)
+    # the answer is kept while the batch looks the same (every context a token longer: the same look)
+    calls = []
+    ops._decode_dealing = lambda lens, nkv, hd=None: calls.append(1) or CudaOps._decode_dealing(ops, lens, nkv, hd)
+    assert deal([1030] * 40) == deal([1031] * 40) == deal([1032] * 40) == CudaOps.SMALL_3 and len(calls) == 1
+    assert deal([1030] * 41) == CudaOps.SMALL_3 and len(calls) == 2
     ops.decode_small = False
     assert deal([1024] * 64) == CudaOps.BY_REQUEST
 
